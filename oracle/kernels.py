@@ -1,0 +1,196 @@
+"""Per-kernel CPU oracles (TEST INFRASTRUCTURE - never imported by the product).
+
+Each function restates, with numpy/torch on the CPU in f32, the arithmetic of one
+backend kernel, following the CPU helpers the reference's own kernel tests use:
+
+  matmul*                ferrotensor-backend/tests/gpu_kernels.rs:80-101
+  rms_norm               gpu_kernels.rs:114-122;  kernels.wgsl:76-98
+  rms_norm_backward      gpu_kernels.rs:1300-1318; kernels.wgsl:100-151
+  rope                   gpu_kernels.rs:1513-1545; kernels.wgsl:45-73
+  silu_gate*             kernels.wgsl:737-780
+  attention / backward   gpu_kernels.rs:132-224; flash_attention_v2_backward.wgsl:5-15
+  masked_cross_entropy   gpu_kernels.rs:1375-1436; kernels.wgsl:672-711
+  sum_squares_partial    kernels.wgsl:713-735
+  adamw                  gpu_kernels.rs:2218-2230; kernels.wgsl:355-387
+  pack_f16               ferrotensor-backend/src/tensor.rs:261-269,490-514
+  embedding              ferrotensor-autograd/src/lib.rs:1159-1179
+"""
+
+import math
+
+import numpy as np
+import torch
+
+MASKED_CE_SKIP = 0xFFFFFFFF
+SUM_SQUARES_CHUNK = 4096
+
+
+def _t(x, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(x), dtype=dtype)
+
+
+def matmul(a, b, dtype=torch.float32):
+    """out[M,N] = a[M,K] @ b[K,N]"""
+    return (_t(a, dtype) @ _t(b, dtype)).numpy()
+
+
+def matmul_bt(a, b, dtype=torch.float32):
+    """out[M,N] = a[M,K] @ b[N,K]^T"""
+    return (_t(a, dtype) @ _t(b, dtype).T).numpy()
+
+
+def matmul_at(a, b, dtype=torch.float32):
+    """out[M,N] = a[K,M]^T @ b[K,N]"""
+    return (_t(a, dtype).T @ _t(b, dtype)).numpy()
+
+
+def f16_round(x):
+    return np.asarray(x, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
+def pack_f16(x):
+    """f32 -> RNE binary16, two per little-endian u32 word, element 2i in the low half.
+    An odd element count is padded with one zero half."""
+    h = np.asarray(x, dtype=np.float32).reshape(-1).astype(np.float16).view(np.uint16)
+    if h.size % 2:
+        h = np.concatenate([h, np.zeros(1, dtype=np.uint16)])
+    return (h[0::2].astype(np.uint32) | (h[1::2].astype(np.uint32) << 16)).astype(np.uint32)
+
+
+def transpose_pack_f16(w_out_in):
+    """HF [out,in] f32 -> [in,out] -> packed f16 words (the frozen-linear upload)."""
+    return pack_f16(np.ascontiguousarray(np.asarray(w_out_in, dtype=np.float32).T))
+
+
+def rms_norm(x, w, eps):
+    x = np.asarray(x, dtype=np.float32)
+    ms = (x * x).sum(-1, dtype=np.float32, keepdims=True) / np.float32(x.shape[-1])
+    inv = np.float32(1.0) / np.sqrt(ms + np.float32(eps))
+    return (x * inv * np.asarray(w, dtype=np.float32)).astype(np.float32)
+
+
+def rms_norm_backward(x, w, g, eps):
+    """gx = g*w*inv - x*inv^3*sum(g*w*x)/n ; gw[i] = sum_rows g*x*inv"""
+    x = np.asarray(x, dtype=np.float64)
+    w = np.asarray(w, dtype=np.float64)
+    g = np.asarray(g, dtype=np.float64)
+    n = x.shape[-1]
+    inv = 1.0 / np.sqrt((x * x).sum(-1, keepdims=True) / n + eps)
+    gwx = (g * w * x).sum(-1, keepdims=True)
+    gx = g * w * inv - x * (gwx * inv ** 3 / n)
+    gw = (g * x * inv).reshape(-1, n).sum(0)
+    return gx.astype(np.float32), gw.astype(np.float32)
+
+
+def rope(x, head_dim, seq_len, heads, pos=0, theta=10000.0, inverse=False):
+    """x flat [tokens*heads*head_dim]; token t sits at position pos + (t % seq_len).
+    angle = +-f32(position) * powf(theta, -2i/d), all in f32."""
+    x = np.array(x, dtype=np.float32).reshape(-1, heads, head_dim)
+    half = head_dim // 2
+    tokens = x.shape[0]
+    i = np.arange(half, dtype=np.float32)
+    freq = np.power(np.float32(theta), np.float32(-2.0) * i / np.float32(head_dim), dtype=np.float32)
+    p = (pos + (np.arange(tokens) % seq_len)).astype(np.float32)
+    angle = (p[:, None] * freq[None, :]).astype(np.float32)
+    if inverse:
+        angle = -angle
+    c, s = np.cos(angle)[:, None, :], np.sin(angle)[:, None, :]
+    x1, x2 = x[..., :half].copy(), x[..., half:].copy()
+    out = np.concatenate([x1 * c - x2 * s, x1 * s + x2 * c], axis=-1)
+    return out.astype(np.float32).reshape(-1)
+
+
+def silu_gate(a, b):
+    """silu(a) * b - the FIRST argument passes through SiLU."""
+    a = np.asarray(a, dtype=np.float32)
+    s = np.float32(1.0) / (np.float32(1.0) + np.exp(-a))
+    return (a * s * np.asarray(b, dtype=np.float32)).astype(np.float32)
+
+
+def silu_gate_backward(a, b, g):
+    """returns (grad wrt a, grad wrt b)"""
+    a = np.asarray(a, dtype=np.float32)
+    b = np.asarray(b, dtype=np.float32)
+    g = np.asarray(g, dtype=np.float32)
+    s = np.float32(1.0) / (np.float32(1.0) + np.exp(-a))
+    ga = g * b * (s * (np.float32(1.0) + a * (np.float32(1.0) - s)))
+    gb = g * (a * s)
+    return ga.astype(np.float32), gb.astype(np.float32)
+
+
+def attention(q, k, v, b, sq, sk, h, hkv, d, causal=True, dtype=torch.float32):
+    """q,out [b,sq,h,d]; k,v [b,sk,hkv,d]. Returns (out, lse [b,h,sq], probs [b,h,sq,sk])."""
+    q = _t(q, dtype).view(b, sq, h, d).transpose(1, 2)
+    k = _t(k, dtype).view(b, sk, hkv, d).transpose(1, 2).repeat_interleave(h // hkv, dim=1)
+    v = _t(v, dtype).view(b, sk, hkv, d).transpose(1, 2).repeat_interleave(h // hkv, dim=1)
+    s = q @ k.transpose(-1, -2) * (1.0 / math.sqrt(d))
+    if causal:
+        vis = torch.ones(sq, sk, dtype=torch.bool).tril()
+        s = s.masked_fill(~vis, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse[..., None])
+    out = (p @ v).transpose(1, 2).contiguous()
+    return out.numpy(), lse.numpy(), p
+
+
+def attention_backward(q, k, v, dout, b, sq, sk, h, hkv, d, causal=True, dtype=torch.float32):
+    """dS = P * (dO.V - sum_j P dO.V) * scale; dK, dV summed over the query heads of a KV group."""
+    grp = h // hkv
+    _, _, p = attention(q, k, v, b, sq, sk, h, hkv, d, causal, dtype)
+    qh = _t(q, dtype).view(b, sq, h, d).transpose(1, 2)
+    kh = _t(k, dtype).view(b, sk, hkv, d).transpose(1, 2).repeat_interleave(grp, dim=1)
+    vh = _t(v, dtype).view(b, sk, hkv, d).transpose(1, 2).repeat_interleave(grp, dim=1)
+    do = _t(dout, dtype).view(b, sq, h, d).transpose(1, 2)
+    dp = do @ vh.transpose(-1, -2)
+    rowsum = (p * dp).sum(-1, keepdim=True)
+    ds = p * (dp - rowsum) * (1.0 / math.sqrt(d))
+    dq = (ds @ kh).transpose(1, 2).contiguous()
+    dk = (ds.transpose(-1, -2) @ qh).view(b, hkv, grp, sk, d).sum(2).transpose(1, 2).contiguous()
+    dv = (p.transpose(-1, -2) @ do).view(b, hkv, grp, sk, d).sum(2).transpose(1, 2).contiguous()
+    return dq.numpy(), dk.numpy(), dv.numpy()
+
+
+def masked_cross_entropy_weighted(logits, targets, weights):
+    """logits [rows,V] f32, targets u32 (MASKED_CE_SKIP = outside the loss), weights [rows].
+    Returns (row_loss [rows], grad [rows,V])."""
+    z = _t(logits, torch.float32)
+    rows, vocab = z.shape
+    t = np.asarray(targets, dtype=np.uint32)
+    w = _t(weights, torch.float32)
+    skip = torch.as_tensor(t == MASKED_CE_SKIP)
+    tt = torch.as_tensor(np.where(t == MASKED_CE_SKIP, 0, t).astype(np.int64))
+    log_z = torch.logsumexp(z, dim=-1)
+    grad = torch.exp(z - log_z[:, None]) * w[:, None]
+    grad[torch.arange(rows), tt] -= w
+    loss = log_z - z[torch.arange(rows), tt]
+    grad[skip] = 0.0
+    loss[skip] = 0.0
+    return loss.numpy(), grad.numpy()
+
+
+def sum_squares_partial(x):
+    x = np.asarray(x, dtype=np.float32).reshape(-1)
+    n = -(-x.size // SUM_SQUARES_CHUNK)
+    return np.array([(x[i * SUM_SQUARES_CHUNK:(i + 1) * SUM_SQUARES_CHUNK] ** 2).sum(dtype=np.float32)
+                     for i in range(n)], dtype=np.float32)
+
+
+def adamw(w, g, m, v, lr, beta1, beta2, eps, wd, t):
+    f = np.float32
+    w, g, m, v = (np.asarray(a, dtype=f) for a in (w, g, m, v))
+    m2 = m * f(beta1) + (f(1.0) - f(beta1)) * g
+    v2 = v * f(beta2) + (f(1.0) - f(beta2)) * g * g
+    m_hat = m2 / (f(1.0) - np.power(f(beta1), f(t), dtype=f))
+    v_hat = v2 / (f(1.0) - np.power(f(beta2), f(t), dtype=f))
+    w2 = w - f(lr) * (m_hat / (np.sqrt(v_hat) + f(eps)) + f(wd) * w)
+    return w2.astype(f), m2.astype(f), v2.astype(f)
+
+
+def embedding(table, ids):
+    """rows of table [V,h]; an id >= V gives a zero row."""
+    table = np.asarray(table, dtype=np.float32)
+    ids = np.asarray(ids).reshape(-1).astype(np.int64)
+    out = np.zeros((ids.size, table.shape[1]), dtype=np.float32)
+    ok = ids < table.shape[0]
+    out[ok] = table[ids[ok]]
+    return out
