@@ -1,0 +1,141 @@
+// Shared declarations of libft_cuda: context object, error reporting, launch helpers and
+// the internal (strided, typed) forms of the kernels that both the per-op C ABI and the
+// fused step driver call.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/ft_cuda.h"
+
+struct FtContext {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int sm_count = 148;
+  int gemm_mode = FT_GEMM_F32;
+  uint64_t launches = 0;
+  // scratch owned by the context; grown on demand (never inside a captured region)
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  // status word written by kernels whose bounded waits ran out (pinned, device-mapped)
+  int* status_host = nullptr;
+  int* status_dev = nullptr;
+  // cuTensorMapEncodeTiled, resolved through the runtime (no link against libcuda)
+  void* encode_tiled = nullptr;
+};
+
+void ft_set_error(const char* fmt, ...);
+int ft_cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+
+#define FT_CUDA(expr)                                                        \
+  do {                                                                       \
+    cudaError_t _e = (expr);                                                 \
+    if (_e != cudaSuccess) return ft_cuda_fail(_e, #expr, __FILE__, __LINE__); \
+  } while (0)
+
+#define FT_REQUIRE(cond, ...)   \
+  do {                          \
+    if (!(cond)) {              \
+      ft_set_error(__VA_ARGS__); \
+      return FT_ERR_INVALID;    \
+    }                           \
+  } while (0)
+
+#define FT_TRY(expr)             \
+  do {                           \
+    int _r = (expr);             \
+    if (_r != FT_OK) return _r;  \
+  } while (0)
+
+// Launch on the context's stream, count the launch and surface launch errors.
+#define FT_LAUNCH(ctx, kernel, grid, block, smem, ...)                          \
+  do {                                                                          \
+    kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__);            \
+    (ctx)->launches++;                                                          \
+    cudaError_t _e = cudaPeekAtLastError();                                     \
+    if (_e != cudaSuccess) return ft_cuda_fail(_e, #kernel, __FILE__, __LINE__); \
+  } while (0)
+
+// Scratch of at least `bytes`, 256-byte aligned.  Stream order makes reuse by consecutive
+// calls safe; growth synchronises the stream before the old block is released.
+int ft_scratch(FtContext* ctx, size_t bytes, void** out);
+
+static inline size_t ft_align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+static inline int ft_cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ----- internal kernels (definitions in the .cu files named on the right) -----------------
+
+// B operand element type of a matmul
+enum FtDType { FT_F32 = 0, FT_F16 = 1, FT_BF16 = 2 };
+
+// C[m,n] (+)= alpha * sum_k A(m,k) B(k,n) with arbitrary element strides; f32 FMA.
+// A is f32; B is f32 or f16.                                         (ft_matmul_simt.cu)
+int ft_gemm_simt(FtContext* ctx, const float* a, long long sam, long long sak, const void* b,
+                 FtDType b_type, long long sbk, long long sbn, float* c, long long ldc, int M,
+                 int N, int K, float alpha, bool accumulate);
+
+// tcgen05 GEMM: C[M,N] f32 (ldc) (+)= A[M,K] bf16 (lda, K contiguous) . B[N,K]^T 16-bit
+// (ldb, K contiguous).  Returns FT_ERR_UNSUPPORTED when the shape breaks a TMA rule.
+//                                                                     (ft_gemm_tc.cu)
+int ft_gemm_tc(FtContext* ctx, const __nv_bfloat16* a, long long lda, const void* b,
+               FtDType b_type, long long ldb, float* c, long long ldc, int M, int N, int K,
+               bool accumulate);
+// f32 [rows, cols] (ld) -> bf16 [rows, cols_padded] (ldo); mode FT_GEMM_BF16X2 also writes
+// the low part to `lo`.                                               (ft_gemm_tc.cu)
+int ft_to_bf16(FtContext* ctx, const float* src, long long ld, __nv_bfloat16* hi,
+               __nv_bfloat16* lo, long long ldo, int rows, int cols);
+
+// elementwise / norm / loss / optimizer kernels with leading dimensions (ft_kernels.cu)
+int ft_k_embedding(FtContext* ctx, const float* table, const uint32_t* ids, float* out,
+                   int tokens, int vocab, int hidden);
+int ft_k_rms_norm(FtContext* ctx, const float* x, const float* w, float* out, int rows, int n,
+                  float eps);
+int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const float* g, float* gx,
+                      float* gw, int rows, int n, float eps, bool accumulate_gx);
+// in place on x[t*ld + h*head_dim + i]; position of token t = pos + t % seq_len
+int ft_k_rope(FtContext* ctx, float* x, long long ld, int tokens, int heads, int head_dim,
+              int seq_len, int pos, float theta, bool inverse);
+int ft_k_add(FtContext* ctx, const float* a, const float* b, float* out, size_t n);
+int ft_k_scale(FtContext* ctx, float* x, size_t n, float s);
+// 2-D SwiGLU: out[t, j] = silu(a[t*lda + j]) * b[t*ldb + j], j < n
+int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
+                   float* out, long long ldo, int rows, int n);
+int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const float* b,
+                       long long ldb, const float* g, long long ldg, float* ga, long long ldga,
+                       float* gb, long long ldgb, int rows, int n);
+// y[t, j] += bias[j]
+int ft_k_add_bias(FtContext* ctx, float* y, long long ld, const float* bias, int rows, int n);
+int ft_k_masked_ce(FtContext* ctx, const float* logits, const uint32_t* targets,
+                   const float* weights, float* grad, float* row_loss, int rows, int vocab,
+                   float grad_scale);
+int ft_k_sum_squares(FtContext* ctx, const float* x, size_t n, float* out, size_t offset);
+int ft_k_adamw(FtContext* ctx, float* w, const float* g, float* m, float* v, size_t n,
+               const FtAdamParams* p);
+// norm (from chunk partials) -> skip/clip -> AdamW, all on the device
+int ft_k_apply_fused(FtContext* ctx, float* w, float* g, float* m, float* v, size_t n,
+                     float grad_scale, float max_norm, const FtAdamParams* p, float* partials,
+                     float* norm_out);
+
+// attention with token strides (elements between consecutive tokens)   (ft_attention.cu)
+struct FtAttnLaunch {
+  const float *q, *k, *v;
+  long long ldq, ldk, ldv;  // elements between tokens
+  float* out;
+  long long ldo;
+  float* stats;             // [b*h*sq*2] or nullptr
+  FtAttnParams p;
+};
+int ft_k_attention_fwd(FtContext* ctx, const FtAttnLaunch& a);
+struct FtAttnBwdLaunch {
+  const float *q, *k, *v, *out, *dout;
+  long long ldq, ldk, ldv, ldo, lddo;
+  float *dq, *dk, *dv;
+  long long lddq, lddk, lddv;
+  float* stats;
+  FtAttnParams p;
+};
+int ft_k_attention_bwd(FtContext* ctx, const FtAttnBwdLaunch& a);

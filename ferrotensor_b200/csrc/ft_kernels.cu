@@ -1,0 +1,531 @@
+// HBM-bound kernels of the LoRA step: embedding gather, RMSNorm forward/backward, RoPE,
+// SwiGLU forward/backward, add/scale/bias, masked cross-entropy, sum of squares, AdamW and
+// the fused norm -> clip -> AdamW tail.  All arithmetic is f32; rows are read with 128-bit
+// loads when alignment allows and reduced with warp shuffles.
+#include <algorithm>
+
+#include "ft_common.cuh"
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the block; every thread receives the result.  `buf` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* buf) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // buf may still be read from a previous reduction
+  if (lane == 0) buf[w] = v;
+  __syncthreads();
+  float r = (lane < nw) ? buf[lane] : 0.f;
+  return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* buf) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) buf[w] = v;
+  __syncthreads();
+  float r = (lane < nw) ? buf[lane] : -INFINITY;
+  return warp_max(r);
+}
+
+__device__ __forceinline__ bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
+
+// ------------------------------------------------------------------------------- embedding
+__global__ void k_embedding(const float* __restrict__ table, const uint32_t* __restrict__ ids,
+                            float* __restrict__ out, int vocab, int hidden) {
+  int t = blockIdx.x;
+  uint32_t id = ids[t];
+  float* o = out + (size_t)t * hidden;
+  if (id >= (uint32_t)vocab) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const float* r = table + (size_t)id * hidden;
+  if ((hidden & 3) == 0 && aligned16(r) && aligned16(o)) {
+    const float4* r4 = (const float4*)r;
+    float4* o4 = (float4*)o;
+    for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) o4[i] = r4[i];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = r[i];
+  }
+}
+
+// --------------------------------------------------------------------------------- RMSNorm
+__global__ void __launch_bounds__(kRowThreads)
+k_rms_norm(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
+           int n, float eps) {
+  __shared__ float red[32];
+  const float* xr = x + (size_t)blockIdx.x * n;
+  float* o = out + (size_t)blockIdx.x * n;
+  bool vec = (n & 3) == 0 && aligned16(xr) && aligned16(o) && aligned16(w);
+  float ss = 0.f;
+  if (vec) {
+    const float4* x4 = (const float4*)xr;
+    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+      float4 v = x4[i];
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
+  }
+  ss = block_sum(ss, red);
+  float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  if (vec) {
+    const float4* x4 = (const float4*)xr;
+    const float4* w4 = (const float4*)w;
+    float4* o4 = (float4*)o;
+    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+      float4 v = x4[i], g = w4[i];
+      o4[i] = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = xr[i] * inv * w[i];
+  }
+}
+
+// gx = g*w*inv - x*inv^3*sum(g*w*x)/n   (optionally added to what gx holds)
+__global__ void __launch_bounds__(kRowThreads)
+k_rms_norm_bwd(const float* __restrict__ x, const float* __restrict__ w,
+               const float* __restrict__ g, float* __restrict__ gx, float* __restrict__ inv_out,
+               int n, float eps, int accumulate) {
+  __shared__ float red[32];
+  size_t off = (size_t)blockIdx.x * n;
+  const float* xr = x + off;
+  const float* gr = g + off;
+  float* o = gx + off;
+  bool vec = (n & 3) == 0 && aligned16(xr) && aligned16(gr) && aligned16(o) && aligned16(w);
+  float ss = 0.f, gwx = 0.f;
+  if (vec) {
+    const float4 *x4 = (const float4*)xr, *g4 = (const float4*)gr, *w4 = (const float4*)w;
+    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+      float4 a = x4[i], b = g4[i], c = w4[i];
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+      gwx += b.x * c.x * a.x + b.y * c.y * a.y + b.z * c.z * a.z + b.w * c.w * a.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float a = xr[i];
+      ss += a * a;
+      gwx += gr[i] * w[i] * a;
+    }
+  }
+  ss = block_sum(ss, red);
+  gwx = block_sum(gwx, red);
+  float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  float coef = gwx * inv * inv * inv / (float)n;
+  if (vec) {
+    const float4 *x4 = (const float4*)xr, *g4 = (const float4*)gr, *w4 = (const float4*)w;
+    float4* o4 = (float4*)o;
+    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+      float4 a = x4[i], b = g4[i], c = w4[i];
+      float4 r = make_float4(b.x * c.x * inv - a.x * coef, b.y * c.y * inv - a.y * coef,
+                             b.z * c.z * inv - a.z * coef, b.w * c.w * inv - a.w * coef);
+      if (accumulate) {
+        float4 p = o4[i];
+        r.x += p.x; r.y += p.y; r.z += p.z; r.w += p.w;
+      }
+      o4[i] = r;
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float r = gr[i] * w[i] * inv - xr[i] * coef;
+      o[i] = accumulate ? o[i] + r : r;
+    }
+  }
+  if (inv_out && threadIdx.x == 0) inv_out[blockIdx.x] = inv;
+}
+
+// partial[c, i] = sum over the rows of chunk c of g*x*inv ; one thread per feature
+__global__ void k_rms_gw_partial(const float* __restrict__ x, const float* __restrict__ g,
+                                 const float* __restrict__ inv, float* __restrict__ partial,
+                                 int rows, int n, int rows_per_chunk) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+  float acc = 0.f;
+  for (int r = r0; r < r1; ++r) acc += g[(size_t)r * n + i] * x[(size_t)r * n + i] * inv[r];
+  partial[(size_t)blockIdx.y * n + i] = acc;
+}
+__global__ void k_rms_gw_final(const float* __restrict__ partial, float* __restrict__ gw, int n,
+                               int chunks) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0.f;
+  for (int c = 0; c < chunks; ++c) acc += partial[(size_t)c * n + i];
+  gw[i] = acc;
+}
+
+// ------------------------------------------------------------------------------------ RoPE
+// One thread per (token, head, pair).  angle = +-f32(position) * powf(theta, -2i/d).
+__global__ void k_rope(float* __restrict__ x, long long ld, long long pairs, int heads,
+                       int head_dim, int seq_len, int pos0, float theta, int inverse) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= pairs) return;
+  int half = head_dim >> 1;
+  int i = (int)(idx % half);
+  long long th = idx / half;
+  int h = (int)(th % heads);
+  long long t = th / heads;
+  float pos = (float)(pos0 + (int)(t % seq_len));
+  float freq = powf(theta, -2.0f * (float)i / (float)head_dim);
+  float angle = (inverse ? -1.0f : 1.0f) * pos * freq;
+  float s, c;
+  sincosf(angle, &s, &c);
+  float* p = x + t * ld + (long long)h * head_dim + i;
+  float v1 = p[0], v2 = p[half];
+  p[0] = v1 * c - v2 * s;
+  p[half] = v1 * s + v2 * c;
+}
+
+// ------------------------------------------------------------------------- add/scale/bias
+__global__ void k_add(const float* __restrict__ a, const float* __restrict__ b,
+                      float* __restrict__ out, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += st) out[i] = a[i] + b[i];
+}
+__global__ void k_add4(const float4* __restrict__ a, const float4* __restrict__ b,
+                       float4* __restrict__ out, size_t n4) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < n4; i += st) {
+    float4 u = a[i], v = b[i];
+    out[i] = make_float4(u.x + v.x, u.y + v.y, u.z + v.z, u.w + v.w);
+  }
+}
+__global__ void k_scale(float* __restrict__ x, size_t n, float s) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += st) x[i] *= s;
+}
+__global__ void k_add_bias(float* __restrict__ y, long long ld, const float* __restrict__ bias,
+                           int rows, int n) {
+  size_t total = (size_t)rows * n;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    size_t r = i / n, c = i % n;
+    y[r * ld + c] += bias[c];
+  }
+}
+
+// ---------------------------------------------------------------------------------- SwiGLU
+__global__ void k_silu_gate(const float* __restrict__ a, long long lda,
+                            const float* __restrict__ b, long long ldb, float* __restrict__ out,
+                            long long ldo, int rows, int n) {
+  size_t total = (size_t)rows * n;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    size_t r = i / n, c = i % n;
+    float x = a[r * lda + c];
+    float s = 1.0f / (1.0f + expf(-x));
+    out[r * ldo + c] = x * s * b[r * ldb + c];
+  }
+}
+__global__ void k_silu_gate_bwd(const float* __restrict__ a, long long lda,
+                                const float* __restrict__ b, long long ldb,
+                                const float* __restrict__ g, long long ldg,
+                                float* __restrict__ ga, long long ldga, float* __restrict__ gb,
+                                long long ldgb, int rows, int n) {
+  size_t total = (size_t)rows * n;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    size_t r = i / n, c = i % n;
+    float x = a[r * lda + c], y = b[r * ldb + c], go = g[r * ldg + c];
+    float s = 1.0f / (1.0f + expf(-x));
+    gb[r * ldgb + c] = go * (x * s);
+    ga[r * ldga + c] = go * y * (s * (1.0f + x * (1.0f - s)));
+  }
+}
+
+// ------------------------------------------------------------------- masked cross-entropy
+// One block per row.  Pass 1 keeps a running (max, sum) per thread; pass 2 writes the
+// gradient.  grad_scale folds the upstream gradient of the loss into the same pass.
+__global__ void __launch_bounds__(kRowThreads)
+k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
+            const float* __restrict__ weights, float* grad, float* __restrict__ row_loss,
+            int vocab, float grad_scale) {
+  // `grad` may alias `logits` (in-place use by the fused step): every element is read for
+  // the last time by the thread that then overwrites it, after both reductions are done.
+  __shared__ float red[32];
+  int row = blockIdx.x;
+  const float* z = logits + (size_t)row * vocab;
+  float* gz = grad ? grad + (size_t)row * vocab : nullptr;
+  uint32_t tgt = targets[row];
+  bool vec = (vocab & 3) == 0 && aligned16(z) && (!gz || aligned16(gz));
+  if (tgt == FT_MASKED_CE_SKIP) {
+    if (gz) {
+      if (vec) {
+        float4* g4 = (float4*)gz;
+        for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x)
+          g4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) gz[i] = 0.f;
+      }
+    }
+    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    return;
+  }
+  float m = -3.4e38f;
+  if (vec) {
+    const float4* z4 = (const float4*)z;
+    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+      float4 v = z4[i];
+      m = fmaxf(m, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, z[i]);
+  }
+  m = block_max(m, red);
+  float se = 0.f;
+  if (vec) {
+    const float4* z4 = (const float4*)z;
+    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+      float4 v = z4[i];
+      se += expf(v.x - m) + expf(v.y - m) + expf(v.z - m) + expf(v.w - m);
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) se += expf(z[i] - m);
+  }
+  se = block_sum(se, red);
+  float log_z = m + logf(se);
+  float inv = weights[row] * grad_scale;
+  if (gz) {
+    if (vec) {
+      const float4* z4 = (const float4*)z;
+      float4* g4 = (float4*)gz;
+      for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+        float4 v = z4[i];
+        float4 r = make_float4(expf(v.x - log_z) * inv, expf(v.y - log_z) * inv,
+                               expf(v.z - log_z) * inv, expf(v.w - log_z) * inv);
+        uint32_t base = (uint32_t)i * 4u;
+        if (tgt - base < 4u) {
+          uint32_t k = tgt - base;
+          if (k == 0) r.x -= inv; else if (k == 1) r.y -= inv;
+          else if (k == 2) r.z -= inv; else r.w -= inv;
+        }
+        g4[i] = r;
+      }
+    } else {
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float gv = expf(z[i] - log_z) * inv;
+        if ((uint32_t)i == tgt) gv -= inv;
+        gz[i] = gv;
+      }
+    }
+  }
+  if (threadIdx.x == 0) row_loss[row] = (tgt < (uint32_t)vocab) ? log_z - z[tgt] : 0.f;
+}
+
+// ------------------------------------------------------------------------- optimizer side
+// One block per 4096-element chunk; chunk b's f32 sum of squares goes to out[offset + b].
+__global__ void __launch_bounds__(kRowThreads)
+k_sum_squares(const float* __restrict__ x, size_t n, float* __restrict__ out, size_t offset,
+              float pre_scale) {
+  __shared__ float red[32];
+  size_t start = (size_t)blockIdx.x * FT_SUM_SQUARES_CHUNK;
+  size_t end = min(start + (size_t)FT_SUM_SQUARES_CHUNK, n);
+  float acc = 0.f;
+  for (size_t i = start + threadIdx.x; i < end; i += blockDim.x) {
+    float v = x[i] * pre_scale;
+    acc += v * v;
+  }
+  acc = block_sum(acc, red);
+  if (threadIdx.x == 0) out[offset + blockIdx.x] = acc;
+}
+
+__device__ __forceinline__ void adamw_one(float& w, float g, float& m, float& v, float lr,
+                                          float b1, float b2, float eps, float wd, float c1,
+                                          float c2) {
+  m = m * b1 + (1.0f - b1) * g;
+  v = v * b2 + (1.0f - b2) * g * g;
+  float m_hat = m / c1, v_hat = v / c2;
+  w = w - lr * (m_hat / (sqrtf(v_hat) + eps) + wd * w);
+}
+
+__global__ void k_adamw(float* __restrict__ w, const float* __restrict__ g,
+                        float* __restrict__ m, float* __restrict__ v, size_t n, FtAdamParams p) {
+  float c1 = 1.0f - powf(p.beta1, p.t), c2 = 1.0f - powf(p.beta2, p.t);
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += st) {
+    float wi = w[i], mi = m[i], vi = v[i];
+    adamw_one(wi, g[i], mi, vi, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, c1, c2);
+    w[i] = wi; m[i] = mi; v[i] = vi;
+  }
+}
+
+// norm_out[0] = norm, [1] = 1 if the step is applied, [2] = factor to apply to the raw
+// gradient (grad_scale, times the clip factor when clipping).  Chunk sums are added in
+// index order in f64, as the reference's host loop does.
+__global__ void k_norm_finalize(const float* __restrict__ partials, size_t chunks,
+                                float grad_scale, float max_norm, float* __restrict__ norm_out) {
+  __shared__ double sred[kRowThreads];
+  // fixed assignment of chunks to threads and a fixed tree => run-to-run identical
+  double acc = 0.0;
+  for (size_t i = threadIdx.x; i < chunks; i += blockDim.x) acc += (double)partials[i];
+  sred[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+    if ((int)threadIdx.x < s) sred[threadIdx.x] += sred[threadIdx.x + s];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    float norm = (float)sqrt(sred[0]);
+    bool finite = isfinite(norm);
+    float factor = grad_scale;
+    if (finite && max_norm > 0.f && norm > max_norm) factor *= max_norm / (norm + 1e-6f);
+    norm_out[0] = norm;
+    norm_out[1] = finite ? 1.f : 0.f;
+    norm_out[2] = factor;
+  }
+}
+
+__global__ void k_adamw_scaled(float* __restrict__ w, const float* __restrict__ g,
+                               float* __restrict__ m, float* __restrict__ v, size_t n,
+                               FtAdamParams p, const float* __restrict__ norm_out) {
+  if (norm_out[1] == 0.f) return;  // non-finite norm: the step is skipped
+  float factor = norm_out[2];
+  float c1 = 1.0f - powf(p.beta1, p.t), c2 = 1.0f - powf(p.beta2, p.t);
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += st) {
+    float wi = w[i], mi = m[i], vi = v[i];
+    adamw_one(wi, g[i] * factor, mi, vi, p.lr, p.beta1, p.beta2, p.eps, p.weight_decay, c1, c2);
+    w[i] = wi; m[i] = mi; v[i] = vi;
+  }
+}
+
+inline int ew_grid(FtContext* ctx, size_t n, int block = 256, int per_thread = 4) {
+  size_t want = (n + (size_t)block * per_thread - 1) / ((size_t)block * per_thread);
+  size_t cap = (size_t)ctx->sm_count * 16;
+  return (int)std::max<size_t>(1, std::min(want, cap));
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------- launchers
+int ft_k_embedding(FtContext* ctx, const float* table, const uint32_t* ids, float* out,
+                   int tokens, int vocab, int hidden) {
+  int block = hidden >= 1024 ? 256 : 128;
+  FT_LAUNCH(ctx, k_embedding, tokens, block, 0, table, ids, out, vocab, hidden);
+  return FT_OK;
+}
+
+int ft_k_rms_norm(FtContext* ctx, const float* x, const float* w, float* out, int rows, int n,
+                  float eps) {
+  int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
+  FT_LAUNCH(ctx, k_rms_norm, rows, block, 0, x, w, out, n, eps);
+  return FT_OK;
+}
+
+int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const float* g, float* gx,
+                      float* gw, int rows, int n, float eps, bool accumulate_gx) {
+  float* inv = nullptr;
+  float* partial = nullptr;
+  int chunks = 0, rows_per_chunk = 0;
+  if (gw) {
+    chunks = std::max(1, std::min(rows, (ctx->sm_count * 8) / std::max(1, ft_cdiv(n, 128))));
+    chunks = std::min(chunks, 1024);
+    rows_per_chunk = ft_cdiv(rows, chunks);
+    chunks = ft_cdiv(rows, rows_per_chunk);
+    void* s = nullptr;
+    FT_TRY(ft_scratch(ctx, ft_align_up((size_t)rows * 4, 256) + (size_t)chunks * n * 4, &s));
+    inv = (float*)s;
+    partial = (float*)((char*)s + ft_align_up((size_t)rows * 4, 256));
+  }
+  int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
+  FT_LAUNCH(ctx, k_rms_norm_bwd, rows, block, 0, x, w, g, gx, inv, n, eps, accumulate_gx ? 1 : 0);
+  if (gw) {
+    dim3 grid(ft_cdiv(n, 128), chunks);
+    FT_LAUNCH(ctx, k_rms_gw_partial, grid, 128, 0, x, g, inv, partial, rows, n, rows_per_chunk);
+    FT_LAUNCH(ctx, k_rms_gw_final, ft_cdiv(n, 128), 128, 0, partial, gw, n, chunks);
+  }
+  return FT_OK;
+}
+
+int ft_k_rope(FtContext* ctx, float* x, long long ld, int tokens, int heads, int head_dim,
+              int seq_len, int pos, float theta, bool inverse) {
+  long long pairs = (long long)tokens * heads * (head_dim / 2);
+  if (pairs == 0) return FT_OK;
+  long long blocks = (pairs + 255) / 256;
+  FT_REQUIRE(blocks <= 0x7fffffffLL, "rope: too many elements");
+  FT_LAUNCH(ctx, k_rope, (unsigned)blocks, 256, 0, x, ld, pairs, heads, head_dim, seq_len, pos,
+            theta, inverse ? 1 : 0);
+  return FT_OK;
+}
+
+int ft_k_add(FtContext* ctx, const float* a, const float* b, float* out, size_t n) {
+  if ((n & 3) == 0 && ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)out)) & 15) == 0) {
+    FT_LAUNCH(ctx, k_add4, ew_grid(ctx, n / 4, 256, 2), 256, 0, (const float4*)a,
+              (const float4*)b, (float4*)out, n / 4);
+  } else {
+    FT_LAUNCH(ctx, k_add, ew_grid(ctx, n), 256, 0, a, b, out, n);
+  }
+  return FT_OK;
+}
+
+int ft_k_scale(FtContext* ctx, float* x, size_t n, float s) {
+  FT_LAUNCH(ctx, k_scale, ew_grid(ctx, n), 256, 0, x, n, s);
+  return FT_OK;
+}
+
+int ft_k_add_bias(FtContext* ctx, float* y, long long ld, const float* bias, int rows, int n) {
+  FT_LAUNCH(ctx, k_add_bias, ew_grid(ctx, (size_t)rows * n), 256, 0, y, ld, bias, rows, n);
+  return FT_OK;
+}
+
+int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
+                   float* out, long long ldo, int rows, int n) {
+  FT_LAUNCH(ctx, k_silu_gate, ew_grid(ctx, (size_t)rows * n), 256, 0, a, lda, b, ldb, out, ldo,
+            rows, n);
+  return FT_OK;
+}
+
+int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const float* b,
+                       long long ldb, const float* g, long long ldg, float* ga, long long ldga,
+                       float* gb, long long ldgb, int rows, int n) {
+  FT_LAUNCH(ctx, k_silu_gate_bwd, ew_grid(ctx, (size_t)rows * n), 256, 0, a, lda, b, ldb, g, ldg,
+            ga, ldga, gb, ldgb, rows, n);
+  return FT_OK;
+}
+
+int ft_k_masked_ce(FtContext* ctx, const float* logits, const uint32_t* targets,
+                   const float* weights, float* grad, float* row_loss, int rows, int vocab,
+                   float grad_scale) {
+  FT_LAUNCH(ctx, k_masked_ce, rows, kRowThreads, 0, logits, targets, weights, grad, row_loss,
+            vocab, grad_scale);
+  return FT_OK;
+}
+
+int ft_k_sum_squares(FtContext* ctx, const float* x, size_t n, float* out, size_t offset) {
+  size_t chunks = (n + FT_SUM_SQUARES_CHUNK - 1) / FT_SUM_SQUARES_CHUNK;
+  FT_REQUIRE(chunks <= 0x7fffffffull, "sum_squares: too many elements");
+  FT_LAUNCH(ctx, k_sum_squares, (unsigned)chunks, kRowThreads, 0, x, n, out, offset, 1.0f);
+  return FT_OK;
+}
+
+int ft_k_adamw(FtContext* ctx, float* w, const float* g, float* m, float* v, size_t n,
+               const FtAdamParams* p) {
+  FT_LAUNCH(ctx, k_adamw, ew_grid(ctx, n), 256, 0, w, g, m, v, n, *p);
+  return FT_OK;
+}
+
+int ft_k_apply_fused(FtContext* ctx, float* w, float* g, float* m, float* v, size_t n,
+                     float grad_scale, float max_norm, const FtAdamParams* p, float* partials,
+                     float* norm_out) {
+  size_t chunks = (n + FT_SUM_SQUARES_CHUNK - 1) / FT_SUM_SQUARES_CHUNK;
+  FT_REQUIRE(chunks <= 0x7fffffffull, "apply: too many parameters");
+  FT_LAUNCH(ctx, k_sum_squares, (unsigned)chunks, kRowThreads, 0, g, n, partials, 0, grad_scale);
+  FT_LAUNCH(ctx, k_norm_finalize, 1, kRowThreads, 0, partials, chunks, grad_scale, max_norm,
+            norm_out);
+  FT_LAUNCH(ctx, k_adamw_scaled, ew_grid(ctx, n), 256, 0, w, g, m, v, n, *p, norm_out);
+  return FT_OK;
+}

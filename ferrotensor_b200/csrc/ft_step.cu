@@ -1,0 +1,628 @@
+// The LoRA step driver: embedding -> blocks -> head -> masked CE -> backward -> LoRA
+// gradients, and the norm/clip/AdamW tail, as one fixed kernel sequence on the context's
+// stream.  It performs the composition the reference's autograd tape performs
+// (ferrotensor-graph/src/lfm.rs:116-139,597-623; ferrotensor-graph/src/lib.rs:112-142;
+// ferrotensor-autograd/src/lib.rs:256-290,509-595,725-749,1328-1390;
+// ferrotensor-trainer/src/lib.rs:296-360,426-502) without a tape: frozen base weights get
+// an input gradient only, adapters get dA/dB added into one flat gradient buffer.
+//
+// Linears that share an input are computed as a group into one wide buffer
+// (q|k|v -> [T, nq+2nkv], gate|up -> [T, 2F]); attention, RoPE and SwiGLU read their slices
+// through leading dimensions, so no slice is ever copied.
+#include <string.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "ft_common.cuh"
+
+namespace {
+
+struct Linear {
+  int in = 0, out = 0;
+  const void* w_io = nullptr;  // [in, out] f32 or f16 (borrowed)
+  const float* bias = nullptr;
+  bool lora = false;
+  size_t a_off = 0, b_off = 0; // offsets of A [in, r] and B [r, out] in the flat buffers
+};
+
+struct Group {
+  int in = 0, n = 0;           // input width, total output width
+  int nlin = 0;
+  Linear* lin[3] = {nullptr, nullptr, nullptr};
+  int col_off[3] = {0, 0, 0};
+  int r_off[3] = {0, 0, 0};
+  int R = 0;                   // total adapter rank in the group
+  // operand copies for the tensor-core path (owned unless they alias w_io)
+  __half* w_nk = nullptr;      // [n, in]   forward operand, K = in contiguous
+  __half* w_kn = nullptr;      // [in, n]   input-gradient operand, K = n contiguous
+  bool own_kn = false;
+};
+
+struct Layer {
+  const float* norm1 = nullptr;
+  const float* norm2 = nullptr;
+  Linear lin[FT_LINEARS];
+  Group qkv, o, gu, down;
+};
+
+// activations one block keeps for its backward pass
+struct BlockActs {
+  float *h1, *qkv, *attn, *stats, *x1, *h2, *gu, *f;
+  float *xa_qkv, *xa_o, *xa_gu, *xa_down;
+};
+
+struct Bump {
+  char* base;
+  size_t off = 0;
+  bool dry;
+  template <typename T>
+  T* take(size_t count) {
+    size_t bytes = ft_align_up(count * sizeof(T), 256);
+    T* p = dry ? nullptr : (T*)(base + off);
+    off += bytes;
+    return p;
+  }
+};
+
+}  // namespace
+
+struct FtLoraModel {
+  FtContext* ctx = nullptr;
+  FtModelConfig cfg;
+  int nq = 0, nkv = 0;
+  float scale = 0.f;  // alpha / rank
+  const float* embed = nullptr;
+  const float* final_norm = nullptr;
+  Linear head_lin;
+  Group head;
+  std::vector<Layer> layers;
+  size_t trainable = 0;
+  float *params = nullptr, *grads = nullptr, *adam_m = nullptr, *adam_v = nullptr;
+  bool prepared = false;
+  std::vector<void*> owned;  // operand copies to free
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  float* apply_scratch = nullptr;  // partials + norm_out (owned)
+
+  // planned pointers of the current micro-batch
+  int T = 0, sequences = 0, seq_len = 0, head_chunk = 0;
+  std::vector<float*> x;           // layers+1 residual-stream buffers
+  std::vector<BlockActs> acts;     // one per layer, or a single shared one when checkpointing
+  float *hN = nullptr, *xa_head = nullptr, *logit_chunk = nullptr;
+  float *dx = nullptr, *dh = nullptr, *dqkv = nullptr, *dattn = nullptr, *dgu = nullptr,
+        *df = nullptr, *g = nullptr;
+  __nv_bfloat16 *cvt_hi = nullptr, *cvt_lo = nullptr;
+  size_t cvt_elems = 0;
+};
+
+namespace {
+
+FtDType base_type(const FtLoraModel* m) { return m->cfg.f16_base ? FT_F16 : FT_F32; }
+bool use_tc(const FtLoraModel* m) { return m->ctx->gemm_mode != FT_GEMM_F32 && m->cfg.f16_base; }
+
+void setup_group(Group& g, std::initializer_list<Linear*> lins, int rank) {
+  g = Group();
+  int col = 0, r = 0;
+  for (Linear* l : lins) {
+    g.lin[g.nlin] = l;
+    g.col_off[g.nlin] = col;
+    g.r_off[g.nlin] = r;
+    col += l->out;
+    if (l->lora) r += rank;
+    g.in = l->in;
+    g.nlin++;
+  }
+  g.n = col;
+  g.R = r;
+}
+
+// ---- plan the workspace: the same walk sizes it (dry) and assigns pointers ----------------
+size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
+  const FtModelConfig& c = m->cfg;
+  const size_t T = (size_t)sequences * seq_len;
+  Bump b{(char*)base, 0, dry};
+  const int L = c.layers;
+  const int nqkv = m->nq + 2 * m->nkv;
+  std::vector<float*> x(L + 1);
+  for (int l = 0; l <= L; ++l) x[l] = b.take<float>(T * c.hidden);
+  const int nact = c.checkpoint_blocks ? 1 : L;
+  std::vector<BlockActs> acts(nact);
+  for (int i = 0; i < nact; ++i) {
+    const Layer& ly = m->layers[c.checkpoint_blocks ? 0 : i];
+    BlockActs& a = acts[i];
+    a.h1 = b.take<float>(T * c.hidden);
+    a.qkv = b.take<float>(T * nqkv);
+    a.attn = b.take<float>(T * m->nq);
+    a.stats = b.take<float>((size_t)sequences * c.heads * seq_len * 2);
+    a.x1 = b.take<float>(T * c.hidden);
+    a.h2 = b.take<float>(T * c.hidden);
+    a.gu = b.take<float>(T * 2 * c.ffn);
+    a.f = b.take<float>(T * c.ffn);
+    // adapter ranks are the same in every layer (one lora_mask for the model)
+    a.xa_qkv = b.take<float>(T * std::max(1, ly.qkv.R));
+    a.xa_o = b.take<float>(T * std::max(1, ly.o.R));
+    a.xa_gu = b.take<float>(T * std::max(1, ly.gu.R));
+    a.xa_down = b.take<float>(T * std::max(1, ly.down.R));
+  }
+  float* hN = b.take<float>(T * c.hidden);
+  // head + loss run in row chunks so that [rows, vocab] never exceeds ~1 GiB
+  size_t per_row = (size_t)c.vocab * sizeof(float);
+  size_t chunk = std::max<size_t>(128, ((size_t)1 << 30) / per_row / 128 * 128);
+  chunk = std::min(chunk, T);
+  float* xa_head = b.take<float>(T * std::max(1, m->head.R));
+  float* logit_chunk = b.take<float>(chunk * c.vocab);
+  float* dx = b.take<float>(T * c.hidden);
+  float* dh = b.take<float>(T * c.hidden);
+  float* dqkv = b.take<float>(T * nqkv);
+  float* dattn = b.take<float>(T * m->nq);
+  float* dgu = b.take<float>(T * 2 * c.ffn);
+  float* df = b.take<float>(T * c.ffn);
+  int rmax = std::max({m->layers[0].qkv.R, m->layers[0].o.R, m->layers[0].gu.R,
+                       m->layers[0].down.R, m->head.R, 1});
+  float* g = b.take<float>(T * rmax);
+  // bf16 staging of a GEMM's activation operand (widest: gate|up gradient or vocab chunk)
+  size_t widest = std::max<size_t>({(size_t)c.hidden, (size_t)nqkv, (size_t)2 * c.ffn});
+  size_t cvt = std::max(T * ft_align_up(widest, 8), chunk * ft_align_up((size_t)c.vocab, 8));
+  __nv_bfloat16* hi = b.take<__nv_bfloat16>(cvt);
+  __nv_bfloat16* lo = b.take<__nv_bfloat16>(cvt);
+  if (!dry) {
+    m->T = (int)T; m->sequences = sequences; m->seq_len = seq_len; m->head_chunk = (int)chunk;
+    m->x = x; m->acts = acts; m->hN = hN; m->xa_head = xa_head; m->logit_chunk = logit_chunk;
+    m->dx = dx; m->dh = dh; m->dqkv = dqkv; m->dattn = dattn; m->dgu = dgu; m->df = df; m->g = g;
+    m->cvt_hi = hi; m->cvt_lo = lo; m->cvt_elems = cvt;
+  }
+  return b.off;
+}
+
+// ---- dense product through the selected path ---------------------------------------------
+// Y[T, n] (ldy) = X[T, in] (ldx) . W for a whole group
+int group_matmul_fwd(FtLoraModel* m, const Group& g, const float* X, long long ldx, float* Y,
+                     long long ldy, int T) {
+  FtContext* ctx = m->ctx;
+  if (use_tc(m) && g.w_nk) {
+    long long kp = (long long)ft_align_up((size_t)g.in, 8);
+    bool x2 = ctx->gemm_mode == FT_GEMM_BF16X2;
+    FT_TRY(ft_to_bf16(ctx, X, ldx, m->cvt_hi, x2 ? m->cvt_lo : nullptr, kp, T, g.in));
+    int r = ft_gemm_tc(ctx, m->cvt_hi, kp, g.w_nk, FT_F16, g.in, Y, ldy, T, g.n, g.in, false);
+    if (r == FT_OK && x2)
+      r = ft_gemm_tc(ctx, m->cvt_lo, kp, g.w_nk, FT_F16, g.in, Y, ldy, T, g.n, g.in, true);
+    if (r != FT_ERR_UNSUPPORTED) return r;
+  }
+  for (int j = 0; j < g.nlin; ++j) {
+    const Linear& l = *g.lin[j];
+    FT_TRY(ft_gemm_simt(ctx, X, ldx, 1, l.w_io, base_type(m), l.out, 1, Y + g.col_off[j], ldy, T,
+                        l.out, l.in, 1.f, false));
+  }
+  return FT_OK;
+}
+
+// dX[T, in] (=|+=) dY[T, n] (lddy) . W^T for a whole group
+int group_matmul_bwd(FtLoraModel* m, const Group& g, const float* dY, long long lddy, float* dX,
+                     long long lddx, int T, bool accumulate) {
+  FtContext* ctx = m->ctx;
+  if (use_tc(m) && g.w_kn) {
+    long long kp = (long long)ft_align_up((size_t)g.n, 8);
+    bool x2 = ctx->gemm_mode == FT_GEMM_BF16X2;
+    FT_TRY(ft_to_bf16(ctx, dY, lddy, m->cvt_hi, x2 ? m->cvt_lo : nullptr, kp, T, g.n));
+    int r = ft_gemm_tc(ctx, m->cvt_hi, kp, g.w_kn, FT_F16, g.n, dX, lddx, T, g.in, g.n, accumulate);
+    if (r == FT_OK && x2)
+      r = ft_gemm_tc(ctx, m->cvt_lo, kp, g.w_kn, FT_F16, g.n, dX, lddx, T, g.in, g.n, true);
+    if (r != FT_ERR_UNSUPPORTED) return r;
+  }
+  for (int j = 0; j < g.nlin; ++j) {
+    const Linear& l = *g.lin[j];
+    // B(k = output feature, n = input feature) = W[n, k]
+    FT_TRY(ft_gemm_simt(ctx, dY + g.col_off[j], lddy, 1, l.w_io, base_type(m), 1, l.out, dX, lddx,
+                        T, l.in, l.out, 1.f, accumulate || j > 0));
+  }
+  return FT_OK;
+}
+
+// Y = X W + (alpha/r) (X A) B + bias, for every linear of the group; xa keeps (alpha/r) X A
+int linear_fwd(FtLoraModel* m, const Group& g, const float* X, long long ldx, float* Y,
+               long long ldy, float* xa, int T) {
+  FtContext* ctx = m->ctx;
+  const int r = m->cfg.lora_rank;
+  FT_TRY(group_matmul_fwd(m, g, X, ldx, Y, ldy, T));
+  for (int j = 0; j < g.nlin; ++j) {
+    const Linear& l = *g.lin[j];
+    if (l.lora) {
+      const float* A = m->params + l.a_off;
+      const float* B = m->params + l.b_off;
+      float* xaj = xa + g.r_off[j];
+      FT_TRY(ft_gemm_simt(ctx, X, ldx, 1, A, FT_F32, r, 1, xaj, g.R, T, r, l.in, m->scale, false));
+      FT_TRY(ft_gemm_simt(ctx, xaj, g.R, 1, B, FT_F32, l.out, 1, Y + g.col_off[j], ldy, T, l.out,
+                          r, 1.f, true));
+    }
+    if (l.bias) FT_TRY(ft_k_add_bias(ctx, Y + g.col_off[j], ldy, l.bias, T, l.out));
+  }
+  return FT_OK;
+}
+
+// Adapter gradients (added into the flat buffer) and, when dX != NULL, the input gradient
+// dX (=|+=) dY W^T + (alpha/r) (dY B^T) A^T.
+int linear_bwd(FtLoraModel* m, const Group& g, const float* X, long long ldx, const float* dY,
+               long long lddy, const float* xa, float* dX, long long lddx, int T,
+               bool accumulate_dx) {
+  FtContext* ctx = m->ctx;
+  const int r = m->cfg.lora_rank;
+  if (dX) FT_TRY(group_matmul_bwd(m, g, dY, lddy, dX, lddx, T, accumulate_dx));
+  for (int j = 0; j < g.nlin; ++j) {
+    const Linear& l = *g.lin[j];
+    if (!l.lora) continue;
+    const float* A = m->params + l.a_off;
+    const float* B = m->params + l.b_off;
+    const float* dYj = dY + g.col_off[j];
+    const float* xaj = xa + g.r_off[j];
+    float* gj = m->g;  // [T, r], pitch r
+    // G = (alpha/r) dY B^T        B operand (k = out, n = r) = B[n, k]
+    FT_TRY(ft_gemm_simt(ctx, dYj, lddy, 1, B, FT_F32, 1, l.out, gj, r, T, r, l.out, m->scale, false));
+    // dB += ((alpha/r) X A)^T dY   [r, out], reduction over tokens
+    FT_TRY(ft_gemm_simt(ctx, xaj, 1, g.R, dYj, FT_F32, lddy, 1, m->grads + l.b_off, l.out, r, l.out,
+                        T, 1.f, true));
+    // dA += X^T G                  [in, r], reduction over tokens
+    FT_TRY(ft_gemm_simt(ctx, X, 1, ldx, gj, FT_F32, r, 1, m->grads + l.a_off, r, l.in, r, T, 1.f,
+                        true));
+    // dX += G A^T                  B operand (k = r, n = in) = A[n, k]
+    if (dX)
+      FT_TRY(ft_gemm_simt(ctx, gj, r, 1, A, FT_F32, 1, r, dX, lddx, T, l.in, r, 1.f, true));
+  }
+  return FT_OK;
+}
+
+int block_forward(FtLoraModel* m, int l, const float* x_in, float* x_out, BlockActs& a) {
+  FtContext* ctx = m->ctx;
+  const FtModelConfig& c = m->cfg;
+  Layer& ly = m->layers[l];
+  const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
+  FT_TRY(ft_k_rms_norm(ctx, x_in, ly.norm1, a.h1, T, h, c.eps));
+  FT_TRY(linear_fwd(m, ly.qkv, a.h1, h, a.qkv, nqkv, a.xa_qkv, T));
+  FT_TRY(ft_k_rope(ctx, a.qkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, false));
+  FT_TRY(ft_k_rope(ctx, a.qkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, false));
+  FtAttnLaunch at;
+  at.q = a.qkv; at.k = a.qkv + nq; at.v = a.qkv + nq + nkv;
+  at.ldq = at.ldk = at.ldv = nqkv;
+  at.out = a.attn; at.ldo = nq; at.stats = a.stats;
+  memset(&at.p, 0, sizeof(at.p));
+  at.p.batch = m->sequences; at.p.heads = c.heads; at.p.kv_heads = c.kv_heads;
+  at.p.seq_q = at.p.seq_k = m->seq_len; at.p.head_dim = c.head_dim; at.p.causal = 1;
+  FT_TRY(ft_k_attention_fwd(ctx, at));
+  FT_TRY(linear_fwd(m, ly.o, a.attn, nq, a.x1, h, a.xa_o, T));
+  FT_TRY(ft_k_add(ctx, x_in, a.x1, a.x1, (size_t)T * h));
+  FT_TRY(ft_k_rms_norm(ctx, a.x1, ly.norm2, a.h2, T, h, c.eps));
+  FT_TRY(linear_fwd(m, ly.gu, a.h2, h, a.gu, 2 * F, a.xa_gu, T));
+  FT_TRY(ft_k_silu_gate(ctx, a.gu, 2 * F, a.gu + F, 2 * F, a.f, F, T, F));
+  FT_TRY(linear_fwd(m, ly.down, a.f, F, x_out, h, a.xa_down, T));
+  FT_TRY(ft_k_add(ctx, a.x1, x_out, x_out, (size_t)T * h));
+  return FT_OK;
+}
+
+// on entry m->dx = dL/d(x_out); on exit m->dx = dL/d(x_in) (undefined for layer 0)
+int block_backward(FtLoraModel* m, int l, const float* x_in, BlockActs& a) {
+  FtContext* ctx = m->ctx;
+  const FtModelConfig& c = m->cfg;
+  Layer& ly = m->layers[l];
+  const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
+  // x_out = x1 + down(f)
+  FT_TRY(linear_bwd(m, ly.down, a.f, F, m->dx, h, a.xa_down, m->df, F, T, false));
+  FT_TRY(ft_k_silu_gate_bwd(ctx, a.gu, 2 * F, a.gu + F, 2 * F, m->df, F, m->dgu, 2 * F,
+                            m->dgu + F, 2 * F, T, F));
+  FT_TRY(linear_bwd(m, ly.gu, a.h2, h, m->dgu, 2 * F, a.xa_gu, m->dh, h, T, false));
+  FT_TRY(ft_k_rms_norm_bwd(ctx, a.x1, ly.norm2, m->dh, m->dx, nullptr, T, h, c.eps, true));
+  // x1 = x_in + o(attn)
+  FT_TRY(linear_bwd(m, ly.o, a.attn, nq, m->dx, h, a.xa_o, m->dattn, nq, T, false));
+  FtAttnBwdLaunch ab;
+  ab.q = a.qkv; ab.k = a.qkv + nq; ab.v = a.qkv + nq + nkv;
+  ab.ldq = ab.ldk = ab.ldv = nqkv;
+  ab.out = a.attn; ab.ldo = nq; ab.dout = m->dattn; ab.lddo = nq;
+  ab.dq = m->dqkv; ab.dk = m->dqkv + nq; ab.dv = m->dqkv + nq + nkv;
+  ab.lddq = ab.lddk = ab.lddv = nqkv;
+  ab.stats = a.stats;
+  memset(&ab.p, 0, sizeof(ab.p));
+  ab.p.batch = m->sequences; ab.p.heads = c.heads; ab.p.kv_heads = c.kv_heads;
+  ab.p.seq_q = ab.p.seq_k = m->seq_len; ab.p.head_dim = c.head_dim; ab.p.causal = 1;
+  ab.p.lse_saved = 1;
+  FT_TRY(ft_k_attention_bwd(ctx, ab));
+  FT_TRY(ft_k_rope(ctx, m->dqkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, true));
+  FT_TRY(ft_k_rope(ctx, m->dqkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, true));
+  // The embedding output is frozen: layer 0 needs adapter gradients only.
+  const bool need_dx = l > 0;
+  FT_TRY(linear_bwd(m, ly.qkv, a.h1, h, m->dqkv, nqkv, a.xa_qkv, need_dx ? m->dh : nullptr, h, T,
+                    false));
+  if (need_dx)
+    FT_TRY(ft_k_rms_norm_bwd(ctx, x_in, ly.norm1, m->dh, m->dx, nullptr, T, h, c.eps, true));
+  return FT_OK;
+}
+
+__global__ void k_copy_f16_2d(const __half* __restrict__ src, long long lds, __half* __restrict__ dst,
+                              long long ldd, int rows, int cols) {
+  size_t total = (size_t)rows * cols;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    size_t r = i / cols, c = i % cols;
+    dst[r * ldd + c] = src[r * lds + c];
+  }
+}
+// dst[c, r] (pitch ldd) = src[r, c] (pitch lds)
+__global__ void k_transpose_f16(const __half* __restrict__ src, long long lds,
+                                __half* __restrict__ dst, long long ldd, int rows, int cols) {
+  __shared__ __half tile[32][34];
+  int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int r = r0 + j, c = c0 + threadIdx.x;
+    tile[j][threadIdx.x] = (r < rows && c < cols) ? src[(long long)r * lds + c] : __half(0.f);
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) dst[(long long)c * ldd + r] = tile[threadIdx.x][j];
+  }
+}
+
+int prepare_group(FtLoraModel* m, Group& g) {
+  FtContext* ctx = m->ctx;
+  if (!m->cfg.f16_base) return FT_OK;  // tensor-core operands exist for f16 bases only
+  if ((g.in % 8) || (g.n % 8)) return FT_OK;  // TMA pitch rule not met: exact path serves it
+  void* p = nullptr;
+  FT_CUDA(cudaMalloc(&p, (size_t)g.n * g.in * sizeof(__half)));
+  m->owned.push_back(p);
+  g.w_nk = (__half*)p;
+  if (g.nlin == 1) {
+    g.w_kn = (__half*)g.lin[0]->w_io;  // [in, out] as the reference stores it
+    g.own_kn = false;
+  } else {
+    FT_CUDA(cudaMalloc(&p, (size_t)g.n * g.in * sizeof(__half)));
+    m->owned.push_back(p);
+    g.w_kn = (__half*)p;
+    g.own_kn = true;
+  }
+  for (int j = 0; j < g.nlin; ++j) {
+    const Linear& l = *g.lin[j];
+    const __half* w = (const __half*)l.w_io;  // [in, out]
+    dim3 grid(ft_cdiv(l.out, 32), ft_cdiv(l.in, 32)), block(32, 8);
+    FT_REQUIRE(grid.y <= 65535, "prepare: input width too large");
+    FT_LAUNCH(ctx, k_transpose_f16, grid, block, 0, w, (long long)l.out,
+              g.w_nk + (size_t)g.col_off[j] * g.in, (long long)g.in, l.in, l.out);
+    if (g.own_kn) {
+      int cg = (int)std::min<size_t>(((size_t)l.in * l.out + 255) / 256, (size_t)ctx->sm_count * 16);
+      FT_LAUNCH(ctx, k_copy_f16_2d, cg, 256, 0, w, (long long)l.out, g.w_kn + g.col_off[j],
+                (long long)g.n, l.in, l.out);
+    }
+  }
+  return FT_OK;
+}
+
+}  // namespace
+
+// =========================================================================================
+extern "C" int ft_model_create(FtContext* ctx, const FtModelConfig* cfg, FtLoraModel** out) {
+  FT_REQUIRE(ctx && cfg && out, "ft_model_create: NULL argument");
+  FT_REQUIRE(cfg->vocab > 0 && cfg->hidden > 0 && cfg->layers > 0 && cfg->heads > 0 &&
+                 cfg->kv_heads > 0 && cfg->head_dim > 0 && cfg->ffn > 0,
+             "ft_model_create: empty dimension");
+  FT_REQUIRE(cfg->heads % cfg->kv_heads == 0, "ft_model_create: heads %% kv_heads != 0");
+  FT_REQUIRE(cfg->head_dim % 4 == 0 && cfg->head_dim <= 128,
+             "ft_model_create: head_dim must be a multiple of 4, at most 128");
+  FT_REQUIRE(cfg->lora_rank >= 0, "ft_model_create: negative rank");
+  FtLoraModel* m = new FtLoraModel();
+  m->ctx = ctx;
+  m->cfg = *cfg;
+  m->nq = cfg->heads * cfg->head_dim;
+  m->nkv = cfg->kv_heads * cfg->head_dim;
+  m->scale = cfg->lora_rank ? cfg->lora_alpha / (float)cfg->lora_rank : 0.f;
+  m->layers.resize(cfg->layers);
+  const int h = cfg->hidden, F = cfg->ffn, r = cfg->lora_rank;
+  const int ins[FT_LINEARS] = {h, h, h, m->nq, h, h, F};
+  const int outs[FT_LINEARS] = {m->nq, m->nkv, m->nkv, h, F, F, h};
+  size_t off = 0;
+  for (int l = 0; l < cfg->layers; ++l) {
+    Layer& ly = m->layers[l];
+    for (int i = 0; i < FT_LINEARS; ++i) {
+      Linear& li = ly.lin[i];
+      li.in = ins[i];
+      li.out = outs[i];
+      li.lora = r > 0 && ((cfg->lora_mask >> i) & 1);
+      if (li.lora) {
+        li.a_off = off; off += (size_t)li.in * r;
+        li.b_off = off; off += (size_t)r * li.out;
+      }
+    }
+    setup_group(ly.qkv, {&ly.lin[FT_Q], &ly.lin[FT_K], &ly.lin[FT_V]}, r);
+    setup_group(ly.o, {&ly.lin[FT_O]}, r);
+    setup_group(ly.gu, {&ly.lin[FT_GATE], &ly.lin[FT_UP]}, r);
+    setup_group(ly.down, {&ly.lin[FT_DOWN]}, r);
+  }
+  m->head_lin.in = h;
+  m->head_lin.out = cfg->vocab;
+  m->head_lin.lora = r > 0 && cfg->lora_head;
+  if (m->head_lin.lora) {
+    m->head_lin.a_off = off; off += (size_t)h * r;
+    m->head_lin.b_off = off; off += (size_t)r * cfg->vocab;
+  }
+  setup_group(m->head, {&m->head_lin}, r);
+  m->trainable = off;
+  *out = m;
+  return FT_OK;
+}
+
+extern "C" int ft_model_destroy(FtLoraModel* m) {
+  if (!m) return FT_OK;
+  cudaStreamSynchronize(m->ctx->stream);
+  for (void* p : m->owned) cudaFree(p);
+  if (m->apply_scratch) cudaFree(m->apply_scratch);
+  delete m;
+  return FT_OK;
+}
+
+extern "C" int ft_model_trainable_count(FtLoraModel* m, size_t* n) {
+  FT_REQUIRE(m && n, "ft_model_trainable_count: NULL argument");
+  *n = m->trainable;
+  return FT_OK;
+}
+
+extern "C" int ft_model_adapter_offset(FtLoraModel* m, int layer, int linear, int which_b,
+                                       size_t* offset, int* rows, int* cols) {
+  FT_REQUIRE(m && offset && rows && cols, "ft_model_adapter_offset: NULL argument");
+  const Linear* li;
+  if (layer < 0) {
+    li = &m->head_lin;
+  } else {
+    FT_REQUIRE(layer < m->cfg.layers && linear >= 0 && linear < FT_LINEARS,
+               "ft_model_adapter_offset: layer %d linear %d out of range", layer, linear);
+    li = &m->layers[layer].lin[linear];
+  }
+  FT_REQUIRE(li->lora, "ft_model_adapter_offset: that linear carries no adapter");
+  const int r = m->cfg.lora_rank;
+  if (which_b) { *offset = li->b_off; *rows = r; *cols = li->out; }
+  else { *offset = li->a_off; *rows = li->in; *cols = r; }
+  return FT_OK;
+}
+
+extern "C" int ft_model_set_embedding(FtLoraModel* m, const float* embed, const float* final_norm,
+                                      const void* head) {
+  FT_REQUIRE(m && embed && final_norm && head, "ft_model_set_embedding: NULL argument");
+  m->embed = embed;
+  m->final_norm = final_norm;
+  m->head_lin.w_io = head;
+  m->prepared = false;
+  return FT_OK;
+}
+
+extern "C" int ft_model_set_layer(FtLoraModel* m, int layer, const float* norm1,
+                                  const float* norm2, const void* const linears[FT_LINEARS],
+                                  const float* const biases[3]) {
+  FT_REQUIRE(m && norm1 && norm2 && linears, "ft_model_set_layer: NULL argument");
+  FT_REQUIRE(layer >= 0 && layer < m->cfg.layers, "ft_model_set_layer: layer %d out of range",
+             layer);
+  Layer& ly = m->layers[layer];
+  ly.norm1 = norm1;
+  ly.norm2 = norm2;
+  for (int i = 0; i < FT_LINEARS; ++i) {
+    FT_REQUIRE(linears[i], "ft_model_set_layer: linear %d is NULL", i);
+    ly.lin[i].w_io = linears[i];
+  }
+  if (m->cfg.qkv_bias) {
+    FT_REQUIRE(biases && biases[0] && biases[1] && biases[2],
+               "ft_model_set_layer: q/k/v biases required by the config");
+    for (int i = 0; i < 3; ++i) ly.lin[i].bias = biases[i];
+  }
+  m->prepared = false;
+  return FT_OK;
+}
+
+extern "C" int ft_model_set_state(FtLoraModel* m, float* params, float* grads, float* adam_m,
+                                  float* adam_v) {
+  FT_REQUIRE(m, "ft_model_set_state: model is NULL");
+  FT_REQUIRE(m->trainable == 0 || (params && grads && adam_m && adam_v),
+             "ft_model_set_state: NULL buffer");
+  m->params = params; m->grads = grads; m->adam_m = adam_m; m->adam_v = adam_v;
+  return FT_OK;
+}
+
+extern "C" int ft_model_prepare(FtLoraModel* m) {
+  FT_REQUIRE(m, "ft_model_prepare: model is NULL");
+  FT_REQUIRE(m->embed && m->head_lin.w_io, "ft_model_prepare: embedding/head not set");
+  for (auto& ly : m->layers)
+    FT_REQUIRE(ly.norm1 && ly.lin[0].w_io, "ft_model_prepare: a layer has no weights");
+  cudaStreamSynchronize(m->ctx->stream);
+  for (void* p : m->owned) cudaFree(p);
+  m->owned.clear();
+  for (auto& ly : m->layers) {
+    FT_TRY(prepare_group(m, ly.qkv));
+    FT_TRY(prepare_group(m, ly.o));
+    FT_TRY(prepare_group(m, ly.gu));
+    FT_TRY(prepare_group(m, ly.down));
+  }
+  FT_TRY(prepare_group(m, m->head));
+  if (!m->apply_scratch) {
+    size_t chunks = (m->trainable + FT_SUM_SQUARES_CHUNK - 1) / FT_SUM_SQUARES_CHUNK;
+    FT_CUDA(cudaMalloc((void**)&m->apply_scratch, (chunks + 8) * sizeof(float)));
+  }
+  m->prepared = true;
+  return FT_OK;
+}
+
+extern "C" int ft_model_workspace_bytes(FtLoraModel* m, int sequences, int seq_len,
+                                        size_t* bytes) {
+  FT_REQUIRE(m && bytes && sequences > 0 && seq_len > 0, "ft_model_workspace_bytes: bad argument");
+  *bytes = plan(m, sequences, seq_len, true, nullptr);
+  return FT_OK;
+}
+
+extern "C" int ft_model_set_workspace(FtLoraModel* m, void* p, size_t bytes) {
+  FT_REQUIRE(m && p, "ft_model_set_workspace: NULL argument");
+  FT_REQUIRE((((uintptr_t)p) & 255) == 0, "ft_model_set_workspace: pointer must be 256-byte aligned");
+  m->ws = p;
+  m->ws_bytes = bytes;
+  m->T = 0;
+  return FT_OK;
+}
+
+extern "C" int ft_model_zero_grad(FtLoraModel* m) {
+  FT_REQUIRE(m, "ft_model_zero_grad: model is NULL");
+  if (m->trainable)
+    FT_CUDA(cudaMemsetAsync(m->grads, 0, m->trainable * sizeof(float), m->ctx->stream));
+  return FT_OK;
+}
+
+extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
+                                         const uint32_t* targets, const float* weights,
+                                         int sequences, int seq_len, float seed, float* row_loss,
+                                         float* logits) {
+  FT_REQUIRE(m && ids && targets && weights && row_loss, "ft_model_forward_backward: NULL argument");
+  FT_REQUIRE(m->prepared, "ft_model_forward_backward: call ft_model_prepare first");
+  FT_REQUIRE(sequences > 0 && seq_len > 0, "ft_model_forward_backward: empty batch");
+  FT_REQUIRE(m->trainable == 0 || m->params, "ft_model_forward_backward: state not set");
+  FtContext* ctx = m->ctx;
+  const FtModelConfig& c = m->cfg;
+  if (m->sequences != sequences || m->seq_len != seq_len || m->T == 0) {
+    size_t need = plan(m, sequences, seq_len, true, nullptr);
+    FT_REQUIRE(m->ws && need <= m->ws_bytes,
+               "ft_model_forward_backward: workspace of %zu bytes needed, %zu given", need,
+               m->ws_bytes);
+    plan(m, sequences, seq_len, false, m->ws);
+  }
+  const int T = m->T, h = c.hidden, L = c.layers, V = c.vocab;
+  const bool ckpt = c.checkpoint_blocks != 0;
+
+  // ---- forward
+  FT_TRY(ft_k_embedding(ctx, m->embed, ids, m->x[0], T, V, h));
+  for (int l = 0; l < L; ++l)
+    FT_TRY(block_forward(m, l, m->x[l], m->x[l + 1], m->acts[ckpt ? 0 : l]));
+  FT_TRY(ft_k_rms_norm(ctx, m->x[L], m->final_norm, m->hN, T, h, c.eps));
+
+  // ---- head + loss + head backward, in row chunks; m->dh collects dL/d(hN)
+  for (int r0 = 0; r0 < T; r0 += m->head_chunk) {
+    const int rows = std::min(m->head_chunk, T - r0);
+    const float* X = m->hN + (size_t)r0 * h;
+    float* xa = m->xa_head + (size_t)r0 * std::max(1, m->head.R);
+    float* z = logits ? logits + (size_t)r0 * V : m->logit_chunk;
+    FT_TRY(linear_fwd(m, m->head, X, h, z, V, xa, rows));
+    FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, m->logit_chunk, row_loss + r0, rows,
+                          V, seed));
+    FT_TRY(linear_bwd(m, m->head, X, h, m->logit_chunk, V, xa, m->dh + (size_t)r0 * h, h, rows,
+                      false));
+  }
+  FT_TRY(ft_k_rms_norm_bwd(ctx, m->x[L], m->final_norm, m->dh, m->dx, nullptr, T, h, c.eps, false));
+
+  // ---- blocks, last to first
+  for (int l = L - 1; l >= 0; --l) {
+    BlockActs& a = m->acts[ckpt ? 0 : l];
+    if (ckpt) FT_TRY(block_forward(m, l, m->x[l], m->x[l + 1], a));  // replay; rewrites x[l+1]
+    FT_TRY(block_backward(m, l, m->x[l], a));
+  }
+  return FT_OK;
+}
+
+extern "C" int ft_model_apply_gradients(FtLoraModel* m, float grad_scale, float max_norm,
+                                        const FtAdamParams* p, float* norm_out) {
+  FT_REQUIRE(m && p, "ft_model_apply_gradients: NULL argument");
+  FT_REQUIRE(m->prepared, "ft_model_apply_gradients: call ft_model_prepare first");
+  if (!m->trainable) return FT_OK;
+  size_t chunks = (m->trainable + FT_SUM_SQUARES_CHUNK - 1) / FT_SUM_SQUARES_CHUNK;
+  float* partials = m->apply_scratch;
+  float* nout = norm_out ? norm_out : m->apply_scratch + chunks;
+  return ft_k_apply_fused(m->ctx, m->params, m->grads, m->adam_m, m->adam_v, m->trainable,
+                          grad_scale, max_norm, p, partials, nout);
+}

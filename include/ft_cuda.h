@@ -1,0 +1,244 @@
+/*
+ * ft_cuda.h - C ABI of libft_cuda.so, the sm_100a `cuda` device for ferrotensor's
+ * LoRA fine-tuning step.
+ *
+ * Every entry point below replaces one method of the reference's operator surface,
+ * `ferrotensor_backend::ComputeEngine` (plus the tensor/context plumbing it needs), and
+ * keeps that method's argument meaning:
+ *   - buffers are plain device pointers owned by the caller; shapes are row-major, dense,
+ *     outermost first, and passed as explicit sizes;
+ *   - outputs are pre-allocated by the caller and OVERWRITTEN, never accumulated, except
+ *     for the methods the reference documents as in place;
+ *   - calls enqueue work on the context's stream in program order and return at once;
+ *     only ft_ctx_synchronize / ft_download* wait for the device;
+ *   - arithmetic is f32; "f16b" weights are IEEE binary16, two per little-endian 32-bit
+ *     word, element 2i in the low half (the reference's FP16 storage format).
+ * Where the reference panics on a precondition these functions return non-zero and
+ * ft_last_error() describes the failure.  A kernel never traps: device-side problems
+ * (a bounded wait that ran out) are reported through ft_ctx_status().
+ *
+ * Paths cited are relative to the reference repository.
+ */
+#ifndef FT_CUDA_H
+#define FT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FT_OK 0
+#define FT_ERR_INVALID 1   /* precondition violated (the reference would panic)     */
+#define FT_ERR_CUDA 2      /* a CUDA runtime call failed                            */
+#define FT_ERR_UNSUPPORTED 3
+#define FT_ERR_DEVICE 4    /* a kernel reported a failed bounded wait               */
+
+/* ferrotensor-backend/src/engine/training.rs:7,11 */
+#define FT_MASKED_CE_SKIP 0xffffffffu
+#define FT_SUM_SQUARES_CHUNK 4096u
+
+/* How the dense contractions round their operands (accumulation is always f32).
+ *   FT_GEMM_F32   exact f32 FMA on CUDA cores - the parity path
+ *   FT_GEMM_BF16  activations rounded to bf16, f16 weights exact, tcgen05 tensor cores
+ *   FT_GEMM_BF16X2 activations split hi+lo bf16 (16 mantissa bits), two tensor-core passes */
+#define FT_GEMM_F32 0
+#define FT_GEMM_BF16 1
+#define FT_GEMM_BF16X2 2
+
+typedef struct FtContext FtContext;
+
+/* ---- context: ferrotensor-backend/src/context.rs:164-237 (new), :373-397 (flush,
+ * synchronize).  `stream` is a cudaStream_t to enqueue on, or NULL for a stream the
+ * context creates.  One context per process and device, as in the reference. */
+int ft_ctx_create(int device_ordinal, void* stream, FtContext** out);
+int ft_ctx_destroy(FtContext* ctx);
+int ft_ctx_flush(FtContext* ctx);        /* no-op: a stream needs no submit            */
+int ft_ctx_synchronize(FtContext* ctx);  /* waits; returns FT_ERR_DEVICE if a kernel failed */
+int ft_ctx_status(FtContext* ctx, int* device_status); /* non-blocking read of the status word */
+int ft_ctx_set_gemm_mode(FtContext* ctx, int mode);    /* FT_GEMM_*; default FT_GEMM_F32 */
+int ft_ctx_launch_count(FtContext* ctx, uint64_t* kernels_launched);
+const char* ft_last_error(void);
+/* Lists, one name per line, every kernel family compiled into the library. */
+const char* ft_build_info(void);
+
+/* ---- tensors: ferrotensor-backend/src/tensor.rs:157-406 (UnifiedTensor::{new, empty,
+ * zeros, from_f32_as_f16, from_f32_transposed, to_vec, write_data}). */
+int ft_tensor_alloc(FtContext* ctx, size_t bytes, void** dev_ptr);
+int ft_tensor_free(FtContext* ctx, void* dev_ptr);
+int ft_tensor_zero(FtContext* ctx, void* dev_ptr, size_t bytes);
+int ft_upload(FtContext* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int ft_download(FtContext* ctx, void* dst_host, const void* src_dev, size_t bytes);
+/* n f32 values on the host -> packed binary16 (round to nearest even) on the device. */
+int ft_upload_f32_as_f16(FtContext* ctx, void* dst_dev, const float* src_host, size_t n);
+/* host f32 [rows, cols] -> device [cols, rows]; as_f16 != 0 also rounds to binary16
+ * (tensor.rs:385-406: how a Hugging Face [out, in] weight becomes the [in, out] operand). */
+int ft_upload_f32_transposed(FtContext* ctx, void* dst_dev, const float* src_host,
+                             size_t rows, size_t cols, int as_f16);
+/* device-side forms of the two conversions (src already on the device, f32) */
+int ft_convert_f32_to_f16(FtContext* ctx, const float* src, void* dst, size_t n);
+int ft_transpose_f32(FtContext* ctx, const float* src, void* dst, size_t rows, size_t cols,
+                     int as_f16);
+
+/* ---- matmul: ferrotensor-backend/src/engine/matmul.rs:94-156.
+ * out[M,N] = a[M,K] b[K,N] | a[M,K] b[N,K]^T | a[K,M]^T b[K,N]; *_f16b: b is packed f16. */
+int ft_matmul(FtContext* ctx, const float* a, const float* b, float* out, int M, int K, int N);
+int ft_matmul_bt(FtContext* ctx, const float* a, const float* b, float* out, int M, int K, int N);
+int ft_matmul_at(FtContext* ctx, const float* a, const float* b, float* out, int M, int K, int N);
+int ft_matmul_f16b(FtContext* ctx, const float* a, const void* b_f16, float* out, int M, int K,
+                   int N);
+int ft_matmul_bt_f16b(FtContext* ctx, const float* a, const void* b_f16, float* out, int M,
+                      int K, int N);
+
+/* ---- rope: engine/attention.rs:21-83, shaders/kernels.wgsl:45-73.  In place on
+ * n_elems f32 laid out [tokens, heads, head_dim]; token t sits at position
+ * pos + (t % seq_len); pairs (x[i], x[i + head_dim/2]); inverse != 0 rotates by the
+ * negated angle (the backward pass). */
+int ft_rope_theta(FtContext* ctx, float* x, size_t n_elems, int head_dim, int seq_len,
+                  int heads, int pos, float theta, int inverse);
+
+/* ---- RMSNorm: engine/norm.rs:20-99, kernels.wgsl:76-151. */
+int ft_rms_norm_eps(FtContext* ctx, const float* x, const float* w, float* out, int rows,
+                    int size, float eps);
+/* gx[rows,size] and gw[size] are both written (gw may be NULL when the norm is frozen). */
+int ft_rms_norm_backward(FtContext* ctx, const float* x, const float* w, const float* g,
+                         float* gx, float* gw, int rows, int size, float eps);
+
+/* ---- elementwise: engine/elementwise.rs:8-17,57-75,183-215; engine/training.rs:189-205;
+ * engine/mod.rs:399-428 (copy_tensor). */
+int ft_add(FtContext* ctx, const float* a, const float* b, float* out, size_t n);
+int ft_add_backward(FtContext* ctx, const float* g, float* ga, float* gb, size_t n);
+int ft_gradient_scale(FtContext* ctx, float* x, size_t n, float scale);
+int ft_copy(FtContext* ctx, const void* src, void* dst, size_t dst_offset_bytes, size_t bytes);
+/* out = silu(a) * b: the FIRST operand passes through SiLU (the model passes the gate
+ * projection first, ferrotensor-graph/src/lib.rs:504-510). */
+int ft_silu_gate_fused(FtContext* ctx, const float* a, const float* b, float* out, size_t n);
+int ft_silu_gate_backward(FtContext* ctx, const float* a, const float* b, const float* g,
+                          float* ga, float* gb, size_t n);
+
+/* ---- attention: engine/attention.rs:139-255 (forward, with stats), :312-441 (backward),
+ * :515-594 (parameter block and AttentionOptions).  q, out, dout, dq are
+ * [batch, seq_q, heads, head_dim]; k, v, dk, dv are [batch, seq_k, kv_heads, head_dim].
+ * stats (may be NULL) has 2 f32 per (batch, head, query) row: element 2*row+1 receives
+ * the row's log-sum-exp in the forward pass, element 2*row is backward scratch (Delta).
+ * The backward pass recomputes the log-sum-exp when stats is NULL or lse_saved == 0. */
+typedef struct FtAttnParams {
+  uint32_t batch, heads, seq_q, seq_k, head_dim, kv_heads;
+  uint32_t causal;        /* hide keys after the query's absolute position           */
+  uint32_t causal_offset; /* absolute position of query 0                            */
+  uint32_t window;        /* sliding window in tokens; 0 = unlimited                 */
+  float scale;            /* 0 => 1/sqrt(head_dim)                                   */
+  float dropout_prob;     /* must be 0: attention dropout is outside this library    */
+  uint32_t lse_saved;     /* backward only: stats already holds the forward's LSE    */
+} FtAttnParams;
+int ft_flash_attention_v2(FtContext* ctx, const float* q, const float* k, const float* v,
+                          float* out, float* stats, const float* mask, const FtAttnParams* p);
+int ft_flash_attention_v2_backward(FtContext* ctx, const float* q, const float* k,
+                                   const float* v, const float* out, const float* dout,
+                                   float* dq, float* dk, float* dv, float* stats,
+                                   const float* mask, const FtAttnParams* p);
+
+/* ---- loss: engine/training.rs:207-258, kernels.wgsl:672-711.  Per row:
+ * row_loss = logZ - logit[target]; grad = (softmax - onehot) * weights[row];
+ * target == FT_MASKED_CE_SKIP => zero loss and gradient. */
+int ft_masked_cross_entropy_weighted(FtContext* ctx, const float* logits,
+                                     const uint32_t* targets, const float* weights, float* grad,
+                                     float* row_loss, int rows, int vocab);
+
+/* ---- optimizer side: engine/training.rs:15-32,54-77,161-171,263-290;
+ * kernels.wgsl:355-387,661-670,713-735. */
+typedef struct FtAdamParams {
+  float lr, beta1, beta2, eps, weight_decay, t;
+  float _pad[2];
+} FtAdamParams;
+/* writes ceil(n/4096) chunk sums to out[offset ...]; *chunks_written receives that count */
+int ft_sum_squares_partial(FtContext* ctx, const float* x, size_t n, float* out, size_t offset,
+                           size_t* chunks_written);
+int ft_clip_grad_by_norm(FtContext* ctx, float* g, size_t n, float scale);
+int ft_adamw_update(FtContext* ctx, float* w, const float* g, float* m, float* v, size_t n,
+                    const FtAdamParams* p);
+
+/* ---- embedding rows: ferrotensor-autograd/src/lib.rs:1159-1179 (a host loop in the
+ * reference).  out[t,:] = table[ids[t],:]; ids[t] >= vocab gives a zero row. */
+int ft_embedding_gather(FtContext* ctx, const float* table, const uint32_t* ids, float* out,
+                        int tokens, int vocab, int hidden);
+
+/* =====================================================================================
+ * Fused step: one object that runs the reference's whole LoRA step
+ * (ferrotensor-trainer/src/lib.rs:426-502 train_chunk, :296-360 apply_gradients;
+ * ferrotensor-graph/src/lfm.rs:116-139,597-623; ferrotensor-graph/src/lib.rs:112-142)
+ * as a fixed sequence of the kernels above plus fused forms of them.  It has no
+ * counterpart function in the reference: it is the composition its autograd tape
+ * performs, with the same results.
+ * ===================================================================================== */
+typedef struct FtLoraModel FtLoraModel;
+
+/* indices of the seven block linears, in the reference's order */
+enum { FT_Q = 0, FT_K, FT_V, FT_O, FT_GATE, FT_UP, FT_DOWN, FT_LINEARS };
+
+typedef struct FtModelConfig {
+  int vocab, hidden, layers, heads, kv_heads, head_dim, ffn;
+  float eps, theta;
+  int qkv_bias;          /* q/k/v projections carry a bias (Qwen2)                     */
+  int lora_rank;         /* 0 = no adapters                                            */
+  float lora_alpha;
+  int lora_mask;         /* bit i set => block linear i carries an adapter             */
+  int lora_head;         /* lm_head carries an adapter                                 */
+  int f16_base;          /* frozen linears and the head are stored as f16              */
+  int checkpoint_blocks; /* keep only block inputs, replay each block in backward      */
+} FtModelConfig;
+
+int ft_model_create(FtContext* ctx, const FtModelConfig* cfg, FtLoraModel** out);
+int ft_model_destroy(FtLoraModel* m);
+/* Number of trainable f32 values, and the offset of each adapter tensor inside the flat
+ * parameter / gradient / moment buffers.  Order: sorted by the reference's parameter name
+ * is NOT used; the flat order is layer-major, then linear index, A before B, then lm_head.
+ * layer == -1 addresses the lm_head adapter. */
+int ft_model_trainable_count(FtLoraModel* m, size_t* n);
+int ft_model_adapter_offset(FtLoraModel* m, int layer, int linear, int which_b, size_t* offset,
+                            int* rows, int* cols);
+/* Frozen weights.  `embed` f32 [vocab, hidden]; norms f32; every linear is given in the
+ * reference's device layout [in, out] (f32, or packed f16 when cfg.f16_base); biases f32.
+ * head may alias nothing: for tied models pass the separate [hidden, vocab] copy the
+ * reference's builder makes (model_builder.rs:653-689).  Pointers are borrowed. */
+int ft_model_set_embedding(FtLoraModel* m, const float* embed, const float* final_norm,
+                           const void* head_in_out);
+int ft_model_set_layer(FtLoraModel* m, int layer, const float* norm1, const float* norm2,
+                       const void* const linears_in_out[FT_LINEARS],
+                       const float* const biases[3]);
+/* Flat trainable state, each `trainable_count` f32: parameters, gradients, m, v. */
+int ft_model_set_state(FtLoraModel* m, float* params, float* grads, float* adam_m,
+                       float* adam_v);
+/* Called once after the weights are set (and again if they change): builds the operand
+ * copies the tensor-core path wants (transposed f16 weights, fused q|k|v and gate|up). */
+int ft_model_prepare(FtLoraModel* m);
+/* Bytes of activation workspace a micro-batch of `sequences` x `seq_len` needs. */
+int ft_model_workspace_bytes(FtLoraModel* m, int sequences, int seq_len, size_t* bytes);
+int ft_model_set_workspace(FtLoraModel* m, void* dev_ptr, size_t bytes);
+
+/* One micro-batch: embedding, blocks, head, masked CE, backward; LoRA gradients are ADDED
+ * into the flat gradient buffer (zero it with ft_model_zero_grad at the window start).
+ *   ids      u32 [sequences*seq_len] device
+ *   targets  u32 [rows] device, FT_MASKED_CE_SKIP for unsupervised rows
+ *   weights  f32 [rows] device, 1/tokens(sequence) or 0   (trainer/lib.rs:689-716)
+ *   seed     upstream gradient of the loss, 1/grad_accum_steps (trainer/lib.rs:474)
+ *   row_loss f32 [rows] device, receives each row's loss (0 for skipped rows)
+ *   logits   f32 [rows, vocab] device or NULL; when given the logits are materialised
+ *            there as the reference does, otherwise the head and the loss are fused. */
+int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids, const uint32_t* targets,
+                              const float* weights, int sequences, int seq_len, float seed,
+                              float* row_loss, float* logits);
+int ft_model_zero_grad(FtLoraModel* m);
+/* After the (optional) cross-rank sum of the gradient buffer: g *= grad_scale (1/world),
+ * global L2 norm on the device (4096-element f32 partials, summed in f64), skip when
+ * non-finite, clip with max_norm/(norm + 1e-6) when norm > max_norm (max_norm <= 0: no
+ * clipping), AdamW.  norm_out: device f32[4] (or NULL) = {norm, applied (1) or skipped (0), factor
+ * applied to the raw gradient, unused}. */
+int ft_model_apply_gradients(FtLoraModel* m, float grad_scale, float max_norm,
+                             const FtAdamParams* p, float* norm_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FT_CUDA_H */
