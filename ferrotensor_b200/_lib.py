@@ -15,7 +15,7 @@ LIB_PATH = PKG / "libft_cuda.so"
 FT_OK = 0
 FT_MASKED_CE_SKIP = 0xFFFFFFFF
 FT_SUM_SQUARES_CHUNK = 4096
-FT_GEMM_F32, FT_GEMM_BF16, FT_GEMM_BF16X2 = 0, 1, 2
+FT_GEMM_F32, FT_GEMM_F16, FT_GEMM_F16X2 = 0, 1, 2
 FT_LINEARS = 7
 
 
@@ -66,6 +66,7 @@ PROTOTYPES = {
     "ft_ctx_flush": [_P],
     "ft_ctx_synchronize": [_P],
     "ft_ctx_status": [_P, C.POINTER(_I)],
+    "ft_ctx_debug_words": [_P, C.POINTER(_I)],
     "ft_ctx_set_gemm_mode": [_P, _I],
     "ft_ctx_launch_count": [_P, C.POINTER(C.c_uint64)],
     "ft_tensor_alloc": [_P, _Z, C.POINTER(_P)],

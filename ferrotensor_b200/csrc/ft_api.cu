@@ -1,6 +1,7 @@
 // Context, error reporting, tensor plumbing and the per-operator C ABI wrappers.
 // Each wrapper validates what the reference asserts, then calls the internal kernel.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -27,7 +28,7 @@ extern "C" const char* ft_last_error(void) { return g_error; }
 extern "C" const char* ft_build_info(void) {
   return "arch: sm_100a\n"
          "gemm_simt_f32\n"
-         "gemm_tcgen05_bf16_f16 (TMA + TMEM)\n"
+         "gemm_tcgen05_f16 (TMA + TMEM)\n"
          "attention_fwd_simt_f32\nattention_bwd_simt_f32\n"
          "rms_norm\nrms_norm_backward\nrope\nsilu_gate\nmasked_cross_entropy\n"
          "sum_squares\nadamw\napply_fused\nembedding_gather\n";
@@ -55,9 +56,16 @@ extern "C" int ft_ctx_create(int device, void* stream, FtContext** out) {
     FT_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
     ctx->own_stream = true;
   }
-  FT_CUDA(cudaHostAlloc((void**)&ctx->status_host, sizeof(int) * 4, cudaHostAllocMapped));
-  memset(ctx->status_host, 0, sizeof(int) * 4);
+  FT_CUDA(cudaHostAlloc((void**)&ctx->status_host, sizeof(int) * 16, cudaHostAllocMapped));
+  memset(ctx->status_host, 0, sizeof(int) * 16);
+  const char* dbg = getenv("FT_GEMM_DEBUG");
+  ctx->debug_markers = dbg && dbg[0] == '1';
   FT_CUDA(cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
+  FT_CUDA(cudaMalloc((void**)&ctx->scale_buf, 8 * sizeof(float)));
+  {
+    const float init[8] = {0.f, 1.0f / 2048.0f, 0.f, 0.f, 1.f, 1.f, 1.0f / 2048.0f, 0.f};
+    FT_CUDA(cudaMemcpy(ctx->scale_buf, init, sizeof(init), cudaMemcpyHostToDevice));
+  }
   cudaDriverEntryPointQueryResult qres;
   void* fn = nullptr;
   cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -71,6 +79,7 @@ extern "C" int ft_ctx_destroy(FtContext* ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->scale_buf) cudaFree(ctx->scale_buf);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
@@ -99,9 +108,15 @@ extern "C" int ft_ctx_status(FtContext* ctx, int* s) {
   return FT_OK;
 }
 
+extern "C" int ft_ctx_debug_words(FtContext* ctx, int* out16) {
+  FT_REQUIRE(ctx && out16, "ft_ctx_debug_words: NULL argument");
+  for (int i = 0; i < 16; ++i) out16[i] = ctx->status_host[i];
+  return FT_OK;
+}
+
 extern "C" int ft_ctx_set_gemm_mode(FtContext* ctx, int mode) {
   FT_REQUIRE(ctx, "ft_ctx_set_gemm_mode: ctx is NULL");
-  FT_REQUIRE(mode == FT_GEMM_F32 || mode == FT_GEMM_BF16 || mode == FT_GEMM_BF16X2,
+  FT_REQUIRE(mode == FT_GEMM_F32 || mode == FT_GEMM_F16 || mode == FT_GEMM_F16X2,
              "ft_ctx_set_gemm_mode: unknown mode %d", mode);
   ctx->gemm_mode = mode;
   return FT_OK;
@@ -258,17 +273,14 @@ static int mm_dispatch(FtContext* ctx, const float* a, long long sam, long long 
                        int N, int K) {
   if (ctx->gemm_mode != FT_GEMM_F32 && sak == 1 && sbk == 1 && bt == FT_F16 && (K % 8) == 0 &&
       M >= 128 && N >= 64 && K >= 64) {
-    // A[M,K] row-major f32 -> bf16 scratch; B[N,K] K-contiguous f16 is used as stored.
+    // A[M,K] row-major f32 -> f16 scratch (auto-scaled: the caller's data may be gradients);
+    // B[N,K] K-contiguous f16 is used as stored.
     size_t kp = ft_align_up((size_t)K, 8);
-    size_t bytes = (size_t)M * kp * sizeof(__nv_bfloat16);
+    size_t bytes = ft_align_up((size_t)M * kp * sizeof(__half), 256);
     void* s = nullptr;
-    bool x2 = ctx->gemm_mode == FT_GEMM_BF16X2;
-    FT_TRY(ft_scratch(ctx, bytes * (x2 ? 2 : 1) + 512, &s));
-    __nv_bfloat16* hi = (__nv_bfloat16*)s;
-    __nv_bfloat16* lo = x2 ? (__nv_bfloat16*)((char*)s + ft_align_up(bytes, 256)) : nullptr;
-    FT_TRY(ft_to_bf16(ctx, a, sam, hi, lo, (long long)kp, M, K));
-    int r = ft_gemm_tc(ctx, hi, (long long)kp, b, bt, sbn, out, N, M, N, K, false);
-    if (r == FT_OK && x2) r = ft_gemm_tc(ctx, lo, (long long)kp, b, bt, sbn, out, N, M, N, K, true);
+    FT_TRY(ft_scratch(ctx, bytes * 2, &s));
+    int r = ft_gemm_tc_f32a(ctx, a, sam, (__half*)s, (__half*)((char*)s + bytes), b, sbn, out, N,
+                            M, N, K, false, true);
     if (r != FT_ERR_UNSUPPORTED) return r;
   }
   return ft_gemm_simt(ctx, a, sam, sak, b, bt, sbk, sbn, out, N, M, N, K, 1.f, false);

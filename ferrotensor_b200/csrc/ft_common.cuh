@@ -22,8 +22,12 @@ struct FtContext {
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   // status word written by kernels whose bounded waits ran out (pinned, device-mapped)
-  int* status_host = nullptr;
+  int* status_host = nullptr;   // 16 words: [0..3] status, [4..15] progress markers
   int* status_dev = nullptr;
+  bool debug_markers = false;   // FT_GEMM_DEBUG=1: kernels record progress markers
+  // device floats: [0] amax bits, [1] the constant 2^-11, [4..6] {S, 1/S, 2^-11/S} of the
+  // operand being converted (consumed by the GEMM that follows in stream order)
+  float* scale_buf = nullptr;
   // cuTensorMapEncodeTiled, resolved through the runtime (no link against libcuda)
   void* encode_tiled = nullptr;
 };
@@ -78,16 +82,22 @@ int ft_gemm_simt(FtContext* ctx, const float* a, long long sam, long long sak, c
                  FtDType b_type, long long sbk, long long sbn, float* c, long long ldc, int M,
                  int N, int K, float alpha, bool accumulate);
 
-// tcgen05 GEMM: C[M,N] f32 (ldc) (+)= A[M,K] bf16 (lda, K contiguous) . B[N,K]^T 16-bit
-// (ldb, K contiguous).  Returns FT_ERR_UNSUPPORTED when the shape breaks a TMA rule.
-//                                                                     (ft_gemm_tc.cu)
-int ft_gemm_tc(FtContext* ctx, const __nv_bfloat16* a, long long lda, const void* b,
-               FtDType b_type, long long ldb, float* c, long long ldc, int M, int N, int K,
-               bool accumulate);
-// f32 [rows, cols] (ld) -> bf16 [rows, cols_padded] (ldo); mode FT_GEMM_BF16X2 also writes
-// the low part to `lo`.                                               (ft_gemm_tc.cu)
-int ft_to_bf16(FtContext* ctx, const float* src, long long ld, __nv_bfloat16* hi,
-               __nv_bfloat16* lo, long long ldo, int rows, int cols);
+// tcgen05 GEMM: C[M,N] f32 (ldc) (=|+=) alpha * A[M,K] (lda) . B[N,K]^T (ldb), A and B both
+// f16 or both bf16, K contiguous.  alpha_ptr (device, may be NULL = 1) is read by the
+// epilogue.  Returns FT_ERR_UNSUPPORTED when the shape breaks a TMA rule.  (ft_gemm_tc.cu)
+int ft_gemm_tc(FtContext* ctx, const void* a, long long lda, const void* b, FtDType ab_type,
+               long long ldb, float* c, long long ldc, int M, int N, int K, bool accumulate,
+               const float* alpha_ptr);
+// f32 [rows, cols] (ld) -> f16 [rows, ldo]; `lo` (optional) receives the rounding remainder
+// x 2^11.  auto_scale first multiplies by the power of two that brings the largest magnitude
+// to [2^11, 2^12) (gradients are far below f16's normal range otherwise); *scales_out then
+// points at device floats {S, 1/S, 2^-11/S}, else it is NULL.
+int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half* lo,
+              long long ldo, int rows, int cols, bool auto_scale, const float** scales_out);
+// conversion + one (FT_GEMM_F16) or two (FT_GEMM_F16X2) tensor-core passes
+int ft_gemm_tc_f32a(FtContext* ctx, const float* a, long long lda_f32, __half* stage_hi,
+                    __half* stage_lo, const void* b_f16, long long ldb, float* c, long long ldc,
+                    int M, int N, int K, bool accumulate, bool auto_scale);
 
 // elementwise / norm / loss / optimizer kernels with leading dimensions (ft_kernels.cu)
 int ft_k_embedding(FtContext* ctx, const float* table, const uint32_t* ids, float* out,

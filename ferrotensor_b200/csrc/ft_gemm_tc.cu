@@ -1,5 +1,6 @@
-// Blackwell tensor-core GEMM:  C[M,N] f32 (+)= A[M,K] bf16 . B[N,K]^T (f16 or bf16),
-// both operands K-contiguous, f32 accumulation in tensor memory.
+// Blackwell tensor-core GEMM:  C[M,N] f32 (+)= alpha * A[M,K] . B[N,K]^T with A and B both
+// f16 (or both bf16: tcgen05.mma.kind::f16 wants the two operands in the same format),
+// both K-contiguous, f32 accumulation in tensor memory.
 //
 // One persistent CTA per SM walks the output tiles.  Warp 0 issues TMA loads
 // (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared-memory stages, warp 1
@@ -152,11 +153,26 @@ struct SmemLayout {
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack to align the base to 1024 bytes
 };
 
+// Progress markers for fault finding: when `dbg` is set, CTA 0 records how far each role got
+// in pinned host memory (which survives a device fault) and lets asynchronous work land
+// before it moves on, so that the last marker names the instruction that failed.
+#define FT_MARK(slot, value)                                  \
+  do {                                                        \
+    if (dbg && blockIdx.x == 0) {                             \
+      ((volatile int*)dbg)[slot] = (value);                   \
+      __threadfence_system();                                 \
+    }                                                         \
+  } while (0)
+#define FT_SETTLE()                                           \
+  do {                                                        \
+    if (dbg) for (int _i = 0; _i < 200; ++_i) __nanosleep(1000); \
+  } while (0)
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
           float* __restrict__ c, long long ldc, int M, int N, int K, uint32_t idesc,
-          int accumulate, int* status) {
+          int accumulate, const float* __restrict__ alpha_ptr, int* status, int* dbg) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -187,18 +203,23 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    FT_MARK(4, 1);
   }
   if (warp == 1) {
+    if (lane == 0) FT_MARK(5, 10);
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(TMEM_COLS)
                  : "memory");
+    if (lane == 0) FT_MARK(5, 11);
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (lane == 0) FT_MARK(5, 12);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) FT_MARK(6, (int)tmem_base);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -207,11 +228,18 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          FT_MARK(7, 20);
           if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, status, 1)) break;
           const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+          FT_MARK(7, 21);
           mbar_expect_tx(bar_full + stage * 8, L::STAGE_BYTES);
+          FT_MARK(7, 22);
           tma_load_2d(sa, &map_a, bar_full + stage * 8, kb * BK, m0);
+          FT_SETTLE();
+          FT_MARK(7, 23);
           tma_load_2d(sb, &map_b, bar_full + stage * 8, kb * BK, n0);
+          FT_SETTLE();
+          FT_MARK(7, 24);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (*abort_flag) break;
@@ -225,11 +253,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       int local = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
         const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+        FT_MARK(8, 30);
         if (!mbar_wait(bar_tempty + buf * 8, acc_phase ^ 1, abort_flag, status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          FT_MARK(8, 31);
           if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, status, 3)) break;
+          FT_MARK(8, 32);
           tc_fence_after();
           const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
           const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sb);
@@ -239,12 +270,18 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             // 16-byte units of the start-address field
             tc_mma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
                        (kb > 0 || k > 0) ? 1u : 0u);
+            FT_SETTLE();
+            FT_MARK(8, 33 + k);
           }
           tc_commit(bar_empty + stage * 8);  // frees the stage when these MMAs have read it
+          FT_SETTLE();
+          FT_MARK(8, 37);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (*abort_flag) break;
         tc_commit(bar_tfull + buf * 8);      // accumulator complete
+        FT_SETTLE();
+        FT_MARK(8, 38);
       }
     }
     __syncwarp();
@@ -253,11 +290,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     const int quad = warp & 3;               // TMEM lanes [32*quad, 32*quad+32)
     int local = 0;
     const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)c) & 15) == 0);
+    const float alpha = alpha_ptr ? *alpha_ptr : 1.0f;  // undoes the operand's power-of-two scale
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+      if (warp == 2 && lane == 0) FT_MARK(9, 40);
       if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 4)) break;
       tc_fence_after();
+      if (warp == 2 && lane == 0) FT_MARK(9, 41);
       const int row = m0 + quad * 32 + lane;
       float* crow = c + (long long)row * ldc;
 #pragma unroll 1
@@ -265,14 +305,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         uint32_t r[32];
         tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + cb * 32, r);
         tc_wait_ld();
+        if (warp == 2 && lane == 0) FT_MARK(9, 42);
         const int col0 = n0 + cb * 32;
         if (row < M && col0 < N) {
           if (vec_ok && col0 + 32 <= N) {
             float4* dst = (float4*)(crow + col0);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              float4 v = make_float4(alpha * __uint_as_float(r[4 * j]),
+                                     alpha * __uint_as_float(r[4 * j + 1]),
+                                     alpha * __uint_as_float(r[4 * j + 2]),
+                                     alpha * __uint_as_float(r[4 * j + 3]));
               if (accumulate) {
                 float4 o = dst[j];
                 v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -283,7 +326,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (col0 + j < N) {
-                float v = __uint_as_float(r[j]);
+                float v = alpha * __uint_as_float(r[j]);
                 crow[col0 + j] = accumulate ? crow[col0 + j] + v : v;
               }
             }
@@ -293,6 +336,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + buf * 8);
+      if (warp == 2 && lane == 0) FT_MARK(9, 45);
     }
   }
 
@@ -307,16 +351,54 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   }
   if (warp == 1) {
     tc_fence_after();
+    if (lane == 0) FT_MARK(10, 50);
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(TMEM_COLS)
                  : "memory");
+    if (lane == 0) FT_MARK(10, 51);
   }
 }
 
-// ------------------------------------------------------------------------------ f32 -> bf16
-__global__ void k_to_bf16(const float* __restrict__ src, long long ld, __nv_bfloat16* __restrict__ hi,
-                          __nv_bfloat16* __restrict__ lo, long long ldo, int rows, int cols) {
-  // one thread per 4 output columns (ldo is a multiple of 8, padding columns are zeroed)
+// ------------------------------------------------------------------------------ f32 -> f16
+// Largest magnitude of a strided matrix, as the bit pattern of a non-negative float (which
+// orders like an integer), combined with atomicMax: the result does not depend on the order.
+__global__ void k_amax(const float* __restrict__ src, long long ld, int rows, int cols,
+                       int* __restrict__ amax_bits) {
+  long long total = (long long)rows * cols;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long st = (long long)gridDim.x * blockDim.x;
+  float m = 0.f;
+  for (; i < total; i += st) {
+    long long r = i / cols, c = i % cols;
+    m = fmaxf(m, fabsf(src[r * ld + c]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax_bits, __float_as_int(m));
+}
+
+// scales[0] = S (power of two bringing the largest magnitude into [2^11, 2^12)),
+// scales[1] = 1/S, scales[2] = 2^-11/S (the factor of the low half in split mode)
+__global__ void k_scale_from_amax(const int* __restrict__ amax_bits, float* __restrict__ scales) {
+  float amax = __int_as_float(*amax_bits);
+  float S = 1.0f;
+  if (amax > 0.f && isfinite(amax)) {
+    int e;
+    frexpf(amax, &e);           // amax = f * 2^e, f in [0.5, 1)
+    S = ldexpf(1.0f, 12 - e);
+  }
+  scales[0] = S;
+  scales[1] = 1.0f / S;
+  scales[2] = ldexpf(1.0f / S, -11);
+}
+
+// f32 [rows, cols] (pitch ld) -> f16 [rows, ldo]: hi = f16(x*S); lo (optional) = the rounding
+// remainder times 2^11, so that x*S = hi + lo * 2^-11 to about 22 significant bits.
+// One thread per 4 output columns; ldo is a multiple of 8, padding columns are zeroed.
+__global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __restrict__ hi,
+                         __half* __restrict__ lo, long long ldo, int rows, int cols,
+                         const float* __restrict__ scales) {
+  const float S = scales ? scales[0] : 1.0f;
   long long per_row = ldo / 4;
   long long total = (long long)rows * per_row;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -333,14 +415,21 @@ __global__ void k_to_bf16(const float* __restrict__ src, long long ld, __nv_bflo
 #pragma unroll
       for (int j = 0; j < 4; ++j) v[j] = (c + j < cols) ? s[j] : 0.f;
     }
-    __nv_bfloat16 h[4], l[4];
+    unsigned short h[4], l[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      h[j] = __float2bfloat16_rn(v[j]);
-      l[j] = __float2bfloat16_rn(v[j] - __bfloat162float(h[j]));
+      float x = v[j] * S;
+      __half hh = __float2half_rn(x);
+      __half ll = __float2half_rn((x - __half2float(hh)) * 2048.0f);
+      h[j] = __half_as_ushort(hh);
+      l[j] = __half_as_ushort(ll);
     }
-    *(uint2*)(hi + r * ldo + c) = *(uint2*)h;
-    if (lo) *(uint2*)(lo + r * ldo + c) = *(uint2*)l;
+    uint2 hv = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+    *(uint2*)(hi + r * ldo + c) = hv;
+    if (lo) {
+      uint2 lv = make_uint2((uint32_t)l[0] | ((uint32_t)l[1] << 16), (uint32_t)l[2] | ((uint32_t)l[3] << 16));
+      *(uint2*)(lo + r * ldo + c) = lv;
+    }
   }
 }
 
@@ -370,7 +459,8 @@ int make_map(FtContext* ctx, CUtensorMap* map, const void* ptr, CUtensorMapDataT
 
 template <int BN, int STAGES>
 int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, float* c,
-              long long ldc, int M, int N, int K, uint32_t idesc, bool accumulate) {
+              long long ldc, int M, int N, int K, uint32_t idesc, bool accumulate,
+              const float* alpha_ptr) {
   using L = SmemLayout<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
@@ -380,44 +470,73 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, floa
   }
   int tiles = ft_cdiv(M, BM) * ft_cdiv(N, BN);
   int grid = std::min(tiles, ctx->sm_count);
+  int* dbg = ctx->debug_markers ? ctx->status_dev : nullptr;
   FT_LAUNCH(ctx, (k_gemm_tc<BN, STAGES>), grid, GEMM_THREADS, L::DYN_BYTES, ma, mb, c, ldc, M, N,
-            K, idesc, accumulate ? 1 : 0, ctx->status_dev);
+            K, idesc, accumulate ? 1 : 0, alpha_ptr, ctx->status_dev, dbg);
   return FT_OK;
 }
 
 }  // namespace
 
-int ft_to_bf16(FtContext* ctx, const float* src, long long ld, __nv_bfloat16* hi,
-               __nv_bfloat16* lo, long long ldo, int rows, int cols) {
-  FT_REQUIRE(ldo % 8 == 0 && ldo >= cols, "to_bf16: output pitch %lld must be a multiple of 8",
-             ldo);
+int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half* lo,
+              long long ldo, int rows, int cols, bool auto_scale, const float** scales_out) {
+  FT_REQUIRE(ldo % 8 == 0 && ldo >= cols, "to_f16: output pitch %lld must be a multiple of 8", ldo);
+  const float* scales = nullptr;
+  if (auto_scale) {
+    FT_CUDA(cudaMemsetAsync(ctx->scale_buf, 0, 4, ctx->stream));
+    long long n = (long long)rows * cols;
+    int g = (int)std::max<long long>(1, std::min<long long>((n + 1023) / 1024,
+                                                            (long long)ctx->sm_count * 8));
+    FT_LAUNCH(ctx, k_amax, g, 256, 0, src, ld, rows, cols, (int*)ctx->scale_buf);
+    FT_LAUNCH(ctx, k_scale_from_amax, 1, 1, 0, (const int*)ctx->scale_buf, ctx->scale_buf + 4);
+    scales = ctx->scale_buf + 4;
+  }
+  if (scales_out) *scales_out = scales;
   long long total = (long long)rows * (ldo / 4);
   int grid = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256,
                                                              (long long)ctx->sm_count * 16));
-  FT_LAUNCH(ctx, k_to_bf16, grid, 256, 0, src, ld, hi, lo, ldo, rows, cols);
+  FT_LAUNCH(ctx, k_to_f16, grid, 256, 0, src, ld, hi, lo, ldo, rows, cols, scales);
   return FT_OK;
 }
 
-int ft_gemm_tc(FtContext* ctx, const __nv_bfloat16* a, long long lda, const void* b,
-               FtDType b_type, long long ldb, float* c, long long ldc, int M, int N, int K,
-               bool accumulate) {
+int ft_gemm_tc(FtContext* ctx, const void* a, long long lda, const void* b, FtDType ab_type,
+               long long ldb, float* c, long long ldc, int M, int N, int K, bool accumulate,
+               const float* alpha_ptr) {
   // TMA rules: 16-byte aligned bases, pitches that are multiples of 16 bytes
-  if (b_type != FT_F16 && b_type != FT_BF16) return FT_ERR_UNSUPPORTED;
+  if (ab_type != FT_F16 && ab_type != FT_BF16) return FT_ERR_UNSUPPORTED;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8) || K < 8 ||
       lda < K || ldb < K)
     return FT_ERR_UNSUPPORTED;
   CUtensorMap ma, mb;
   const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
-  FT_TRY(make_map(ctx, &ma, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (uint64_t)K, (uint64_t)M,
-                  (uint64_t)lda, BK, BM));
-  FT_TRY(make_map(ctx, &mb, b,
-                  b_type == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                   : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                  (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN));
-  const uint32_t idesc = make_idesc(BM, BN, /*a=bf16*/ 1, b_type == FT_F16 ? 0 : 1);
+  const CUtensorMapDataType dt = ab_type == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  FT_TRY(make_map(ctx, &ma, a, dt, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM));
+  FT_TRY(make_map(ctx, &mb, b, dt, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN));
+  // A and B formats must be equal: a mixed descriptor is rejected by the hardware
+  const int fmt = ab_type == FT_F16 ? 0 : 1;
+  const uint32_t idesc = make_idesc(BM, BN, fmt, fmt);
   switch (BN) {
-    case 256: return launch_tc<256, 4>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate);
-    case 128: return launch_tc<128, 6>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate);
-    default: return launch_tc<64, 8>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate);
+    case 256: return launch_tc<256, 4>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate, alpha_ptr);
+    case 128: return launch_tc<128, 6>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate, alpha_ptr);
+    default: return launch_tc<64, 8>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate, alpha_ptr);
   }
+}
+
+// C (=|+=) A(f32, rounded to f16 with optional auto scale) . B(f16)^T, single or split pass.
+int ft_gemm_tc_f32a(FtContext* ctx, const float* a, long long lda_f32, __half* stage_hi,
+                    __half* stage_lo, const void* b_f16, long long ldb, float* c, long long ldc,
+                    int M, int N, int K, bool accumulate, bool auto_scale) {
+  const long long kp = (long long)ft_align_up((size_t)K, 8);
+  const bool split = ctx->gemm_mode == FT_GEMM_F16X2;
+  const float* scales = nullptr;
+  FT_TRY(ft_to_f16(ctx, a, lda_f32, stage_hi, split ? stage_lo : nullptr, kp, M, K, auto_scale,
+                   &scales));
+  // without auto scale: alpha 1 for the high half, 2^-11 (a constant in scale_buf) for the low
+  const float* alpha_hi = scales ? scales + 1 : nullptr;
+  const float* alpha_lo = scales ? scales + 2 : ctx->scale_buf + 1;
+  int r = ft_gemm_tc(ctx, stage_hi, kp, b_f16, FT_F16, ldb, c, ldc, M, N, K, accumulate, alpha_hi);
+  if (r == FT_OK && split)
+    r = ft_gemm_tc(ctx, stage_lo, kp, b_f16, FT_F16, ldb, c, ldc, M, N, K, true, alpha_lo);
+  return r;
 }

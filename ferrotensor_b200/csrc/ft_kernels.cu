@@ -275,6 +275,8 @@ k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
     if (threadIdx.x == 0) row_loss[row] = 0.f;
     return;
   }
+  // read before the gradient pass: in in-place use that pass overwrites the logits
+  const float z_target = (threadIdx.x == 0 && tgt < (uint32_t)vocab) ? z[tgt] : 0.f;
   float m = -3.4e38f;
   if (vec) {
     const float4* z4 = (const float4*)z;
@@ -323,7 +325,7 @@ k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
       }
     }
   }
-  if (threadIdx.x == 0) row_loss[row] = (tgt < (uint32_t)vocab) ? log_z - z[tgt] : 0.f;
+  if (threadIdx.x == 0) row_loss[row] = (tgt < (uint32_t)vocab) ? log_z - z_target : 0.f;
 }
 
 // ------------------------------------------------------------------------- optimizer side

@@ -92,7 +92,7 @@ struct FtLoraModel {
   float *hN = nullptr, *xa_head = nullptr, *logit_chunk = nullptr;
   float *dx = nullptr, *dh = nullptr, *dqkv = nullptr, *dattn = nullptr, *dgu = nullptr,
         *df = nullptr, *g = nullptr;
-  __nv_bfloat16 *cvt_hi = nullptr, *cvt_lo = nullptr;
+  __half *cvt_hi = nullptr, *cvt_lo = nullptr;
   size_t cvt_elems = 0;
 };
 
@@ -161,11 +161,11 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   int rmax = std::max({m->layers[0].qkv.R, m->layers[0].o.R, m->layers[0].gu.R,
                        m->layers[0].down.R, m->head.R, 1});
   float* g = b.take<float>(T * rmax);
-  // bf16 staging of a GEMM's activation operand (widest: gate|up gradient or vocab chunk)
+  // f16 staging of a GEMM's activation operand (widest: gate|up gradient or vocab chunk)
   size_t widest = std::max<size_t>({(size_t)c.hidden, (size_t)nqkv, (size_t)2 * c.ffn});
   size_t cvt = std::max(T * ft_align_up(widest, 8), chunk * ft_align_up((size_t)c.vocab, 8));
-  __nv_bfloat16* hi = b.take<__nv_bfloat16>(cvt);
-  __nv_bfloat16* lo = b.take<__nv_bfloat16>(cvt);
+  __half* hi = b.take<__half>(cvt);
+  __half* lo = b.take<__half>(cvt);
   if (!dry) {
     m->T = (int)T; m->sequences = sequences; m->seq_len = seq_len; m->head_chunk = (int)chunk;
     m->x = x; m->acts = acts; m->hN = hN; m->xa_head = xa_head; m->logit_chunk = logit_chunk;
@@ -181,12 +181,9 @@ int group_matmul_fwd(FtLoraModel* m, const Group& g, const float* X, long long l
                      long long ldy, int T) {
   FtContext* ctx = m->ctx;
   if (use_tc(m) && g.w_nk) {
-    long long kp = (long long)ft_align_up((size_t)g.in, 8);
-    bool x2 = ctx->gemm_mode == FT_GEMM_BF16X2;
-    FT_TRY(ft_to_bf16(ctx, X, ldx, m->cvt_hi, x2 ? m->cvt_lo : nullptr, kp, T, g.in));
-    int r = ft_gemm_tc(ctx, m->cvt_hi, kp, g.w_nk, FT_F16, g.in, Y, ldy, T, g.n, g.in, false);
-    if (r == FT_OK && x2)
-      r = ft_gemm_tc(ctx, m->cvt_lo, kp, g.w_nk, FT_F16, g.in, Y, ldy, T, g.n, g.in, true);
+    // activations are O(1): f16 holds them without scaling
+    int r = ft_gemm_tc_f32a(ctx, X, ldx, m->cvt_hi, m->cvt_lo, g.w_nk, g.in, Y, ldy, T, g.n, g.in,
+                            false, false);
     if (r != FT_ERR_UNSUPPORTED) return r;
   }
   for (int j = 0; j < g.nlin; ++j) {
@@ -202,12 +199,9 @@ int group_matmul_bwd(FtLoraModel* m, const Group& g, const float* dY, long long 
                      long long lddx, int T, bool accumulate) {
   FtContext* ctx = m->ctx;
   if (use_tc(m) && g.w_kn) {
-    long long kp = (long long)ft_align_up((size_t)g.n, 8);
-    bool x2 = ctx->gemm_mode == FT_GEMM_BF16X2;
-    FT_TRY(ft_to_bf16(ctx, dY, lddy, m->cvt_hi, x2 ? m->cvt_lo : nullptr, kp, T, g.n));
-    int r = ft_gemm_tc(ctx, m->cvt_hi, kp, g.w_kn, FT_F16, g.n, dX, lddx, T, g.in, g.n, accumulate);
-    if (r == FT_OK && x2)
-      r = ft_gemm_tc(ctx, m->cvt_lo, kp, g.w_kn, FT_F16, g.n, dX, lddx, T, g.in, g.n, true);
+    // gradients are many orders of magnitude below f16's normal range: scale by a power of two
+    int r = ft_gemm_tc_f32a(ctx, dY, lddy, m->cvt_hi, m->cvt_lo, g.w_kn, g.n, dX, lddx, T, g.in,
+                            g.n, accumulate, true);
     if (r != FT_ERR_UNSUPPORTED) return r;
   }
   for (int j = 0; j < g.nlin; ++j) {

@@ -36,8 +36,8 @@ class DType(enum.Enum):
 
 class GemmMode(enum.IntEnum):
     F32 = _lib.FT_GEMM_F32
-    BF16 = _lib.FT_GEMM_BF16
-    BF16X2 = _lib.FT_GEMM_BF16X2
+    F16 = _lib.FT_GEMM_F16
+    F16X2 = _lib.FT_GEMM_F16X2
 
 
 class CudaContext:
@@ -54,7 +54,10 @@ class CudaContext:
         torch.cuda.set_device(self.device)
         self.stream = torch.cuda.current_stream(self.device)
         handle = C.c_void_p()
-        call("ft_ctx_create", device, C.c_void_p(self.stream.cuda_stream), C.byref(handle))
+        # torch's default stream is the legacy NULL stream: hand the library cudaStreamLegacy
+        # (handle value 1) so that its kernels are ordered with torch's copies and NCCL calls
+        raw = self.stream.cuda_stream or 1
+        call("ft_ctx_create", device, C.c_void_p(raw), C.byref(handle))
         self.handle = handle
         self.uploads = 0
         self.readbacks = 0

@@ -41,22 +41,28 @@ extern "C" {
 
 /* How the dense contractions round their operands (accumulation is always f32).
  *   FT_GEMM_F32   exact f32 FMA on CUDA cores - the parity path
- *   FT_GEMM_BF16  activations rounded to bf16, f16 weights exact, tcgen05 tensor cores
- *   FT_GEMM_BF16X2 activations split hi+lo bf16 (16 mantissa bits), two tensor-core passes */
+ *   FT_GEMM_F16   activations (and their gradients, after a power-of-two scale) rounded to
+ *                 f16, f16 weights exact, tcgen05 tensor cores, one pass
+ *   FT_GEMM_F16X2 activations split into two f16 halves (22 significant bits), two passes */
 #define FT_GEMM_F32 0
-#define FT_GEMM_BF16 1
-#define FT_GEMM_BF16X2 2
+#define FT_GEMM_F16 1
+#define FT_GEMM_F16X2 2
 
 typedef struct FtContext FtContext;
 
 /* ---- context: ferrotensor-backend/src/context.rs:164-237 (new), :373-397 (flush,
- * synchronize).  `stream` is a cudaStream_t to enqueue on, or NULL for a stream the
- * context creates.  One context per process and device, as in the reference. */
+ * synchronize).  `stream` is a cudaStream_t to enqueue on (cudaStreamLegacy, handle value 1,
+ * names the legacy default stream), or NULL for a stream the context creates.  One context
+ * per process and device, as in the reference. */
 int ft_ctx_create(int device_ordinal, void* stream, FtContext** out);
 int ft_ctx_destroy(FtContext* ctx);
 int ft_ctx_flush(FtContext* ctx);        /* no-op: a stream needs no submit            */
 int ft_ctx_synchronize(FtContext* ctx);  /* waits; returns FT_ERR_DEVICE if a kernel failed */
 int ft_ctx_status(FtContext* ctx, int* device_status); /* non-blocking read of the status word */
+/* Diagnostics: the 16 status words kernels write to pinned host memory ([0..3] status of a
+ * failed bounded wait, [4..15] progress markers recorded when FT_GEMM_DEBUG=1 is set in the
+ * environment at context creation).  Makes no CUDA call, so it works after a device fault. */
+int ft_ctx_debug_words(FtContext* ctx, int* out16);
 int ft_ctx_set_gemm_mode(FtContext* ctx, int mode);    /* FT_GEMM_*; default FT_GEMM_F32 */
 int ft_ctx_launch_count(FtContext* ctx, uint64_t* kernels_launched);
 const char* ft_last_error(void);

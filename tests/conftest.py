@@ -18,3 +18,15 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden_dir():
     return ROOT / "tests" / "golden"
+
+
+@pytest.fixture(scope="session")
+def cuda_ctx():
+    """One context per test process, as in the reference (one device, one queue)."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from ferrotensor_b200.engine import CudaContext
+    ctx = CudaContext(0)
+    yield ctx
+    ctx.synchronize()
