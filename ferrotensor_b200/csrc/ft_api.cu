@@ -80,6 +80,7 @@ extern "C" int ft_ctx_destroy(FtContext* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->scale_buf) cudaFree(ctx->scale_buf);
+  for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
@@ -111,6 +112,31 @@ extern "C" int ft_ctx_status(FtContext* ctx, int* s) {
 extern "C" int ft_ctx_debug_words(FtContext* ctx, int* out16) {
   FT_REQUIRE(ctx && out16, "ft_ctx_debug_words: NULL argument");
   for (int i = 0; i < 16; ++i) out16[i] = ctx->status_host[i];
+  return FT_OK;
+}
+
+extern "C" int ft_ctx_profile(FtContext* ctx, int enable) {
+  FT_REQUIRE(ctx, "ft_ctx_profile: ctx is NULL");
+  ctx->profile = enable != 0;
+  return FT_OK;
+}
+
+extern "C" int ft_ctx_profile_read(FtContext* ctx, double* gemm_ms, double* gemm_flops,
+                                   uint64_t* gemm_launches) {
+  FT_REQUIRE(ctx && gemm_ms && gemm_flops && gemm_launches, "ft_ctx_profile_read: NULL argument");
+  FT_CUDA(cudaStreamSynchronize(ctx->stream));
+  double ms = 0.0;
+  for (size_t i = 0; i + 1 < ctx->prof_used; i += 2) {
+    float t = 0.f;
+    FT_CUDA(cudaEventElapsedTime(&t, ctx->prof_events[i], ctx->prof_events[i + 1]));
+    ms += t;
+  }
+  *gemm_ms = ms;
+  *gemm_flops = ctx->prof_flops;
+  *gemm_launches = ctx->prof_launches;
+  ctx->prof_used = 0;
+  ctx->prof_flops = 0.0;
+  ctx->prof_launches = 0;
   return FT_OK;
 }
 

@@ -9,6 +9,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <vector>
+
 #include "../../include/ft_cuda.h"
 
 struct FtContext {
@@ -28,6 +30,12 @@ struct FtContext {
   // device floats: [0] amax bits, [1] the constant 2^-11, [4..6] {S, 1/S, 2^-11/S} of the
   // operand being converted (consumed by the GEMM that follows in stream order)
   float* scale_buf = nullptr;
+  // optional timing of the tensor-core GEMM launches (CUDA events on the launch stream)
+  bool profile = false;
+  std::vector<cudaEvent_t> prof_events;  // start/stop pairs, reused
+  size_t prof_used = 0;                  // events handed out since the last read
+  double prof_flops = 0.0;
+  uint64_t prof_launches = 0;
   // cuTensorMapEncodeTiled, resolved through the runtime (no link against libcuda)
   void* encode_tiled = nullptr;
 };

@@ -471,8 +471,24 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, floa
   int tiles = ft_cdiv(M, BM) * ft_cdiv(N, BN);
   int grid = std::min(tiles, ctx->sm_count);
   int* dbg = ctx->debug_markers ? ctx->status_dev : nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (ctx->profile) {
+    while (ctx->prof_events.size() < ctx->prof_used + 2) {
+      cudaEvent_t e;
+      FT_CUDA(cudaEventCreate(&e));
+      ctx->prof_events.push_back(e);
+    }
+    e0 = ctx->prof_events[ctx->prof_used++];
+    e1 = ctx->prof_events[ctx->prof_used++];
+    FT_CUDA(cudaEventRecord(e0, ctx->stream));
+  }
   FT_LAUNCH(ctx, (k_gemm_tc<BN, STAGES>), grid, GEMM_THREADS, L::DYN_BYTES, ma, mb, c, ldc, M, N,
             K, idesc, accumulate ? 1 : 0, alpha_ptr, ctx->status_dev, dbg);
+  if (ctx->profile) {
+    FT_CUDA(cudaEventRecord(e1, ctx->stream));
+    ctx->prof_flops += 2.0 * (double)M * (double)N * (double)K;
+    ctx->prof_launches++;
+  }
   return FT_OK;
 }
 

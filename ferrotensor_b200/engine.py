@@ -71,6 +71,16 @@ class CudaContext:
     def set_gemm_mode(self, mode: GemmMode) -> None:
         call("ft_ctx_set_gemm_mode", self.handle, int(mode))
 
+    def profile(self, enable: bool) -> None:
+        """Bracket every tensor-core GEMM launch with CUDA events (see `profile_read`)."""
+        call("ft_ctx_profile", self.handle, 1 if enable else 0)
+
+    def profile_read(self):
+        """(kernel ms, algorithmic FLOPs, launches) of the GEMM launches since the last read."""
+        ms, fl, n = C.c_double(), C.c_double(), C.c_uint64()
+        call("ft_ctx_profile_read", self.handle, C.byref(ms), C.byref(fl), C.byref(n))
+        return ms.value, fl.value, n.value
+
     def launch_count(self) -> int:
         n = C.c_uint64()
         call("ft_ctx_launch_count", self.handle, C.byref(n))

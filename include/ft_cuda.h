@@ -63,6 +63,13 @@ int ft_ctx_status(FtContext* ctx, int* device_status); /* non-blocking read of t
  * failed bounded wait, [4..15] progress markers recorded when FT_GEMM_DEBUG=1 is set in the
  * environment at context creation).  Makes no CUDA call, so it works after a device fault. */
 int ft_ctx_debug_words(FtContext* ctx, int* out16);
+/* Timing of the tensor-core GEMM launches with CUDA events on the launch stream.  While
+ * enabled every launch is bracketed by two events; ft_ctx_profile_read waits for the stream,
+ * returns the summed kernel time, the algorithmic FLOPs (2 M N K per launch) and the launch
+ * count since the previous read, and resets them. */
+int ft_ctx_profile(FtContext* ctx, int enable);
+int ft_ctx_profile_read(FtContext* ctx, double* gemm_ms, double* gemm_flops,
+                        uint64_t* gemm_launches);
 int ft_ctx_set_gemm_mode(FtContext* ctx, int mode);    /* FT_GEMM_*; default FT_GEMM_F32 */
 int ft_ctx_launch_count(FtContext* ctx, uint64_t* kernels_launched);
 const char* ft_last_error(void);
