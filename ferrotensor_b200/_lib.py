@@ -110,6 +110,7 @@ PROTOTYPES = {
     "ft_model_set_layer": [_P, _I, _P, _P, C.POINTER(_P), C.POINTER(_P)],
     "ft_model_set_state": [_P, _P, _P, _P, _P],
     "ft_model_prepare": [_P],
+    "ft_model_params_changed": [_P],
     "ft_model_workspace_bytes": [_P, _I, _I, C.POINTER(_Z)],
     "ft_model_set_workspace": [_P, _P, _Z],
     "ft_model_forward_backward": [_P, _P, _P, _P, _I, _I, _F, _P, _P],

@@ -96,12 +96,40 @@ int ft_gemm_simt(FtContext* ctx, const float* a, long long sam, long long sak, c
 int ft_gemm_tc(FtContext* ctx, const void* a, long long lda, const void* b, FtDType ab_type,
                long long ldb, float* c, long long ldc, int M, int N, int K, bool accumulate,
                const float* alpha_ptr);
+// General form: C[M,N] = alpha_dev * alpha * (A[M,K].B[N,K]^T + A2[M,K2].B2[N,K2]^T)
+//                         (+ bias[col]) (+ residual[row, col]), written as f32 and/or f16.
+// The optional second operand pair extends the contraction (how the rank-r adapter product
+// rides in the same accumulator as the frozen projection).
+struct FtGemmArgs {
+  const void* a = nullptr; long long lda = 0;
+  const void* b = nullptr; long long ldb = 0;
+  const void* a2 = nullptr; long long lda2 = 0;
+  const void* b2 = nullptr; long long ldb2 = 0;
+  int K2 = 0;
+  FtDType ab_type = FT_F16;
+  int M = 0, N = 0, K = 0;
+  float* c = nullptr; long long ldc = 0;
+  __half* c16 = nullptr; long long ldc16 = 0;
+  const float* alpha_ptr = nullptr; float alpha = 1.f;
+  const float* bias = nullptr;
+  const float* residual = nullptr; long long ldr = 0;
+};
+int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g);
+// Token-reduction product P[M, N<=64] = sum_t A[t,m] B[t,n] (A [T,M], B [T,N], f16) as K-split
+// f32 slabs [nslabs][M][64] in context scratch; ft_slab_reduce adds the slabs in order into a
+// strided sub-block: out[(m-m0)*som + (n-n0)*son] (=|+=) alpha_dev*alpha*sum.
+int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* b, long long ldb,
+                      int M, int N, int T, float** slabs_out, int* nslabs_out);
+int ft_slab_reduce(FtContext* ctx, const float* slabs, int nslabs, int M, float* out, int m0,
+                   int mcount, int n0, int ncount, long long som, long long son,
+                   const float* alpha_ptr, float alpha, bool accumulate);
 // f32 [rows, cols] (ld) -> f16 [rows, ldo]; `lo` (optional) receives the rounding remainder
 // x 2^11.  auto_scale first multiplies by the power of two that brings the largest magnitude
 // to [2^11, 2^12) (gradients are far below f16's normal range otherwise); *scales_out then
 // points at device floats {S, 1/S, 2^-11/S}, else it is NULL.
 int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half* lo,
-              long long ldo, int rows, int cols, bool auto_scale, const float** scales_out);
+              long long ldo, int rows, int cols, bool auto_scale, const float** scales_out,
+              int target_exp = 12);
 // conversion + one (FT_GEMM_F16) or two (FT_GEMM_F16X2) tensor-core passes
 int ft_gemm_tc_f32a(FtContext* ctx, const float* a, long long lda_f32, __half* stage_hi,
                     __half* stage_lo, const void* b_f16, long long ldb, float* c, long long ldc,
@@ -112,6 +140,9 @@ int ft_k_embedding(FtContext* ctx, const float* table, const uint32_t* ids, floa
                    int tokens, int vocab, int hidden);
 int ft_k_rms_norm(FtContext* ctx, const float* x, const float* w, float* out, int rows, int n,
                   float eps);
+// same, writing f32 (out, may be NULL) and/or f16 (out16, may be NULL)
+int ft_k_rms_norm16(FtContext* ctx, const float* x, const float* w, float* out, __half* out16,
+                    int rows, int n, float eps);
 int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const float* g, float* gx,
                       float* gw, int rows, int n, float eps, bool accumulate_gx);
 // in place on x[t*ld + h*head_dim + i]; position of token t = pos + t % seq_len
@@ -122,6 +153,8 @@ int ft_k_scale(FtContext* ctx, float* x, size_t n, float s);
 // 2-D SwiGLU: out[t, j] = silu(a[t*lda + j]) * b[t*ldb + j], j < n
 int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
                    float* out, long long ldo, int rows, int n);
+int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
+                     __half* out, long long ldo, int rows, int n);
 int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const float* b,
                        long long ldb, const float* g, long long ldg, float* ga, long long ldga,
                        float* gb, long long ldgb, int rows, int n);

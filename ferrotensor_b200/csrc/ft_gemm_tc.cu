@@ -168,11 +168,44 @@ struct SmemLayout {
     if (dbg) for (int _i = 0; _i < 200; ++_i) __nanosleep(1000); \
   } while (0)
 
-template <int BN, int STAGES>
+// What the epilogue does with a finished accumulator tile:
+//   v = alpha_dev * alpha * acc (+ bias[col]) (+ residual[row, col]);  c = v;  c16 = f16(v)
+struct Epilogue {
+  float* c;
+  long long ldc;
+  __half* c16;
+  long long ldc16;
+  const float* alpha_ptr;
+  float alpha;
+  const float* bias;
+  const float* residual;
+  long long ldr;
+};
+
+// Shared-memory descriptor of an operand whose CONTRACTION index is the slow one (rows of the
+// global matrix are K, 64 consecutive M/N elements make one 128-byte swizzled row): 8 K-rows
+// form a 1024-byte atom (stride byte offset), 64-wide M/N blocks follow each other every
+// `mn_block_bytes` (leading byte offset).
+__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(mn_block_bytes >> 4) << 16;    // leading byte offset
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// KOUTER = false:  C[M,N] = A[M,K] . B[N,K]^T (+ A2[M,K2] . B2[N,K2]^T), operands K-contiguous.
+// KOUTER = true :  C[M,N] = sum_t A[t,m] B[t,n], operands given as [T, M] and [T, N] (the
+//                  token-reduction products of the adapter gradients); BN = 64, the tile list
+//                  is (m tile, K split) and each split writes its own f32 slab of C.
+template <int BN, int STAGES, bool KOUTER>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-          float* __restrict__ c, long long ldc, int M, int N, int K, uint32_t idesc,
-          int accumulate, const float* __restrict__ alpha_ptr, int* status, int* dbg) {
+          const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
+          Epilogue ep, int M, int N, int K, int K2, int splits, uint32_t idesc, int* status,
+          int* dbg) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -187,9 +220,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = KOUTER ? splits : (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (K + BK - 1) / BK;
+  const int kb_main = (K + BK - 1) / BK;
+  const int kb_total = kb_main + (KOUTER ? 0 : (K2 + BK - 1) / BK);
+  const int kb_per_split = KOUTER ? (kb_main + splits - 1) / splits : kb_total;
   constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators; a power of two >= 32
 
   if (threadIdx.x == 0) {
@@ -206,12 +242,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     FT_MARK(4, 1);
   }
   if (warp == 1) {
-    if (lane == 0) FT_MARK(5, 10);
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(TMEM_COLS)
                  : "memory");
-    if (lane == 0) FT_MARK(5, 11);
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     if (lane == 0) FT_MARK(5, 12);
   }
@@ -219,25 +253,33 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) FT_MARK(6, (int)tmem_base);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int m0 = (tile % tiles_m) * BM, nt = tile / tiles_m;
+        const int kb0 = KOUTER ? nt * kb_per_split : 0;
+        const int kb1 = KOUTER ? min(kb_main, kb0 + kb_per_split) : kb_total;
+        for (int kb = kb0; kb < kb1; ++kb) {
           FT_MARK(7, 20);
           if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, status, 1)) break;
           const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
-          FT_MARK(7, 21);
-          mbar_expect_tx(bar_full + stage * 8, L::STAGE_BYTES);
-          FT_MARK(7, 22);
-          tma_load_2d(sa, &map_a, bar_full + stage * 8, kb * BK, m0);
-          FT_SETTLE();
-          FT_MARK(7, 23);
-          tma_load_2d(sb, &map_b, bar_full + stage * 8, kb * BK, n0);
+          const uint32_t bar = bar_full + stage * 8;
+          mbar_expect_tx(bar, L::STAGE_BYTES);
+          if constexpr (KOUTER) {
+            // {x = M/N index (64 wide), y = token row}
+            tma_load_2d(sa, &map_a, bar, m0, kb * BK);
+            tma_load_2d(sa + 64 * 128, &map_a, bar, m0 + 64, kb * BK);
+            tma_load_2d(sb, &map_b, bar, 0, kb * BK);
+          } else if (kb < kb_main) {
+            tma_load_2d(sa, &map_a, bar, kb * BK, m0);
+            tma_load_2d(sb, &map_b, bar, kb * BK, nt * BN);
+          } else {
+            tma_load_2d(sa, &map_a2, bar, (kb - kb_main) * BK, m0);
+            tma_load_2d(sb, &map_b2, bar, (kb - kb_main) * BK, nt * BN);
+          }
           FT_SETTLE();
           FT_MARK(7, 24);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -252,30 +294,42 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       uint32_t stage = 0, phase = 0;
       int local = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+        const int nt = tile / tiles_m;
+        const int kb0 = KOUTER ? nt * kb_per_split : 0;
+        const int kb1 = KOUTER ? min(kb_main, kb0 + kb_per_split) : kb_total;
         const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
         FT_MARK(8, 30);
         if (!mbar_wait(bar_tempty + buf * 8, acc_phase ^ 1, abort_flag, status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          FT_MARK(8, 31);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, status, 3)) break;
           FT_MARK(8, 32);
           tc_fence_after();
           const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
-          const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sb);
+          if constexpr (KOUTER) {
+            const uint64_t da = make_desc_mn_sw128(sa, 64 * 128), db = make_desc_mn_sw128(sb, 64 * 128);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the
-            // 16-byte units of the start-address field
-            tc_mma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
-                       (kb > 0 || k > 0) ? 1u : 0u);
-            FT_SETTLE();
-            FT_MARK(8, 33 + k);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // 16 token rows further = two 1024-byte atoms = +128 in 16-byte units
+              tc_mma_f16(d_tmem, da + (uint64_t)(k * 128), db + (uint64_t)(k * 128), idesc,
+                         (kb > kb0 || k > 0) ? 1u : 0u);
+              FT_SETTLE();
+              FT_MARK(8, 33 + k);
+            }
+          } else {
+            const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sb);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the
+              // 16-byte units of the start-address field
+              tc_mma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                         (kb > kb0 || k > 0) ? 1u : 0u);
+              FT_SETTLE();
+              FT_MARK(8, 33 + k);
+            }
           }
           tc_commit(bar_empty + stage * 8);  // frees the stage when these MMAs have read it
-          FT_SETTLE();
-          FT_MARK(8, 37);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (*abort_flag) break;
@@ -289,46 +343,80 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;               // TMEM lanes [32*quad, 32*quad+32)
     int local = 0;
-    const bool vec_ok = ((ldc & 3) == 0) && ((((uintptr_t)c) & 15) == 0);
-    const float alpha = alpha_ptr ? *alpha_ptr : 1.0f;  // undoes the operand's power-of-two scale
+    const bool vec_c = ep.c && ((ep.ldc & 3) == 0) && ((((uintptr_t)ep.c) & 15) == 0);
+    const bool vec_r = !ep.residual || (((ep.ldr & 3) == 0) && ((((uintptr_t)ep.residual) & 15) == 0));
+    const bool vec_h = ep.c16 && ((ep.ldc16 & 7) == 0) && ((((uintptr_t)ep.c16) & 15) == 0);
+    const float alpha = (ep.alpha_ptr ? *ep.alpha_ptr : 1.0f) * ep.alpha;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = (tile % tiles_m) * BM, nt = tile / tiles_m;
+      const int n0 = KOUTER ? 0 : nt * BN;
       const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
-      if (warp == 2 && lane == 0) FT_MARK(9, 40);
       if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 4)) break;
       tc_fence_after();
       if (warp == 2 && lane == 0) FT_MARK(9, 41);
       const int row = m0 + quad * 32 + lane;
-      float* crow = c + (long long)row * ldc;
+      // a K split of the token-reduction product writes its own slab
+      float* cbase = ep.c ? ep.c + (KOUTER ? (long long)nt * M * ep.ldc : 0) : nullptr;
 #pragma unroll 1
       for (int cb = 0; cb < BN / 32; ++cb) {
         uint32_t r[32];
         tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + cb * 32, r);
         tc_wait_ld();
-        if (warp == 2 && lane == 0) FT_MARK(9, 42);
         const int col0 = n0 + cb * 32;
         if (row < M && col0 < N) {
-          if (vec_ok && col0 + 32 <= N) {
-            float4* dst = (float4*)(crow + col0);
+          const bool full = col0 + 32 <= N;
+          float v[32];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 v = make_float4(alpha * __uint_as_float(r[4 * j]),
-                                     alpha * __uint_as_float(r[4 * j + 1]),
-                                     alpha * __uint_as_float(r[4 * j + 2]),
-                                     alpha * __uint_as_float(r[4 * j + 3]));
-              if (accumulate) {
-                float4 o = dst[j];
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+          for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(r[j]);
+          if (ep.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < N) v[j] += ep.bias[col0 + j];
+          }
+          if (ep.residual) {
+            const float* rr = ep.residual + (long long)row * ep.ldr + col0;
+            if (full && vec_r) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 o = ((const float4*)rr)[j];
+                v[4 * j] += o.x; v[4 * j + 1] += o.y; v[4 * j + 2] += o.z; v[4 * j + 3] += o.w;
               }
-              dst[j] = v;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) v[j] += rr[j];
             }
-          } else {
+          }
+          if (cbase) {
+            float* crow = cbase + (long long)row * ep.ldc + col0;
+            if (full && vec_c) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < N) {
-                float v = alpha * __uint_as_float(r[j]);
-                crow[col0 + j] = accumulate ? crow[col0 + j] + v : v;
+              for (int j = 0; j < 8; ++j)
+                ((float4*)crow)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) crow[j] = v[j];
+            }
+          }
+          if (ep.c16) {
+            __half* hrow = ep.c16 + (long long)row * ep.ldc16 + col0;
+            if (full && vec_h) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 pk;
+                __half2 h0 = __floats2half2_rn(v[8 * j], v[8 * j + 1]);
+                __half2 h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
+                __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]);
+                __half2 h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
+                pk.x = *(uint32_t*)&h0; pk.y = *(uint32_t*)&h1;
+                pk.z = *(uint32_t*)&h2; pk.w = *(uint32_t*)&h3;
+                ((uint4*)hrow)[j] = pk;
               }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) hrow[j] = __float2half_rn(v[j]);
             }
           }
         }
@@ -351,11 +439,29 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   }
   if (warp == 1) {
     tc_fence_after();
-    if (lane == 0) FT_MARK(10, 50);
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(TMEM_COLS)
                  : "memory");
     if (lane == 0) FT_MARK(10, 51);
+  }
+}
+
+// out[(m - m0) * som + (n - n0) * son] (=|+=) alpha * sum over slabs of part[s][m][n],
+// slabs added in index order.
+__global__ void k_slab_reduce(const float* __restrict__ part, int slabs, int M, int ldp,
+                              float* __restrict__ out, int m0, int mcount, int n0, int ncount,
+                              long long som, long long son, const float* __restrict__ alpha_ptr,
+                              float alpha, int accumulate) {
+  const float a = (alpha_ptr ? *alpha_ptr : 1.0f) * alpha;
+  size_t total = (size_t)mcount * ncount;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    int m = (int)(i / ncount), n = (int)(i % ncount);
+    float acc = 0.f;
+    for (int s = 0; s < slabs; ++s)
+      acc += part[((size_t)s * M + (m0 + m)) * ldp + (n0 + n)];
+    float* o = out + (long long)m * som + (long long)n * son;
+    *o = accumulate ? *o + a * acc : a * acc;
   }
 }
 
@@ -364,28 +470,38 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 // orders like an integer), combined with atomicMax: the result does not depend on the order.
 __global__ void k_amax(const float* __restrict__ src, long long ld, int rows, int cols,
                        int* __restrict__ amax_bits) {
-  long long total = (long long)rows * cols;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long st = (long long)gridDim.x * blockDim.x;
   float m = 0.f;
-  for (; i < total; i += st) {
-    long long r = i / cols, c = i % cols;
-    m = fmaxf(m, fabsf(src[r * ld + c]));
+  if ((cols & 3) == 0 && (ld & 3) == 0 && (((uintptr_t)src) & 15) == 0) {
+    long long per_row = cols / 4, total = (long long)rows * per_row;
+    for (; i < total; i += st) {
+      long long r = i / per_row, c = (i % per_row) * 4;
+      float4 v = *(const float4*)(src + r * ld + c);
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+  } else {
+    long long total = (long long)rows * cols;
+    for (; i < total; i += st) {
+      long long r = i / cols, c = i % cols;
+      m = fmaxf(m, fabsf(src[r * ld + c]));
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax_bits, __float_as_int(m));
 }
 
-// scales[0] = S (power of two bringing the largest magnitude into [2^11, 2^12)),
-// scales[1] = 1/S, scales[2] = 2^-11/S (the factor of the low half in split mode)
-__global__ void k_scale_from_amax(const int* __restrict__ amax_bits, float* __restrict__ scales) {
+// scales[0] = S (power of two bringing the largest magnitude into [2^(t-1), 2^t), t =
+// target_exp), scales[1] = 1/S, scales[2] = 2^-11/S (the factor of the low half in split mode)
+__global__ void k_scale_from_amax(const int* __restrict__ amax_bits, float* __restrict__ scales,
+                                  int target_exp) {
   float amax = __int_as_float(*amax_bits);
   float S = 1.0f;
   if (amax > 0.f && isfinite(amax)) {
     int e;
     frexpf(amax, &e);           // amax = f * 2^e, f in [0.5, 1)
-    S = ldexpf(1.0f, 12 - e);
+    S = ldexpf(1.0f, target_exp - e);
   }
   scales[0] = S;
   scales[1] = 1.0f / S;
@@ -457,18 +573,18 @@ int make_map(FtContext* ctx, CUtensorMap* map, const void* ptr, CUtensorMapDataT
   return FT_OK;
 }
 
-template <int BN, int STAGES>
-int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, float* c,
-              long long ldc, int M, int N, int K, uint32_t idesc, bool accumulate,
-              const float* alpha_ptr) {
+template <int BN, int STAGES, bool KOUTER>
+int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2,
+              const CUtensorMap& mb2, const Epilogue& ep, int M, int N, int K, int K2, int splits,
+              uint32_t idesc, double flops) {
   using L = SmemLayout<BN, STAGES>;
   static bool configured = false;
   if (!configured) {
-    FT_CUDA(cudaFuncSetAttribute(k_gemm_tc<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 L::DYN_BYTES));
+    FT_CUDA(cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, KOUTER>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
     configured = true;
   }
-  int tiles = ft_cdiv(M, BM) * ft_cdiv(N, BN);
+  int tiles = ft_cdiv(M, BM) * (KOUTER ? splits : ft_cdiv(N, BN));
   int grid = std::min(tiles, ctx->sm_count);
   int* dbg = ctx->debug_markers ? ctx->status_dev : nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -482,11 +598,11 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, floa
     e1 = ctx->prof_events[ctx->prof_used++];
     FT_CUDA(cudaEventRecord(e0, ctx->stream));
   }
-  FT_LAUNCH(ctx, (k_gemm_tc<BN, STAGES>), grid, GEMM_THREADS, L::DYN_BYTES, ma, mb, c, ldc, M, N,
-            K, idesc, accumulate ? 1 : 0, alpha_ptr, ctx->status_dev, dbg);
+  FT_LAUNCH(ctx, (k_gemm_tc<BN, STAGES, KOUTER>), grid, GEMM_THREADS, L::DYN_BYTES, ma, mb, ma2, mb2,
+            ep, M, N, K, K2, splits, idesc, ctx->status_dev, dbg);
   if (ctx->profile) {
     FT_CUDA(cudaEventRecord(e1, ctx->stream));
-    ctx->prof_flops += 2.0 * (double)M * (double)N * (double)K;
+    ctx->prof_flops += flops;
     ctx->prof_launches++;
   }
   return FT_OK;
@@ -495,16 +611,18 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, floa
 }  // namespace
 
 int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half* lo,
-              long long ldo, int rows, int cols, bool auto_scale, const float** scales_out) {
+              long long ldo, int rows, int cols, bool auto_scale, const float** scales_out,
+              int target_exp) {
   FT_REQUIRE(ldo % 8 == 0 && ldo >= cols, "to_f16: output pitch %lld must be a multiple of 8", ldo);
   const float* scales = nullptr;
   if (auto_scale) {
     FT_CUDA(cudaMemsetAsync(ctx->scale_buf, 0, 4, ctx->stream));
     long long n = (long long)rows * cols;
-    int g = (int)std::max<long long>(1, std::min<long long>((n + 1023) / 1024,
+    int g = (int)std::max<long long>(1, std::min<long long>((n + 4095) / 4096,
                                                             (long long)ctx->sm_count * 8));
     FT_LAUNCH(ctx, k_amax, g, 256, 0, src, ld, rows, cols, (int*)ctx->scale_buf);
-    FT_LAUNCH(ctx, k_scale_from_amax, 1, 1, 0, (const int*)ctx->scale_buf, ctx->scale_buf + 4);
+    FT_LAUNCH(ctx, k_scale_from_amax, 1, 1, 0, (const int*)ctx->scale_buf, ctx->scale_buf + 4,
+              target_exp);
     scales = ctx->scale_buf + 4;
   }
   if (scales_out) *scales_out = scales;
@@ -515,28 +633,91 @@ int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half
   return FT_OK;
 }
 
+static bool tma_ok(const void* p, long long ld, int k) {
+  return p && (((uintptr_t)p) & 15) == 0 && (ld % 8) == 0 && ld >= k;
+}
+
+int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
+  if (g.ab_type != FT_F16 && g.ab_type != FT_BF16) return FT_ERR_UNSUPPORTED;
+  if (!tma_ok(g.a, g.lda, g.K) || !tma_ok(g.b, g.ldb, g.K) || g.K < 8) return FT_ERR_UNSUPPORTED;
+  const bool tail = g.K2 > 0;
+  if (tail && (!tma_ok(g.a2, g.lda2, g.K2) || !tma_ok(g.b2, g.ldb2, g.K2))) return FT_ERR_UNSUPPORTED;
+  CUtensorMap ma, mb, ma2, mb2;
+  const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+  const CUtensorMapDataType dt = g.ab_type == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  FT_TRY(make_map(ctx, &ma, g.a, dt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM));
+  FT_TRY(make_map(ctx, &mb, g.b, dt, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)BN));
+  if (tail) {
+    FT_TRY(make_map(ctx, &ma2, g.a2, dt, (uint64_t)g.K2, (uint64_t)g.M, (uint64_t)g.lda2, BK, BM));
+    FT_TRY(make_map(ctx, &mb2, g.b2, dt, (uint64_t)g.K2, (uint64_t)g.N, (uint64_t)g.ldb2, BK,
+                    (uint32_t)BN));
+  } else {
+    ma2 = ma;
+    mb2 = mb;
+  }
+  // A and B formats must be equal: a mixed descriptor is rejected by the hardware
+  const int fmt = g.ab_type == FT_F16 ? 0 : 1;
+  const uint32_t idesc = make_idesc(BM, BN, fmt, fmt);
+  Epilogue ep;
+  ep.c = g.c; ep.ldc = g.ldc; ep.c16 = g.c16; ep.ldc16 = g.ldc16;
+  ep.alpha_ptr = g.alpha_ptr; ep.alpha = g.alpha; ep.bias = g.bias;
+  ep.residual = g.residual; ep.ldr = g.ldr;
+  const double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
+  switch (BN) {
+    case 256: return launch_tc<256, 4, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
+    case 128: return launch_tc<128, 6, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
+    default: return launch_tc<64, 8, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
+  }
+}
+
 int ft_gemm_tc(FtContext* ctx, const void* a, long long lda, const void* b, FtDType ab_type,
                long long ldb, float* c, long long ldc, int M, int N, int K, bool accumulate,
                const float* alpha_ptr) {
-  // TMA rules: 16-byte aligned bases, pitches that are multiples of 16 bytes
-  if (ab_type != FT_F16 && ab_type != FT_BF16) return FT_ERR_UNSUPPORTED;
-  if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8) || K < 8 ||
-      lda < K || ldb < K)
-    return FT_ERR_UNSUPPORTED;
+  FtGemmArgs g;
+  g.a = a; g.lda = lda; g.b = b; g.ldb = ldb; g.ab_type = ab_type;
+  g.M = M; g.N = N; g.K = K;
+  g.c = c; g.ldc = ldc; g.alpha_ptr = alpha_ptr;
+  if (accumulate) { g.residual = c; g.ldr = ldc; }
+  return ft_gemm_tc_ex(ctx, g);
+}
+
+// P[M, N<=64] (slabs) = sum_t A[t, m] B[t, n] on the tensor cores, then a deterministic
+// reduction of the K-split slabs.  A is [T, M] (lda), B is [T, N] (ldb), both f16.
+int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* b, long long ldb,
+                      int M, int N, int T, float** slabs_out, int* nslabs_out) {
+  if (N > 64 || !tma_ok(a, lda, M) || !tma_ok(b, ldb, N) || (M % 8) || (N % 8)) return FT_ERR_UNSUPPORTED;
   CUtensorMap ma, mb;
-  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
-  const CUtensorMapDataType dt = ab_type == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                                    : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  FT_TRY(make_map(ctx, &ma, a, dt, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM));
-  FT_TRY(make_map(ctx, &mb, b, dt, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN));
-  // A and B formats must be equal: a mixed descriptor is rejected by the hardware
-  const int fmt = ab_type == FT_F16 ? 0 : 1;
-  const uint32_t idesc = make_idesc(BM, BN, fmt, fmt);
-  switch (BN) {
-    case 256: return launch_tc<256, 4>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate, alpha_ptr);
-    case 128: return launch_tc<128, 6>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate, alpha_ptr);
-    default: return launch_tc<64, 8>(ctx, ma, mb, c, ldc, M, N, K, idesc, accumulate, alpha_ptr);
-  }
+  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  // inner dimension = M/N index, outer = token row; box = 64 x 64
+  FT_TRY(make_map(ctx, &ma, a, dt, (uint64_t)M, (uint64_t)T, (uint64_t)lda, 64, BK));
+  FT_TRY(make_map(ctx, &mb, b, dt, (uint64_t)N, (uint64_t)T, (uint64_t)ldb, 64, BK));
+  const int tiles_m = ft_cdiv(M, BM), kb = ft_cdiv(T, BK);
+  int splits = std::max(1, std::min(std::min(kb, 32), ft_cdiv(2 * ctx->sm_count, tiles_m)));
+  const int per = ft_cdiv(kb, splits);
+  splits = ft_cdiv(kb, per);
+  void* s = nullptr;
+  FT_TRY(ft_scratch(ctx, (size_t)splits * M * 64 * sizeof(float), &s));
+  Epilogue ep;
+  ep.c = (float*)s; ep.ldc = 64; ep.c16 = nullptr; ep.ldc16 = 0;
+  ep.alpha_ptr = nullptr; ep.alpha = 1.f; ep.bias = nullptr; ep.residual = nullptr; ep.ldr = 0;
+  // both operands M/N-major: bits 15 and 16 of the instruction descriptor
+  const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
+  *slabs_out = (float*)s;
+  *nslabs_out = splits;
+  return launch_tc<64, 8, true>(ctx, ma, mb, ma, mb, ep, M, 64, T, 0, splits, idesc,
+                                2.0 * M * 64.0 * T);
+}
+
+int ft_slab_reduce(FtContext* ctx, const float* slabs, int nslabs, int M, float* out, int m0,
+                   int mcount, int n0, int ncount, long long som, long long son,
+                   const float* alpha_ptr, float alpha, bool accumulate) {
+  size_t total = (size_t)mcount * ncount;
+  if (!total) return FT_OK;
+  int grid = (int)std::min<size_t>((total + 255) / 256, (size_t)ctx->sm_count * 8);
+  FT_LAUNCH(ctx, k_slab_reduce, grid, 256, 0, slabs, nslabs, M, 64, out, m0, mcount, n0, ncount, som,
+            son, alpha_ptr, alpha, accumulate ? 1 : 0);
+  return FT_OK;
 }
 
 // C (=|+=) A(f32, rounded to f16 with optional auto scale) . B(f16)^T, single or split pass.

@@ -66,11 +66,13 @@ __global__ void k_embedding(const float* __restrict__ table, const uint32_t* __r
 // --------------------------------------------------------------------------------- RMSNorm
 __global__ void __launch_bounds__(kRowThreads)
 k_rms_norm(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
-           int n, float eps) {
+           __half* __restrict__ out16, int n, float eps) {
   __shared__ float red[32];
   const float* xr = x + (size_t)blockIdx.x * n;
-  float* o = out + (size_t)blockIdx.x * n;
-  bool vec = (n & 3) == 0 && aligned16(xr) && aligned16(o) && aligned16(w);
+  float* o = out ? out + (size_t)blockIdx.x * n : nullptr;
+  __half* o16 = out16 ? out16 + (size_t)blockIdx.x * n : nullptr;
+  bool vec = (n & 3) == 0 && aligned16(xr) && (!o || aligned16(o)) && aligned16(w) &&
+             (!o16 || (((uintptr_t)o16) & 7) == 0);
   float ss = 0.f;
   if (vec) {
     const float4* x4 = (const float4*)xr;
@@ -89,10 +91,19 @@ k_rms_norm(const float* __restrict__ x, const float* __restrict__ w, float* __re
     float4* o4 = (float4*)o;
     for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
       float4 v = x4[i], g = w4[i];
-      o4[i] = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+      float4 r = make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w);
+      if (o) o4[i] = r;
+      if (o16) {
+        __half2 a = __floats2half2_rn(r.x, r.y), b = __floats2half2_rn(r.z, r.w);
+        ((uint2*)o16)[i] = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+      }
     }
   } else {
-    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = xr[i] * inv * w[i];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float r = xr[i] * inv * w[i];
+      if (o) o[i] = r;
+      if (o16) o16[i] = __float2half_rn(r);
+    }
   }
 }
 
@@ -231,6 +242,23 @@ __global__ void k_silu_gate(const float* __restrict__ a, long long lda,
     out[r * ldo + c] = x * s * b[r * ldb + c];
   }
 }
+// SwiGLU forward with an f16 result (the down projection's tensor-core operand); 4 columns
+// per thread, n and the pitches multiples of 4
+__global__ void k_silu_gate16(const float* __restrict__ a, long long lda,
+                              const float* __restrict__ b, long long ldb,
+                              __half* __restrict__ out, long long ldo, int rows, int n) {
+  size_t per_row = (size_t)n / 4, total = (size_t)rows * per_row;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    size_t r = i / per_row, c = (i % per_row) * 4;
+    float4 x = *(const float4*)(a + r * lda + c), y = *(const float4*)(b + r * ldb + c);
+    float v0 = x.x / (1.0f + expf(-x.x)) * y.x, v1 = x.y / (1.0f + expf(-x.y)) * y.y;
+    float v2 = x.z / (1.0f + expf(-x.z)) * y.z, v3 = x.w / (1.0f + expf(-x.w)) * y.w;
+    __half2 h0 = __floats2half2_rn(v0, v1), h1 = __floats2half2_rn(v2, v3);
+    *(uint2*)(out + r * ldo + c) = make_uint2(*(uint32_t*)&h0, *(uint32_t*)&h1);
+  }
+}
+
 __global__ void k_silu_gate_bwd(const float* __restrict__ a, long long lda,
                                 const float* __restrict__ b, long long ldb,
                                 const float* __restrict__ g, long long ldg,
@@ -424,7 +452,14 @@ int ft_k_embedding(FtContext* ctx, const float* table, const uint32_t* ids, floa
 int ft_k_rms_norm(FtContext* ctx, const float* x, const float* w, float* out, int rows, int n,
                   float eps) {
   int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
-  FT_LAUNCH(ctx, k_rms_norm, rows, block, 0, x, w, out, n, eps);
+  FT_LAUNCH(ctx, k_rms_norm, rows, block, 0, x, w, out, (__half*)nullptr, n, eps);
+  return FT_OK;
+}
+
+int ft_k_rms_norm16(FtContext* ctx, const float* x, const float* w, float* out, __half* out16,
+                    int rows, int n, float eps) {
+  int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
+  FT_LAUNCH(ctx, k_rms_norm, rows, block, 0, x, w, out, out16, n, eps);
   return FT_OK;
 }
 
@@ -487,6 +522,16 @@ int ft_k_add_bias(FtContext* ctx, float* y, long long ld, const float* bias, int
 int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
                    float* out, long long ldo, int rows, int n) {
   FT_LAUNCH(ctx, k_silu_gate, ew_grid(ctx, (size_t)rows * n), 256, 0, a, lda, b, ldb, out, ldo,
+            rows, n);
+  return FT_OK;
+}
+
+int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
+                     __half* out, long long ldo, int rows, int n) {
+  FT_REQUIRE((n % 4) == 0 && (lda % 4) == 0 && (ldb % 4) == 0 && (ldo % 4) == 0 &&
+                 ((((uintptr_t)a) | ((uintptr_t)b)) & 15) == 0 && (((uintptr_t)out) & 7) == 0,
+             "silu_gate16: width and pitches must be multiples of 4");
+  FT_LAUNCH(ctx, k_silu_gate16, ew_grid(ctx, (size_t)rows * n / 4), 256, 0, a, lda, b, ldb, out, ldo,
             rows, n);
   return FT_OK;
 }

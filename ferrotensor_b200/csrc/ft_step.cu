@@ -37,7 +37,17 @@ struct Group {
   __half* w_nk = nullptr;      // [n, in]   forward operand, K = in contiguous
   __half* w_kn = nullptr;      // [in, n]   input-gradient operand, K = n contiguous
   bool own_kn = false;
+  // f16 operand forms of the group's adapters, rebuilt whenever the parameters change.
+  // RP = 64: the group's total rank padded to one 128-byte swizzle row.
+  __half* a_catT16 = nullptr;  // [64, in]  (x . A) product:        N = 64, K = in
+  __half* b_bdT16 = nullptr;   // [n, 64]   forward tail operand:   N = n,  K = 64 (block diagonal)
+  __half* b_bd16 = nullptr;    // [64, n]   (dY . B^T) product:     N = 64, K = n
+  __half* a_cat16 = nullptr;   // [in, 64]  backward tail operand:  N = in, K = 64
+  float* bias_cat = nullptr;   // [n] concatenated biases, or NULL
+  bool tc_lora = false;        // adapters ride on the tensor-core path
 };
+
+constexpr int RP = 64;
 
 struct Layer {
   const float* norm1 = nullptr;
@@ -50,6 +60,9 @@ struct Layer {
 struct BlockActs {
   float *h1, *qkv, *attn, *stats, *x1, *h2, *gu, *f;
   float *xa_qkv, *xa_o, *xa_gu, *xa_down;
+  // fused tensor-core path: GEMM inputs are kept as f16 only
+  __half *h1_16, *attn16, *h2_16, *f_16;
+  __half *xa16_qkv, *xa16_o, *xa16_gu, *xa16_down;
 };
 
 struct Bump {
@@ -94,12 +107,24 @@ struct FtLoraModel {
         *df = nullptr, *g = nullptr;
   __half *cvt_hi = nullptr, *cvt_lo = nullptr;
   size_t cvt_elems = 0;
+  bool plan_fused = false;         // the planned workspace is the fused tensor-core layout
+  __half *hN16 = nullptr, *xa16_head = nullptr, *g16 = nullptr;
+  bool packs_dirty = true;         // adapter operand forms must be rebuilt before use
 };
 
 namespace {
 
 FtDType base_type(const FtLoraModel* m) { return m->cfg.f16_base ? FT_F16 : FT_F32; }
 bool use_tc(const FtLoraModel* m) { return m->ctx->gemm_mode != FT_GEMM_F32 && m->cfg.f16_base; }
+// The fused path (f16 activations, adapters inside the GEMMs) needs every group on the tensor
+// cores; the split mode keeps the unfused route, which holds activations in f32.
+bool use_fused(const FtLoraModel* m) {
+  if (m->ctx->gemm_mode != FT_GEMM_F16 || !m->cfg.f16_base) return false;
+  for (const auto& ly : m->layers)
+    for (const Group* g : {&ly.qkv, &ly.o, &ly.gu, &ly.down})
+      if (!g->w_nk || (g->R > 0 && !g->tc_lora)) return false;
+  return m->head.w_nk && (m->head.R == 0 || m->head.tc_lora) && (m->cfg.ffn % 4) == 0;
+}
 
 void setup_group(Group& g, std::initializer_list<Linear*> lins, int rank) {
   g = Group();
@@ -124,6 +149,7 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   Bump b{(char*)base, 0, dry};
   const int L = c.layers;
   const int nqkv = m->nq + 2 * m->nkv;
+  const bool fused = use_fused(m);
   std::vector<float*> x(L + 1);
   for (int l = 0; l <= L; ++l) x[l] = b.take<float>(T * c.hidden);
   const int nact = c.checkpoint_blocks ? 1 : L;
@@ -131,6 +157,23 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   for (int i = 0; i < nact; ++i) {
     const Layer& ly = m->layers[c.checkpoint_blocks ? 0 : i];
     BlockActs& a = acts[i];
+    memset(&a, 0, sizeof(a));
+    if (fused) {
+      a.h1_16 = b.take<__half>(T * c.hidden);
+      a.qkv = b.take<float>(T * nqkv);
+      a.attn = b.take<float>(T * m->nq);
+      a.attn16 = b.take<__half>(T * m->nq);
+      a.stats = b.take<float>((size_t)sequences * c.heads * seq_len * 2);
+      a.x1 = b.take<float>(T * c.hidden);
+      a.h2_16 = b.take<__half>(T * c.hidden);
+      a.gu = b.take<float>(T * 2 * c.ffn);
+      a.f_16 = b.take<__half>(T * c.ffn);
+      a.xa16_qkv = b.take<__half>(T * RP);
+      a.xa16_o = b.take<__half>(T * RP);
+      a.xa16_gu = b.take<__half>(T * RP);
+      a.xa16_down = b.take<__half>(T * RP);
+      continue;
+    }
     a.h1 = b.take<float>(T * c.hidden);
     a.qkv = b.take<float>(T * nqkv);
     a.attn = b.take<float>(T * m->nq);
@@ -165,8 +208,12 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   size_t widest = std::max<size_t>({(size_t)c.hidden, (size_t)nqkv, (size_t)2 * c.ffn});
   size_t cvt = std::max(T * ft_align_up(widest, 8), chunk * ft_align_up((size_t)c.vocab, 8));
   __half* hi = b.take<__half>(cvt);
-  __half* lo = b.take<__half>(cvt);
+  __half* lo = fused ? nullptr : b.take<__half>(cvt);
+  __half* hN16 = fused ? b.take<__half>(T * c.hidden) : nullptr;
+  __half* xa16_head = fused ? b.take<__half>(T * RP) : nullptr;
+  __half* g16 = fused ? b.take<__half>(T * RP) : nullptr;
   if (!dry) {
+    m->plan_fused = fused; m->hN16 = hN16; m->xa16_head = xa16_head; m->g16 = g16;
     m->T = (int)T; m->sequences = sequences; m->seq_len = seq_len; m->head_chunk = (int)chunk;
     m->x = x; m->acts = acts; m->hN = hN; m->xa_head = xa_head; m->logit_chunk = logit_chunk;
     m->dx = dx; m->dh = dh; m->dqkv = dqkv; m->dattn = dattn; m->dgu = dgu; m->df = df; m->g = g;
@@ -329,6 +376,213 @@ int block_backward(FtLoraModel* m, int l, const float* x_in, BlockActs& a) {
   return FT_OK;
 }
 
+
+// ======================================================================================
+// Fused tensor-core path
+// ======================================================================================
+
+struct PackMeta {
+  int nlin, in, n, r;
+  int col_off[3], out[3], r_off[3], lora[3];
+  unsigned long long a_off[3], b_off[3];
+};
+
+// Writes the four f16 operand forms of a group's adapters (blockIdx.y selects the form).
+__global__ void k_pack_adapters(const float* __restrict__ params, PackMeta g,
+                                __half* __restrict__ a_catT16, __half* __restrict__ b_bdT16,
+                                __half* __restrict__ b_bd16, __half* __restrict__ a_cat16) {
+  const int which = blockIdx.y;
+  const size_t total = (size_t)RP * (which == 0 || which == 3 ? g.in : g.n);
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    int rr, other;  // rr = padded rank index, other = input feature or output column
+    if (which == 0 || which == 2) { rr = (int)(i / (which == 0 ? g.in : g.n)); other = (int)(i % (which == 0 ? g.in : g.n)); }
+    else { other = (int)(i / RP); rr = (int)(i % RP); }
+    float v = 0.f;
+    if (which == 0 || which == 3) {
+      for (int j = 0; j < g.nlin; ++j)
+        if (g.lora[j] && rr >= g.r_off[j] && rr < g.r_off[j] + g.r)
+          v = params[g.a_off[j] + (size_t)other * g.r + (rr - g.r_off[j])];
+    } else {
+      for (int j = 0; j < g.nlin; ++j)
+        if (g.lora[j] && other >= g.col_off[j] && other < g.col_off[j] + g.out[j] &&
+            rr >= g.r_off[j] && rr < g.r_off[j] + g.r)
+          v = params[g.b_off[j] + (size_t)(rr - g.r_off[j]) * g.out[j] + (other - g.col_off[j])];
+    }
+    __half h = __float2half_rn(v);
+    if (which == 0) a_catT16[i] = h;
+    else if (which == 1) b_bdT16[i] = h;
+    else if (which == 2) b_bd16[i] = h;
+    else a_cat16[i] = h;
+  }
+}
+
+int pack_group(FtLoraModel* m, const Group& g) {
+  if (!g.tc_lora) return FT_OK;
+  PackMeta pm;
+  memset(&pm, 0, sizeof(pm));
+  pm.nlin = g.nlin; pm.in = g.in; pm.n = g.n; pm.r = m->cfg.lora_rank;
+  for (int j = 0; j < g.nlin; ++j) {
+    pm.col_off[j] = g.col_off[j]; pm.out[j] = g.lin[j]->out; pm.r_off[j] = g.r_off[j];
+    pm.lora[j] = g.lin[j]->lora ? 1 : 0;
+    pm.a_off[j] = g.lin[j]->a_off; pm.b_off[j] = g.lin[j]->b_off;
+  }
+  size_t most = (size_t)RP * std::max(g.in, g.n);
+  dim3 grid((unsigned)std::min<size_t>((most + 255) / 256, 1024), 4);
+  FT_LAUNCH(m->ctx, k_pack_adapters, grid, 256, 0, m->params, pm, g.a_catT16, g.b_bdT16, g.b_bd16,
+            g.a_cat16);
+  return FT_OK;
+}
+
+int pack_all(FtLoraModel* m) {
+  for (auto& ly : m->layers) {
+    FT_TRY(pack_group(m, ly.qkv));
+    FT_TRY(pack_group(m, ly.o));
+    FT_TRY(pack_group(m, ly.gu));
+    FT_TRY(pack_group(m, ly.down));
+  }
+  FT_TRY(pack_group(m, m->head));
+  m->packs_dirty = false;
+  return FT_OK;
+}
+
+// Y[T, n] = X16 . W + (alpha/r)(X16 . A) . B (+ bias) (+ residual); keeps xa16 = (alpha/r) X16 . A
+int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y, long long ldy,
+                     __half* xa16, const float* residual, long long ldr, int T) {
+  FtContext* ctx = m->ctx;
+  if (g.R > 0) {
+    FtGemmArgs a;
+    a.a = X16; a.lda = g.in; a.b = g.a_catT16; a.ldb = g.in;
+    a.M = T; a.N = RP; a.K = g.in;
+    a.c16 = xa16; a.ldc16 = RP; a.alpha = m->scale;
+    FT_TRY(ft_gemm_tc_ex(ctx, a));
+  }
+  FtGemmArgs a;
+  a.a = X16; a.lda = g.in; a.b = g.w_nk; a.ldb = g.in;
+  a.M = T; a.N = g.n; a.K = g.in;
+  if (g.R > 0) { a.a2 = xa16; a.lda2 = RP; a.b2 = g.b_bdT16; a.ldb2 = RP; a.K2 = RP; }
+  a.c = Y; a.ldc = ldy; a.bias = g.bias_cat; a.residual = residual; a.ldr = ldr;
+  return ft_gemm_tc_ex(ctx, a);
+}
+
+// Adapter gradients (added to the flat buffer) and dX (=|+ residual) = dY W^T + G A^T.
+// dY is rounded to f16 after a power-of-two scale S chosen from its largest magnitude; S is
+// carried through G and removed by the epilogues (1/S is a device scalar).
+int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const float* dY,
+                     long long lddy, const __half* xa16, float* dX, long long lddx,
+                     const float* residual, long long ldr, int T) {
+  FtContext* ctx = m->ctx;
+  const int r = m->cfg.lora_rank;
+  const long long np = (long long)ft_align_up((size_t)g.n, 8);
+  const float* scales = nullptr;
+  FT_TRY(ft_to_f16(ctx, dY, lddy, m->cvt_hi, nullptr, np, T, g.n, true, &scales, 8));
+  const float* inv_s = scales + 1;
+  if (g.R > 0) {
+    FtGemmArgs a;   // G16 = (alpha/r) * (S dY) . B^T
+    a.a = m->cvt_hi; a.lda = np; a.b = g.b_bd16; a.ldb = g.n;
+    a.M = T; a.N = RP; a.K = g.n;
+    a.c16 = m->g16; a.ldc16 = RP; a.alpha = m->scale;
+    FT_TRY(ft_gemm_tc_ex(ctx, a));
+  }
+  if (dX) {
+    FtGemmArgs a;
+    a.a = m->cvt_hi; a.lda = np; a.b = g.w_kn; a.ldb = g.n;
+    a.M = T; a.N = g.in; a.K = g.n;
+    if (g.R > 0) { a.a2 = m->g16; a.lda2 = RP; a.b2 = g.a_cat16; a.ldb2 = RP; a.K2 = RP; }
+    a.c = dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
+    FT_TRY(ft_gemm_tc_ex(ctx, a));
+  }
+  if (g.R > 0) {
+    float* slabs = nullptr;
+    int ns = 0;
+    // dB^T [n, 64] = (S dY)^T . xa16, reduced over tokens
+    FT_TRY(ft_gemm_tc_kouter(ctx, m->cvt_hi, np, xa16, RP, g.n, RP, T, &slabs, &ns));
+    for (int j = 0; j < g.nlin; ++j) {
+      const Linear& l = *g.lin[j];
+      if (!l.lora) continue;
+      FT_TRY(ft_slab_reduce(ctx, slabs, ns, g.n, m->grads + l.b_off, g.col_off[j], l.out,
+                            g.r_off[j], r, 1, l.out, inv_s, 1.f, true));
+    }
+    // dA [in, 64] = X16^T . G16
+    FT_TRY(ft_gemm_tc_kouter(ctx, X16, g.in, m->g16, RP, g.in, RP, T, &slabs, &ns));
+    for (int j = 0; j < g.nlin; ++j) {
+      const Linear& l = *g.lin[j];
+      if (!l.lora) continue;
+      FT_TRY(ft_slab_reduce(ctx, slabs, ns, g.in, m->grads + l.a_off, 0, l.in, g.r_off[j], r, r, 1,
+                            inv_s, 1.f, true));
+    }
+  }
+  return FT_OK;
+}
+
+int attention_launch(FtLoraModel* m, BlockActs& a, bool backward) {
+  const FtModelConfig& c = m->cfg;
+  const int nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv;
+  FtAttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.batch = m->sequences; p.heads = c.heads; p.kv_heads = c.kv_heads;
+  p.seq_q = p.seq_k = m->seq_len; p.head_dim = c.head_dim; p.causal = 1;
+  if (!backward) {
+    FtAttnLaunch at;
+    at.q = a.qkv; at.k = a.qkv + nq; at.v = a.qkv + nq + nkv;
+    at.ldq = at.ldk = at.ldv = nqkv;
+    at.out = a.attn; at.ldo = nq; at.stats = a.stats; at.p = p;
+    return ft_k_attention_fwd(m->ctx, at);
+  }
+  FtAttnBwdLaunch ab;
+  ab.q = a.qkv; ab.k = a.qkv + nq; ab.v = a.qkv + nq + nkv;
+  ab.ldq = ab.ldk = ab.ldv = nqkv;
+  ab.out = a.attn; ab.ldo = nq; ab.dout = m->dattn; ab.lddo = nq;
+  ab.dq = m->dqkv; ab.dk = m->dqkv + nq; ab.dv = m->dqkv + nq + nkv;
+  ab.lddq = ab.lddk = ab.lddv = nqkv;
+  ab.stats = a.stats;
+  p.lse_saved = 1;
+  ab.p = p;
+  return ft_k_attention_bwd(m->ctx, ab);
+}
+
+int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, BlockActs& a) {
+  FtContext* ctx = m->ctx;
+  const FtModelConfig& c = m->cfg;
+  Layer& ly = m->layers[l];
+  const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
+  FT_TRY(ft_k_rms_norm16(ctx, x_in, ly.norm1, nullptr, a.h1_16, T, h, c.eps));
+  FT_TRY(linear_fwd_fused(m, ly.qkv, a.h1_16, a.qkv, nqkv, a.xa16_qkv, nullptr, 0, T));
+  FT_TRY(ft_k_rope(ctx, a.qkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, false));
+  FT_TRY(ft_k_rope(ctx, a.qkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, false));
+  FT_TRY(attention_launch(m, a, false));
+  FT_TRY(ft_to_f16(ctx, a.attn, nq, a.attn16, nullptr, nq, T, nq, false, nullptr));
+  // x1 = x_in + o(attn): the residual rides in the GEMM epilogue
+  FT_TRY(linear_fwd_fused(m, ly.o, a.attn16, a.x1, h, a.xa16_o, x_in, h, T));
+  FT_TRY(ft_k_rms_norm16(ctx, a.x1, ly.norm2, nullptr, a.h2_16, T, h, c.eps));
+  FT_TRY(linear_fwd_fused(m, ly.gu, a.h2_16, a.gu, 2 * F, a.xa16_gu, nullptr, 0, T));
+  FT_TRY(ft_k_silu_gate16(ctx, a.gu, 2 * F, a.gu + F, 2 * F, a.f_16, F, T, F));
+  FT_TRY(linear_fwd_fused(m, ly.down, a.f_16, x_out, h, a.xa16_down, a.x1, h, T));
+  return FT_OK;
+}
+
+int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a) {
+  FtContext* ctx = m->ctx;
+  const FtModelConfig& c = m->cfg;
+  Layer& ly = m->layers[l];
+  const int T = m->T, h = c.hidden, nq = m->nq, nqkv = nq + 2 * m->nkv, F = c.ffn;
+  FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, m->dx, h, a.xa16_down, m->df, F, nullptr, 0, T));
+  FT_TRY(ft_k_silu_gate_bwd(ctx, a.gu, 2 * F, a.gu + F, 2 * F, m->df, F, m->dgu, 2 * F,
+                            m->dgu + F, 2 * F, T, F));
+  FT_TRY(linear_bwd_fused(m, ly.gu, a.h2_16, m->dgu, 2 * F, a.xa16_gu, m->dh, h, nullptr, 0, T));
+  FT_TRY(ft_k_rms_norm_bwd(ctx, a.x1, ly.norm2, m->dh, m->dx, nullptr, T, h, c.eps, true));
+  FT_TRY(linear_bwd_fused(m, ly.o, a.attn16, m->dx, h, a.xa16_o, m->dattn, nq, nullptr, 0, T));
+  FT_TRY(attention_launch(m, a, true));
+  FT_TRY(ft_k_rope(ctx, m->dqkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, true));
+  FT_TRY(ft_k_rope(ctx, m->dqkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, true));
+  const bool need_dx = l > 0;
+  FT_TRY(linear_bwd_fused(m, ly.qkv, a.h1_16, m->dqkv, nqkv, a.xa16_qkv, need_dx ? m->dh : nullptr,
+                          h, nullptr, 0, T));
+  if (need_dx)
+    FT_TRY(ft_k_rms_norm_bwd(ctx, x_in, ly.norm1, m->dh, m->dx, nullptr, T, h, c.eps, true));
+  return FT_OK;
+}
+
 __global__ void k_copy_f16_2d(const __half* __restrict__ src, long long lds, __half* __restrict__ dst,
                               long long ldd, int rows, int cols) {
   size_t total = (size_t)rows * cols;
@@ -370,6 +624,29 @@ int prepare_group(FtLoraModel* m, Group& g) {
     m->owned.push_back(p);
     g.w_kn = (__half*)p;
     g.own_kn = true;
+  }
+  bool any_bias = false;
+  for (int j = 0; j < g.nlin; ++j) any_bias |= g.lin[j]->bias != nullptr;
+  if (any_bias) {
+    FT_CUDA(cudaMalloc(&p, (size_t)g.n * sizeof(float)));
+    m->owned.push_back(p);
+    g.bias_cat = (float*)p;
+    FT_CUDA(cudaMemsetAsync(p, 0, (size_t)g.n * sizeof(float), ctx->stream));
+    for (int j = 0; j < g.nlin; ++j)
+      if (g.lin[j]->bias)
+        FT_CUDA(cudaMemcpyAsync(g.bias_cat + g.col_off[j], g.lin[j]->bias,
+                                (size_t)g.lin[j]->out * sizeof(float), cudaMemcpyDeviceToDevice,
+                                ctx->stream));
+  }
+  if (g.R > 0 && g.R <= RP) {
+    __half** slots[4] = {&g.a_catT16, &g.b_bdT16, &g.b_bd16, &g.a_cat16};
+    size_t sizes[4] = {(size_t)RP * g.in, (size_t)g.n * RP, (size_t)RP * g.n, (size_t)g.in * RP};
+    for (int k = 0; k < 4; ++k) {
+      FT_CUDA(cudaMalloc(&p, sizes[k] * sizeof(__half)));
+      m->owned.push_back(p);
+      *slots[k] = (__half*)p;
+    }
+    g.tc_lora = true;
   }
   for (int j = 0; j < g.nlin; ++j) {
     const Linear& l = *g.lin[j];
@@ -511,6 +788,7 @@ extern "C" int ft_model_set_state(FtLoraModel* m, float* params, float* grads, f
   FT_REQUIRE(m->trainable == 0 || (params && grads && adam_m && adam_v),
              "ft_model_set_state: NULL buffer");
   m->params = params; m->grads = grads; m->adam_m = adam_m; m->adam_v = adam_v;
+  m->packs_dirty = true;
   return FT_OK;
 }
 
@@ -534,6 +812,14 @@ extern "C" int ft_model_prepare(FtLoraModel* m) {
     FT_CUDA(cudaMalloc((void**)&m->apply_scratch, (chunks + 8) * sizeof(float)));
   }
   m->prepared = true;
+  m->packs_dirty = true;
+  m->T = 0;  // the workspace layout depends on which groups reached the tensor cores
+  return FT_OK;
+}
+
+extern "C" int ft_model_params_changed(FtLoraModel* m) {
+  FT_REQUIRE(m, "ft_model_params_changed: model is NULL");
+  m->packs_dirty = true;
   return FT_OK;
 }
 
@@ -570,7 +856,8 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
   FT_REQUIRE(m->trainable == 0 || m->params, "ft_model_forward_backward: state not set");
   FtContext* ctx = m->ctx;
   const FtModelConfig& c = m->cfg;
-  if (m->sequences != sequences || m->seq_len != seq_len || m->T == 0) {
+  const bool fused = use_fused(m);
+  if (m->sequences != sequences || m->seq_len != seq_len || m->T == 0 || m->plan_fused != fused) {
     size_t need = plan(m, sequences, seq_len, true, nullptr);
     FT_REQUIRE(m->ws && need <= m->ws_bytes,
                "ft_model_forward_backward: workspace of %zu bytes needed, %zu given", need,
@@ -579,32 +866,51 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
   }
   const int T = m->T, h = c.hidden, L = c.layers, V = c.vocab;
   const bool ckpt = c.checkpoint_blocks != 0;
+  if (fused && m->packs_dirty) FT_TRY(pack_all(m));
 
   // ---- forward
   FT_TRY(ft_k_embedding(ctx, m->embed, ids, m->x[0], T, V, h));
-  for (int l = 0; l < L; ++l)
-    FT_TRY(block_forward(m, l, m->x[l], m->x[l + 1], m->acts[ckpt ? 0 : l]));
-  FT_TRY(ft_k_rms_norm(ctx, m->x[L], m->final_norm, m->hN, T, h, c.eps));
+  for (int l = 0; l < L; ++l) {
+    BlockActs& a = m->acts[ckpt ? 0 : l];
+    FT_TRY(fused ? block_forward_fused(m, l, m->x[l], m->x[l + 1], a)
+                 : block_forward(m, l, m->x[l], m->x[l + 1], a));
+  }
+  if (fused)
+    FT_TRY(ft_k_rms_norm16(ctx, m->x[L], m->final_norm, nullptr, m->hN16, T, h, c.eps));
+  else
+    FT_TRY(ft_k_rms_norm(ctx, m->x[L], m->final_norm, m->hN, T, h, c.eps));
 
   // ---- head + loss + head backward, in row chunks; m->dh collects dL/d(hN)
   for (int r0 = 0; r0 < T; r0 += m->head_chunk) {
     const int rows = std::min(m->head_chunk, T - r0);
-    const float* X = m->hN + (size_t)r0 * h;
-    float* xa = m->xa_head + (size_t)r0 * std::max(1, m->head.R);
     float* z = logits ? logits + (size_t)r0 * V : m->logit_chunk;
-    FT_TRY(linear_fwd(m, m->head, X, h, z, V, xa, rows));
-    FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, m->logit_chunk, row_loss + r0, rows,
-                          V, seed));
-    FT_TRY(linear_bwd(m, m->head, X, h, m->logit_chunk, V, xa, m->dh + (size_t)r0 * h, h, rows,
-                      false));
+    if (fused) {
+      const __half* X16 = m->hN16 + (size_t)r0 * h;
+      __half* xa16 = m->xa16_head + (size_t)r0 * RP;
+      FT_TRY(linear_fwd_fused(m, m->head, X16, z, V, xa16, nullptr, 0, rows));
+      FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, m->logit_chunk, row_loss + r0, rows,
+                            V, seed));
+      FT_TRY(linear_bwd_fused(m, m->head, X16, m->logit_chunk, V, xa16, m->dh + (size_t)r0 * h, h,
+                              nullptr, 0, rows));
+    } else {
+      const float* X = m->hN + (size_t)r0 * h;
+      float* xa = m->xa_head + (size_t)r0 * std::max(1, m->head.R);
+      FT_TRY(linear_fwd(m, m->head, X, h, z, V, xa, rows));
+      FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, m->logit_chunk, row_loss + r0, rows,
+                            V, seed));
+      FT_TRY(linear_bwd(m, m->head, X, h, m->logit_chunk, V, xa, m->dh + (size_t)r0 * h, h, rows,
+                        false));
+    }
   }
   FT_TRY(ft_k_rms_norm_bwd(ctx, m->x[L], m->final_norm, m->dh, m->dx, nullptr, T, h, c.eps, false));
 
   // ---- blocks, last to first
   for (int l = L - 1; l >= 0; --l) {
     BlockActs& a = m->acts[ckpt ? 0 : l];
-    if (ckpt) FT_TRY(block_forward(m, l, m->x[l], m->x[l + 1], a));  // replay; rewrites x[l+1]
-    FT_TRY(block_backward(m, l, m->x[l], a));
+    if (ckpt)  // replay; rewrites x[l+1] with the same values
+      FT_TRY(fused ? block_forward_fused(m, l, m->x[l], m->x[l + 1], a)
+                   : block_forward(m, l, m->x[l], m->x[l + 1], a));
+    FT_TRY(fused ? block_backward_fused(m, l, m->x[l], a) : block_backward(m, l, m->x[l], a));
   }
   return FT_OK;
 }
@@ -617,6 +923,7 @@ extern "C" int ft_model_apply_gradients(FtLoraModel* m, float grad_scale, float 
   size_t chunks = (m->trainable + FT_SUM_SQUARES_CHUNK - 1) / FT_SUM_SQUARES_CHUNK;
   float* partials = m->apply_scratch;
   float* nout = norm_out ? norm_out : m->apply_scratch + chunks;
+  m->packs_dirty = true;  // the adapters change: their f16 operand forms are stale
   return ft_k_apply_fused(m->ctx, m->params, m->grads, m->adam_m, m->adam_v, m->trainable,
                           grad_scale, max_norm, p, partials, nout);
 }

@@ -59,6 +59,7 @@ class CudaContext:
         raw = self.stream.cuda_stream or 1
         call("ft_ctx_create", device, C.c_void_p(raw), C.byref(handle))
         self.handle = handle
+        self.gemm_mode = GemmMode.F32
         self.uploads = 0
         self.readbacks = 0
 
@@ -70,6 +71,7 @@ class CudaContext:
 
     def set_gemm_mode(self, mode: GemmMode) -> None:
         call("ft_ctx_set_gemm_mode", self.handle, int(mode))
+        self.gemm_mode = GemmMode(int(mode))
 
     def profile(self, enable: bool) -> None:
         """Bracket every tensor-core GEMM launch with CUDA events (see `profile_read`)."""

@@ -129,6 +129,7 @@ class LoraModel:
     def load_adapters(self, adapters: Dict[str, torch.Tensor]) -> None:
         for name in self._slices:
             self._view(self.params, name).copy_(adapters[name].to(self.params.device, torch.float32))
+        call("ft_model_params_changed", self.handle)
 
     def named_lora_params(self) -> Dict[str, torch.Tensor]:
         """name -> view into the flat parameter buffer (lfm.rs:744-770)."""
@@ -148,7 +149,7 @@ class LoraModel:
         return n.value
 
     def _ensure_workspace(self, sequences: int, seq_len: int) -> None:
-        key = (sequences, seq_len)
+        key = (sequences, seq_len, int(self.ctx.gemm_mode))  # the layout depends on the mode
         if self._ws_key == key:
             return
         need = self.workspace_bytes(sequences, seq_len)

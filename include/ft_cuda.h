@@ -226,6 +226,9 @@ int ft_model_set_state(FtLoraModel* m, float* params, float* grads, float* adam_
 /* Called once after the weights are set (and again if they change): builds the operand
  * copies the tensor-core path wants (transposed f16 weights, fused q|k|v and gate|up). */
 int ft_model_prepare(FtLoraModel* m);
+/* Tell the model that the caller wrote the flat parameter buffer directly (loading an
+ * adapter): derived operand copies are rebuilt before the next micro-batch. */
+int ft_model_params_changed(FtLoraModel* m);
 /* Bytes of activation workspace a micro-batch of `sequences` x `seq_len` needs. */
 int ft_model_workspace_bytes(FtLoraModel* m, int sequences, int seq_len, size_t* bytes);
 int ft_model_set_workspace(FtLoraModel* m, void* dev_ptr, size_t bytes);
