@@ -11,136 +11,11 @@
 // Every mbarrier wait is bounded: when a wait runs out the CTA raises a sticky abort flag,
 // records a status word the host reads, lets all roles fall through, waits out its
 // in-flight copies, frees its tensor memory and returns.  Nothing traps.
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
-#include "ft_common.cuh"
+#include "ft_tc.cuh"
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BK = 64;            // 64 x 16-bit = 128 bytes = one swizzle row
-constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192; // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
-constexpr uint32_t SPIN_LIMIT = 1u << 26;  // ~ seconds of polling at most
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false (and raises the abort flag) when it gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int where) {
-  if (*abort_flag) return false;
-  uint32_t spins = 0;
-  while (!mbar_test(bar, parity)) {
-    if (++spins > SPIN_LIMIT || *abort_flag) {
-      if (!*abort_flag) {
-        *abort_flag = 1;
-        // the status word lives in pinned host memory: plain stores, first writer wins
-        // only approximately, which is enough to report "some wait ran out, here"
-        volatile int* st = status;
-        if (st[0] == 0) {
-          st[1] = (int)blockIdx.x;
-          st[2] = (int)parity;
-          st[0] = 100 + where;
-        }
-      }
-      return false;
-    }
-    if ((spins & 1023u) == 0) __nanosleep(64);
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
-      "{%3, %4}], [%2];"
-      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, written by TMA
-// with 128-byte swizzle: 8-row atoms of 1024 bytes follow each other along M/N (stride byte
-// offset 1024); the leading byte offset is not used by swizzled K-major layouts.
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address, bits [0,14)
-  d |= (uint64_t)0 << 16;                        // leading byte offset, bits [16,30)
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset, bits [32,46)
-  d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell), bits [46,48)
-  d |= (uint64_t)2 << 61;                        // layout type: 128-byte swizzle, bits [61,64)
-  return d;
-}
-
-// Instruction descriptor of tcgen05.mma.kind::f16: f32 accumulator, A and B K-major.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_fmt, int b_fmt) {
-  return (1u << 4)                    // D format: f32
-         | ((uint32_t)a_fmt << 7)     // A format: 0 f16, 1 bf16
-         | ((uint32_t)b_fmt << 10)    // B format
-         | (0u << 15) | (0u << 16)    // A, B major: K
-         | ((uint32_t)(n >> 3) << 17) // N / 8
-         | ((uint32_t)(m >> 4) << 24);// M / 16
-}
+using namespace ft_tc;
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -181,20 +56,6 @@ struct Epilogue {
   const float* residual;
   long long ldr;
 };
-
-// Shared-memory descriptor of an operand whose CONTRACTION index is the slow one (rows of the
-// global matrix are K, 64 consecutive M/N elements make one 128-byte swizzled row): 8 K-rows
-// form a 1024-byte atom (stride byte offset), 64-wide M/N blocks follow each other every
-// `mn_block_bytes` (leading byte offset).
-__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_block_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)(mn_block_bytes >> 4) << 16;    // leading byte offset
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
 
 // KOUTER = false:  C[M,N] = A[M,K] . B[N,K]^T (+ A2[M,K2] . B2[N,K2]^T), operands K-contiguous.
 // KOUTER = true :  C[M,N] = sum_t A[t,m] B[t,n], operands given as [T, M] and [T, N] (the
@@ -547,30 +408,6 @@ __global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __
       *(uint2*)(lo + r * ldo + c) = lv;
     }
   }
-}
-
-int make_map(FtContext* ctx, CUtensorMap* map, const void* ptr, CUtensorMapDataType dt,
-             uint64_t inner, uint64_t outer, uint64_t ld_elems, uint32_t box_inner,
-             uint32_t box_outer) {
-  auto encode = (PFN_cuTensorMapEncodeTiled_v12000)ctx->encode_tiled;
-  if (!encode) {
-    ft_set_error("gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
-    return FT_ERR_UNSUPPORTED;
-  }
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld_elems * 2};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = encode(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    ft_set_error("gemm_tc: cuTensorMapEncodeTiled failed with %d (inner %llu outer %llu ld %llu)",
-                 (int)r, (unsigned long long)inner, (unsigned long long)outer,
-                 (unsigned long long)ld_elems);
-    return FT_ERR_UNSUPPORTED;
-  }
-  return FT_OK;
 }
 
 template <int BN, int STAGES, bool KOUTER>
