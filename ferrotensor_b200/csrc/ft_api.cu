@@ -443,6 +443,21 @@ extern "C" int ft_flash_attention_v2(FtContext* ctx, const float* q, const float
                                      const FtAttnParams* p) {
   FT_REQUIRE(ctx && q && k && v && out, "ft_flash_attention_v2: NULL argument");
   FT_TRY(check_attn("ft_flash_attention_v2", p, mask));
+  if (ctx->gemm_mode == FT_GEMM_F16 && p->head_dim == 64 && p->causal && !p->causal_offset &&
+      !p->window && p->seq_q == p->seq_k && p->seq_q >= 64) {
+    // tensor-core form: q, k, v are rounded to f16 side by side, one row per token
+    const int nq = p->heads * 64, nkv = p->kv_heads * 64, ld = nq + 2 * nkv;
+    const int T = (int)(p->batch * p->seq_q);
+    void* s = nullptr;
+    FT_TRY(ft_scratch(ctx, (size_t)T * ld * sizeof(__half), &s));
+    __half* qkv16 = (__half*)s;
+    FT_TRY(ft_to_f16(ctx, q, nq, qkv16, nullptr, ld, T, nq, false, nullptr));
+    FT_TRY(ft_to_f16(ctx, k, nkv, qkv16 + nq, nullptr, ld, T, nkv, false, nullptr));
+    FT_TRY(ft_to_f16(ctx, v, nkv, qkv16 + nq + nkv, nullptr, ld, T, nkv, false, nullptr));
+    int r = ft_attention_fwd_tc(ctx, qkv16, ld, 0, nq, nq + nkv, nullptr, 0, out, nq, stats,
+                                (int)p->batch, (int)p->seq_q, (int)p->heads, (int)p->kv_heads, 64);
+    if (r != FT_ERR_UNSUPPORTED) return r;
+  }
   FtAttnLaunch a;
   a.q = q; a.k = k; a.v = v; a.out = out; a.stats = stats; a.p = *p;
   a.ldq = a.ldo = (long long)p->heads * p->head_dim;

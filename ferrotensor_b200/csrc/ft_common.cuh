@@ -190,3 +190,11 @@ struct FtAttnBwdLaunch {
   FtAttnParams p;
 };
 int ft_k_attention_bwd(FtContext* ctx, const FtAttnBwdLaunch& a);
+
+// Causal attention on the tensor cores (head_dim 64).  qkv16: f16 rows [tokens, ld] holding
+// q at column q_col0, k at k_col0, v at v_col0 (RoPE applied); writes f16 and/or f32 output
+// rows [tokens, heads*64] and the log-sum-exp of every row into stats[2*row+1].
+// FT_ERR_UNSUPPORTED when the shape is outside the kernel's domain.   (ft_attention_tc.cu)
+int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q_col0, int k_col0,
+                        int v_col0, __half* out16, long long ldo16, float* out32, long long ldo32,
+                        float* stats, int batch, int seq, int heads, int kv_heads, int head_dim);

@@ -371,12 +371,13 @@ __global__ void k_scale_from_amax(const int* __restrict__ amax_bits, float* __re
 
 // f32 [rows, cols] (pitch ld) -> f16 [rows, ldo]: hi = f16(x*S); lo (optional) = the rounding
 // remainder times 2^11, so that x*S = hi + lo * 2^-11 to about 22 significant bits.
-// One thread per 4 output columns; ldo is a multiple of 8, padding columns are zeroed.
+// One thread per 4 output columns; only the group holding the last column is zero-padded
+// (TMA zero-fills beyond the tensor map's extent, so the rest of the pitch is never read).
 __global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __restrict__ hi,
                          __half* __restrict__ lo, long long ldo, int rows, int cols,
                          const float* __restrict__ scales) {
   const float S = scales ? scales[0] : 1.0f;
-  long long per_row = ldo / 4;
+  long long per_row = (cols + 3) / 4;
   long long total = (long long)rows * per_row;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   long long st = (long long)gridDim.x * blockDim.x;
@@ -463,7 +464,7 @@ int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half
     scales = ctx->scale_buf + 4;
   }
   if (scales_out) *scales_out = scales;
-  long long total = (long long)rows * (ldo / 4);
+  long long total = (long long)rows * ((cols + 3) / 4);
   int grid = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256,
                                                              (long long)ctx->sm_count * 16));
   FT_LAUNCH(ctx, k_to_f16, grid, 256, 0, src, ld, hi, lo, ldo, rows, cols, scales);

@@ -61,7 +61,7 @@ struct BlockActs {
   float *h1, *qkv, *attn, *stats, *x1, *h2, *gu, *f;
   float *xa_qkv, *xa_o, *xa_gu, *xa_down;
   // fused tensor-core path: GEMM inputs are kept as f16 only
-  __half *h1_16, *attn16, *h2_16, *f_16;
+  __half *h1_16, *qkv16, *attn16, *h2_16, *f_16;
   __half *xa16_qkv, *xa16_o, *xa16_gu, *xa16_down;
 };
 
@@ -161,6 +161,7 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
     if (fused) {
       a.h1_16 = b.take<__half>(T * c.hidden);
       a.qkv = b.take<float>(T * nqkv);
+      a.qkv16 = b.take<__half>(T * nqkv);
       a.attn = b.take<float>(T * m->nq);
       a.attn16 = b.take<__half>(T * m->nq);
       a.stats = b.take<float>((size_t)sequences * c.heads * seq_len * 2);
@@ -550,8 +551,18 @@ int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, 
   FT_TRY(linear_fwd_fused(m, ly.qkv, a.h1_16, a.qkv, nqkv, a.xa16_qkv, nullptr, 0, T));
   FT_TRY(ft_k_rope(ctx, a.qkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, false));
   FT_TRY(ft_k_rope(ctx, a.qkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, false));
-  FT_TRY(attention_launch(m, a, false));
-  FT_TRY(ft_to_f16(ctx, a.attn, nq, a.attn16, nullptr, nq, T, nq, false, nullptr));
+  // attention on the tensor cores when the head size allows, else the exact kernel
+  int ar = FT_ERR_UNSUPPORTED;
+  if (c.head_dim == 64 && (nqkv % 8) == 0) {
+    FT_TRY(ft_to_f16(ctx, a.qkv, nqkv, a.qkv16, nullptr, nqkv, T, nqkv, false, nullptr));
+    ar = ft_attention_fwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, a.attn, nq, a.stats,
+                             m->sequences, m->seq_len, c.heads, c.kv_heads, c.head_dim);
+    if (ar != FT_OK && ar != FT_ERR_UNSUPPORTED) return ar;
+  }
+  if (ar == FT_ERR_UNSUPPORTED) {
+    FT_TRY(attention_launch(m, a, false));
+    FT_TRY(ft_to_f16(ctx, a.attn, nq, a.attn16, nullptr, nq, T, nq, false, nullptr));
+  }
   // x1 = x_in + o(attn): the residual rides in the GEMM epilogue
   FT_TRY(linear_fwd_fused(m, ly.o, a.attn16, a.x1, h, a.xa16_o, x_in, h, T));
   FT_TRY(ft_k_rms_norm16(ctx, a.x1, ly.norm2, nullptr, a.h2_16, T, h, c.eps));

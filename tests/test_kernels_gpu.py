@@ -264,3 +264,29 @@ def test_shape_errors_raise_instead_of_launching(cuda_ctx, eng):
         eng.matmul(cuda_ctx, a, b, _empty(cuda_ctx, (4, 3)))
     with pytest.raises(FtError):
         eng.matmul_f16b(cuda_ctx, a, b, _empty(cuda_ctx, (4, 3)))   # b is not FP16
+
+
+# Tensor-core attention (tcgen05): q, k, v are rounded to f16 (11 significant bits) and the
+# probabilities to f16 before P.V; accumulation and softmax are f32.  Stated tolerance against
+# the f64 oracle: 2e-3 absolute + 1e-2 relative on outputs of O(1) inputs.
+@pytest.mark.parametrize("b,s,h,hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 1024, 3, 3),
+                                       (2, 200, 2, 1), (1, 77, 2, 2), (1, 640, 14, 2)])
+def test_attention_forward_on_tensor_cores(cuda_ctx, eng, b, s, h, hkv):
+    from ferrotensor_b200.engine import AttentionOptions, GemmMode, UnifiedTensor
+    d = 64
+    rng = np.random.default_rng(s + h)
+    q = rng.standard_normal((b, s, h, d), dtype=np.float32)
+    k = rng.standard_normal((b, s, hkv, d), dtype=np.float32)
+    v = rng.standard_normal((b, s, hkv, d), dtype=np.float32)
+    Q, K, V = (UnifiedTensor.new(cuda_ctx, t, list(t.shape)) for t in (q, k, v))
+    out = _empty(cuda_ctx, (b, s, h, d))
+    stats = UnifiedTensor.zeros(cuda_ctx, [b, h, s, 2])
+    cuda_ctx.set_gemm_mode(GemmMode.F16)
+    try:
+        eng.flash_attention_v2_with_stats(cuda_ctx, Q, K, V, out, stats, AttentionOptions(causal=True))
+        got, lse = out.to_vec(cuda_ctx), stats.to_vec(cuda_ctx).reshape(-1, 2)[:, 1]
+    finally:
+        cuda_ctx.set_gemm_mode(GemmMode.F32)
+    eo, elses, _ = ok.attention(q, k, v, b, s, s, h, hkv, d, True, torch.float64)
+    _close(got, eo, 2e-3, 1e-2, "tc attention out")
+    _close(lse, elses, 2e-3, 1e-3, "tc attention lse")
