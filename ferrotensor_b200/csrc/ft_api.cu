@@ -473,6 +473,29 @@ extern "C" int ft_flash_attention_v2_backward(FtContext* ctx, const float* q, co
   FT_REQUIRE(ctx && q && k && v && out && dout && dq && dk && dv,
              "ft_flash_attention_v2_backward: NULL argument");
   FT_TRY(check_attn("ft_flash_attention_v2_backward", p, mask));
+  if (ctx->gemm_mode == FT_GEMM_F16 && p->head_dim == 64 && p->causal && !p->causal_offset &&
+      !p->window && p->seq_q == p->seq_k && p->seq_q >= 64 && stats && p->lse_saved) {
+    // tensor-core form: operands rounded to f16 (dout after a power-of-two scale)
+    const int nq = p->heads * 64, nkv = p->kv_heads * 64, ld = nq + 2 * nkv;
+    const int T = (int)(p->batch * p->seq_q);
+    void* s = nullptr;
+    const size_t n_qkv = ft_align_up((size_t)T * ld * sizeof(__half), 256);
+    const size_t n_o = ft_align_up((size_t)T * nq * sizeof(__half), 256);
+    FT_TRY(ft_scratch(ctx, n_qkv + 2 * n_o, &s));
+    __half* qkv16 = (__half*)s;
+    __half* o16 = (__half*)((char*)s + n_qkv);
+    __half* do16 = (__half*)((char*)s + n_qkv + n_o);
+    FT_TRY(ft_to_f16(ctx, q, nq, qkv16, nullptr, ld, T, nq, false, nullptr));
+    FT_TRY(ft_to_f16(ctx, k, nkv, qkv16 + nq, nullptr, ld, T, nkv, false, nullptr));
+    FT_TRY(ft_to_f16(ctx, v, nkv, qkv16 + nq + nkv, nullptr, ld, T, nkv, false, nullptr));
+    FT_TRY(ft_to_f16(ctx, out, nq, o16, nullptr, nq, T, nq, false, nullptr));
+    const float* scales = nullptr;
+    FT_TRY(ft_to_f16(ctx, dout, nq, do16, nullptr, nq, T, nq, true, &scales, 8));
+    int r = ft_attention_bwd_tc(ctx, qkv16, ld, 0, nq, nq + nkv, o16, nq, do16, nq, dq, nq, dk, dv,
+                                nkv, stats, scales + 1, (int)p->batch, (int)p->seq_q,
+                                (int)p->heads, (int)p->kv_heads, 64);
+    if (r != FT_ERR_UNSUPPORTED) return r;
+  }
   FtAttnBwdLaunch a;
   a.q = q; a.k = k; a.v = v; a.out = out; a.dout = dout; a.dq = dq; a.dk = dk; a.dv = dv;
   a.stats = stats; a.p = *p;

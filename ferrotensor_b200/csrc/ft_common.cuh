@@ -198,3 +198,11 @@ int ft_k_attention_bwd(FtContext* ctx, const FtAttnBwdLaunch& a);
 int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q_col0, int k_col0,
                         int v_col0, __half* out16, long long ldo16, float* out32, long long ldo32,
                         float* stats, int batch, int seq, int heads, int kv_heads, int head_dim);
+// Backward: o16 = forward output (f16), do16 = output gradient (f16, times the power-of-two
+// scale whose inverse is the device scalar *inv_scale, NULL = 1); stats must hold the forward
+// log-sum-exp at [2*row+1] and receives Delta at [2*row].  dq [tokens, lddq]; dk, dv [tokens, ldd].
+int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q_col0, int k_col0,
+                        int v_col0, const __half* o16, long long ldo, const __half* do16,
+                        long long lddo, float* dq, long long lddq, float* dk, float* dv,
+                        long long ldd, float* stats, const float* inv_scale, int batch, int seq,
+                        int heads, int kv_heads, int head_dim);

@@ -583,7 +583,17 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   FT_TRY(linear_bwd_fused(m, ly.gu, a.h2_16, m->dgu, 2 * F, a.xa16_gu, m->dh, h, nullptr, 0, T));
   FT_TRY(ft_k_rms_norm_bwd(ctx, a.x1, ly.norm2, m->dh, m->dx, nullptr, T, h, c.eps, true));
   FT_TRY(linear_bwd_fused(m, ly.o, a.attn16, m->dx, h, a.xa16_o, m->dattn, nq, nullptr, 0, T));
-  FT_TRY(attention_launch(m, a, true));
+  int ar = FT_ERR_UNSUPPORTED;
+  if (c.head_dim == 64 && (nqkv % 8) == 0) {
+    // the output gradient goes to f16 after a power-of-two scale, undone by the kernels
+    const float* scales = nullptr;
+    FT_TRY(ft_to_f16(ctx, m->dattn, nq, m->cvt_hi, nullptr, nq, T, nq, true, &scales, 8));
+    ar = ft_attention_bwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + m->nkv, a.attn16, nq, m->cvt_hi, nq,
+                             m->dqkv, nqkv, m->dqkv + nq, m->dqkv + nq + m->nkv, nqkv, a.stats,
+                             scales + 1, m->sequences, m->seq_len, c.heads, c.kv_heads, c.head_dim);
+    if (ar != FT_OK && ar != FT_ERR_UNSUPPORTED) return ar;
+  }
+  if (ar == FT_ERR_UNSUPPORTED) FT_TRY(attention_launch(m, a, true));
   FT_TRY(ft_k_rope(ctx, m->dqkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, true));
   FT_TRY(ft_k_rope(ctx, m->dqkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, true));
   const bool need_dx = l > 0;

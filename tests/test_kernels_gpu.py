@@ -290,3 +290,36 @@ def test_attention_forward_on_tensor_cores(cuda_ctx, eng, b, s, h, hkv):
     eo, elses, _ = ok.attention(q, k, v, b, s, s, h, hkv, d, True, torch.float64)
     _close(got, eo, 2e-3, 1e-2, "tc attention out")
     _close(lse, elses, 2e-3, 1e-3, "tc attention lse")
+
+
+# Tensor-core attention backward: operands in f16 (the output gradient after a power-of-two
+# scale), P and dS rounded to f16 before the second products, f32 accumulation.  Stated
+# tolerance against the f64 oracle: 2e-3 of the tensor's largest magnitude + 1e-2 relative.
+@pytest.mark.parametrize("b,s,h,hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 1024, 3, 3),
+                                       (2, 200, 2, 1), (1, 77, 2, 2), (1, 640, 14, 2)])
+def test_attention_backward_on_tensor_cores(cuda_ctx, eng, b, s, h, hkv):
+    from ferrotensor_b200.engine import AttentionOptions, GemmMode, UnifiedTensor
+    d = 64
+    rng = np.random.default_rng(s * 3 + h)
+    q = rng.standard_normal((b, s, h, d), dtype=np.float32)
+    k = rng.standard_normal((b, s, hkv, d), dtype=np.float32)
+    v = rng.standard_normal((b, s, hkv, d), dtype=np.float32)
+    do = (rng.standard_normal((b, s, h, d)) * 1e-4).astype(np.float32)   # gradient-sized values
+    Q, K, V, DO = (UnifiedTensor.new(cuda_ctx, t, list(t.shape)) for t in (q, k, v, do))
+    out = _empty(cuda_ctx, (b, s, h, d))
+    stats = UnifiedTensor.zeros(cuda_ctx, [b, h, s, 2])
+    dq, dk, dv = _empty(cuda_ctx, q.shape), _empty(cuda_ctx, k.shape), _empty(cuda_ctx, v.shape)
+    opts = AttentionOptions(causal=True)
+    cuda_ctx.set_gemm_mode(GemmMode.F16)
+    try:
+        eng.flash_attention_v2_with_stats(cuda_ctx, Q, K, V, out, stats, opts)
+        eng.flash_attention_v2_backward_with_stats(cuda_ctx, Q, K, V, out, DO, dq, dk, dv, stats, opts)
+        got = [t.to_vec(cuda_ctx) for t in (dq, dk, dv)]
+        eng.flash_attention_v2_backward_with_stats(cuda_ctx, Q, K, V, out, DO, dq, dk, dv, stats, opts)
+        again = [t.to_vec(cuda_ctx) for t in (dq, dk, dv)]
+    finally:
+        cuda_ctx.set_gemm_mode(GemmMode.F32)
+    exp = ok.attention_backward(q, k, v, do, b, s, s, h, hkv, d, True, torch.float64)
+    for name, g, e, a in zip(("dq", "dk", "dv"), got, exp, again):
+        _close(g, e, 2e-3 * np.abs(e).max(), 1e-2, f"tc {name}")
+        assert np.array_equal(g, a), f"{name}: two runs differ"
