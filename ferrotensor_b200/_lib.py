@@ -88,6 +88,7 @@ PROTOTYPES = {
     "ft_rope_theta": [_P, _P, _Z, _I, _I, _I, _I, _F, _I],
     "ft_rms_norm_eps": [_P, _P, _P, _P, _I, _I, _F],
     "ft_rms_norm_backward": [_P, _P, _P, _P, _P, _P, _I, _I, _F],
+    "ft_rms_norm_backward_noalloc": [_P, _P, _P, _P, _P, _P, _I, _I, _F],
     "ft_add": [_P, _P, _P, _P, _Z],
     "ft_add_backward": [_P, _P, _P, _P, _Z],
     "ft_gradient_scale": [_P, _P, _Z, _F],

@@ -488,6 +488,70 @@ int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const floa
   return FT_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate.
+//
+// Some hosts of this library cannot let a call reach cudaMalloc: a runtime that has handed all
+// of its device memory to its own pool, or code running where an allocation would serialise or
+// fail (inside a latency-critical loop, under a memory cap set by the embedding program).  The
+// regular entry point borrows per-row scratch from the context, which grows it with cudaMalloc
+// on demand.  This variant keeps that scratch in a fixed array inside the library image
+// instead: 2 MiB that every GPU loading the library holds until the process exits.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kNoAllocFloats = 512 * 1024;  // 2 MiB
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address:
+// the address is asked for once per device (with that device current) and cached.
+constexpr int kMaxDevices = 64;
+static float* g_noalloc_ptr[kMaxDevices] = {};
+
+extern "C" int ft_rms_norm_backward_noalloc(FtContext* ctx, const float* x, const float* w,
+                                            const float* g, float* gx, float* gw, int rows,
+                                            int size, float eps) {
+  FT_REQUIRE(ctx && x && w && g && gx, "ft_rms_norm_backward_noalloc: NULL argument");
+  FT_REQUIRE(rows >= 0 && size > 0, "ft_rms_norm_backward_noalloc: bad shape");
+  if (!rows) return FT_OK;
+  // scratch layout: inv[rows] (256-byte aligned), then partial[chunks][size]
+  const size_t inv_floats = ft_align_up((size_t)rows, 64);
+  FT_REQUIRE(!gw || inv_floats + (size_t)size <= kNoAllocFloats,
+             "ft_rms_norm_backward_noalloc: rows (rounded up to 64) + size = %zu floats exceeds the "
+             "fixed scratch of %zu floats; use ft_rms_norm_backward",
+             inv_floats + (size_t)size, kNoAllocFloats);
+  FT_REQUIRE(ctx->device >= 0 && ctx->device < kMaxDevices,
+             "ft_rms_norm_backward_noalloc: device ordinal %d out of range", ctx->device);
+  float* scratch = g_noalloc_ptr[ctx->device];
+  if (!scratch) {
+    // first call on this device: resolve the symbol (do this before any stream capture)
+    FT_CUDA(cudaSetDevice(ctx->device));
+    void* p = nullptr;
+    FT_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    FT_REQUIRE(p != nullptr, "ft_rms_norm_backward_noalloc: symbol address is NULL");
+    scratch = g_noalloc_ptr[ctx->device] = (float*)p;
+  }
+  float* inv = nullptr;
+  float* partial = nullptr;
+  int chunks = 0, rows_per_chunk = 0;
+  if (gw) {
+    const size_t fit = (kNoAllocFloats - inv_floats) / (size_t)size;
+    chunks = std::max(1, std::min(rows, (ctx->sm_count * 8) / std::max(1, ft_cdiv(size, 128))));
+    chunks = (int)std::min<size_t>((size_t)std::min(chunks, 1024), fit);
+    rows_per_chunk = ft_cdiv(rows, chunks);
+    chunks = ft_cdiv(rows, rows_per_chunk);
+    inv = scratch;
+    partial = scratch + inv_floats;
+  }
+  // every scratch word that is read is written first by these launches: nothing to clear
+  int block = size >= 1024 ? kRowThreads : (size >= 256 ? 128 : 32);
+  FT_LAUNCH(ctx, k_rms_norm_bwd, rows, block, 0, x, w, g, gx, inv, size, eps, 0);
+  if (gw) {
+    dim3 grid(ft_cdiv(size, 128), chunks);
+    FT_LAUNCH(ctx, k_rms_gw_partial, grid, 128, 0, x, g, inv, partial, rows, size, rows_per_chunk);
+    FT_LAUNCH(ctx, k_rms_gw_final, ft_cdiv(size, 128), 128, 0, partial, gw, size, chunks);
+  }
+  return FT_OK;
+}
+
 int ft_k_rope(FtContext* ctx, float* x, long long ld, int tokens, int heads, int head_dim,
               int seq_len, int pos, float theta, bool inverse) {
   long long pairs = (long long)tokens * heads * (head_dim / 2);

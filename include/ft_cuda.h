@@ -118,6 +118,20 @@ int ft_rms_norm_eps(FtContext* ctx, const float* x, const float* w, float* out, 
 int ft_rms_norm_backward(FtContext* ctx, const float* x, const float* w, const float* g,
                          float* gx, float* gw, int rows, int size, float eps);
 
+/* No counterpart in the reference.  ft_rms_norm_backward for hosts that cannot allocate
+ * device memory during a call (all memory already handed to their own pool, an embedding
+ * program's memory cap, a loop where a cudaMalloc stall is not acceptable): same arguments
+ * and results, but the per-row scratch lives in a fixed 2 MiB array inside the library image
+ * (held by every GPU that loads the library until the process exits) and the call makes no
+ * cudaMalloc/cudaFree.  Limit: with gw != NULL, rows rounded up to 64 plus size must not
+ * exceed 524288 floats; larger shapes are rejected with FT_ERR_INVALID.  The first call on a
+ * device resolves the array's address - make that call before any stream capture.  All
+ * calls share the one array, which keeps the previous call's contents (every word read is
+ * first rewritten, so nothing needs clearing); calls that overlap on the GPU (different
+ * streams or contexts of one device) race on it. */
+int ft_rms_norm_backward_noalloc(FtContext* ctx, const float* x, const float* w, const float* g,
+                                 float* gx, float* gw, int rows, int size, float eps);
+
 /* ---- elementwise: engine/elementwise.rs:8-17,57-75,183-215; engine/training.rs:189-205;
  * engine/mod.rs:399-428 (copy_tensor). */
 int ft_add(FtContext* ctx, const float* a, const float* b, float* out, size_t n);
