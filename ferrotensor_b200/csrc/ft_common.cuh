@@ -30,6 +30,11 @@ struct FtContext {
   // device floats: [0] amax bits, [1] the constant 2^-11, [4..6] {S, 1/S, 2^-11/S} of the
   // operand being converted (consumed by the GEMM that follows in stream order)
   float* scale_buf = nullptr;
+  // "amax in the producer": while armed, kernels that support it fold the largest magnitude
+  // of what they write into scale_buf[0] (atomicMax), and the next auto-scaled conversion
+  // uses it instead of making its own pass over the tensor.
+  int* amax_out = nullptr;
+  bool amax_ready = false;
   // optional timing of the tensor-core GEMM launches (CUDA events on the launch stream)
   bool profile = false;
   std::vector<cudaEvent_t> prof_events;  // start/stop pairs, reused
@@ -113,6 +118,7 @@ struct FtGemmArgs {
   const float* alpha_ptr = nullptr; float alpha = 1.f;
   const float* bias = nullptr;
   const float* residual = nullptr; long long ldr = 0;
+  bool want_amax = false;   // contribute the output's largest magnitude to an armed amax slot
 };
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g);
 // Token-reduction product P[M, N<=64] = sum_t A[t,m] B[t,n] (A [T,M], B [T,N], f16) as K-split
@@ -130,6 +136,11 @@ int ft_slab_reduce(FtContext* ctx, const float* slabs, int nslabs, int M, float*
 int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half* lo,
               long long ldo, int rows, int cols, bool auto_scale, const float** scales_out,
               int target_exp = 12);
+// Arms the producer-side amax (see FtContext::amax_out): zeroes the slot; the kernels launched
+// until the next auto-scaled ft_to_f16 contribute to it.
+int ft_amax_arm(FtContext* ctx);
+int ft_scales_from_amax_or_pass(FtContext* ctx, const float* src, long long ld, int rows, int cols,
+                                int target_exp, const float** scales_out);
 // conversion + one (FT_GEMM_F16) or two (FT_GEMM_F16X2) tensor-core passes
 int ft_gemm_tc_f32a(FtContext* ctx, const float* a, long long lda_f32, __half* stage_hi,
                     __half* stage_lo, const void* b_f16, long long ldb, float* c, long long ldc,
@@ -148,6 +159,14 @@ int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const floa
 // in place on x[t*ld + h*head_dim + i]; position of token t = pos + t % seq_len
 int ft_k_rope(FtContext* ctx, float* x, long long ld, int tokens, int heads, int head_dim,
               int seq_len, int pos, float theta, bool inverse);
+// RoPE for the tensor-core path.  table: float2 {cos, sin} [seq_len, head_dim/2] built with the
+// same f32 recipe as ft_k_rope.  forward: f32 q|k|v rows -> f16 rows (q, k rotated, v copied).
+// backward: f32 gradient rows -> f16 rows times the scale in `scales[0]`, q, k parts rotated
+// by the negated angle.  Rows are [tokens, nq + 2 nkv], head_dim 64.
+int ft_k_rope_table(FtContext* ctx, float* table, int seq_len, int head_dim, float theta);
+int ft_k_rope_to_f16(FtContext* ctx, const float* src, __half* dst, long long ld, int tokens,
+                     int nq, int nkv, int seq_len, const float* table, bool inverse,
+                     const float* scales);
 int ft_k_add(FtContext* ctx, const float* a, const float* b, float* out, size_t n);
 int ft_k_scale(FtContext* ctx, float* x, size_t n, float s);
 // 2-D SwiGLU: out[t, j] = silu(a[t*lda + j]) * b[t*ldb + j], j < n

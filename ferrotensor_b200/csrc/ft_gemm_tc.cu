@@ -55,6 +55,7 @@ struct Epilogue {
   const float* bias;
   const float* residual;
   long long ldr;
+  int* amax_slot;   // when set, the largest |v| written is folded into it (atomicMax)
 };
 
 // KOUTER = false:  C[M,N] = A[M,K] . B[N,K]^T (+ A2[M,K2] . B2[N,K2]^T), operands K-contiguous.
@@ -208,6 +209,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     const bool vec_r = !ep.residual || (((ep.ldr & 3) == 0) && ((((uintptr_t)ep.residual) & 15) == 0));
     const bool vec_h = ep.c16 && ((ep.ldc16 & 7) == 0) && ((((uintptr_t)ep.c16) & 15) == 0);
     const float alpha = (ep.alpha_ptr ? *ep.alpha_ptr : 1.0f) * ep.alpha;
+    float amax_seen = 0.f;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int m0 = (tile % tiles_m) * BM, nt = tile / tiles_m;
       const int n0 = KOUTER ? 0 : nt * BN;
@@ -248,6 +250,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 if (col0 + j < N) v[j] += rr[j];
             }
           }
+          if (ep.amax_slot) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < N) amax_seen = fmaxf(amax_seen, fabsf(v[j]));
+          }
           if (cbase) {
             float* crow = cbase + (long long)row * ep.ldc + col0;
             if (full && vec_c) {
@@ -286,6 +293,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + buf * 8);
       if (warp == 2 && lane == 0) FT_MARK(9, 45);
+    }
+    if (ep.amax_slot) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        amax_seen = fmaxf(amax_seen, __shfl_xor_sync(0xffffffffu, amax_seen, o));
+      if (lane == 0 && amax_seen > 0.f) atomicMax(ep.amax_slot, __float_as_int(amax_seen));
     }
   }
 
@@ -448,20 +461,39 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
 
 }  // namespace
 
+int ft_amax_arm(FtContext* ctx) {
+  FT_CUDA(cudaMemsetAsync(ctx->scale_buf, 0, 4, ctx->stream));
+  ctx->amax_out = (int*)ctx->scale_buf;
+  ctx->amax_ready = false;
+  return FT_OK;
+}
+
+// {S, 1/S, 2^-11/S} from the amax a producer left in the slot, or from a pass over `src`.
+int ft_scales_from_amax_or_pass(FtContext* ctx, const float* src, long long ld, int rows, int cols,
+                                int target_exp, const float** scales_out) {
+  const bool ready = ctx->amax_ready && ctx->amax_out;
+  ctx->amax_out = nullptr;
+  ctx->amax_ready = false;
+  if (!ready) {
+    FT_CUDA(cudaMemsetAsync(ctx->scale_buf, 0, 4, ctx->stream));
+    long long n = (long long)rows * cols;
+    int g = (int)std::max<long long>(1, std::min<long long>((n + 4095) / 4096,
+                                                            (long long)ctx->sm_count * 8));
+    FT_LAUNCH(ctx, k_amax, g, 256, 0, src, ld, rows, cols, (int*)ctx->scale_buf);
+  }
+  FT_LAUNCH(ctx, k_scale_from_amax, 1, 1, 0, (const int*)ctx->scale_buf, ctx->scale_buf + 4,
+            target_exp);
+  *scales_out = ctx->scale_buf + 4;
+  return FT_OK;
+}
+
 int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half* lo,
               long long ldo, int rows, int cols, bool auto_scale, const float** scales_out,
               int target_exp) {
   FT_REQUIRE(ldo % 8 == 0 && ldo >= cols, "to_f16: output pitch %lld must be a multiple of 8", ldo);
   const float* scales = nullptr;
   if (auto_scale) {
-    FT_CUDA(cudaMemsetAsync(ctx->scale_buf, 0, 4, ctx->stream));
-    long long n = (long long)rows * cols;
-    int g = (int)std::max<long long>(1, std::min<long long>((n + 4095) / 4096,
-                                                            (long long)ctx->sm_count * 8));
-    FT_LAUNCH(ctx, k_amax, g, 256, 0, src, ld, rows, cols, (int*)ctx->scale_buf);
-    FT_LAUNCH(ctx, k_scale_from_amax, 1, 1, 0, (const int*)ctx->scale_buf, ctx->scale_buf + 4,
-              target_exp);
-    scales = ctx->scale_buf + 4;
+    FT_TRY(ft_scales_from_amax_or_pass(ctx, src, ld, rows, cols, target_exp, &scales));
   }
   if (scales_out) *scales_out = scales;
   long long total = (long long)rows * ((cols + 3) / 4);
@@ -501,6 +533,11 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   ep.c = g.c; ep.ldc = g.ldc; ep.c16 = g.c16; ep.ldc16 = g.ldc16;
   ep.alpha_ptr = g.alpha_ptr; ep.alpha = g.alpha; ep.bias = g.bias;
   ep.residual = g.residual; ep.ldr = g.ldr;
+  ep.amax_slot = nullptr;
+  if (g.want_amax && ctx->amax_out) {
+    ep.amax_slot = ctx->amax_out;
+    ctx->amax_ready = true;
+  }
   const double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
   switch (BN) {
     case 256: return launch_tc<256, 4, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
@@ -539,6 +576,7 @@ int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* 
   Epilogue ep;
   ep.c = (float*)s; ep.ldc = 64; ep.c16 = nullptr; ep.ldc16 = 0;
   ep.alpha_ptr = nullptr; ep.alpha = 1.f; ep.bias = nullptr; ep.residual = nullptr; ep.ldr = 0;
+  ep.amax_slot = nullptr;
   // both operands M/N-major: bits 15 and 16 of the instruction descriptor
   const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
   *slabs_out = (float*)s;

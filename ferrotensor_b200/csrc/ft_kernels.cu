@@ -43,6 +43,17 @@ __device__ __forceinline__ float block_max(float v, float* buf) {
 
 __device__ __forceinline__ bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
+// Folds a thread's largest written magnitude into the context's amax slot.  Must be reached
+// by every lane of the warp.  Non-negative floats order like their bit patterns.
+__device__ __forceinline__ void amax_commit(float m, int* slot) {
+  if (!slot) return;
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(slot, __float_as_int(m));
+}
+__device__ __forceinline__ float amax4(float m, float4 v) {
+  return fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+}
+
 // ------------------------------------------------------------------------------- embedding
 __global__ void k_embedding(const float* __restrict__ table, const uint32_t* __restrict__ ids,
                             float* __restrict__ out, int vocab, int hidden) {
@@ -111,7 +122,8 @@ k_rms_norm(const float* __restrict__ x, const float* __restrict__ w, float* __re
 __global__ void __launch_bounds__(kRowThreads)
 k_rms_norm_bwd(const float* __restrict__ x, const float* __restrict__ w,
                const float* __restrict__ g, float* __restrict__ gx, float* __restrict__ inv_out,
-               int n, float eps, int accumulate) {
+               int n, float eps, int accumulate, int* amax_slot) {
+  float am = 0.f;
   __shared__ float red[32];
   size_t off = (size_t)blockIdx.x * n;
   const float* xr = x + off;
@@ -149,13 +161,17 @@ k_rms_norm_bwd(const float* __restrict__ x, const float* __restrict__ w,
         r.x += p.x; r.y += p.y; r.z += p.z; r.w += p.w;
       }
       o4[i] = r;
+      am = amax4(am, r);
     }
   } else {
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       float r = gr[i] * w[i] * inv - xr[i] * coef;
-      o[i] = accumulate ? o[i] + r : r;
+      r = accumulate ? o[i] + r : r;
+      o[i] = r;
+      am = fmaxf(am, fabsf(r));
     }
   }
+  amax_commit(am, amax_slot);
   if (inv_out && threadIdx.x == 0) inv_out[blockIdx.x] = inv;
 }
 
@@ -199,6 +215,64 @@ __global__ void k_rope(float* __restrict__ x, long long ld, long long pairs, int
   float v1 = p[0], v2 = p[half];
   p[0] = v1 * c - v2 * s;
   p[half] = v1 * s + v2 * c;
+}
+
+// {cos, sin} of f32(position) * powf(theta, -2i/d): the angle recipe of k_rope, evaluated once
+__global__ void k_rope_table(float2* __restrict__ table, int seq_len, int half, int head_dim,
+                             float theta) {
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= seq_len * half) return;
+  int pos = idx / half, i = idx % half;
+  float freq = powf(theta, -2.0f * (float)i / (float)head_dim);
+  float s, c;
+  sincosf((float)pos * freq, &s, &c);
+  table[idx] = make_float2(c, s);
+}
+
+// One thread per 8 elements of a q|k|v row with head_dim 64: in the q and k parts the thread
+// owns pairs (i..i+3, i+32..i+35) of one head, in the v part 8 consecutive values.
+// out = f16(scale * rotate(+-angle)(x)).
+__global__ void k_rope_to_f16(const float* __restrict__ src, __half* __restrict__ dst, long long ld,
+                              long long tokens, int nq, int nkv, int seq_len,
+                              const float2* __restrict__ table, int inverse,
+                              const float* __restrict__ scales) {
+  const float S = scales ? scales[0] : 1.0f;
+  const int per_tok = (nq + 2 * nkv) / 8;
+  const long long total = tokens * per_tok;
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long st = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += st) {
+    const long long t = idx / per_tok;
+    const int u = (int)(idx % per_tok);
+    const float* row = src + t * ld;
+    __half* orow = dst + t * ld;
+    const int rot_units = (nq + nkv) / 8;
+    if (u < rot_units) {
+      const int head = u >> 3, i = (u & 7) * 4;      // 8 threads per 64-wide head
+      const int c0 = head * 64 + i;
+      const float4 lo = *(const float4*)(row + c0), hi = *(const float4*)(row + c0 + 32);
+      const float2* tb = table + (size_t)(t % seq_len) * 32 + i;
+      const float a[4] = {lo.x, lo.y, lo.z, lo.w}, b[4] = {hi.x, hi.y, hi.z, hi.w};
+      float o1[4], o2[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 cs = tb[k];
+        const float sn = inverse ? -cs.y : cs.y;
+        o1[k] = (a[k] * cs.x - b[k] * sn) * S;
+        o2[k] = (a[k] * sn + b[k] * cs.x) * S;
+      }
+      __half2 p0 = __floats2half2_rn(o1[0], o1[1]), p1 = __floats2half2_rn(o1[2], o1[3]);
+      __half2 q0 = __floats2half2_rn(o2[0], o2[1]), q1 = __floats2half2_rn(o2[2], o2[3]);
+      *(uint2*)(orow + c0) = make_uint2(*(uint32_t*)&p0, *(uint32_t*)&p1);
+      *(uint2*)(orow + c0 + 32) = make_uint2(*(uint32_t*)&q0, *(uint32_t*)&q1);
+    } else {
+      const int c0 = (nq + nkv) + (u - rot_units) * 8;
+      const float4 x = *(const float4*)(row + c0), y = *(const float4*)(row + c0 + 4);
+      __half2 h0 = __floats2half2_rn(x.x * S, x.y * S), h1 = __floats2half2_rn(x.z * S, x.w * S);
+      __half2 h2 = __floats2half2_rn(y.x * S, y.y * S), h3 = __floats2half2_rn(y.z * S, y.w * S);
+      *(uint4*)(orow + c0) = make_uint4(*(uint32_t*)&h0, *(uint32_t*)&h1, *(uint32_t*)&h2, *(uint32_t*)&h3);
+    }
+  }
 }
 
 // ------------------------------------------------------------------------- add/scale/bias
@@ -263,16 +337,48 @@ __global__ void k_silu_gate_bwd(const float* __restrict__ a, long long lda,
                                 const float* __restrict__ b, long long ldb,
                                 const float* __restrict__ g, long long ldg,
                                 float* __restrict__ ga, long long ldga, float* __restrict__ gb,
-                                long long ldgb, int rows, int n) {
+                                long long ldgb, int rows, int n, int* amax_slot) {
   size_t total = (size_t)rows * n;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  float am = 0.f;
   for (; i < total; i += st) {
     size_t r = i / n, c = i % n;
     float x = a[r * lda + c], y = b[r * ldb + c], go = g[r * ldg + c];
     float s = 1.0f / (1.0f + expf(-x));
-    gb[r * ldgb + c] = go * (x * s);
-    ga[r * ldga + c] = go * y * (s * (1.0f + x * (1.0f - s)));
+    float vb = go * (x * s), va = go * y * (s * (1.0f + x * (1.0f - s)));
+    gb[r * ldgb + c] = vb;
+    ga[r * ldga + c] = va;
+    am = fmaxf(am, fmaxf(fabsf(va), fabsf(vb)));
   }
+  amax_commit(am, amax_slot);
+}
+
+// the same with 4 columns per thread (width and pitches multiples of 4, 16-byte aligned)
+__global__ void k_silu_gate_bwd4(const float* __restrict__ a, long long lda,
+                                 const float* __restrict__ b, long long ldb,
+                                 const float* __restrict__ g, long long ldg,
+                                 float* __restrict__ ga, long long ldga, float* __restrict__ gb,
+                                 long long ldgb, int rows, int n, int* amax_slot) {
+  size_t per_row = (size_t)n / 4, total = (size_t)rows * per_row;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  float am = 0.f;
+  for (; i < total; i += st) {
+    size_t r = i / per_row, c = (i % per_row) * 4;
+    float4 x = *(const float4*)(a + r * lda + c), y = *(const float4*)(b + r * ldb + c);
+    float4 go = *(const float4*)(g + r * ldg + c);
+    float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w}, gs[4] = {go.x, go.y, go.z, go.w};
+    float va[4], vb[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float s = 1.0f / (1.0f + expf(-xs[k]));
+      vb[k] = gs[k] * (xs[k] * s);
+      va[k] = gs[k] * ys[k] * (s * (1.0f + xs[k] * (1.0f - s)));
+      am = fmaxf(am, fmaxf(fabsf(va[k]), fabsf(vb[k])));
+    }
+    *(float4*)(ga + r * ldga + c) = make_float4(va[0], va[1], va[2], va[3]);
+    *(float4*)(gb + r * ldgb + c) = make_float4(vb[0], vb[1], vb[2], vb[3]);
+  }
+  amax_commit(am, amax_slot);
 }
 
 // ------------------------------------------------------------------- masked cross-entropy
@@ -281,7 +387,7 @@ __global__ void k_silu_gate_bwd(const float* __restrict__ a, long long lda,
 __global__ void __launch_bounds__(kRowThreads)
 k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
             const float* __restrict__ weights, float* grad, float* __restrict__ row_loss,
-            int vocab, float grad_scale) {
+            int vocab, float grad_scale, int* amax_slot) {
   // `grad` may alias `logits` (in-place use by the fused step): every element is read for
   // the last time by the thread that then overwrites it, after both reductions are done.
   __shared__ float red[32];
@@ -329,6 +435,8 @@ k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
   se = block_sum(se, red);
   float log_z = m + logf(se);
   float inv = weights[row] * grad_scale;
+  // |(softmax - onehot) * inv| <= |inv|: a tight bound serves as this row's amax
+  if (amax_slot && threadIdx.x == 0 && inv != 0.f) atomicMax(amax_slot, __float_as_int(fabsf(inv)));
   if (gz) {
     if (vec) {
       const float4* z4 = (const float4*)z;
@@ -479,7 +587,9 @@ int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const floa
     partial = (float*)((char*)s + ft_align_up((size_t)rows * 4, 256));
   }
   int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
-  FT_LAUNCH(ctx, k_rms_norm_bwd, rows, block, 0, x, w, g, gx, inv, n, eps, accumulate_gx ? 1 : 0);
+  int* am = ctx->amax_out;
+  if (am) ctx->amax_ready = true;
+  FT_LAUNCH(ctx, k_rms_norm_bwd, rows, block, 0, x, w, g, gx, inv, n, eps, accumulate_gx ? 1 : 0, am);
   if (gw) {
     dim3 grid(ft_cdiv(n, 128), chunks);
     FT_LAUNCH(ctx, k_rms_gw_partial, grid, 128, 0, x, g, inv, partial, rows, n, rows_per_chunk);
@@ -543,7 +653,7 @@ extern "C" int ft_rms_norm_backward_noalloc(FtContext* ctx, const float* x, cons
   }
   // every scratch word that is read is written first by these launches: nothing to clear
   int block = size >= 1024 ? kRowThreads : (size >= 256 ? 128 : 32);
-  FT_LAUNCH(ctx, k_rms_norm_bwd, rows, block, 0, x, w, g, gx, inv, size, eps, 0);
+  FT_LAUNCH(ctx, k_rms_norm_bwd, rows, block, 0, x, w, g, gx, inv, size, eps, 0, (int*)nullptr);
   if (gw) {
     dim3 grid(ft_cdiv(size, 128), chunks);
     FT_LAUNCH(ctx, k_rms_gw_partial, grid, 128, 0, x, g, inv, partial, rows, size, rows_per_chunk);
@@ -560,6 +670,24 @@ int ft_k_rope(FtContext* ctx, float* x, long long ld, int tokens, int heads, int
   FT_REQUIRE(blocks <= 0x7fffffffLL, "rope: too many elements");
   FT_LAUNCH(ctx, k_rope, (unsigned)blocks, 256, 0, x, ld, pairs, heads, head_dim, seq_len, pos,
             theta, inverse ? 1 : 0);
+  return FT_OK;
+}
+
+int ft_k_rope_table(FtContext* ctx, float* table, int seq_len, int head_dim, float theta) {
+  int half = head_dim / 2, n = seq_len * half;
+  FT_LAUNCH(ctx, k_rope_table, ft_cdiv(n, 256), 256, 0, (float2*)table, seq_len, half, head_dim, theta);
+  return FT_OK;
+}
+
+int ft_k_rope_to_f16(FtContext* ctx, const float* src, __half* dst, long long ld, int tokens,
+                     int nq, int nkv, int seq_len, const float* table, bool inverse,
+                     const float* scales) {
+  FT_REQUIRE((nq % 64) == 0 && (nkv % 64) == 0 && (ld % 8) == 0 && ld >= nq + 2 * nkv &&
+                 (((uintptr_t)src) & 15) == 0 && (((uintptr_t)dst) & 15) == 0,
+             "rope_to_f16: needs head_dim 64 and 16-byte aligned rows");
+  size_t total = (size_t)tokens * ((nq + 2 * nkv) / 8);
+  FT_LAUNCH(ctx, k_rope_to_f16, ew_grid(ctx, total, 256, 2), 256, 0, src, dst, ld, (long long)tokens, nq,
+            nkv, seq_len, (const float2*)table, inverse ? 1 : 0, scales);
   return FT_OK;
 }
 
@@ -603,16 +731,27 @@ int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float*
 int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const float* b,
                        long long ldb, const float* g, long long ldg, float* ga, long long ldga,
                        float* gb, long long ldgb, int rows, int n) {
-  FT_LAUNCH(ctx, k_silu_gate_bwd, ew_grid(ctx, (size_t)rows * n), 256, 0, a, lda, b, ldb, g, ldg,
-            ga, ldga, gb, ldgb, rows, n);
+  int* am = ctx->amax_out;
+  if (am) ctx->amax_ready = true;
+  const bool vec = (n % 4) == 0 && ((lda | ldb | ldg | ldga | ldgb) % 4) == 0 &&
+                   ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)g) | ((uintptr_t)ga) |
+                     ((uintptr_t)gb)) & 15) == 0;
+  if (vec)
+    FT_LAUNCH(ctx, k_silu_gate_bwd4, ew_grid(ctx, (size_t)rows * n / 4, 256, 2), 256, 0, a, lda, b,
+              ldb, g, ldg, ga, ldga, gb, ldgb, rows, n, am);
+  else
+    FT_LAUNCH(ctx, k_silu_gate_bwd, ew_grid(ctx, (size_t)rows * n), 256, 0, a, lda, b, ldb, g, ldg,
+              ga, ldga, gb, ldgb, rows, n, am);
   return FT_OK;
 }
 
 int ft_k_masked_ce(FtContext* ctx, const float* logits, const uint32_t* targets,
                    const float* weights, float* grad, float* row_loss, int rows, int vocab,
                    float grad_scale) {
+  int* am = ctx->amax_out;
+  if (am) ctx->amax_ready = true;
   FT_LAUNCH(ctx, k_masked_ce, rows, kRowThreads, 0, logits, targets, weights, grad, row_loss,
-            vocab, grad_scale);
+            vocab, grad_scale, am);
   return FT_OK;
 }
 

@@ -110,6 +110,9 @@ struct FtLoraModel {
   bool plan_fused = false;         // the planned workspace is the fused tensor-core layout
   __half *hN16 = nullptr, *xa16_head = nullptr, *g16 = nullptr;
   bool packs_dirty = true;         // adapter operand forms must be rebuilt before use
+  bool tc_attention = false;       // head_dim 64: attention and RoPE take the tensor-core route
+  float* rope_table = nullptr;     // {cos, sin} [seq_len, 32] in the workspace
+  int table_seq = 0;
 };
 
 namespace {
@@ -150,8 +153,13 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   const int L = c.layers;
   const int nqkv = m->nq + 2 * m->nkv;
   const bool fused = use_fused(m);
+  const bool tc_attention = fused && c.head_dim == 64 && (nqkv % 8) == 0 && (m->nq % 64) == 0 &&
+                            (long long)sequences * c.heads <= 65535;
   std::vector<float*> x(L + 1);
   for (int l = 0; l <= L; ++l) x[l] = b.take<float>(T * c.hidden);
+  // with attention on the tensor cores only the f16 q|k|v rows are kept per block: the f32
+  // projection output is a scratch shared by all blocks and the f32 attention output is gone
+  float* qkv_shared = tc_attention ? b.take<float>(T * nqkv) : nullptr;
   const int nact = c.checkpoint_blocks ? 1 : L;
   std::vector<BlockActs> acts(nact);
   for (int i = 0; i < nact; ++i) {
@@ -160,9 +168,9 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
     memset(&a, 0, sizeof(a));
     if (fused) {
       a.h1_16 = b.take<__half>(T * c.hidden);
-      a.qkv = b.take<float>(T * nqkv);
+      a.qkv = tc_attention ? qkv_shared : b.take<float>(T * nqkv);
       a.qkv16 = b.take<__half>(T * nqkv);
-      a.attn = b.take<float>(T * m->nq);
+      a.attn = tc_attention ? nullptr : b.take<float>(T * m->nq);
       a.attn16 = b.take<__half>(T * m->nq);
       a.stats = b.take<float>((size_t)sequences * c.heads * seq_len * 2);
       a.x1 = b.take<float>(T * c.hidden);
@@ -210,11 +218,14 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   size_t cvt = std::max(T * ft_align_up(widest, 8), chunk * ft_align_up((size_t)c.vocab, 8));
   __half* hi = b.take<__half>(cvt);
   __half* lo = fused ? nullptr : b.take<__half>(cvt);
+  float* rope_table = fused ? b.take<float>((size_t)seq_len * c.head_dim) : nullptr;
   __half* hN16 = fused ? b.take<__half>(T * c.hidden) : nullptr;
   __half* xa16_head = fused ? b.take<__half>(T * RP) : nullptr;
   __half* g16 = fused ? b.take<__half>(T * RP) : nullptr;
   if (!dry) {
     m->plan_fused = fused; m->hN16 = hN16; m->xa16_head = xa16_head; m->g16 = g16;
+    m->rope_table = rope_table; m->table_seq = 0;
+    m->tc_attention = tc_attention;
     m->T = (int)T; m->sequences = sequences; m->seq_len = seq_len; m->head_chunk = (int)chunk;
     m->x = x; m->acts = acts; m->hN = hN; m->xa_head = xa_head; m->logit_chunk = logit_chunk;
     m->dx = dx; m->dh = dh; m->dqkv = dqkv; m->dattn = dattn; m->dgu = dgu; m->df = df; m->g = g;
@@ -469,35 +480,47 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
 // Adapter gradients (added to the flat buffer) and dX (=|+ residual) = dY W^T + G A^T.
 // dY is rounded to f16 after a power-of-two scale S chosen from its largest magnitude; S is
 // carried through G and removed by the epilogues (1/S is a device scalar).
+// When dY16 is given, dY has already been converted (pitch lddy, scale in scales16).  With
+// amax_on_dx the dX product also reports its largest magnitude for the conversion that follows.
 int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const float* dY,
                      long long lddy, const __half* xa16, float* dX, long long lddx,
-                     const float* residual, long long ldr, int T) {
+                     const float* residual, long long ldr, int T, const __half* dY16 = nullptr,
+                     const float* scales16 = nullptr, bool amax_on_dx = false) {
   FtContext* ctx = m->ctx;
   const int r = m->cfg.lora_rank;
-  const long long np = (long long)ft_align_up((size_t)g.n, 8);
-  const float* scales = nullptr;
-  FT_TRY(ft_to_f16(ctx, dY, lddy, m->cvt_hi, nullptr, np, T, g.n, true, &scales, 8));
+  long long np = (long long)ft_align_up((size_t)g.n, 8);
+  const float* scales = scales16;
+  if (dY16) {
+    np = lddy;
+  } else {
+    FT_TRY(ft_to_f16(ctx, dY, lddy, m->cvt_hi, nullptr, np, T, g.n, true, &scales, 8));
+    dY16 = m->cvt_hi;
+  }
   const float* inv_s = scales + 1;
   if (g.R > 0) {
     FtGemmArgs a;   // G16 = (alpha/r) * (S dY) . B^T
-    a.a = m->cvt_hi; a.lda = np; a.b = g.b_bd16; a.ldb = g.n;
+    a.a = dY16; a.lda = np; a.b = g.b_bd16; a.ldb = g.n;
     a.M = T; a.N = RP; a.K = g.n;
     a.c16 = m->g16; a.ldc16 = RP; a.alpha = m->scale;
     FT_TRY(ft_gemm_tc_ex(ctx, a));
   }
   if (dX) {
     FtGemmArgs a;
-    a.a = m->cvt_hi; a.lda = np; a.b = g.w_kn; a.ldb = g.n;
+    a.a = dY16; a.lda = np; a.b = g.w_kn; a.ldb = g.n;
     a.M = T; a.N = g.in; a.K = g.n;
     if (g.R > 0) { a.a2 = m->g16; a.lda2 = RP; a.b2 = g.a_cat16; a.ldb2 = RP; a.K2 = RP; }
     a.c = dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
+    if (amax_on_dx) {
+      FT_TRY(ft_amax_arm(ctx));
+      a.want_amax = true;
+    }
     FT_TRY(ft_gemm_tc_ex(ctx, a));
   }
   if (g.R > 0) {
     float* slabs = nullptr;
     int ns = 0;
     // dB^T [n, 64] = (S dY)^T . xa16, reduced over tokens
-    FT_TRY(ft_gemm_tc_kouter(ctx, m->cvt_hi, np, xa16, RP, g.n, RP, T, &slabs, &ns));
+    FT_TRY(ft_gemm_tc_kouter(ctx, dY16, np, xa16, RP, g.n, RP, T, &slabs, &ns));
     for (int j = 0; j < g.nlin; ++j) {
       const Linear& l = *g.lin[j];
       if (!l.lora) continue;
@@ -549,17 +572,15 @@ int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, 
   const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
   FT_TRY(ft_k_rms_norm16(ctx, x_in, ly.norm1, nullptr, a.h1_16, T, h, c.eps));
   FT_TRY(linear_fwd_fused(m, ly.qkv, a.h1_16, a.qkv, nqkv, a.xa16_qkv, nullptr, 0, T));
-  FT_TRY(ft_k_rope(ctx, a.qkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, false));
-  FT_TRY(ft_k_rope(ctx, a.qkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, false));
-  // attention on the tensor cores when the head size allows, else the exact kernel
-  int ar = FT_ERR_UNSUPPORTED;
-  if (c.head_dim == 64 && (nqkv % 8) == 0) {
-    FT_TRY(ft_to_f16(ctx, a.qkv, nqkv, a.qkv16, nullptr, nqkv, T, nqkv, false, nullptr));
-    ar = ft_attention_fwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, a.attn, nq, a.stats,
-                             m->sequences, m->seq_len, c.heads, c.kv_heads, c.head_dim);
-    if (ar != FT_OK && ar != FT_ERR_UNSUPPORTED) return ar;
-  }
-  if (ar == FT_ERR_UNSUPPORTED) {
+  if (m->tc_attention) {
+    // RoPE (from the table) and the f16 rounding in one pass; attention on the tensor cores
+    FT_TRY(ft_k_rope_to_f16(ctx, a.qkv, a.qkv16, nqkv, T, nq, nkv, m->seq_len, m->rope_table, false,
+                            nullptr));
+    FT_TRY(ft_attention_fwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, nullptr, 0, a.stats,
+                               m->sequences, m->seq_len, c.heads, c.kv_heads, c.head_dim));
+  } else {
+    FT_TRY(ft_k_rope(ctx, a.qkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, false));
+    FT_TRY(ft_k_rope(ctx, a.qkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, false));
     FT_TRY(attention_launch(m, a, false));
     FT_TRY(ft_to_f16(ctx, a.attn, nq, a.attn16, nullptr, nq, T, nq, false, nullptr));
   }
@@ -576,31 +597,46 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   FtContext* ctx = m->ctx;
   const FtModelConfig& c = m->cfg;
   Layer& ly = m->layers[l];
-  const int T = m->T, h = c.hidden, nq = m->nq, nqkv = nq + 2 * m->nkv, F = c.ffn;
+  const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
+  // On entry an armed amax of m->dx is pending (left by the norm backward that produced it).
   FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, m->dx, h, a.xa16_down, m->df, F, nullptr, 0, T));
+  FT_TRY(ft_amax_arm(ctx));
   FT_TRY(ft_k_silu_gate_bwd(ctx, a.gu, 2 * F, a.gu + F, 2 * F, m->df, F, m->dgu, 2 * F,
                             m->dgu + F, 2 * F, T, F));
   FT_TRY(linear_bwd_fused(m, ly.gu, a.h2_16, m->dgu, 2 * F, a.xa16_gu, m->dh, h, nullptr, 0, T));
+  FT_TRY(ft_amax_arm(ctx));
   FT_TRY(ft_k_rms_norm_bwd(ctx, a.x1, ly.norm2, m->dh, m->dx, nullptr, T, h, c.eps, true));
-  FT_TRY(linear_bwd_fused(m, ly.o, a.attn16, m->dx, h, a.xa16_o, m->dattn, nq, nullptr, 0, T));
-  int ar = FT_ERR_UNSUPPORTED;
-  if (c.head_dim == 64 && (nqkv % 8) == 0) {
-    // the output gradient goes to f16 after a power-of-two scale, undone by the kernels
+  const bool need_dx = l > 0;
+  if (m->tc_attention) {
+    // the o projection's input gradient reports its amax; attention consumes it as f16
+    FT_TRY(linear_bwd_fused(m, ly.o, a.attn16, m->dx, h, a.xa16_o, m->dattn, nq, nullptr, 0, T,
+                            nullptr, nullptr, true));
     const float* scales = nullptr;
     FT_TRY(ft_to_f16(ctx, m->dattn, nq, m->cvt_hi, nullptr, nq, T, nq, true, &scales, 8));
-    ar = ft_attention_bwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + m->nkv, a.attn16, nq, m->cvt_hi, nq,
-                             m->dqkv, nqkv, m->dqkv + nq, m->dqkv + nq + m->nkv, nqkv, a.stats,
-                             scales + 1, m->sequences, m->seq_len, c.heads, c.kv_heads, c.head_dim);
-    if (ar != FT_OK && ar != FT_ERR_UNSUPPORTED) return ar;
+    FT_TRY(ft_amax_arm(ctx));
+    FT_TRY(ft_attention_bwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, m->cvt_hi, nq,
+                               m->dqkv, nqkv, m->dqkv + nq, m->dqkv + nq + nkv, nqkv, a.stats,
+                               scales + 1, m->sequences, m->seq_len, c.heads, c.kv_heads,
+                               c.head_dim));
+    // inverse RoPE + f16 rounding in one pass; a rotation grows a component by at most sqrt(2),
+    // hence the target exponent one below the usual one
+    FT_TRY(ft_scales_from_amax_or_pass(ctx, m->dqkv, nqkv, T, nqkv, 7, &scales));
+    FT_TRY(ft_k_rope_to_f16(ctx, m->dqkv, m->cvt_hi, nqkv, T, nq, nkv, m->seq_len, m->rope_table, true,
+                            scales));
+    FT_TRY(linear_bwd_fused(m, ly.qkv, a.h1_16, nullptr, nqkv, a.xa16_qkv, need_dx ? m->dh : nullptr,
+                            h, nullptr, 0, T, m->cvt_hi, scales));
+  } else {
+    FT_TRY(linear_bwd_fused(m, ly.o, a.attn16, m->dx, h, a.xa16_o, m->dattn, nq, nullptr, 0, T));
+    FT_TRY(attention_launch(m, a, true));
+    FT_TRY(ft_k_rope(ctx, m->dqkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, true));
+    FT_TRY(ft_k_rope(ctx, m->dqkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, true));
+    FT_TRY(linear_bwd_fused(m, ly.qkv, a.h1_16, m->dqkv, nqkv, a.xa16_qkv, need_dx ? m->dh : nullptr,
+                            h, nullptr, 0, T));
   }
-  if (ar == FT_ERR_UNSUPPORTED) FT_TRY(attention_launch(m, a, true));
-  FT_TRY(ft_k_rope(ctx, m->dqkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, true));
-  FT_TRY(ft_k_rope(ctx, m->dqkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, true));
-  const bool need_dx = l > 0;
-  FT_TRY(linear_bwd_fused(m, ly.qkv, a.h1_16, m->dqkv, nqkv, a.xa16_qkv, need_dx ? m->dh : nullptr,
-                          h, nullptr, 0, T));
-  if (need_dx)
+  if (need_dx) {
+    FT_TRY(ft_amax_arm(ctx));
     FT_TRY(ft_k_rms_norm_bwd(ctx, x_in, ly.norm1, m->dh, m->dx, nullptr, T, h, c.eps, true));
+  }
   return FT_OK;
 }
 
@@ -888,6 +924,10 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
   const int T = m->T, h = c.hidden, L = c.layers, V = c.vocab;
   const bool ckpt = c.checkpoint_blocks != 0;
   if (fused && m->packs_dirty) FT_TRY(pack_all(m));
+  if (fused && m->tc_attention && m->table_seq != seq_len) {
+    FT_TRY(ft_k_rope_table(ctx, m->rope_table, seq_len, c.head_dim, c.theta));
+    m->table_seq = seq_len;
+  }
 
   // ---- forward
   FT_TRY(ft_k_embedding(ctx, m->embed, ids, m->x[0], T, V, h));
@@ -909,6 +949,7 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
       const __half* X16 = m->hN16 + (size_t)r0 * h;
       __half* xa16 = m->xa16_head + (size_t)r0 * RP;
       FT_TRY(linear_fwd_fused(m, m->head, X16, z, V, xa16, nullptr, 0, rows));
+      FT_TRY(ft_amax_arm(ctx));   // the loss kernel reports the gradient's amax
       FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, m->logit_chunk, row_loss + r0, rows,
                             V, seed));
       FT_TRY(linear_bwd_fused(m, m->head, X16, m->logit_chunk, V, xa16, m->dh + (size_t)r0 * h, h,
@@ -923,6 +964,7 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
                         false));
     }
   }
+  if (fused) FT_TRY(ft_amax_arm(ctx));   // consumed by the last block's first conversion
   FT_TRY(ft_k_rms_norm_bwd(ctx, m->x[L], m->final_norm, m->dh, m->dx, nullptr, T, h, c.eps, false));
 
   // ---- blocks, last to first
