@@ -46,6 +46,9 @@ def parse_args():
                          "the line then says so in config and is not the headline)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: device-timed loop only")
     ap.add_argument("--cpu-sample-tokens", type=int, default=0)
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="time every launch of one extra step by kernel name (CUDA events) and "
+                         "add the table to the JSON line as kernel_ms")
     return ap.parse_args()
 
 
@@ -318,6 +321,15 @@ def run_cuda(args):
     gemm_ms, gemm_flops, gemm_launches = ctx.profile_read()
     ctx.profile(False)
 
+    kernel_ms = None
+    if args.kernel_times:
+        ctx.profile(2)
+        resident_step()
+        rep = ctx.profile_report()
+        ctx.profile(0)
+        kernel_ms = {k: {"launches": n, "ms": round(ms, 3)}
+                     for k, (n, ms) in sorted(rep.items(), key=lambda kv: -kv[1][1])}
+
     # ---- end to end through the trainer with host inputs ---------------------------------------
     def e2e_step():
         trainer.train_arrays(ids, tg, mk)
@@ -368,6 +380,8 @@ def run_cuda(args):
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    if kernel_ms is not None:
+        out["kernel_ms"] = kernel_ms
     if want_cpu:
         sample = args.cpu_sample_tokens or default_cpu_sample(w)
         tps, cores, sec = cpu_step_tokens_per_s(w, weights_cpu, adapters_cpu, sample)

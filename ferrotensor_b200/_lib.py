@@ -68,8 +68,10 @@ PROTOTYPES = {
     "ft_ctx_status": [_P, C.POINTER(_I)],
     "ft_ctx_debug_words": [_P, C.POINTER(_I)],
     "ft_ctx_profile": [_P, _I],
+    "ft_ctx_profile_report": [_P, C.c_char_p, _Z],
     "ft_ctx_profile_read": [_P, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_uint64)],
     "ft_ctx_set_gemm_mode": [_P, _I],
+    "ft_ctx_set_gemm_tile_m": [_P, _I],
     "ft_ctx_launch_count": [_P, C.POINTER(C.c_uint64)],
     "ft_tensor_alloc": [_P, _Z, C.POINTER(_P)],
     "ft_tensor_free": [_P, _P],

@@ -60,6 +60,7 @@ extern "C" int ft_ctx_create(int device, void* stream, FtContext** out) {
   memset(ctx->status_host, 0, sizeof(int) * 16);
   const char* dbg = getenv("FT_GEMM_DEBUG");
   ctx->debug_markers = dbg && dbg[0] == '1';
+  if (const char* tm = getenv("FT_GEMM_TILE_M")) ctx->tile_m_override = atoi(tm);
   FT_CUDA(cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
   FT_CUDA(cudaMalloc((void**)&ctx->scale_buf, 8 * sizeof(float)));
   {
@@ -115,9 +116,56 @@ extern "C" int ft_ctx_debug_words(FtContext* ctx, int* out16) {
   return FT_OK;
 }
 
+void ft_prof_begin(FtContext* ctx, const char* name) {
+  FtContext::ProfRec r;
+  r.name = name;
+  cudaEvent_t* ev[2] = {&r.e0, &r.e1};
+  for (auto* e : ev) {
+    if (ctx->prof_pool.empty()) {
+      cudaEventCreate(e);
+    } else {
+      *e = ctx->prof_pool.back();
+      ctx->prof_pool.pop_back();
+    }
+  }
+  cudaEventRecord(r.e0, ctx->stream);
+  ctx->prof_recs.push_back(r);
+}
+
+void ft_prof_end(FtContext* ctx) { cudaEventRecord(ctx->prof_recs.back().e1, ctx->stream); }
+
 extern "C" int ft_ctx_profile(FtContext* ctx, int enable) {
   FT_REQUIRE(ctx, "ft_ctx_profile: ctx is NULL");
-  ctx->profile = enable != 0;
+  ctx->profile = enable == 1;
+  ctx->profile_all = enable == 2;
+  return FT_OK;
+}
+
+// Text table "kernel launches total_ms" of everything launched while ft_ctx_profile(ctx, 2)
+// was on; waits for the stream and resets the records.
+extern "C" int ft_ctx_profile_report(FtContext* ctx, char* buf, size_t cap) {
+  FT_REQUIRE(ctx && buf && cap > 0, "ft_ctx_profile_report: bad argument");
+  FT_CUDA(cudaStreamSynchronize(ctx->stream));
+  struct Agg { const char* name; int n; double ms; };
+  std::vector<Agg> agg;
+  for (auto& r : ctx->prof_recs) {
+    float t = 0.f;
+    cudaEventElapsedTime(&t, r.e0, r.e1);
+    bool found = false;
+    for (auto& a : agg)
+      if (!strcmp(a.name, r.name)) { a.n++; a.ms += t; found = true; break; }
+    if (!found) agg.push_back({r.name, 1, (double)t});
+    ctx->prof_pool.push_back(r.e0);
+    ctx->prof_pool.push_back(r.e1);
+  }
+  ctx->prof_recs.clear();
+  size_t off = 0;
+  buf[0] = 0;
+  for (auto& a : agg) {
+    int w = snprintf(buf + off, cap - off, "%s %d %.4f\n", a.name, a.n, a.ms);
+    if (w < 0 || (size_t)w >= cap - off) break;
+    off += (size_t)w;
+  }
   return FT_OK;
 }
 
@@ -145,6 +193,13 @@ extern "C" int ft_ctx_set_gemm_mode(FtContext* ctx, int mode) {
   FT_REQUIRE(mode == FT_GEMM_F32 || mode == FT_GEMM_F16 || mode == FT_GEMM_F16X2,
              "ft_ctx_set_gemm_mode: unknown mode %d", mode);
   ctx->gemm_mode = mode;
+  return FT_OK;
+}
+
+extern "C" int ft_ctx_set_gemm_tile_m(FtContext* ctx, int rows) {
+  FT_REQUIRE(ctx, "ft_ctx_set_gemm_tile_m: ctx is NULL");
+  FT_REQUIRE(rows == 0 || rows == 128 || rows == 256, "ft_ctx_set_gemm_tile_m: 0, 128 or 256");
+  ctx->tile_m_override = rows;
   return FT_OK;
 }
 

@@ -35,12 +35,18 @@ struct FtContext {
   // uses it instead of making its own pass over the tensor.
   int* amax_out = nullptr;
   bool amax_ready = false;
+  int tile_m_override = 0;   // FT_GEMM_TILE_M: 128 or 256 forces the GEMM tile height
   // optional timing of the tensor-core GEMM launches (CUDA events on the launch stream)
   bool profile = false;
   std::vector<cudaEvent_t> prof_events;  // start/stop pairs, reused
   size_t prof_used = 0;                  // events handed out since the last read
   double prof_flops = 0.0;
   uint64_t prof_launches = 0;
+  // optional timing of EVERY launch by kernel name (ft_ctx_profile(ctx, 2))
+  bool profile_all = false;
+  struct ProfRec { const char* name; cudaEvent_t e0, e1; };
+  std::vector<ProfRec> prof_recs;
+  std::vector<cudaEvent_t> prof_pool;
   // cuTensorMapEncodeTiled, resolved through the runtime (no link against libcuda)
   void* encode_tiled = nullptr;
 };
@@ -68,10 +74,15 @@ int ft_cuda_fail(cudaError_t e, const char* what, const char* file, int line);
     if (_r != FT_OK) return _r;  \
   } while (0)
 
+void ft_prof_begin(FtContext* ctx, const char* name);
+void ft_prof_end(FtContext* ctx);
+
 // Launch on the context's stream, count the launch and surface launch errors.
 #define FT_LAUNCH(ctx, kernel, grid, block, smem, ...)                          \
   do {                                                                          \
+    if ((ctx)->profile_all) ft_prof_begin((ctx), #kernel);                      \
     kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__);            \
+    if ((ctx)->profile_all) ft_prof_end((ctx));                                 \
     (ctx)->launches++;                                                          \
     cudaError_t _e = cudaPeekAtLastError();                                     \
     if (_e != cudaSuccess) return ft_cuda_fail(_e, #kernel, __FILE__, __LINE__); \

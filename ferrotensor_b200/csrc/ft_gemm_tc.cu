@@ -17,12 +17,16 @@ namespace {
 
 using namespace ft_tc;
 
-template <int BN, int STAGES>
+// MH = number of 128-row halves of the output tile (1: 128 x BN with two accumulators so the
+// epilogue overlaps the next tile; 2: 256 x 256 with one accumulator pair - a third less
+// operand traffic from L2 per FLOP, which is what bounds the 128-row form).
+template <int BN, int STAGES, int MH = 1>
 struct SmemLayout {
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_BYTES = MH * BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;     // 4 epilogue warps x 4 KiB staging
+  static constexpr int BAR_OFFSET = EPI_OFFSET + 4 * 4096;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack to align the base to 1024 bytes
@@ -62,13 +66,15 @@ struct Epilogue {
 // KOUTER = true :  C[M,N] = sum_t A[t,m] B[t,n], operands given as [T, M] and [T, N] (the
 //                  token-reduction products of the adapter gradients); BN = 64, the tile list
 //                  is (m tile, K split) and each split writes its own f32 slab of C.
-template <int BN, int STAGES, bool KOUTER>
+template <int BN, int STAGES, bool KOUTER, int MH = 1>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
           const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
           Epilogue ep, int M, int N, int K, int K2, int splits, uint32_t idesc, int* status,
           int* dbg) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, MH>;
+  static_assert(MH == 1 || (BN == 256 && !KOUTER), "the 256-row tile exists for BN = 256 only");
+  constexpr int TM = MH * BM;  // rows of an output tile
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -82,13 +88,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_m = (M + TM - 1) / TM;
   const int tiles_n = KOUTER ? splits : (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int kb_main = (K + BK - 1) / BK;
   const int kb_total = kb_main + (KOUTER ? 0 : (K2 + BK - 1) / BK);
   const int kb_per_split = KOUTER ? (kb_main + splits - 1) / splits : kb_total;
-  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators; a power of two >= 32
+  // MH = 1: two accumulators of BN columns (epilogue of one overlaps the products of the
+  // other); MH = 2: one pair of 256-column accumulators, all of tensor memory
+  constexpr uint32_t TMEM_COLS = 2 * BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -121,7 +129,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, nt = tile / tiles_m;
+        const int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
         const int kb0 = KOUTER ? nt * kb_per_split : 0;
         const int kb1 = KOUTER ? min(kb_main, kb0 + kb_per_split) : kb_total;
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -159,7 +167,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         const int nt = tile / tiles_m;
         const int kb0 = KOUTER ? nt * kb_per_split : 0;
         const int kb1 = KOUTER ? min(kb_main, kb0 + kb_per_split) : kb_total;
-        const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+        const uint32_t buf = MH == 1 ? (local & 1) : 0;
+        const uint32_t acc_phase = MH == 1 ? ((local >> 1) & 1) : (local & 1);
         FT_MARK(8, 30);
         if (!mbar_wait(bar_tempty + buf * 8, acc_phase ^ 1, abort_flag, status, 2)) break;
         tc_fence_after();
@@ -187,6 +196,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
               // 16-byte units of the start-address field
               tc_mma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
                          (kb > kb0 || k > 0) ? 1u : 0u);
+              if constexpr (MH == 2)  // rows 128..255 of the tile: 16 KiB further in the A stage
+                tc_mma_f16(d_tmem + BN, da + (uint64_t)(1024 + k * 2), db + (uint64_t)(k * 2), idesc,
+                           (kb > kb0 || k > 0) ? 1u : 0u);
               FT_SETTLE();
               FT_MARK(8, 33 + k);
             }
@@ -205,89 +217,99 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;               // TMEM lanes [32*quad, 32*quad+32)
     int local = 0;
+    uint8_t* stage_base = gbase + L::EPI_OFFSET + (warp - 2) * 4096;   // 32 x 128 bytes per warp
     const bool vec_c = ep.c && ((ep.ldc & 3) == 0) && ((((uintptr_t)ep.c) & 15) == 0);
     const bool vec_r = !ep.residual || (((ep.ldr & 3) == 0) && ((((uintptr_t)ep.residual) & 15) == 0));
-    const bool vec_h = ep.c16 && ((ep.ldc16 & 7) == 0) && ((((uintptr_t)ep.c16) & 15) == 0);
+    const bool vec_h = ep.c16 && ((ep.ldc16 & 3) == 0) && ((((uintptr_t)ep.c16) & 7) == 0);
     const float alpha = (ep.alpha_ptr ? *ep.alpha_ptr : 1.0f) * ep.alpha;
     float amax_seen = 0.f;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-      const int m0 = (tile % tiles_m) * BM, nt = tile / tiles_m;
+      const int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
       const int n0 = KOUTER ? 0 : nt * BN;
-      const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+      const uint32_t buf = MH == 1 ? (local & 1) : 0;
+      const uint32_t acc_phase = MH == 1 ? ((local >> 1) & 1) : (local & 1);
       if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 4)) break;
       tc_fence_after();
       if (warp == 2 && lane == 0) FT_MARK(9, 41);
-      const int row = m0 + quad * 32 + lane;
       // a K split of the token-reduction product writes its own slab
       float* cbase = ep.c ? ep.c + (KOUTER ? (long long)nt * M * ep.ldc : 0) : nullptr;
 #pragma unroll 1
-      for (int cb = 0; cb < BN / 32; ++cb) {
+      for (int cbh = 0; cbh < MH * (BN / 32); ++cbh) {
+        const int half = cbh / (BN / 32), cb = cbh % (BN / 32);
+        const int row = m0 + half * BM + quad * 32 + lane;
         uint32_t r[32];
-        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + cb * 32, r);
+        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (buf + half) * BN + cb * 32, r);
         tc_wait_ld();
         const int col0 = n0 + cb * 32;
-        if (row < M && col0 < N) {
-          const bool full = col0 + 32 <= N;
-          float v[32];
+        // Transpose the 32 x 32 chunk through a swizzled staging tile so that global traffic
+        // is coalesced: in tensor memory a thread owns a ROW (32 consecutive floats of one
+        // output row); after staging, 8 lanes cover one row's 128 bytes and a warp
+        // instruction touches 4 rows instead of 32.
+        {
+          uint8_t* st = stage_base + lane * 128;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(r[j]);
-          if (ep.bias) {
+          for (int j = 0; j < 8; ++j)
+            *(float4*)(st + ((j ^ (lane & 7)) << 4)) =
+                make_float4(alpha * __uint_as_float(r[4 * j]), alpha * __uint_as_float(r[4 * j + 1]),
+                            alpha * __uint_as_float(r[4 * j + 2]), alpha * __uint_as_float(r[4 * j + 3]));
+        }
+        __syncwarp();
+        const int row_base = m0 + half * BM + quad * 32;
+        if (row_base < M && col0 < N) {
+          const int j = lane & 7, gcol = col0 + 4 * j;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full || col0 + j < N) v[j] += ep.bias[col0 + j];
-          }
-          if (ep.residual) {
-            const float* rr = ep.residual + (long long)row * ep.ldr + col0;
-            if (full && vec_r) {
+          for (int t = 0; t < 8; ++t) {
+            const int rr = 4 * t + (lane >> 3);
+            const int grow = row_base + rr;
+            float4 v4 = *(const float4*)(stage_base + rr * 128 + ((j ^ (rr & 7)) << 4));
+            if (grow >= M || gcol >= N) continue;
+            float v[4] = {v4.x, v4.y, v4.z, v4.w};
+            const bool full = gcol + 4 <= N;
+            if (ep.bias) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 o = ((const float4*)rr)[j];
-                v[4 * j] += o.x; v[4 * j + 1] += o.y; v[4 * j + 2] += o.z; v[4 * j + 3] += o.w;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < N) v[j] += rr[j];
+              for (int e = 0; e < 4; ++e)
+                if (full || gcol + e < N) v[e] += ep.bias[gcol + e];
             }
-          }
-          if (ep.amax_slot) {
+            if (ep.residual) {
+              const float* rp = ep.residual + (long long)grow * ep.ldr + gcol;
+              if (full && vec_r) {
+                float4 o = *(const float4*)rp;
+                v[0] += o.x; v[1] += o.y; v[2] += o.z; v[3] += o.w;
+              } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (full || col0 + j < N) amax_seen = fmaxf(amax_seen, fabsf(v[j]));
-          }
-          if (cbase) {
-            float* crow = cbase + (long long)row * ep.ldc + col0;
-            if (full && vec_c) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                ((float4*)crow)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < N) crow[j] = v[j];
-            }
-          }
-          if (ep.c16) {
-            __half* hrow = ep.c16 + (long long)row * ep.ldc16 + col0;
-            if (full && vec_h) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 pk;
-                __half2 h0 = __floats2half2_rn(v[8 * j], v[8 * j + 1]);
-                __half2 h1 = __floats2half2_rn(v[8 * j + 2], v[8 * j + 3]);
-                __half2 h2 = __floats2half2_rn(v[8 * j + 4], v[8 * j + 5]);
-                __half2 h3 = __floats2half2_rn(v[8 * j + 6], v[8 * j + 7]);
-                pk.x = *(uint32_t*)&h0; pk.y = *(uint32_t*)&h1;
-                pk.z = *(uint32_t*)&h2; pk.w = *(uint32_t*)&h3;
-                ((uint4*)hrow)[j] = pk;
+                for (int e = 0; e < 4; ++e)
+                  if (gcol + e < N) v[e] += rp[e];
               }
-            } else {
+            }
+            if (ep.amax_slot) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < N) hrow[j] = __float2half_rn(v[j]);
+              for (int e = 0; e < 4; ++e)
+                if (full || gcol + e < N) amax_seen = fmaxf(amax_seen, fabsf(v[e]));
+            }
+            if (cbase) {
+              float* cp = cbase + (long long)grow * ep.ldc + gcol;
+              if (full && vec_c) {
+                *(float4*)cp = make_float4(v[0], v[1], v[2], v[3]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (gcol + e < N) cp[e] = v[e];
+              }
+            }
+            if (ep.c16) {
+              __half* hp = ep.c16 + (long long)grow * ep.ldc16 + gcol;
+              if (full && vec_h) {
+                __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                *(uint2*)hp = make_uint2(*(uint32_t*)&h0, *(uint32_t*)&h1);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (gcol + e < N) hp[e] = __float2half_rn(v[e]);
+              }
             }
           }
         }
+        __syncwarp();   // the staging tile is reused by the next chunk
       }
       tc_fence_before();
       __syncwarp();
@@ -424,18 +446,18 @@ __global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __
   }
 }
 
-template <int BN, int STAGES, bool KOUTER>
+template <int BN, int STAGES, bool KOUTER, int MH = 1>
 int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2,
               const CUtensorMap& mb2, const Epilogue& ep, int M, int N, int K, int K2, int splits,
               uint32_t idesc, double flops) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, MH>;
   static bool configured = false;
   if (!configured) {
-    FT_CUDA(cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, KOUTER>,
+    FT_CUDA(cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, KOUTER, MH>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
     configured = true;
   }
-  int tiles = ft_cdiv(M, BM) * (KOUTER ? splits : ft_cdiv(N, BN));
+  int tiles = ft_cdiv(M, MH * BM) * (KOUTER ? splits : ft_cdiv(N, BN));
   int grid = std::min(tiles, ctx->sm_count);
   int* dbg = ctx->debug_markers ? ctx->status_dev : nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -449,8 +471,22 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
     e1 = ctx->prof_events[ctx->prof_used++];
     FT_CUDA(cudaEventRecord(e0, ctx->stream));
   }
-  FT_LAUNCH(ctx, (k_gemm_tc<BN, STAGES, KOUTER>), grid, GEMM_THREADS, L::DYN_BYTES, ma, mb, ma2, mb2,
-            ep, M, N, K, K2, splits, idesc, ctx->status_dev, dbg);
+  {
+    // by-name profiling: one name per instantiation
+    const char* nm = KOUTER ? "k_gemm_tc<64,token-reduction>"
+                            : (BN == 256 ? (MH == 2 ? "k_gemm_tc<256x256>" : "k_gemm_tc<128x256>")
+                                         : (BN == 128 ? "k_gemm_tc<128x128>" : "k_gemm_tc<128x64>"));
+    const bool pa = ctx->profile_all;
+    if (pa) ft_prof_begin(ctx, nm);
+    ctx->profile_all = false;
+    k_gemm_tc<BN, STAGES, KOUTER, MH><<<grid, GEMM_THREADS, L::DYN_BYTES, ctx->stream>>>(
+        ma, mb, ma2, mb2, ep, M, N, K, K2, splits, idesc, ctx->status_dev, dbg);
+    ctx->profile_all = pa;
+    if (pa) ft_prof_end(ctx);
+    ctx->launches++;
+    cudaError_t le = cudaPeekAtLastError();
+    if (le != cudaSuccess) return ft_cuda_fail(le, "k_gemm_tc", __FILE__, __LINE__);
+  }
   if (ctx->profile) {
     FT_CUDA(cudaEventRecord(e1, ctx->stream));
     ctx->prof_flops += flops;
@@ -514,12 +550,30 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   if (tail && (!tma_ok(g.a2, g.lda2, g.K2) || !tma_ok(g.b2, g.ldb2, g.K2))) return FT_ERR_UNSUPPORTED;
   CUtensorMap ma, mb, ma2, mb2;
   const int BN = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+  // 256-row tiles move a third less operand data per FLOP (the 128-row form is bound by L2
+  // bandwidth) but cannot overlap their epilogue and come in coarser waves: take them when
+  // the estimated time, waves x relative tile cost, is lower.  FT_GEMM_TILE_M=128|256 forces.
+  int MH = 1;
+  if (BN == 256 && g.M >= 256) {
+    const int sms = ctx->sm_count;
+    const long long t1 = (long long)ft_cdiv(g.M, 128) * ft_cdiv(g.N, 256);
+    const long long t2 = (long long)ft_cdiv(g.M, 256) * ft_cdiv(g.N, 256);
+    const double kk = (double)(g.K + g.K2);
+    // measured on B200, in units of one K element of a 128-row tile: a 128 x 256 tile costs
+    // K + 470, a 256 x 256 tile 1.63 K + 2470 (its epilogue is not hidden)
+    const double cost1 = (double)((t1 + sms - 1) / sms) * (kk + 470.0);
+    const double cost2 = (double)((t2 + sms - 1) / sms) * (1.63 * kk + 2470.0);
+    MH = cost2 < cost1 ? 2 : 1;
+    if (ctx->tile_m_override == 128) MH = 1;
+    if (ctx->tile_m_override == 256) MH = 2;
+  }
   const CUtensorMapDataType dt = g.ab_type == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  FT_TRY(make_map(ctx, &ma, g.a, dt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, BM));
+  const uint32_t a_rows = (uint32_t)(MH * BM);
+  FT_TRY(make_map(ctx, &ma, g.a, dt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, a_rows));
   FT_TRY(make_map(ctx, &mb, g.b, dt, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)BN));
   if (tail) {
-    FT_TRY(make_map(ctx, &ma2, g.a2, dt, (uint64_t)g.K2, (uint64_t)g.M, (uint64_t)g.lda2, BK, BM));
+    FT_TRY(make_map(ctx, &ma2, g.a2, dt, (uint64_t)g.K2, (uint64_t)g.M, (uint64_t)g.lda2, BK, a_rows));
     FT_TRY(make_map(ctx, &mb2, g.b2, dt, (uint64_t)g.K2, (uint64_t)g.N, (uint64_t)g.ldb2, BK,
                     (uint32_t)BN));
   } else {
@@ -539,6 +593,8 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
     ctx->amax_ready = true;
   }
   const double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
+  if (MH == 2)
+    return launch_tc<256, 3, false, 2>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
   switch (BN) {
     case 256: return launch_tc<256, 4, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
     case 128: return launch_tc<128, 6, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);

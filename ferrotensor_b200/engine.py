@@ -73,9 +73,20 @@ class CudaContext:
         call("ft_ctx_set_gemm_mode", self.handle, int(mode))
         self.gemm_mode = GemmMode(int(mode))
 
-    def profile(self, enable: bool) -> None:
-        """Bracket every tensor-core GEMM launch with CUDA events (see `profile_read`)."""
-        call("ft_ctx_profile", self.handle, 1 if enable else 0)
+    def profile(self, enable) -> None:
+        """1/True: bracket every tensor-core GEMM launch with CUDA events (`profile_read`);
+        2: every launch, by kernel name (`profile_report`); 0/False: off."""
+        call("ft_ctx_profile", self.handle, int(enable))
+
+    def profile_report(self):
+        """{kernel name: (launches, total ms)} since the last report (mode 2)."""
+        buf = C.create_string_buffer(1 << 16)
+        call("ft_ctx_profile_report", self.handle, buf, len(buf))
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, n, ms = line.rsplit(" ", 2)
+            out[name] = (int(n), float(ms))
+        return out
 
     def profile_read(self):
         """(kernel ms, algorithmic FLOPs, launches) of the GEMM launches since the last read."""

@@ -67,10 +67,16 @@ int ft_ctx_debug_words(FtContext* ctx, int* out16);
  * enabled every launch is bracketed by two events; ft_ctx_profile_read waits for the stream,
  * returns the summed kernel time, the algorithmic FLOPs (2 M N K per launch) and the launch
  * count since the previous read, and resets them. */
-int ft_ctx_profile(FtContext* ctx, int enable);
+int ft_ctx_profile(FtContext* ctx, int enable);   /* 0 off, 1 GEMM launches, 2 every launch by name */
+/* After ft_ctx_profile(ctx, 2): one line "kernel launches total_ms" per kernel name for all
+ * launches since the last report (CUDA events on the launch stream); waits for the stream. */
+int ft_ctx_profile_report(FtContext* ctx, char* buf, size_t cap);
 int ft_ctx_profile_read(FtContext* ctx, double* gemm_ms, double* gemm_flops,
                         uint64_t* gemm_launches);
 int ft_ctx_set_gemm_mode(FtContext* ctx, int mode);    /* FT_GEMM_*; default FT_GEMM_F32 */
+/* Tuning/diagnostics: force the tensor-core GEMM's output tile height (128 or 256 rows;
+ * 0 = choose per shape, the default; FT_GEMM_TILE_M in the environment sets the initial value). */
+int ft_ctx_set_gemm_tile_m(FtContext* ctx, int rows);
 int ft_ctx_launch_count(FtContext* ctx, uint64_t* kernels_launched);
 const char* ft_last_error(void);
 /* Lists, one name per line, every kernel family compiled into the library. */

@@ -323,3 +323,29 @@ def test_attention_backward_on_tensor_cores(cuda_ctx, eng, b, s, h, hkv):
     for name, g, e, a in zip(("dq", "dk", "dv"), got, exp, again):
         _close(g, e, 2e-3 * np.abs(e).max(), 1e-2, f"tc {name}")
         assert np.array_equal(g, a), f"{name}: two runs differ"
+
+
+# tcgen05 GEMM through ft_matmul_bt_f16b in F16 mode: activations with 8 significant bits times
+# f16 weights give exact products, so only f32 accumulation order separates the result from
+# the f64 product.  Both output tile heights, ragged M/N/K tails.
+@pytest.mark.parametrize("tile_m", [128, 256])
+@pytest.mark.parametrize("m,n,k", [(128, 64, 64), (256, 256, 128), (384, 320, 192), (1000, 1000, 520),
+                                   (2048, 768, 4096), (777, 2048, 264)])
+def test_tensor_core_gemm_shapes(cuda_ctx, eng, tile_m, m, n, k):
+    from ferrotensor_b200._lib import call
+    from ferrotensor_b200.engine import GemmMode, UnifiedTensor
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16).float()
+    b = (torch.randn(n, k, generator=g) * 0.1).to(torch.float16).float()
+    out = _empty(cuda_ctx, (m, n))
+    cuda_ctx.set_gemm_mode(GemmMode.F16)
+    call("ft_ctx_set_gemm_tile_m", cuda_ctx.handle, tile_m)
+    try:
+        eng.matmul_bt_f16b(cuda_ctx, _ut(cuda_ctx, a.numpy()),
+                           UnifiedTensor.from_f32_as_f16(cuda_ctx, b.numpy(), [n, k]), out)
+        got = out.to_vec(cuda_ctx)
+    finally:
+        call("ft_ctx_set_gemm_tile_m", cuda_ctx.handle, 0)
+        cuda_ctx.set_gemm_mode(GemmMode.F32)
+    exp = (a.double() @ b.double().T).numpy()
+    _close(got, exp, 1e-4 * max(1.0, np.abs(exp).max()), 1e-4, "tcgen05 gemm")
