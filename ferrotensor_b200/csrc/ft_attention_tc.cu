@@ -568,8 +568,8 @@ struct BwdKSmem {
   static constexpr int DO_OFF = Q_OFF + 2 * HALF_TILE;    // 2 stages of 64 q x 64
   static constexpr int PT_OFF = DO_OFF + 2 * HALF_TILE;   // 128 keys x 64 q, K-major
   static constexpr int DST_OFF = PT_OFF + TILE_BYTES;     // 128 keys x 64 q, K-major
-  static constexpr int ROW_OFF = DST_OFF + TILE_BYTES;    // 2 x 64 x {lse2, delta}
-  static constexpr int BAR_OFF = ROW_OFF + 2 * 64 * 2 * 4;
+  static constexpr int ROW_OFF = DST_OFF + TILE_BYTES;    // per warp: 64 x {delta, lse2}
+  static constexpr int BAR_OFF = ROW_OFF + 4 * 64 * 2 * 4;
   static constexpr int NBAR = 8;  // kv_full, qd_full[2], sp_full, sp_free, ds_full, acc_done, spare
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
@@ -708,9 +708,21 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
     for (int it = 0; ok && it < niter; ++it) {
       const int g = it / nqb, i = it % nqb, h = kvh * group + g;
       const int qs = k0 + i * 64;
-      // per-query {Delta, LSE} of this block: every key row reads the same 64 pairs (a
-      // broadcast load each), so they come straight from global memory
-      const float2* qinfo = (const float2*)(stats + 2 * (((size_t)b * heads + h) * seq));
+      // per-query {Delta, LSE in the log2 domain} of this block: every key row needs the same
+      // 64 pairs, so each warp stages its own copy in shared memory (no cross-warp barrier)
+      float2* qi_s = (float2*)(gbase + BwdKSmem::ROW_OFF) + warp * 64;
+      {
+        const float2* qinfo = (const float2*)(stats + 2 * (((size_t)b * heads + h) * seq));
+        __syncwarp();
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int col = lane + 32 * t;
+          float2 dl = qinfo[min(qs + col, seq - 1)];
+          dl.y *= 1.4426950408889634f;
+          qi_s[col] = dl;
+        }
+        __syncwarp();
+      }
       ok = mbar_wait(bar_spfull, it & 1, abort_flag, status, 61);
       if (!ok) break;
       tc_fence_after();
@@ -728,8 +740,8 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int col = cb * 32 + c + e, qq = qs + col;
-            const float2 dl = qinfo[min(qq, seq - 1)];   // x = Delta, y = LSE (natural log)
-            float p = ex2(fmaf(__uint_as_float(rs[c + e]), c2, -dl.y * 1.4426950408889634f));
+            const float2 dl = qi_s[col];   // x = Delta, y = LSE (log2 domain)
+            float p = ex2(fmaf(__uint_as_float(rs[c + e]), c2, -dl.y));
             if (!row_ok || (need_mask && (kj > qq || qq >= seq))) p = 0.f;
             pv[e] = p;
             dsv[e] = p * (__uint_as_float(rp[c + e]) - dl.x);

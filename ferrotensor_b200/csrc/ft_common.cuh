@@ -130,6 +130,11 @@ struct FtGemmArgs {
   const float* bias = nullptr;
   const float* residual = nullptr; long long ldr = 0;
   bool want_amax = false;   // contribute the output's largest magnitude to an armed amax slot
+  // SwiGLU backward in the epilogue (the product is d(silu(gate) * up), N = F): gu holds
+  // gate | up rows of pitch swiglu_ld, dgu receives d(gate) | d(up); nothing else is stored
+  const float* swiglu_gu = nullptr;
+  float* swiglu_dgu = nullptr;
+  long long swiglu_ld = 0;
 };
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g);
 // Token-reduction product P[M, N<=64] = sum_t A[t,m] B[t,n] (A [T,M], B [T,N], f16) as K-split
@@ -140,6 +145,11 @@ int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* 
 int ft_slab_reduce(FtContext* ctx, const float* slabs, int nslabs, int M, float* out, int m0,
                    int mcount, int n0, int ncount, long long som, long long son,
                    const float* alpha_ptr, float alpha, bool accumulate);
+int ft_slab_reduce_multi(FtContext* ctx, const float* slabs, int nslabs, int M, int count,
+                         float* const out[3], const int m0[3], const int mcount[3],
+                         const int n0[3], const int ncount[3], const long long som[3],
+                         const long long son[3], const float* alpha_ptr, float alpha,
+                         bool accumulate);
 // f32 [rows, cols] (ld) -> f16 [rows, ldo]; `lo` (optional) receives the rounding remainder
 // x 2^11.  auto_scale first multiplies by the power of two that brings the largest magnitude
 // to [2^11, 2^12) (gradients are far below f16's normal range otherwise); *scales_out then

@@ -60,6 +60,13 @@ struct Epilogue {
   const float* residual;
   long long ldr;
   int* amax_slot;   // when set, the largest |v| written is folded into it (atomicMax)
+  // SwiGLU backward fused into the product that yields d(f) (N = F): instead of storing v,
+  // with gate = gu[row, col], up = gu[row, F + col]:
+  //   dgu[row, col] = v * up * s (1 + gate (1 - s)),  dgu[row, F + col] = v * gate * s,  s = sigmoid(gate)
+  const float* swiglu_gu;
+  float* swiglu_dgu;
+  long long swiglu_ld;
+  int swiglu_f;
 };
 
 // KOUTER = false:  C[M,N] = A[M,K] . B[N,K]^T (+ A2[M,K2] . B2[N,K2]^T), operands K-contiguous.
@@ -281,6 +288,24 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                   if (gcol + e < N) v[e] += rp[e];
               }
             }
+            if (ep.swiglu_gu) {
+              // N = F is a multiple of 4 and the rows are 16-byte aligned (checked on the host)
+              const float* gp = ep.swiglu_gu + (long long)grow * ep.swiglu_ld + gcol;
+              const float4 g4 = *(const float4*)gp, u4 = *(const float4*)(gp + ep.swiglu_f);
+              const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
+              float dg[4], du[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float sg = 1.0f / (1.0f + expf(-gs[e]));
+                du[e] = v[e] * (gs[e] * sg);
+                dg[e] = v[e] * us[e] * (sg * (1.0f + gs[e] * (1.0f - sg)));
+                amax_seen = fmaxf(amax_seen, fmaxf(fabsf(du[e]), fabsf(dg[e])));
+              }
+              float* op = ep.swiglu_dgu + (long long)grow * ep.swiglu_ld + gcol;
+              *(float4*)op = make_float4(dg[0], dg[1], dg[2], dg[3]);
+              *(float4*)(op + ep.swiglu_f) = make_float4(du[0], du[1], du[2], du[3]);
+              continue;
+            }
             if (ep.amax_slot) {
 #pragma unroll
               for (int e = 0; e < 4; ++e)
@@ -342,6 +367,32 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   }
 }
 
+// Up to three sub-blocks of one slab set in a single launch (the adapters of a q|k|v group).
+struct SlabSegs {
+  int count;
+  float* out[3];
+  int m0[3], mcount[3], n0[3], ncount[3];
+  long long som[3], son[3];
+};
+__global__ void k_slab_reduce_multi(const float* __restrict__ part, int slabs, int M, int ldp,
+                                    SlabSegs sg, const float* __restrict__ alpha_ptr, float alpha,
+                                    int accumulate) {
+  const float a = (alpha_ptr ? *alpha_ptr : 1.0f) * alpha;
+  const int seg = blockIdx.y;
+  if (seg >= sg.count) return;
+  const int ncount = sg.ncount[seg];
+  size_t total = (size_t)sg.mcount[seg] * ncount;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    int m = (int)(i / ncount), n = (int)(i % ncount);
+    float acc = 0.f;
+    for (int s = 0; s < slabs; ++s)
+      acc += part[((size_t)s * M + (sg.m0[seg] + m)) * ldp + (sg.n0[seg] + n)];
+    float* o = sg.out[seg] + (long long)m * sg.som[seg] + (long long)n * sg.son[seg];
+    *o = accumulate ? *o + a * acc : a * acc;
+  }
+}
+
 // out[(m - m0) * som + (n - n0) * son] (=|+=) alpha * sum over slabs of part[s][m][n],
 // slabs added in index order.
 __global__ void k_slab_reduce(const float* __restrict__ part, int slabs, int M, int ldp,
@@ -388,6 +439,14 @@ __global__ void k_amax(const float* __restrict__ src, long long ld, int rows, in
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax_bits, __float_as_int(m));
 }
 
+__device__ __forceinline__ float scale_from_amax_bits(int bits, int target_exp) {
+  float amax = __int_as_float(bits);
+  if (!(amax > 0.f) || !isfinite(amax)) return 1.0f;
+  int e;
+  frexpf(amax, &e);           // amax = f * 2^e, f in [0.5, 1)
+  return ldexpf(1.0f, target_exp - e);
+}
+
 // scales[0] = S (power of two bringing the largest magnitude into [2^(t-1), 2^t), t =
 // target_exp), scales[1] = 1/S, scales[2] = 2^-11/S (the factor of the low half in split mode)
 __global__ void k_scale_from_amax(const int* __restrict__ amax_bits, float* __restrict__ scales,
@@ -410,8 +469,19 @@ __global__ void k_scale_from_amax(const int* __restrict__ amax_bits, float* __re
 // (TMA zero-fills beyond the tensor map's extent, so the rest of the pitch is never read).
 __global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __restrict__ hi,
                          __half* __restrict__ lo, long long ldo, int rows, int cols,
-                         const float* __restrict__ scales) {
-  const float S = scales ? scales[0] : 1.0f;
+                         const float* __restrict__ scales, const int* __restrict__ amax_bits,
+                         int target_exp, float* __restrict__ scales_out) {
+  // the scale is either given, or derived here from the amax a producer left behind (then
+  // one thread also publishes {S, 1/S, 2^-11/S} for the products that follow)
+  float S = scales ? scales[0] : 1.0f;
+  if (amax_bits) {
+    S = scale_from_amax_bits(*amax_bits, target_exp);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      scales_out[0] = S;
+      scales_out[1] = 1.0f / S;
+      scales_out[2] = ldexpf(1.0f / S, -11);
+    }
+  }
   long long per_row = (cols + 3) / 4;
   long long total = (long long)rows * per_row;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -528,14 +598,26 @@ int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half
               int target_exp) {
   FT_REQUIRE(ldo % 8 == 0 && ldo >= cols, "to_f16: output pitch %lld must be a multiple of 8", ldo);
   const float* scales = nullptr;
+  const int* amax_bits = nullptr;
   if (auto_scale) {
-    FT_TRY(ft_scales_from_amax_or_pass(ctx, src, ld, rows, cols, target_exp, &scales));
+    if (ctx->amax_ready && ctx->amax_out) {
+      // a producer already left the amax: the conversion derives the scale itself
+      amax_bits = (const int*)ctx->scale_buf;
+      ctx->amax_out = nullptr;
+      ctx->amax_ready = false;
+      if (scales_out) *scales_out = ctx->scale_buf + 4;
+    } else {
+      FT_TRY(ft_scales_from_amax_or_pass(ctx, src, ld, rows, cols, target_exp, &scales));
+      if (scales_out) *scales_out = scales;
+    }
+  } else if (scales_out) {
+    *scales_out = nullptr;
   }
-  if (scales_out) *scales_out = scales;
   long long total = (long long)rows * ((cols + 3) / 4);
   int grid = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256,
                                                              (long long)ctx->sm_count * 16));
-  FT_LAUNCH(ctx, k_to_f16, grid, 256, 0, src, ld, hi, lo, ldo, rows, cols, scales);
+  FT_LAUNCH(ctx, k_to_f16, grid, 256, 0, src, ld, hi, lo, ldo, rows, cols, scales, amax_bits,
+            target_exp, ctx->scale_buf + 4);
   return FT_OK;
 }
 
@@ -587,6 +669,13 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   ep.c = g.c; ep.ldc = g.ldc; ep.c16 = g.c16; ep.ldc16 = g.ldc16;
   ep.alpha_ptr = g.alpha_ptr; ep.alpha = g.alpha; ep.bias = g.bias;
   ep.residual = g.residual; ep.ldr = g.ldr;
+  ep.swiglu_gu = g.swiglu_gu; ep.swiglu_dgu = g.swiglu_dgu; ep.swiglu_ld = g.swiglu_ld;
+  ep.swiglu_f = g.N;
+  if (g.swiglu_gu) {
+    if ((g.N % 4) || (g.swiglu_ld % 4) || (((uintptr_t)g.swiglu_gu) & 15) ||
+        (((uintptr_t)g.swiglu_dgu) & 15) || g.bias || g.residual)
+      return FT_ERR_UNSUPPORTED;
+  }
   ep.amax_slot = nullptr;
   if (g.want_amax && ctx->amax_out) {
     ep.amax_slot = ctx->amax_out;
@@ -633,12 +722,37 @@ int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* 
   ep.c = (float*)s; ep.ldc = 64; ep.c16 = nullptr; ep.ldc16 = 0;
   ep.alpha_ptr = nullptr; ep.alpha = 1.f; ep.bias = nullptr; ep.residual = nullptr; ep.ldr = 0;
   ep.amax_slot = nullptr;
+  ep.swiglu_gu = nullptr; ep.swiglu_dgu = nullptr; ep.swiglu_ld = 0; ep.swiglu_f = 0;
   // both operands M/N-major: bits 15 and 16 of the instruction descriptor
   const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
   *slabs_out = (float*)s;
   *nslabs_out = splits;
   return launch_tc<64, 8, true>(ctx, ma, mb, ma, mb, ep, M, 64, T, 0, splits, idesc,
                                 2.0 * M * 64.0 * T);
+}
+
+int ft_slab_reduce_multi(FtContext* ctx, const float* slabs, int nslabs, int M, int count,
+                         float* const out[3], const int m0[3], const int mcount[3],
+                         const int n0[3], const int ncount[3], const long long som[3],
+                         const long long son[3], const float* alpha_ptr, float alpha,
+                         bool accumulate) {
+  if (count <= 0) return FT_OK;
+  SlabSegs sg;
+  sg.count = count;
+  size_t most = 0;
+  for (int i = 0; i < 3; ++i) {
+    const bool on = i < count;
+    sg.out[i] = on ? out[i] : nullptr;
+    sg.m0[i] = on ? m0[i] : 0; sg.mcount[i] = on ? mcount[i] : 0;
+    sg.n0[i] = on ? n0[i] : 0; sg.ncount[i] = on ? ncount[i] : 0;
+    sg.som[i] = on ? som[i] : 0; sg.son[i] = on ? son[i] : 0;
+    if (on) most = std::max(most, (size_t)mcount[i] * ncount[i]);
+  }
+  if (!most) return FT_OK;
+  dim3 grid((unsigned)std::min<size_t>((most + 255) / 256, (size_t)ctx->sm_count * 4), count);
+  FT_LAUNCH(ctx, k_slab_reduce_multi, grid, 256, 0, slabs, nslabs, M, 64, sg, alpha_ptr, alpha,
+            accumulate ? 1 : 0);
+  return FT_OK;
 }
 
 int ft_slab_reduce(FtContext* ctx, const float* slabs, int nslabs, int M, float* out, int m0,

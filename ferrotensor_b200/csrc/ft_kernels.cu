@@ -175,6 +175,87 @@ k_rms_norm_bwd(const float* __restrict__ x, const float* __restrict__ w,
   if (inv_out && threadIdx.x == 0) inv_out[blockIdx.x] = inv;
 }
 
+// Register-resident forms for rows of up to 256 * 4 * NV elements (16-byte aligned, n % 4 == 0):
+// every input element is read from memory exactly once.
+template <int NV>
+__global__ void __launch_bounds__(kRowThreads)
+k_rms_norm_reg(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
+               __half* __restrict__ out16, int n, float eps) {
+  __shared__ float red[32];
+  const int n4 = n >> 2;
+  const float4* x4 = (const float4*)(x + (size_t)blockIdx.x * n);
+  float4 xv[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * kRowThreads;
+    xv[k] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  const float4* w4 = (const float4*)w;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * kRowThreads;
+    if (i >= n4) continue;
+    const float4 g = w4[i];
+    const float4 r = make_float4(xv[k].x * inv * g.x, xv[k].y * inv * g.y, xv[k].z * inv * g.z,
+                                 xv[k].w * inv * g.w);
+    if (out) ((float4*)(out + (size_t)blockIdx.x * n))[i] = r;
+    if (out16) {
+      __half2 a = __floats2half2_rn(r.x, r.y), b = __floats2half2_rn(r.z, r.w);
+      ((uint2*)(out16 + (size_t)blockIdx.x * n))[i] = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(kRowThreads)
+k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
+                   const float* __restrict__ g, float* __restrict__ gx, int n, float eps,
+                   int accumulate, int* amax_slot) {
+  __shared__ float red[32];
+  const int n4 = n >> 2;
+  const size_t off = (size_t)blockIdx.x * n;
+  const float4 *x4 = (const float4*)(x + off), *g4 = (const float4*)(g + off), *w4 = (const float4*)w;
+  float4* o4 = (float4*)(gx + off);
+  float4 xv[NV], gv[NV];   // gv holds g * w
+  float ss = 0.f, gwx = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * kRowThreads;
+    if (i < n4) {
+      xv[k] = x4[i];
+      const float4 b = g4[i], c = w4[i];
+      gv[k] = make_float4(b.x * c.x, b.y * c.y, b.z * c.z, b.w * c.w);
+    } else {
+      xv[k] = gv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
+    gwx += gv[k].x * xv[k].x + gv[k].y * xv[k].y + gv[k].z * xv[k].z + gv[k].w * xv[k].w;
+  }
+  ss = block_sum(ss, red);
+  gwx = block_sum(gwx, red);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  const float coef = gwx * inv * inv * inv / (float)n;
+  float am = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * kRowThreads;
+    if (i >= n4) continue;
+    float4 r = make_float4(gv[k].x * inv - xv[k].x * coef, gv[k].y * inv - xv[k].y * coef,
+                           gv[k].z * inv - xv[k].z * coef, gv[k].w * inv - xv[k].w * coef);
+    if (accumulate) {
+      const float4 p = o4[i];
+      r.x += p.x; r.y += p.y; r.z += p.z; r.w += p.w;
+    }
+    o4[i] = r;
+    am = amax4(am, r);
+  }
+  amax_commit(am, amax_slot);
+}
+
 // partial[c, i] = sum over the rows of chunk c of g*x*inv ; one thread per feature
 __global__ void k_rms_gw_partial(const float* __restrict__ x, const float* __restrict__ g,
                                  const float* __restrict__ inv, float* __restrict__ partial,
@@ -566,6 +647,15 @@ int ft_k_rms_norm(FtContext* ctx, const float* x, const float* w, float* out, in
 
 int ft_k_rms_norm16(FtContext* ctx, const float* x, const float* w, float* out, __half* out16,
                     int rows, int n, float eps) {
+  const bool al = (n % 4) == 0 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) == 0 &&
+                  (((uintptr_t)out16) & 7) == 0;
+  if (al && n >= 1024 && n <= 4096) {
+    if (n <= 2048)
+      FT_LAUNCH(ctx, k_rms_norm_reg<2>, rows, kRowThreads, 0, x, w, out, out16, n, eps);
+    else
+      FT_LAUNCH(ctx, k_rms_norm_reg<4>, rows, kRowThreads, 0, x, w, out, out16, n, eps);
+    return FT_OK;
+  }
   int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
   FT_LAUNCH(ctx, k_rms_norm, rows, block, 0, x, w, out, out16, n, eps);
   return FT_OK;
@@ -589,6 +679,17 @@ int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const floa
   int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
   int* am = ctx->amax_out;
   if (am) ctx->amax_ready = true;
+  const bool al = (n % 4) == 0 &&
+                  ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)g) | ((uintptr_t)gx)) & 15) == 0;
+  if (!gw && al && n >= 1024 && n <= 4096) {
+    if (n <= 2048)
+      FT_LAUNCH(ctx, k_rms_norm_bwd_reg<2>, rows, kRowThreads, 0, x, w, g, gx, n, eps,
+                accumulate_gx ? 1 : 0, am);
+    else
+      FT_LAUNCH(ctx, k_rms_norm_bwd_reg<4>, rows, kRowThreads, 0, x, w, g, gx, n, eps,
+                accumulate_gx ? 1 : 0, am);
+    return FT_OK;
+  }
   FT_LAUNCH(ctx, k_rms_norm_bwd, rows, block, 0, x, w, g, gx, inv, n, eps, accumulate_gx ? 1 : 0, am);
   if (gw) {
     dim3 grid(ft_cdiv(n, 128), chunks);

@@ -485,7 +485,9 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
 int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const float* dY,
                      long long lddy, const __half* xa16, float* dX, long long lddx,
                      const float* residual, long long ldr, int T, const __half* dY16 = nullptr,
-                     const float* scales16 = nullptr, bool amax_on_dx = false) {
+                     const float* scales16 = nullptr, bool amax_on_dx = false,
+                     const float* swiglu_gu = nullptr, float* swiglu_dgu = nullptr,
+                     long long swiglu_ld = 0) {
   FtContext* ctx = m->ctx;
   const int r = m->cfg.lora_rank;
   long long np = (long long)ft_align_up((size_t)g.n, 8);
@@ -504,12 +506,13 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     a.c16 = m->g16; a.ldc16 = RP; a.alpha = m->scale;
     FT_TRY(ft_gemm_tc_ex(ctx, a));
   }
-  if (dX) {
+  if (dX || swiglu_gu) {
     FtGemmArgs a;
     a.a = dY16; a.lda = np; a.b = g.w_kn; a.ldb = g.n;
     a.M = T; a.N = g.in; a.K = g.n;
     if (g.R > 0) { a.a2 = m->g16; a.lda2 = RP; a.b2 = g.a_cat16; a.ldb2 = RP; a.K2 = RP; }
-    a.c = dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
+    a.c = swiglu_gu ? nullptr : dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
+    a.swiglu_gu = swiglu_gu; a.swiglu_dgu = swiglu_dgu; a.swiglu_ld = swiglu_ld;
     if (amax_on_dx) {
       FT_TRY(ft_amax_arm(ctx));
       a.want_amax = true;
@@ -521,20 +524,30 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     int ns = 0;
     // dB^T [n, 64] = (S dY)^T . xa16, reduced over tokens
     FT_TRY(ft_gemm_tc_kouter(ctx, dY16, np, xa16, RP, g.n, RP, T, &slabs, &ns));
+    float* outs[3];
+    int m0[3], mc[3], n0[3], nc[3], cnt = 0;
+    long long som[3], son[3];
     for (int j = 0; j < g.nlin; ++j) {
       const Linear& l = *g.lin[j];
       if (!l.lora) continue;
-      FT_TRY(ft_slab_reduce(ctx, slabs, ns, g.n, m->grads + l.b_off, g.col_off[j], l.out,
-                            g.r_off[j], r, 1, l.out, inv_s, 1.f, true));
+      outs[cnt] = m->grads + l.b_off; m0[cnt] = g.col_off[j]; mc[cnt] = l.out;
+      n0[cnt] = g.r_off[j]; nc[cnt] = r; som[cnt] = 1; son[cnt] = l.out;
+      ++cnt;
     }
+    FT_TRY(ft_slab_reduce_multi(ctx, slabs, ns, g.n, cnt, outs, m0, mc, n0, nc, som, son, inv_s, 1.f,
+                                true));
     // dA [in, 64] = X16^T . G16
     FT_TRY(ft_gemm_tc_kouter(ctx, X16, g.in, m->g16, RP, g.in, RP, T, &slabs, &ns));
+    cnt = 0;
     for (int j = 0; j < g.nlin; ++j) {
       const Linear& l = *g.lin[j];
       if (!l.lora) continue;
-      FT_TRY(ft_slab_reduce(ctx, slabs, ns, g.in, m->grads + l.a_off, 0, l.in, g.r_off[j], r, r, 1,
-                            inv_s, 1.f, true));
+      outs[cnt] = m->grads + l.a_off; m0[cnt] = 0; mc[cnt] = l.in;
+      n0[cnt] = g.r_off[j]; nc[cnt] = r; som[cnt] = r; son[cnt] = 1;
+      ++cnt;
     }
+    FT_TRY(ft_slab_reduce_multi(ctx, slabs, ns, g.in, cnt, outs, m0, mc, n0, nc, som, son, inv_s, 1.f,
+                                true));
   }
   return FT_OK;
 }
@@ -599,6 +612,8 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   Layer& ly = m->layers[l];
   const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
   // On entry an armed amax of m->dx is pending (left by the norm backward that produced it).
+  // (Fusing SwiGLU's backward into this product's epilogue was measured slower: the epilogue
+  // warps become latency-bound on the gate/up loads and stall the accumulator hand-over.)
   FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, m->dx, h, a.xa16_down, m->df, F, nullptr, 0, T));
   FT_TRY(ft_amax_arm(ctx));
   FT_TRY(ft_k_silu_gate_bwd(ctx, a.gu, 2 * F, a.gu + F, 2 * F, m->df, F, m->dgu, 2 * F,
