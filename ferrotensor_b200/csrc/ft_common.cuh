@@ -194,7 +194,10 @@ int ft_k_scale(FtContext* ctx, float* x, size_t n, float s);
 int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
                    float* out, long long ldo, int rows, int n);
 int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
-                     __half* out, long long ldo, int rows, int n);
+                     __half* out, long long ldo, int rows, int n, int* in_amax = nullptr);
+int ft_k_silu_gate_bwd16(FtContext* ctx, const float* a, long long lda, const float* b,
+                         long long ldb, const float* g, long long ldg, __half* out, long long ldo,
+                         int rows, int n, const int* in_amax, const float** scales_out);
 int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const float* b,
                        long long ldb, const float* g, long long ldg, float* ga, long long ldga,
                        float* gb, long long ldgb, int rows, int n);

@@ -113,6 +113,7 @@ struct FtLoraModel {
   bool tc_attention = false;       // head_dim 64: attention and RoPE take the tensor-core route
   float* rope_table = nullptr;     // {cos, sin} [seq_len, 32] in the workspace
   int table_seq = 0;
+  int* gu_amax = nullptr;          // per layer: largest |gate| or |up| of the forward pass
 };
 
 namespace {
@@ -208,7 +209,8 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   float* dh = b.take<float>(T * c.hidden);
   float* dqkv = b.take<float>(T * nqkv);
   float* dattn = b.take<float>(T * m->nq);
-  float* dgu = b.take<float>(T * 2 * c.ffn);
+  // (the fused path writes the gate|up gradient straight to f16)
+  float* dgu = fused ? nullptr : b.take<float>(T * 2 * c.ffn);
   float* df = b.take<float>(T * c.ffn);
   int rmax = std::max({m->layers[0].qkv.R, m->layers[0].o.R, m->layers[0].gu.R,
                        m->layers[0].down.R, m->head.R, 1});
@@ -222,7 +224,9 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   __half* hN16 = fused ? b.take<__half>(T * c.hidden) : nullptr;
   __half* xa16_head = fused ? b.take<__half>(T * RP) : nullptr;
   __half* g16 = fused ? b.take<__half>(T * RP) : nullptr;
+  int* gu_amax = fused ? b.take<int>((size_t)L) : nullptr;
   if (!dry) {
+    m->gu_amax = gu_amax;
     m->plan_fused = fused; m->hN16 = hN16; m->xa16_head = xa16_head; m->g16 = g16;
     m->rope_table = rope_table; m->table_seq = 0;
     m->tc_attention = tc_attention;
@@ -601,7 +605,7 @@ int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, 
   FT_TRY(linear_fwd_fused(m, ly.o, a.attn16, a.x1, h, a.xa16_o, x_in, h, T));
   FT_TRY(ft_k_rms_norm16(ctx, a.x1, ly.norm2, nullptr, a.h2_16, T, h, c.eps));
   FT_TRY(linear_fwd_fused(m, ly.gu, a.h2_16, a.gu, 2 * F, a.xa16_gu, nullptr, 0, T));
-  FT_TRY(ft_k_silu_gate16(ctx, a.gu, 2 * F, a.gu + F, 2 * F, a.f_16, F, T, F));
+  FT_TRY(ft_k_silu_gate16(ctx, a.gu, 2 * F, a.gu + F, 2 * F, a.f_16, F, T, F, m->gu_amax + l));
   FT_TRY(linear_fwd_fused(m, ly.down, a.f_16, x_out, h, a.xa16_down, a.x1, h, T));
   return FT_OK;
 }
@@ -614,11 +618,15 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   // On entry an armed amax of m->dx is pending (left by the norm backward that produced it).
   // (Fusing SwiGLU's backward into this product's epilogue was measured slower: the epilogue
   // warps become latency-bound on the gate/up loads and stall the accumulator hand-over.)
-  FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, m->dx, h, a.xa16_down, m->df, F, nullptr, 0, T));
-  FT_TRY(ft_amax_arm(ctx));
-  FT_TRY(ft_k_silu_gate_bwd(ctx, a.gu, 2 * F, a.gu + F, 2 * F, m->df, F, m->dgu, 2 * F,
-                            m->dgu + F, 2 * F, T, F));
-  FT_TRY(linear_bwd_fused(m, ly.gu, a.h2_16, m->dgu, 2 * F, a.xa16_gu, m->dh, h, nullptr, 0, T));
+  // The down projection's input gradient reports its amax; SwiGLU's backward bounds its own
+  // output with it and writes the gate|up gradient as f16 operands in the same pass.
+  FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, m->dx, h, a.xa16_down, m->df, F, nullptr, 0, T,
+                          nullptr, nullptr, true));
+  const float* gu_scales = nullptr;
+  FT_TRY(ft_k_silu_gate_bwd16(ctx, a.gu, 2 * F, a.gu + F, 2 * F, m->df, F, m->cvt_hi, 2 * F, T, F,
+                              m->gu_amax + l, &gu_scales));
+  FT_TRY(linear_bwd_fused(m, ly.gu, a.h2_16, nullptr, 2 * F, a.xa16_gu, m->dh, h, nullptr, 0, T,
+                          m->cvt_hi, gu_scales));
   FT_TRY(ft_amax_arm(ctx));
   FT_TRY(ft_k_rms_norm_bwd(ctx, a.x1, ly.norm2, m->dh, m->dx, nullptr, T, h, c.eps, true));
   const bool need_dx = l > 0;
@@ -945,6 +953,7 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
   }
 
   // ---- forward
+  if (fused) FT_CUDA(cudaMemsetAsync(m->gu_amax, 0, sizeof(int) * (size_t)L, ctx->stream));
   FT_TRY(ft_k_embedding(ctx, m->embed, ids, m->x[0], T, V, h));
   for (int l = 0; l < L; ++l) {
     BlockActs& a = m->acts[ckpt ? 0 : l];
