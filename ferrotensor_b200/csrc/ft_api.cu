@@ -61,6 +61,7 @@ extern "C" int ft_ctx_create(int device, void* stream, FtContext** out) {
   const char* dbg = getenv("FT_GEMM_DEBUG");
   ctx->debug_markers = dbg && dbg[0] == '1';
   if (const char* tm = getenv("FT_GEMM_TILE_M")) ctx->tile_m_override = atoi(tm);
+  if (const char* pd = getenv("FT_PDL")) ctx->pdl = atoi(pd) != 0;
   FT_CUDA(cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
   FT_CUDA(cudaMalloc((void**)&ctx->scale_buf, 8 * sizeof(float)));
   {

@@ -55,6 +55,8 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
               __half* __restrict__ out16, long long ldo16, float* __restrict__ out32,
               long long ldo32, float* __restrict__ stats, int seq, int heads, int kv_heads,
               int q_col0, int k_col0, int v_col0, float scale_log2e, int* status) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -337,6 +339,8 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
                  float* __restrict__ dq, long long lddq, float* __restrict__ stats, int seq,
                  int heads, int kv_heads, int q_col0, int k_col0, int v_col0, float scale,
                  const float* __restrict__ inv_scale_ptr, int* amax_slot, int* status) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -581,6 +585,8 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
                   float* __restrict__ dv, long long ldd, const float* __restrict__ stats, int seq,
                   int heads, int kv_heads, int q_col0, int k_col0, int v_col0, float scale,
                   const float* __restrict__ inv_scale_ptr, int* amax_slot, int* status) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -844,7 +850,7 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
   }
   dim3 grid(ft_cdiv(seq, AT_Q), batch * heads);
   const float scale_log2e = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
-  FT_LAUNCH(ctx, k_attn_fwd_tc, grid, AT_THREADS, AttnSmem::DYN_BYTES, q128, kv64, out16, ldo16, out32,
+  FT_LAUNCH_PDL(ctx, k_attn_fwd_tc, grid, AT_THREADS, AttnSmem::DYN_BYTES, q128, kv64, out16, ldo16, out32,
             ldo32, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale_log2e,
             ctx->status_dev);
   return FT_OK;
@@ -885,13 +891,13 @@ int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
   if (am) ctx->amax_ready = true;
   {
     dim3 grid(ft_cdiv(seq, AT_Q), batch * heads);
-    FT_LAUNCH(ctx, k_attn_bwd_dq_tc, grid, AT_THREADS, BwdQSmem::DYN_BYTES, q128, kv64, do128, do16,
+    FT_LAUNCH_PDL(ctx, k_attn_bwd_dq_tc, grid, AT_THREADS, BwdQSmem::DYN_BYTES, q128, kv64, do128, do16,
               lddo, o16, ldo, dq, lddq, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale,
               inv_scale, am, ctx->status_dev);
   }
   {
     dim3 grid(ft_cdiv(seq, AT_KV), batch * kv_heads);
-    FT_LAUNCH(ctx, k_attn_bwd_dkv_tc, grid, AT_THREADS, BwdKSmem::DYN_BYTES, q128, kv64, do64, dk, dv,
+    FT_LAUNCH_PDL(ctx, k_attn_bwd_dkv_tc, grid, AT_THREADS, BwdKSmem::DYN_BYTES, q128, kv64, do64, dk, dv,
               ldd, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale, inv_scale, am,
               ctx->status_dev);
   }

@@ -33,6 +33,7 @@ struct FtContext {
   // "amax in the producer": while armed, kernels that support it fold the largest magnitude
   // of what they write into scale_buf[0] (atomicMax), and the next auto-scaled conversion
   // uses it instead of making its own pass over the tensor.
+  bool pdl = true;   // programmatic dependent launch for the kernels that support it
   int* amax_out = nullptr;
   bool amax_ready = false;
   int tile_m_override = 0;   // FT_GEMM_TILE_M: 128 or 256 forces the GEMM tile height
@@ -88,6 +89,49 @@ void ft_prof_end(FtContext* ctx);
     if (_e != cudaSuccess) return ft_cuda_fail(_e, #kernel, __FILE__, __LINE__); \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched through FT_LAUNCH_PDL may start while the
+// kernel before it in the stream is still draining; it must call ft_pdl_wait() before it
+// touches global memory (what ran before is complete and visible from then on) and may call
+// ft_pdl_launch() to let its own successor start early.  Both are no-ops in a plain launch.
+#ifdef __CUDACC__
+__device__ __forceinline__ void ft_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ft_pdl_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t ft_launch_ex(FtContext* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                size_t smem, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess && ctx->pdl) {
+    // the attribute is refused on this stream or driver: drop it for good and launch plainly
+    (void)cudaGetLastError();
+    ctx->pdl = false;
+    cfg.numAttrs = 0;
+    e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  }
+  return e;
+}
+#define FT_LAUNCH_PDL(ctx, kernel, grid, block, smem, ...)                       \
+  do {                                                                          \
+    if ((ctx)->profile_all) ft_prof_begin((ctx), #kernel);                      \
+    cudaError_t _e = ft_launch_ex((ctx), kernel, (grid), (block), (smem), __VA_ARGS__); \
+    if ((ctx)->profile_all) ft_prof_end((ctx));                                 \
+    (ctx)->launches++;                                                          \
+    if (_e == cudaSuccess) _e = cudaPeekAtLastError();                          \
+    if (_e != cudaSuccess) return ft_cuda_fail(_e, #kernel, __FILE__, __LINE__); \
+  } while (0)
+#endif
+
 // Scratch of at least `bytes`, 256-byte aligned.  Stream order makes reuse by consecutive
 // calls safe; growth synchronises the stream before the old block is released.
 int ft_scratch(FtContext* ctx, size_t bytes, void** out);
@@ -130,11 +174,6 @@ struct FtGemmArgs {
   const float* bias = nullptr;
   const float* residual = nullptr; long long ldr = 0;
   bool want_amax = false;   // contribute the output's largest magnitude to an armed amax slot
-  // SwiGLU backward in the epilogue (the product is d(silu(gate) * up), N = F): gu holds
-  // gate | up rows of pitch swiglu_ld, dgu receives d(gate) | d(up); nothing else is stored
-  const float* swiglu_gu = nullptr;
-  float* swiglu_dgu = nullptr;
-  long long swiglu_ld = 0;
 };
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g);
 // Token-reduction product P[M, N<=64] = sum_t A[t,m] B[t,n] (A [T,M], B [T,N], f16) as K-split

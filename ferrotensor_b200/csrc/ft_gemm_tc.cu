@@ -25,8 +25,8 @@ struct SmemLayout {
   static constexpr int A_BYTES = MH * BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;     // 4 epilogue warps x 4 KiB staging
-  static constexpr int BAR_OFFSET = EPI_OFFSET + 4 * 4096;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;     // 8 epilogue warps x 4 KiB staging
+  static constexpr int BAR_OFFSET = EPI_OFFSET + 8 * 4096;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack to align the base to 1024 bytes
@@ -60,13 +60,6 @@ struct Epilogue {
   const float* residual;
   long long ldr;
   int* amax_slot;   // when set, the largest |v| written is folded into it (atomicMax)
-  // SwiGLU backward fused into the product that yields d(f) (N = F): instead of storing v,
-  // with gate = gu[row, col], up = gu[row, F + col]:
-  //   dgu[row, col] = v * up * s (1 + gate (1 - s)),  dgu[row, F + col] = v * gate * s,  s = sigmoid(gate)
-  const float* swiglu_gu;
-  float* swiglu_dgu;
-  long long swiglu_ld;
-  int swiglu_f;
 };
 
 // KOUTER = false:  C[M,N] = A[M,K] . B[N,K]^T (+ A2[M,K2] . B2[N,K2]^T), operands K-contiguous.
@@ -112,7 +105,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + b * 8, 1);
-      mbar_init(bar_tempty + b * 8, 4);  // one arrival per epilogue warp
+      mbar_init(bar_tempty + b * 8, 8);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -130,6 +123,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched only this CTA's shared and tensor memory: it may run while the
+  // previous kernel in the stream drains; global memory is touched from here on
+  ft_pdl_wait();
+  ft_pdl_launch();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -222,7 +219,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue
+    // Eight warps: a warp reaches only the 32 TMEM lanes of its quadrant (warp % 4), so two
+    // warps share each quadrant and take alternate 32-column chunks.
     const int quad = warp & 3;               // TMEM lanes [32*quad, 32*quad+32)
+    const int grp = (warp - 2) >> 2;
     int local = 0;
     uint8_t* stage_base = gbase + L::EPI_OFFSET + (warp - 2) * 4096;   // 32 x 128 bytes per warp
     const bool vec_c = ep.c && ((ep.ldc & 3) == 0) && ((((uintptr_t)ep.c) & 15) == 0);
@@ -230,6 +230,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     const bool vec_h = ep.c16 && ((ep.ldc16 & 3) == 0) && ((((uintptr_t)ep.c16) & 7) == 0);
     const float alpha = (ep.alpha_ptr ? *ep.alpha_ptr : 1.0f) * ep.alpha;
     float amax_seen = 0.f;
+    constexpr int NCH = MH * (BN / 32);
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
       const int n0 = KOUTER ? 0 : nt * BN;
@@ -240,12 +241,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       if (warp == 2 && lane == 0) FT_MARK(9, 41);
       // a K split of the token-reduction product writes its own slab
       float* cbase = ep.c ? ep.c + (KOUTER ? (long long)nt * M * ep.ldc : 0) : nullptr;
+      const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+      uint32_t r[32];
+      // chunk c of the tile: half c / (BN/32) (a 128-row half), 32 columns from (c % (BN/32)) * 32
+      tc_ld32(t_lane + (buf + grp / (BN / 32)) * BN + (grp % (BN / 32)) * 32, r);
 #pragma unroll 1
-      for (int cbh = 0; cbh < MH * (BN / 32); ++cbh) {
+      for (int cbh = grp; cbh < NCH; cbh += 2) {
         const int half = cbh / (BN / 32), cb = cbh % (BN / 32);
-        const int row = m0 + half * BM + quad * 32 + lane;
-        uint32_t r[32];
-        tc_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (buf + half) * BN + cb * 32, r);
         tc_wait_ld();
         const int col0 = n0 + cb * 32;
         // Transpose the 32 x 32 chunk through a swizzled staging tile so that global traffic
@@ -260,51 +262,46 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 make_float4(alpha * __uint_as_float(r[4 * j]), alpha * __uint_as_float(r[4 * j + 1]),
                             alpha * __uint_as_float(r[4 * j + 2]), alpha * __uint_as_float(r[4 * j + 3]));
         }
+        // the next chunk's accumulator read travels while this one is stored
+        if (cbh + 2 < NCH) {
+          const int nh = (cbh + 2) / (BN / 32), nc = (cbh + 2) % (BN / 32);
+          tc_ld32(t_lane + (buf + nh) * BN + nc * 32, r);
+        }
         __syncwarp();
         const int row_base = m0 + half * BM + quad * 32;
-        if (row_base < M && col0 < N) {
-          const int j = lane & 7, gcol = col0 + 4 * j;
+        const int j = lane & 7, gcol = col0 + 4 * j;
+        if (row_base < M && gcol < N) {
+          const bool full = gcol + 4 <= N;
+          const bool fast_r = ep.residual && full && vec_r;
+          float4 resv[8];
+          if (fast_r) {   // all residual loads in flight before the first store
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              const int grow = row_base + 4 * t + (lane >> 3);
+              resv[t] = grow < M ? *(const float4*)(ep.residual + (long long)grow * ep.ldr + gcol)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+          float bv[4] = {0.f, 0.f, 0.f, 0.f};
+          if (ep.bias) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (gcol + e < N) bv[e] = ep.bias[gcol + e];
+          }
 #pragma unroll
           for (int t = 0; t < 8; ++t) {
             const int rr = 4 * t + (lane >> 3);
             const int grow = row_base + rr;
             float4 v4 = *(const float4*)(stage_base + rr * 128 + ((j ^ (rr & 7)) << 4));
-            if (grow >= M || gcol >= N) continue;
-            float v[4] = {v4.x, v4.y, v4.z, v4.w};
-            const bool full = gcol + 4 <= N;
-            if (ep.bias) {
+            if (grow >= M) continue;
+            float v[4] = {v4.x + bv[0], v4.y + bv[1], v4.z + bv[2], v4.w + bv[3]};
+            if (fast_r) {
+              v[0] += resv[t].x; v[1] += resv[t].y; v[2] += resv[t].z; v[3] += resv[t].w;
+            } else if (ep.residual) {
+              const float* rp = ep.residual + (long long)grow * ep.ldr + gcol;
 #pragma unroll
               for (int e = 0; e < 4; ++e)
-                if (full || gcol + e < N) v[e] += ep.bias[gcol + e];
-            }
-            if (ep.residual) {
-              const float* rp = ep.residual + (long long)grow * ep.ldr + gcol;
-              if (full && vec_r) {
-                float4 o = *(const float4*)rp;
-                v[0] += o.x; v[1] += o.y; v[2] += o.z; v[3] += o.w;
-              } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  if (gcol + e < N) v[e] += rp[e];
-              }
-            }
-            if (ep.swiglu_gu) {
-              // N = F is a multiple of 4 and the rows are 16-byte aligned (checked on the host)
-              const float* gp = ep.swiglu_gu + (long long)grow * ep.swiglu_ld + gcol;
-              const float4 g4 = *(const float4*)gp, u4 = *(const float4*)(gp + ep.swiglu_f);
-              const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
-              float dg[4], du[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float sg = 1.0f / (1.0f + expf(-gs[e]));
-                du[e] = v[e] * (gs[e] * sg);
-                dg[e] = v[e] * us[e] * (sg * (1.0f + gs[e] * (1.0f - sg)));
-                amax_seen = fmaxf(amax_seen, fmaxf(fabsf(du[e]), fabsf(dg[e])));
-              }
-              float* op = ep.swiglu_dgu + (long long)grow * ep.swiglu_ld + gcol;
-              *(float4*)op = make_float4(dg[0], dg[1], dg[2], dg[3]);
-              *(float4*)(op + ep.swiglu_f) = make_float4(du[0], du[1], du[2], du[3]);
-              continue;
+                if (gcol + e < N) v[e] += rp[e];
             }
             if (ep.amax_slot) {
 #pragma unroll
@@ -377,6 +374,8 @@ struct SlabSegs {
 __global__ void k_slab_reduce_multi(const float* __restrict__ part, int slabs, int M, int ldp,
                                     SlabSegs sg, const float* __restrict__ alpha_ptr, float alpha,
                                     int accumulate) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   const float a = (alpha_ptr ? *alpha_ptr : 1.0f) * alpha;
   const int seg = blockIdx.y;
   if (seg >= sg.count) return;
@@ -451,6 +450,8 @@ __device__ __forceinline__ float scale_from_amax_bits(int bits, int target_exp) 
 // target_exp), scales[1] = 1/S, scales[2] = 2^-11/S (the factor of the low half in split mode)
 __global__ void k_scale_from_amax(const int* __restrict__ amax_bits, float* __restrict__ scales,
                                   int target_exp) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   float amax = __int_as_float(*amax_bits);
   float S = 1.0f;
   if (amax > 0.f && isfinite(amax)) {
@@ -471,6 +472,8 @@ __global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __
                          __half* __restrict__ lo, long long ldo, int rows, int cols,
                          const float* __restrict__ scales, const int* __restrict__ amax_bits,
                          int target_exp, float* __restrict__ scales_out) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   // the scale is either given, or derived here from the amax a producer left behind (then
   // one thread also publishes {S, 1/S, 2^-11/S} for the products that follow)
   float S = scales ? scales[0] : 1.0f;
@@ -549,12 +552,13 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
     const bool pa = ctx->profile_all;
     if (pa) ft_prof_begin(ctx, nm);
     ctx->profile_all = false;
-    k_gemm_tc<BN, STAGES, KOUTER, MH><<<grid, GEMM_THREADS, L::DYN_BYTES, ctx->stream>>>(
-        ma, mb, ma2, mb2, ep, M, N, K, K2, splits, idesc, ctx->status_dev, dbg);
+    cudaError_t le = ft_launch_ex(ctx, k_gemm_tc<BN, STAGES, KOUTER, MH>, grid, GEMM_THREADS,
+                                  L::DYN_BYTES, ma, mb, ma2, mb2, ep, M, N, K, K2, splits, idesc,
+                                  ctx->status_dev, dbg);
     ctx->profile_all = pa;
     if (pa) ft_prof_end(ctx);
     ctx->launches++;
-    cudaError_t le = cudaPeekAtLastError();
+    if (le == cudaSuccess) le = cudaPeekAtLastError();
     if (le != cudaSuccess) return ft_cuda_fail(le, "k_gemm_tc", __FILE__, __LINE__);
   }
   if (ctx->profile) {
@@ -587,7 +591,7 @@ int ft_scales_from_amax_or_pass(FtContext* ctx, const float* src, long long ld, 
                                                             (long long)ctx->sm_count * 8));
     FT_LAUNCH(ctx, k_amax, g, 256, 0, src, ld, rows, cols, (int*)ctx->scale_buf);
   }
-  FT_LAUNCH(ctx, k_scale_from_amax, 1, 1, 0, (const int*)ctx->scale_buf, ctx->scale_buf + 4,
+  FT_LAUNCH_PDL(ctx, k_scale_from_amax, 1, 1, 0, (const int*)ctx->scale_buf, ctx->scale_buf + 4,
             target_exp);
   *scales_out = ctx->scale_buf + 4;
   return FT_OK;
@@ -616,7 +620,7 @@ int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half
   long long total = (long long)rows * ((cols + 3) / 4);
   int grid = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256,
                                                              (long long)ctx->sm_count * 16));
-  FT_LAUNCH(ctx, k_to_f16, grid, 256, 0, src, ld, hi, lo, ldo, rows, cols, scales, amax_bits,
+  FT_LAUNCH_PDL(ctx, k_to_f16, grid, 256, 0, src, ld, hi, lo, ldo, rows, cols, scales, amax_bits,
             target_exp, ctx->scale_buf + 4);
   return FT_OK;
 }
@@ -641,10 +645,11 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
     const long long t1 = (long long)ft_cdiv(g.M, 128) * ft_cdiv(g.N, 256);
     const long long t2 = (long long)ft_cdiv(g.M, 256) * ft_cdiv(g.N, 256);
     const double kk = (double)(g.K + g.K2);
-    // measured on B200, in units of one K element of a 128-row tile: a 128 x 256 tile costs
-    // K + 470, a 256 x 256 tile 1.63 K + 2470 (its epilogue is not hidden)
-    const double cost1 = (double)((t1 + sms - 1) / sms) * (kk + 470.0);
-    const double cost2 = (double)((t2 + sms - 1) / sms) * (1.63 * kk + 2470.0);
+    // measured on B200, in units of one K element of a 128-row tile (about 7 ns): a 128 x 256
+    // tile costs K + 200, a 256 x 256 tile 1.6 K + 1680 (its epilogue is not hidden, and every
+    // SM stores its 256 KiB at the same moment)
+    const double cost1 = (double)((t1 + sms - 1) / sms) * (kk + 200.0);
+    const double cost2 = (double)((t2 + sms - 1) / sms) * (1.6 * kk + 1680.0);
     MH = cost2 < cost1 ? 2 : 1;
     if (ctx->tile_m_override == 128) MH = 1;
     if (ctx->tile_m_override == 256) MH = 2;
@@ -669,13 +674,6 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   ep.c = g.c; ep.ldc = g.ldc; ep.c16 = g.c16; ep.ldc16 = g.ldc16;
   ep.alpha_ptr = g.alpha_ptr; ep.alpha = g.alpha; ep.bias = g.bias;
   ep.residual = g.residual; ep.ldr = g.ldr;
-  ep.swiglu_gu = g.swiglu_gu; ep.swiglu_dgu = g.swiglu_dgu; ep.swiglu_ld = g.swiglu_ld;
-  ep.swiglu_f = g.N;
-  if (g.swiglu_gu) {
-    if ((g.N % 4) || (g.swiglu_ld % 4) || (((uintptr_t)g.swiglu_gu) & 15) ||
-        (((uintptr_t)g.swiglu_dgu) & 15) || g.bias || g.residual)
-      return FT_ERR_UNSUPPORTED;
-  }
   ep.amax_slot = nullptr;
   if (g.want_amax && ctx->amax_out) {
     ep.amax_slot = ctx->amax_out;
@@ -722,7 +720,6 @@ int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* 
   ep.c = (float*)s; ep.ldc = 64; ep.c16 = nullptr; ep.ldc16 = 0;
   ep.alpha_ptr = nullptr; ep.alpha = 1.f; ep.bias = nullptr; ep.residual = nullptr; ep.ldr = 0;
   ep.amax_slot = nullptr;
-  ep.swiglu_gu = nullptr; ep.swiglu_dgu = nullptr; ep.swiglu_ld = 0; ep.swiglu_f = 0;
   // both operands M/N-major: bits 15 and 16 of the instruction descriptor
   const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
   *slabs_out = (float*)s;
@@ -750,7 +747,7 @@ int ft_slab_reduce_multi(FtContext* ctx, const float* slabs, int nslabs, int M, 
   }
   if (!most) return FT_OK;
   dim3 grid((unsigned)std::min<size_t>((most + 255) / 256, (size_t)ctx->sm_count * 4), count);
-  FT_LAUNCH(ctx, k_slab_reduce_multi, grid, 256, 0, slabs, nslabs, M, 64, sg, alpha_ptr, alpha,
+  FT_LAUNCH_PDL(ctx, k_slab_reduce_multi, grid, 256, 0, slabs, nslabs, M, 64, sg, alpha_ptr, alpha,
             accumulate ? 1 : 0);
   return FT_OK;
 }

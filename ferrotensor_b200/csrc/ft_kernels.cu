@@ -181,6 +181,8 @@ template <int NV>
 __global__ void __launch_bounds__(kRowThreads)
 k_rms_norm_reg(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
                __half* __restrict__ out16, int n, float eps) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   __shared__ float red[32];
   const int n4 = n >> 2;
   const float4* x4 = (const float4*)(x + (size_t)blockIdx.x * n);
@@ -215,6 +217,8 @@ __global__ void __launch_bounds__(kRowThreads)
 k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
                    const float* __restrict__ g, float* __restrict__ gx, int n, float eps,
                    int accumulate, int* amax_slot) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   __shared__ float red[32];
   const int n4 = n >> 2;
   const size_t off = (size_t)blockIdx.x * n;
@@ -317,6 +321,8 @@ __global__ void k_rope_to_f16(const float* __restrict__ src, __half* __restrict_
                               long long tokens, int nq, int nkv, int seq_len,
                               const float2* __restrict__ table, int inverse,
                               const float* __restrict__ scales) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   const float S = scales ? scales[0] : 1.0f;
   const int per_tok = (nq + 2 * nkv) / 8;
   const long long total = tokens * per_tok;
@@ -404,6 +410,8 @@ __global__ void k_silu_gate16(const float* __restrict__ a, long long lda,
                               const float* __restrict__ b, long long ldb,
                               __half* __restrict__ out, long long ldo, int rows, int n,
                               int* in_amax) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   size_t per_row = (size_t)n / 4, total = (size_t)rows * per_row;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
   float am = 0.f;
@@ -430,6 +438,8 @@ __global__ void k_silu_gate_bwd16(const float* __restrict__ a, long long lda,
                                   __half* __restrict__ out, long long ldo, int rows, int n,
                                   const int* __restrict__ g_amax, const int* __restrict__ in_amax,
                                   float* __restrict__ scales_out) {
+  ft_pdl_wait();
+  ft_pdl_launch();
   float S = 1.0f;
   {
     float bound = 1.1f * __int_as_float(*g_amax) * __int_as_float(*in_amax);
@@ -703,9 +713,9 @@ int ft_k_rms_norm16(FtContext* ctx, const float* x, const float* w, float* out, 
                   (((uintptr_t)out16) & 7) == 0;
   if (al && n >= 1024 && n <= 4096) {
     if (n <= 2048)
-      FT_LAUNCH(ctx, k_rms_norm_reg<2>, rows, kRowThreads, 0, x, w, out, out16, n, eps);
+      FT_LAUNCH_PDL(ctx, k_rms_norm_reg<2>, rows, kRowThreads, 0, x, w, out, out16, n, eps);
     else
-      FT_LAUNCH(ctx, k_rms_norm_reg<4>, rows, kRowThreads, 0, x, w, out, out16, n, eps);
+      FT_LAUNCH_PDL(ctx, k_rms_norm_reg<4>, rows, kRowThreads, 0, x, w, out, out16, n, eps);
     return FT_OK;
   }
   int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
@@ -735,10 +745,10 @@ int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const floa
                   ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)g) | ((uintptr_t)gx)) & 15) == 0;
   if (!gw && al && n >= 1024 && n <= 4096) {
     if (n <= 2048)
-      FT_LAUNCH(ctx, k_rms_norm_bwd_reg<2>, rows, kRowThreads, 0, x, w, g, gx, n, eps,
+      FT_LAUNCH_PDL(ctx, k_rms_norm_bwd_reg<2>, rows, kRowThreads, 0, x, w, g, gx, n, eps,
                 accumulate_gx ? 1 : 0, am);
     else
-      FT_LAUNCH(ctx, k_rms_norm_bwd_reg<4>, rows, kRowThreads, 0, x, w, g, gx, n, eps,
+      FT_LAUNCH_PDL(ctx, k_rms_norm_bwd_reg<4>, rows, kRowThreads, 0, x, w, g, gx, n, eps,
                 accumulate_gx ? 1 : 0, am);
     return FT_OK;
   }
@@ -839,7 +849,7 @@ int ft_k_rope_to_f16(FtContext* ctx, const float* src, __half* dst, long long ld
                  (((uintptr_t)src) & 15) == 0 && (((uintptr_t)dst) & 15) == 0,
              "rope_to_f16: needs head_dim 64 and 16-byte aligned rows");
   size_t total = (size_t)tokens * ((nq + 2 * nkv) / 8);
-  FT_LAUNCH(ctx, k_rope_to_f16, ew_grid(ctx, total, 256, 2), 256, 0, src, dst, ld, (long long)tokens, nq,
+  FT_LAUNCH_PDL(ctx, k_rope_to_f16, ew_grid(ctx, total, 256, 2), 256, 0, src, dst, ld, (long long)tokens, nq,
             nkv, seq_len, (const float2*)table, inverse ? 1 : 0, scales);
   return FT_OK;
 }
@@ -876,7 +886,7 @@ int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float*
   FT_REQUIRE((n % 4) == 0 && (lda % 4) == 0 && (ldb % 4) == 0 && (ldo % 4) == 0 &&
                  ((((uintptr_t)a) | ((uintptr_t)b)) & 15) == 0 && (((uintptr_t)out) & 7) == 0,
              "silu_gate16: width and pitches must be multiples of 4");
-  FT_LAUNCH(ctx, k_silu_gate16, ew_grid(ctx, (size_t)rows * n / 4), 256, 0, a, lda, b, ldb, out, ldo,
+  FT_LAUNCH_PDL(ctx, k_silu_gate16, ew_grid(ctx, (size_t)rows * n / 4), 256, 0, a, lda, b, ldb, out, ldo,
             rows, n, in_amax);
   return FT_OK;
 }
@@ -895,7 +905,7 @@ int ft_k_silu_gate_bwd16(FtContext* ctx, const float* a, long long lda, const fl
   const int* g_amax = ctx->amax_out;
   ctx->amax_out = nullptr;
   ctx->amax_ready = false;
-  FT_LAUNCH(ctx, k_silu_gate_bwd16, ew_grid(ctx, (size_t)rows * n / 4, 256, 2), 256, 0, a, lda, b,
+  FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16, ew_grid(ctx, (size_t)rows * n / 4, 256, 2), 256, 0, a, lda, b,
             ldb, g, ldg, out, ldo, rows, n, g_amax, in_amax, ctx->scale_buf + 4);
   *scales_out = ctx->scale_buf + 4;
   return FT_OK;

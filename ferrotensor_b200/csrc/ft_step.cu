@@ -489,9 +489,7 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
 int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const float* dY,
                      long long lddy, const __half* xa16, float* dX, long long lddx,
                      const float* residual, long long ldr, int T, const __half* dY16 = nullptr,
-                     const float* scales16 = nullptr, bool amax_on_dx = false,
-                     const float* swiglu_gu = nullptr, float* swiglu_dgu = nullptr,
-                     long long swiglu_ld = 0) {
+                     const float* scales16 = nullptr, bool amax_on_dx = false) {
   FtContext* ctx = m->ctx;
   const int r = m->cfg.lora_rank;
   long long np = (long long)ft_align_up((size_t)g.n, 8);
@@ -510,13 +508,12 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     a.c16 = m->g16; a.ldc16 = RP; a.alpha = m->scale;
     FT_TRY(ft_gemm_tc_ex(ctx, a));
   }
-  if (dX || swiglu_gu) {
+  if (dX) {
     FtGemmArgs a;
     a.a = dY16; a.lda = np; a.b = g.w_kn; a.ldb = g.n;
     a.M = T; a.N = g.in; a.K = g.n;
     if (g.R > 0) { a.a2 = m->g16; a.lda2 = RP; a.b2 = g.a_cat16; a.ldb2 = RP; a.K2 = RP; }
-    a.c = swiglu_gu ? nullptr : dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
-    a.swiglu_gu = swiglu_gu; a.swiglu_dgu = swiglu_dgu; a.swiglu_ld = swiglu_ld;
+    a.c = dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
     if (amax_on_dx) {
       FT_TRY(ft_amax_arm(ctx));
       a.want_amax = true;
@@ -616,8 +613,6 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   Layer& ly = m->layers[l];
   const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
   // On entry an armed amax of m->dx is pending (left by the norm backward that produced it).
-  // (Fusing SwiGLU's backward into this product's epilogue was measured slower: the epilogue
-  // warps become latency-bound on the gate/up loads and stall the accumulator hand-over.)
   // The down projection's input gradient reports its amax; SwiGLU's backward bounds its own
   // output with it and writes the gate|up gradient as f16 operands in the same pass.
   FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, m->dx, h, a.xa16_down, m->df, F, nullptr, 0, T,

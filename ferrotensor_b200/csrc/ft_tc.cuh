@@ -13,7 +13,7 @@ namespace ft_tc {
 constexpr int BM = 128;
 constexpr int BK = 64;            // 64 x 16-bit = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192; // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int GEMM_THREADS = 320; // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr uint32_t SPIN_LIMIT = 1u << 26;  // ~ seconds of polling at most
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
