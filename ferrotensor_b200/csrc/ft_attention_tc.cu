@@ -36,34 +36,39 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 struct AttnSmem {
-  static constexpr int Q_OFF = 0;                          // 128 x 64
-  static constexpr int K_OFF = Q_OFF + TILE_BYTES;         // 2 stages of 64 keys x 64
-  static constexpr int V_OFF = K_OFF + 2 * HALF_TILE;      // 2 stages of 64 keys x 64
-  static constexpr int P_OFF = V_OFF + 2 * HALF_TILE;      // 128 q x 64 keys, K-major
-  static constexpr int BAR_OFF = P_OFF + TILE_BYTES;
-  // q_full, kv_full[2], s_full[2], s_free[2], p_full, o_full
-  static constexpr int NBAR = 9;
+  static constexpr int KV_STAGES = 3;
+  static constexpr int Q_OFF = 0;                                   // 128 x 64
+  static constexpr int K_OFF = Q_OFF + TILE_BYTES;                  // 3 stages of 64 keys x 64
+  static constexpr int V_OFF = K_OFF + KV_STAGES * HALF_TILE;       // 3 stages of 64 keys x 64
+  static constexpr int ONES_OFF = V_OFF + KV_STAGES * HALF_TILE;    // 64 keys x 64: column 0 = 1
+  static constexpr int P_OFF = ONES_OFF + HALF_TILE;                // 2 x (128 q x 64 keys), K-major
+  static constexpr int BAR_OFF = P_OFF + 2 * TILE_BYTES;
+  // q_full, kv_full[3], s_full[2], s_free[2], p_full[2], o_full[2]
+  static constexpr int NBAR = 12;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
 
-// Forward.  64-key blocks; the S accumulator is double-buffered in tensor memory so the
-// product of block j+1 runs while the softmax warps work on block j; each softmax thread
-// reads its 64 scores with one wait and makes a single pass over them.
+// Forward.  64-key blocks; S is double-buffered in tensor memory so the product of block j+1
+// runs while the softmax warps work on block j.  The output stays in tensor memory for the
+// whole row of blocks: P V accumulates there, and an extra all-ones column appended to V makes
+// column 64 of the accumulator the running sum of P, i.e. the softmax denominator, rounded
+// exactly as the numerator is.  The running maximum is only raised (and the accumulator
+// rescaled, by the softmax warps themselves) when a block exceeds it by more than 2^8: until
+// then exp2(s - m) <= 256 is harmless in f16 and the final O / l is unchanged.  Exponentials
+// are taken two at a time in f16 (P is rounded to f16 for the product anyway).
 __global__ void __launch_bounds__(AT_THREADS, 2)
 k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constant__ CUtensorMap map_kv64,
               __half* __restrict__ out16, long long ldo16, float* __restrict__ out32,
               long long ldo32, float* __restrict__ stats, int seq, int heads, int kv_heads,
               int q_col0, int k_col0, int v_col0, float scale_log2e, int* status) {
-  ft_pdl_wait();
-  ft_pdl_launch();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - raw);
   const uint32_t bar0 = base + AttnSmem::BAR_OFF;
-  const uint32_t bar_q = bar0, bar_kv = bar0 + 8, bar_sfull = bar0 + 24, bar_sfree = bar0 + 40,
-                 bar_pfull = bar0 + 56, bar_ofull = bar0 + 64;
+  const uint32_t bar_q = bar0, bar_kv = bar0 + 8, bar_sfull = bar0 + 32, bar_sfree = bar0 + 48,
+                 bar_pfull = bar0 + 64, bar_ofull = bar0 + 80;
   uint32_t* tmem_slot = (uint32_t*)(gbase + AttnSmem::BAR_OFF + AttnSmem::NBAR * 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -75,17 +80,18 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
   const int q0 = qblk * AT_Q;
   const int nblk = min((q0 + AT_Q) / 64, (seq + 63) / 64);  // 64-key blocks at or below the diagonal
   const int tok0 = b * seq;
-  constexpr uint32_t TMEM_COLS = 256;  // S0 [0,64), S1 [64,128), O_j [128,192)
+  constexpr uint32_t TMEM_COLS = 256;  // S0 [0,64), S1 [64,128), O [128,192), sum of P at 192
+  constexpr int O_COLS = 80;           // 64 outputs + the ones column, padded to a multiple of 16
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
+    for (int s = 0; s < 3; ++s) mbar_init(bar_kv + s * 8, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_kv + s * 8, 1);
       mbar_init(bar_sfull + s * 8, 1);
       mbar_init(bar_sfree + s * 8, 4);
+      mbar_init(bar_pfull + s * 8, 4);
+      mbar_init(bar_ofull + s * 8, 1);
     }
-    mbar_init(bar_pfull, 4);
-    mbar_init(bar_ofull, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -95,29 +101,43 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
                  "r"(TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  } else {
+    // the ones block: same swizzled layout as a V tile (row = key, 128 bytes = 64 columns; the
+    // 16-byte chunk c of row k sits at chunk c ^ (k & 7)): column 0 of every key row is 1, the
+    // rest 0.  Thread t writes half a row.
+    uint8_t* ones = gbase + AttnSmem::ONES_OFF;
+    const int t = threadIdx.x, k = t >> 1, hf = t & 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = 4 * hf + i;
+      *(uint4*)(ones + k * 128 + c * 16) = make_uint4(c == (k & 7) ? 0x3C00u : 0u, 0u, 0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 128;
+  ft_pdl_wait();
+  ft_pdl_launch();
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA + MMA issuer
     if (lane == 0) {
       const uint32_t sq = base + AttnSmem::Q_OFF, sk = base + AttnSmem::K_OFF,
                      sv = base + AttnSmem::V_OFF, sp = base + AttnSmem::P_OFF;
-      const uint32_t idesc_s = make_idesc(128, 64, 0, 0);                  // Q, K both K-major
-      const uint32_t idesc_o = make_idesc(128, 64, 0, 0) | (1u << 16);     // V is N-major
+      const uint32_t idesc_s = make_idesc(128, 64, 0, 0);                      // Q, K both K-major
+      const uint32_t idesc_o = make_idesc(128, O_COLS, 0, 0) | (1u << 16);     // V is N-major
       auto load_kv = [&](int j) {
-        const int s = j & 1;
+        const int s = j % 3;
         mbar_expect_tx(bar_kv + s * 8, 2 * HALF_TILE);
         tma_load_2d(sk + s * HALF_TILE, &map_kv64, bar_kv + s * 8, k_col0 + kvh * AT_D, tok0 + j * 64);
         tma_load_2d(sv + s * HALF_TILE, &map_kv64, bar_kv + s * 8, v_col0 + kvh * AT_D, tok0 + j * 64);
       };
       auto mma_s = [&](int j) {
         const int s = j & 1;
-        const uint64_t da = make_desc_sw128(sq), db = make_desc_sw128(sk + s * HALF_TILE);
+        const uint64_t da = make_desc_sw128(sq), db = make_desc_sw128(sk + (j % 3) * HALF_TILE);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           tc_mma_f16(tmem_base + s * 64, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s,
@@ -126,8 +146,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
       };
       mbar_expect_tx(bar_q, TILE_BYTES);
       tma_load_2d(sq, &map_q128, bar_q, q_col0 + h * AT_D, tok0 + q0);
-      load_kv(0);
-      if (nblk > 1) load_kv(1);
+      for (int j = 0; j < 3 && j < nblk; ++j) load_kv(j);
       bool ok = mbar_wait(bar_q, 0, abort_flag, status, 11) &&
                 mbar_wait(bar_kv, 0, abort_flag, status, 12);
       if (ok) {
@@ -138,29 +157,32 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
         if (j + 1 < nblk) {
           // S(j+1) goes to the other accumulator, free once block j-1's scores were read
           const int s = (j + 1) & 1;
-          ok = mbar_wait(bar_kv + s * 8, ((j + 1) >> 1) & 1, abort_flag, status, 13);
+          ok = mbar_wait(bar_kv + ((j + 1) % 3) * 8, ((j + 1) / 3) & 1, abort_flag, status, 13);
           if (ok && j >= 1) ok = mbar_wait(bar_sfree + s * 8, ((j - 1) >> 1) & 1, abort_flag, status, 14);
           if (!ok) break;
           tc_fence_after();
           mma_s(j + 1);
         }
-        ok = mbar_wait(bar_pfull, j & 1, abort_flag, status, 15);
+        if (j >= 1 && j + 2 < nblk) {
+          // stage (j+2) % 3 held block j-1: free once P V(j-1) has run
+          ok = mbar_wait(bar_ofull + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1, abort_flag, status, 17);
+          if (!ok) break;
+          load_kv(j + 2);
+        }
+        ok = mbar_wait(bar_pfull + (j & 1) * 8, (j >> 1) & 1, abort_flag, status, 15);
         if (!ok) break;
         tc_fence_after();
         {
-          // O_j = P[128 q x 64 keys] . V[64 keys x 64 d]: V in place as an N-major operand
-          const uint64_t dp = make_desc_sw128(sp);
-          const uint64_t dv = make_desc_mn_sw128(sv + (j & 1) * HALF_TILE, HALF_TILE);
+          // O += P[128 q x 64 keys] . [V | 1][64 keys x 80]: V in place as an N-major operand,
+          // its second 64-column block is the ones block
+          const uint32_t vs = sv + (j % 3) * HALF_TILE;
+          const uint64_t dp = make_desc_sw128(sp + (j & 1) * TILE_BYTES);
+          const uint64_t dv = make_desc_mn_sw128(vs, (base + AttnSmem::ONES_OFF) - vs);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_o, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * 128), idesc_o, k > 0 ? 1u : 0u);
-          tc_commit(bar_ofull);
-        }
-        if (j + 2 < nblk) {
-          // K/V stage j&1 is free once P V(j) is done (S(j) finished long before)
-          ok = mbar_wait(bar_ofull, j & 1, abort_flag, status, 17);
-          if (!ok) break;
-          load_kv(j + 2);
+            tc_mma_f16(tmem_o, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * 128), idesc_o,
+                       (j > 0 || k > 0) ? 1u : 0u);
+          tc_commit(bar_ofull + (j & 1) * 8);
         }
       }
     }
@@ -170,12 +192,8 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
     const int row = warp * 32 + lane;          // query row in the tile = TMEM lane
     const int qi = q0 + row;                   // position in the sequence
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    uint8_t* p_smem = gbase + AttnSmem::P_OFF;
-    uint8_t* rowp = p_smem + (row >> 3) * 1024 + (row & 7) * 128;
-    float o_acc[AT_D];
-#pragma unroll
-    for (int i = 0; i < AT_D; ++i) o_acc[i] = 0.f;
-    float m2 = -INFINITY, l = 0.f;   // running maximum (log2 domain, scaled) and sum
+    uint8_t* rowp = gbase + AttnSmem::P_OFF + (row >> 3) * 1024 + (row & 7) * 128;
+    float m_st = -INFINITY;   // the maximum the exponentials are taken against (log2 domain)
     bool ok = true;
     for (int j = 0; ok && j < nblk; ++j) {
       const int sb = j & 1;
@@ -191,103 +209,111 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_sfree + sb * 8);
       const int key0 = j * 64;
-      const bool diag = key0 + 63 > q0;         // block touches the diagonal for some row
-      const int lim = diag ? qi - key0 : 64;    // keys [0, lim] of the block are visible
+      if (key0 + 63 > q0) {                     // the block touches the diagonal for some row
+        const int lim = qi - key0;              // keys [0, lim] of the block are visible
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (c > lim) r0[c] = 0xff800000u;     // -inf
+          if (c + 32 > lim) r1[c] = 0xff800000u;
+        }
+      }
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float a = __uint_as_float(r0[c]), bb = __uint_as_float(r1[c]);
-        if (diag) {
-          if (c > lim) a = -INFINITY;
-          if (c + 32 > lim) bb = -INFINITY;
+      for (int c = 0; c < 32; ++c)
+        mx = fmaxf(mx, fmaxf(__uint_as_float(r0[c]), __uint_as_float(r1[c])));
+      const float mxs = mx * scale_log2e;
+      if (j == 0) {
+        m_st = mxs;   // key 0 is visible to every row, so this is finite
+      } else {
+        const bool need = mxs > m_st + 8.0f;
+        if (__any_sync(0xffffffffu, need)) {
+          // raise the maximum and rescale the accumulator (rows that do not need it use 1);
+          // P V(j-1) must have finished, P V(j) cannot start before this warp publishes P(j)
+          const float m_new = need ? mxs : m_st;
+          const float corr = ex2(m_st - m_new);
+          ok = mbar_wait(bar_ofull + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1, abort_flag, status, 22);
+          if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+          tc_fence_after();
+          uint32_t a[32];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            tc_ld32(tmem_o + lane_addr + hh * 32, a);
+            tc_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * corr);
+            tc_st32(tmem_o + lane_addr + hh * 32, a);
+          }
+          uint32_t s16[16];
+          tc_ld16(tmem_o + lane_addr + 64, s16);
+          tc_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 16; ++c) s16[c] = __float_as_uint(__uint_as_float(s16[c]) * corr);
+          tc_st16(tmem_o + lane_addr + 64, s16);
+          tc_wait_st();
+          m_st = m_new;
         }
-        mx = fmaxf(mx, fmaxf(a, bb));
       }
-      const float m_new = fmaxf(m2, mx * scale_log2e);
-      const float corr = ex2(m2 - m_new);       // 0 on the first block (m2 = -inf)
-      float sum = 0.f;
+      // P = exp2(s * scale - m), two at a time in f16
+      const float nm = -m_st;
       uint32_t packed[32];
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
-        float p0 = ex2(fmaf(__uint_as_float(r0[c]), scale_log2e, -m_new));
-        float p1 = ex2(fmaf(__uint_as_float(r0[c + 1]), scale_log2e, -m_new));
-        float p2 = ex2(fmaf(__uint_as_float(r1[c]), scale_log2e, -m_new));
-        float p3 = ex2(fmaf(__uint_as_float(r1[c + 1]), scale_log2e, -m_new));
-        if (diag) {
-          if (c > lim) p0 = 0.f;
-          if (c + 1 > lim) p1 = 0.f;
-          if (c + 32 > lim) p2 = 0.f;
-          if (c + 33 > lim) p3 = 0.f;
-        }
-        sum += (p0 + p1) + (p2 + p3);
-        __half2 h0 = __floats2half2_rn(p0, p1), h1 = __floats2half2_rn(p2, p3);
-        packed[c >> 1] = *(uint32_t*)&h0;
-        packed[16 + (c >> 1)] = *(uint32_t*)&h1;
+        float x0, x1, y0, y1;
+        ffma2(x0, x1, __uint_as_float(r0[c]), __uint_as_float(r0[c + 1]), scale_log2e, scale_log2e, nm, nm);
+        ffma2(y0, y1, __uint_as_float(r1[c]), __uint_as_float(r1[c + 1]), scale_log2e, scale_log2e, nm, nm);
+        packed[c >> 1] = ex2_h2(pack_h2(x0, x1));
+        packed[16 + (c >> 1)] = ex2_h2(pack_h2(y0, y1));
       }
-      // fold the previous block's P V into the running output, then rescale
-      if (j > 0) {
-        ok = mbar_wait(bar_ofull, (j - 1) & 1, abort_flag, status, 22);
+      // this P buffer was last read by P V(j-2)
+      if (j >= 2) {
+        ok = mbar_wait(bar_ofull + sb * 8, ((j - 2) >> 1) & 1, abort_flag, status, 23);
         if (!ok) break;
-        tc_fence_after();
-        uint32_t a0[32], a1[32];
-        tc_ld32(tmem_o + lane_addr, a0);
-        tc_ld32(tmem_o + lane_addr + 32, a1);
-        tc_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          o_acc[c] = (o_acc[c] + __uint_as_float(a0[c])) * corr;
-          o_acc[32 + c] = (o_acc[32 + c] + __uint_as_float(a1[c])) * corr;
-        }
       }
-      // P(j) may be written now: P V(j-1) has finished reading the tile
+      uint8_t* rp = rowp + sb * TILE_BYTES;
 #pragma unroll
       for (int q = 0; q < 8; ++q)
-        *(uint4*)(rowp + ((q ^ (row & 7)) << 4)) =
+        *(uint4*)(rp + ((q ^ (row & 7)) << 4)) =
             make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-      l = l * corr + sum;
-      m2 = m_new;
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull);
+      if (lane == 0) mbar_arrive(bar_pfull + sb * 8);
     }
-    if (ok) ok = mbar_wait(bar_ofull, (nblk - 1) & 1, abort_flag, status, 23);
+    if (ok) ok = mbar_wait(bar_ofull + ((nblk - 1) & 1) * 8, ((nblk - 1) >> 1) & 1, abort_flag, status, 24);
     if (ok) {
       tc_fence_after();
-      uint32_t a0[32], a1[32];
+      uint32_t a0[32], a1[32], s16[16];
       tc_ld32(tmem_o + lane_addr, a0);
       tc_ld32(tmem_o + lane_addr + 32, a1);
+      tc_ld16(tmem_o + lane_addr + 64, s16);
       tc_wait_ld();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        o_acc[c] += __uint_as_float(a0[c]);
-        o_acc[32 + c] += __uint_as_float(a1[c]);
-      }
       if (qi < seq) {
+        const float l = __uint_as_float(s16[0]);
         const float inv = l > 0.f ? 1.0f / l : 0.f;
+        float o_acc[AT_D];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          o_acc[c] = __uint_as_float(a0[c]) * inv;
+          o_acc[32 + c] = __uint_as_float(a1[c]) * inv;
+        }
         const long long tok = (long long)tok0 + qi;
         if (out16) {
           __half* o = out16 + tok * ldo16 + (long long)h * AT_D;
 #pragma unroll
-          for (int i = 0; i < AT_D; i += 8) {
-            __half2 a = __floats2half2_rn(o_acc[i] * inv, o_acc[i + 1] * inv);
-            __half2 bb = __floats2half2_rn(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
-            __half2 c = __floats2half2_rn(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
-            __half2 d = __floats2half2_rn(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
-            *(uint4*)(o + i) = make_uint4(*(uint32_t*)&a, *(uint32_t*)&bb, *(uint32_t*)&c, *(uint32_t*)&d);
-          }
+          for (int i = 0; i < AT_D; i += 8)
+            *(uint4*)(o + i) = make_uint4(pack_h2(o_acc[i], o_acc[i + 1]), pack_h2(o_acc[i + 2], o_acc[i + 3]),
+                                          pack_h2(o_acc[i + 4], o_acc[i + 5]), pack_h2(o_acc[i + 6], o_acc[i + 7]));
         }
         if (out32) {
           float* o = out32 + tok * ldo32 + (long long)h * AT_D;
 #pragma unroll
           for (int i = 0; i < AT_D; i += 4)
-            *(float4*)(o + i) = make_float4(o_acc[i] * inv, o_acc[i + 1] * inv, o_acc[i + 2] * inv,
-                                            o_acc[i + 3] * inv);
+            *(float4*)(o + i) = make_float4(o_acc[i], o_acc[i + 1], o_acc[i + 2], o_acc[i + 3]);
         }
         if (stats) {
           const size_t srow = ((size_t)b * heads + h) * seq + qi;
           // natural-log LSE of the scaled scores
-          stats[2 * srow + 1] = l > 0.f ? (m2 + log2f(l)) * 0.6931471805599453f : 3.0e38f;
+          stats[2 * srow + 1] = l > 0.f ? (m_st + log2f(l)) * 0.6931471805599453f : 3.0e38f;
         }
       }
     }
