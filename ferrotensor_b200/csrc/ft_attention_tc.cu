@@ -14,6 +14,7 @@
 // as the softmax warps have read block j, so it overlaps with their arithmetic and with P V.
 // All waits are bounded (see ft_tc.cuh).
 #include <math.h>
+#include <stdlib.h>
 
 #include "ft_tc.cuh"
 
@@ -24,7 +25,9 @@ using namespace ft_tc;
 constexpr int AT_Q = 128;        // queries per CTA
 constexpr int AT_KV = 128;       // keys per block
 constexpr int AT_D = 64;         // head_dim
-constexpr int AT_THREADS = 160;  // warps 0..3 softmax, warp 4 issuer
+constexpr int AT_THREADS = 160;  // forward: warps 0..3 softmax, warp 4 issuer
+constexpr int BW_THREADS = 288;  // backward: warps 0..7 arithmetic, warp 8 issuer
+constexpr int BW_ISSUER = 8;
 constexpr int TILE_BYTES = 128 * 64 * 2;  // one 128 x 64 f16 tile = 16 KiB
 
 constexpr int HALF_TILE = 64 * 64 * 2;  // 64 x 64 f16 tile = 8 KiB
@@ -57,6 +60,7 @@ struct AttnSmem {
 // rescaled, by the softmax warps themselves) when a block exceeds it by more than 2^8: until
 // then exp2(s - m) <= 256 is harmless in f16 and the final O / l is unchanged.  Exponentials
 // are taken two at a time in f16 (P is rounded to f16 for the product anyway).
+template <int VARIANT>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constant__ CUtensorMap map_kv64,
               __half* __restrict__ out16, long long ldo16, float* __restrict__ out32,
@@ -259,10 +263,20 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
         float x0, x1, y0, y1;
-        ffma2(x0, x1, __uint_as_float(r0[c]), __uint_as_float(r0[c + 1]), scale_log2e, scale_log2e, nm, nm);
-        ffma2(y0, y1, __uint_as_float(r1[c]), __uint_as_float(r1[c + 1]), scale_log2e, scale_log2e, nm, nm);
-        packed[c >> 1] = ex2_h2(pack_h2(x0, x1));
-        packed[16 + (c >> 1)] = ex2_h2(pack_h2(y0, y1));
+        if (VARIANT & 1) {
+          x0 = fmaf(__uint_as_float(r0[c]), scale_log2e, nm); x1 = fmaf(__uint_as_float(r0[c + 1]), scale_log2e, nm);
+          y0 = fmaf(__uint_as_float(r1[c]), scale_log2e, nm); y1 = fmaf(__uint_as_float(r1[c + 1]), scale_log2e, nm);
+        } else {
+          ffma2(x0, x1, __uint_as_float(r0[c]), __uint_as_float(r0[c + 1]), scale_log2e, scale_log2e, nm, nm);
+          ffma2(y0, y1, __uint_as_float(r1[c]), __uint_as_float(r1[c + 1]), scale_log2e, scale_log2e, nm, nm);
+        }
+        if (VARIANT & 2) {
+          packed[c >> 1] = pack_h2(ex2(x0), ex2(x1));
+          packed[16 + (c >> 1)] = pack_h2(ex2(y0), ex2(y1));
+        } else {
+          packed[c >> 1] = ex2_h2(pack_h2(x0, x1));
+          packed[16 + (c >> 1)] = ex2_h2(pack_h2(y0, y1));
+        }
       }
       // this P buffer was last read by P V(j-2)
       if (j >= 2) {
@@ -358,7 +372,7 @@ struct BwdQSmem {
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
 
-__global__ void __launch_bounds__(AT_THREADS, 2)
+__global__ void __launch_bounds__(BW_THREADS, 2)
 k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constant__ CUtensorMap map_kv64,
                  const __grid_constant__ CUtensorMap map_do128, const __half* __restrict__ do16,
                  long long lddo, const __half* __restrict__ o16, long long ldo,
@@ -391,13 +405,13 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
     mbar_init(bar_kv, 1);
     mbar_init(bar_kv + 8, 1);
     mbar_init(bar_spfull, 1);
-    mbar_init(bar_spfree, 4);
-    mbar_init(bar_dsfull, 4);
+    mbar_init(bar_spfree, 8);
+    mbar_init(bar_dsfull, 8);
     mbar_init(bar_dqdone, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == BW_ISSUER) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(TMEM_COLS)
@@ -410,7 +424,7 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 64, tmem_dq = tmem_base + 128;
 
-  if (warp == 4) {
+  if (warp == BW_ISSUER) {
     if (lane == 0) {
       const uint32_t sq = base + BwdQSmem::Q_OFF, sdo = base + BwdQSmem::DO_OFF,
                      sk = base + BwdQSmem::K_OFF, sv = base + BwdQSmem::V_OFF,
@@ -476,10 +490,13 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
     }
     __syncwarp();
   } else {
-    const int row = warp * 32 + lane;
+    // eight warps: warp w works on the 32 query rows of TMEM quadrant w % 4 and on the 32-key
+    // half w / 4 of every block
+    const int quad = warp & 3, hc = warp >> 2;
+    const int row = quad * 32 + lane;
     const int qi = q0 + row;
     const bool row_ok = qi < seq;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     uint8_t* ds_smem = gbase + BwdQSmem::DS_OFF;
     const size_t srow = ((size_t)b * heads + h) * seq + (row_ok ? qi : 0);
     // Delta = dO . O for this row (both f16 in global memory)
@@ -500,7 +517,7 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
         }
       }
       lse2 = stats[2 * srow + 1] * 1.4426950408889634f;
-      stats[2 * srow] = delta;
+      if (hc == 0) stats[2 * srow] = delta;
     }
     const float c2 = scale * 1.4426950408889634f;
     bool ok = true;
@@ -509,25 +526,23 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
       if (!ok) break;
       tc_fence_after();
       const bool need_mask = (j * 64 + 63) > q0;  // block touches the diagonal
-      uint32_t packed[32];
-#pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
+      uint32_t packed[16];
+      {
         uint32_t rs[32], rp[32];
-        tc_ld32(tmem_s + lane_addr + cb * 32, rs);
-        tc_ld32(tmem_dp + lane_addr + cb * 32, rp);
+        tc_ld32(tmem_s + lane_addr + hc * 32, rs);
+        tc_ld32(tmem_dp + lane_addr + hc * 32, rp);
         tc_wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           float v[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int key = j * 64 + cb * 32 + c + e;
+            const int key = j * 64 + hc * 32 + c + e;
             float p = ex2(fmaf(__uint_as_float(rs[c + e]), c2, -lse2));
             if (!row_ok || (need_mask && key > qi)) p = 0.f;
             v[e] = p * (__uint_as_float(rp[c + e]) - delta);
           }
-          __half2 hv = __floats2half2_rn(v[0], v[1]);
-          packed[cb * 16 + (c >> 1)] = *(uint32_t*)&hv;
+          packed[c >> 1] = pack_h2(v[0], v[1]);
         }
       }
       // S and dP are in registers: the next pair of products may overwrite them
@@ -541,8 +556,8 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
       }
       uint8_t* rowp = ds_smem + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        *(uint4*)(rowp + ((q ^ (row & 7)) << 4)) =
+      for (int q = 0; q < 4; ++q)
+        *(uint4*)(rowp + (((hc * 4 + q) ^ (row & 7)) << 4)) =
             make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
@@ -553,8 +568,8 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
       tc_fence_after();
       const float alpha = scale * (inv_scale_ptr ? *inv_scale_ptr : 1.0f);
       float am = 0.f;
-#pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
+      {
+        const int cb = hc;
         uint32_t r[32];
         tc_ld32(tmem_dq + lane_addr + cb * 32, r);
         tc_wait_ld();
@@ -572,7 +587,8 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
       if (amax_slot) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        if (lane == 0 && am > 0.f) atomicMax(amax_slot, __float_as_int(am));
+        if (lane == 0 && am > 0.f && __float_as_int(am) > *(volatile int*)amax_slot)
+          atomicMax(amax_slot, __float_as_int(am));
       }
     }
   }
@@ -583,7 +599,7 @@ k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_cons
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == BW_ISSUER) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(TMEM_COLS)
@@ -598,14 +614,14 @@ struct BwdKSmem {
   static constexpr int DO_OFF = Q_OFF + 2 * HALF_TILE;    // 2 stages of 64 q x 64
   static constexpr int PT_OFF = DO_OFF + 2 * HALF_TILE;   // 128 keys x 64 q, K-major
   static constexpr int DST_OFF = PT_OFF + TILE_BYTES;     // 128 keys x 64 q, K-major
-  static constexpr int ROW_OFF = DST_OFF + TILE_BYTES;    // per warp: 64 x {delta, lse2}
-  static constexpr int BAR_OFF = ROW_OFF + 4 * 64 * 2 * 4;
+  static constexpr int ROW_OFF = DST_OFF + TILE_BYTES;    // per warp: 32 x {delta, lse2}
+  static constexpr int BAR_OFF = ROW_OFF + 8 * 32 * 2 * 4;
   static constexpr int NBAR = 8;  // kv_full, qd_full[2], sp_full, sp_free, ds_full, acc_done, spare
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
 
-__global__ void __launch_bounds__(AT_THREADS, 2)
+__global__ void __launch_bounds__(BW_THREADS, 2)
 k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_constant__ CUtensorMap map_q64,
                   const __grid_constant__ CUtensorMap map_do64, float* __restrict__ dk,
                   float* __restrict__ dv, long long ldd, const float* __restrict__ stats, int seq,
@@ -638,13 +654,13 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
     mbar_init(bar_qd, 1);
     mbar_init(bar_qd + 8, 1);
     mbar_init(bar_spfull, 1);
-    mbar_init(bar_spfree, 4);
-    mbar_init(bar_dsfull, 4);
+    mbar_init(bar_spfree, 8);
+    mbar_init(bar_dsfull, 8);
     mbar_init(bar_acc, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == BW_ISSUER) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(TMEM_COLS)
@@ -658,7 +674,7 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
   const uint32_t tmem_st = tmem_base, tmem_dpt = tmem_base + 64, tmem_dk = tmem_base + 128,
                  tmem_dv = tmem_base + 192;
 
-  if (warp == 4) {
+  if (warp == BW_ISSUER) {
     if (lane == 0) {
       const uint32_t sk = base + BwdKSmem::K_OFF, sv = base + BwdKSmem::V_OFF,
                      sq = base + BwdKSmem::Q_OFF, sdo = base + BwdKSmem::DO_OFF,
@@ -729,10 +745,13 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
     }
     __syncwarp();
   } else {
-    const int row = warp * 32 + lane;       // key row in the tile
+    // eight warps: warp w works on the 32 key rows of TMEM quadrant w % 4 and on the 32-query
+    // half w / 4 of every block
+    const int quad = warp & 3, hc = warp >> 2;
+    const int row = quad * 32 + lane;       // key row in the tile
     const int kj = k0 + row;
     const bool row_ok = kj < seq;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     uint8_t* pt_smem = gbase + BwdKSmem::PT_OFF;
     uint8_t* dst_smem = gbase + BwdKSmem::DST_OFF;
     const float c2 = scale * 1.4426950408889634f;
@@ -740,47 +759,41 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
     for (int it = 0; ok && it < niter; ++it) {
       const int g = it / nqb, i = it % nqb, h = kvh * group + g;
       const int qs = k0 + i * 64;
-      // per-query {Delta, LSE in the log2 domain} of this block: every key row needs the same
-      // 64 pairs, so each warp stages its own copy in shared memory (no cross-warp barrier)
-      float2* qi_s = (float2*)(gbase + BwdKSmem::ROW_OFF) + warp * 64;
+      // per-query {Delta, LSE in the log2 domain} of this warp's 32 queries: every key row needs
+      // the same pairs, so each warp stages its own copy in shared memory (no cross-warp barrier)
+      float2* qi_s = (float2*)(gbase + BwdKSmem::ROW_OFF) + warp * 32;
       {
         const float2* qinfo = (const float2*)(stats + 2 * (((size_t)b * heads + h) * seq));
         __syncwarp();
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const int col = lane + 32 * t;
-          float2 dl = qinfo[min(qs + col, seq - 1)];
-          dl.y *= 1.4426950408889634f;
-          qi_s[col] = dl;
-        }
+        float2 dl = qinfo[min(qs + hc * 32 + lane, seq - 1)];
+        dl.y *= 1.4426950408889634f;
+        qi_s[lane] = dl;
         __syncwarp();
       }
       ok = mbar_wait(bar_spfull, it & 1, abort_flag, status, 61);
       if (!ok) break;
       tc_fence_after();
       const bool need_mask = qs < k0 + AT_KV - 1 || qs + 64 > seq;
-      uint32_t pk_p[32], pk_ds[32];
-#pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
+      uint32_t pk_p[16], pk_ds[16];
+      {
         uint32_t rs[32], rp[32];
-        tc_ld32(tmem_st + lane_addr + cb * 32, rs);
-        tc_ld32(tmem_dpt + lane_addr + cb * 32, rp);
+        tc_ld32(tmem_st + lane_addr + hc * 32, rs);
+        tc_ld32(tmem_dpt + lane_addr + hc * 32, rp);
         tc_wait_ld();
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           float pv[2], dsv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int col = cb * 32 + c + e, qq = qs + col;
-            const float2 dl = qi_s[col];   // x = Delta, y = LSE (log2 domain)
+            const int qq = qs + hc * 32 + c + e;
+            const float2 dl = qi_s[c + e];   // x = Delta, y = LSE (log2 domain)
             float p = ex2(fmaf(__uint_as_float(rs[c + e]), c2, -dl.y));
             if (!row_ok || (need_mask && (kj > qq || qq >= seq))) p = 0.f;
             pv[e] = p;
             dsv[e] = p * (__uint_as_float(rp[c + e]) - dl.x);
           }
-          __half2 hp = __floats2half2_rn(pv[0], pv[1]), hd = __floats2half2_rn(dsv[0], dsv[1]);
-          pk_p[cb * 16 + (c >> 1)] = *(uint32_t*)&hp;
-          pk_ds[cb * 16 + (c >> 1)] = *(uint32_t*)&hd;
+          pk_p[c >> 1] = pack_h2(pv[0], pv[1]);
+          pk_ds[c >> 1] = pack_h2(dsv[0], dsv[1]);
         }
       }
       tc_fence_before();
@@ -792,8 +805,8 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
       }
       const int off = (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const int sw = ((q ^ (row & 7)) << 4);
+      for (int q = 0; q < 4; ++q) {
+        const int sw = (((hc * 4 + q) ^ (row & 7)) << 4);
         *(uint4*)(pt_smem + off + sw) = make_uint4(pk_p[4 * q], pk_p[4 * q + 1], pk_p[4 * q + 2], pk_p[4 * q + 3]);
         *(uint4*)(dst_smem + off + sw) = make_uint4(pk_ds[4 * q], pk_ds[4 * q + 1], pk_ds[4 * q + 2], pk_ds[4 * q + 3]);
       }
@@ -807,8 +820,8 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
       const float inv_s = inv_scale_ptr ? *inv_scale_ptr : 1.0f;
       const float ak = scale * inv_s, av = inv_s;
       float am = 0.f;
-#pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
+      {
+        const int cb = hc;
         uint32_t rk[32], rv[32];
         tc_ld32(tmem_dk + lane_addr + cb * 32, rk);
         tc_ld32(tmem_dv + lane_addr + cb * 32, rv);
@@ -832,7 +845,8 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
       if (amax_slot) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        if (lane == 0 && am > 0.f) atomicMax(amax_slot, __float_as_int(am));
+        if (lane == 0 && am > 0.f && __float_as_int(am) > *(volatile int*)amax_slot)
+          atomicMax(amax_slot, __float_as_int(am));
       }
     }
   }
@@ -843,7 +857,7 @@ k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_co
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == BW_ISSUER) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(TMEM_COLS)
@@ -869,16 +883,28 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
   FT_TRY(ft_tc::make_map(ctx, &kv64, qkv16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)ld,
                          (uint64_t)batch * seq, (uint64_t)ld, 64, 64));
   static bool configured = false;
+  static int variant = 0;
   if (!configured) {
-    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 AttnSmem::DYN_BYTES));
+    if (const char* v = getenv("FT_ATTN_VARIANT")) variant = atoi(v) & 3;
+    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::DYN_BYTES));
+    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::DYN_BYTES));
+    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::DYN_BYTES));
+    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::DYN_BYTES));
     configured = true;
   }
   dim3 grid(ft_cdiv(seq, AT_Q), batch * heads);
   const float scale_log2e = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
-  FT_LAUNCH_PDL(ctx, k_attn_fwd_tc, grid, AT_THREADS, AttnSmem::DYN_BYTES, q128, kv64, out16, ldo16, out32,
-            ldo32, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale_log2e,
-            ctx->status_dev);
+#define FT_FWD_LAUNCH(V)                                                                          \
+  FT_LAUNCH_PDL(ctx, k_attn_fwd_tc<V>, grid, AT_THREADS, AttnSmem::DYN_BYTES, q128, kv64, out16, \
+                ldo16, out32, ldo32, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0,        \
+                scale_log2e, ctx->status_dev)
+  switch (variant) {
+    case 1: FT_FWD_LAUNCH(1); break;
+    case 2: FT_FWD_LAUNCH(2); break;
+    case 3: FT_FWD_LAUNCH(3); break;
+    default: FT_FWD_LAUNCH(0); break;
+  }
+#undef FT_FWD_LAUNCH
   return FT_OK;
 }
 
@@ -917,13 +943,13 @@ int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
   if (am) ctx->amax_ready = true;
   {
     dim3 grid(ft_cdiv(seq, AT_Q), batch * heads);
-    FT_LAUNCH_PDL(ctx, k_attn_bwd_dq_tc, grid, AT_THREADS, BwdQSmem::DYN_BYTES, q128, kv64, do128, do16,
+    FT_LAUNCH_PDL(ctx, k_attn_bwd_dq_tc, grid, BW_THREADS, BwdQSmem::DYN_BYTES, q128, kv64, do128, do16,
               lddo, o16, ldo, dq, lddq, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale,
               inv_scale, am, ctx->status_dev);
   }
   {
     dim3 grid(ft_cdiv(seq, AT_KV), batch * kv_heads);
-    FT_LAUNCH_PDL(ctx, k_attn_bwd_dkv_tc, grid, AT_THREADS, BwdKSmem::DYN_BYTES, q128, kv64, do64, dk, dv,
+    FT_LAUNCH_PDL(ctx, k_attn_bwd_dkv_tc, grid, BW_THREADS, BwdKSmem::DYN_BYTES, q128, kv64, do64, dk, dv,
               ldd, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale, inv_scale, am,
               ctx->status_dev);
   }

@@ -234,6 +234,11 @@ int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b
                    float* out, long long ldo, int rows, int n);
 int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
                      __half* out, long long ldo, int rows, int n, int* in_amax = nullptr);
+int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* out, long long ldo,
+                      int rows, int n, int* in_amax);
+int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const float* g,
+                          long long ldg, __half* out, long long ldo, int rows, int n,
+                          const int* in_amax, const float** scales_out);
 int ft_k_silu_gate_bwd16(FtContext* ctx, const float* a, long long lda, const float* b,
                          long long ldb, const float* g, long long ldg, __half* out, long long ldo,
                          int rows, int n, const int* in_amax, const float** scales_out);

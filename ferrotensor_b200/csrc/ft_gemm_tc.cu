@@ -342,7 +342,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1)
         amax_seen = fmaxf(amax_seen, __shfl_xor_sync(0xffffffffu, amax_seen, o));
-      if (lane == 0 && amax_seen > 0.f) atomicMax(ep.amax_slot, __float_as_int(amax_seen));
+      if (lane == 0 && amax_seen > 0.f && __float_as_int(amax_seen) > *(volatile int*)ep.amax_slot)
+        atomicMax(ep.amax_slot, __float_as_int(amax_seen));
     }
   }
 

@@ -31,6 +31,17 @@ __device__ __forceinline__ float block_sum(float v, float* buf) {
   float r = (lane < nw) ? buf[lane] : 0.f;
   return warp_sum(r);
 }
+// Two sums with one pair of barriers.  `buf` holds 64 floats.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* buf) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  __syncthreads();
+  if (lane == 0) { buf[w] = a; buf[32 + w] = b; }
+  __syncthreads();
+  a = warp_sum((lane < nw) ? buf[lane] : 0.f);
+  b = warp_sum((lane < nw) ? buf[32 + lane] : 0.f);
+}
 __device__ __forceinline__ float block_max(float v, float* buf) {
   int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
   v = warp_max(v);
@@ -48,7 +59,10 @@ __device__ __forceinline__ bool aligned16(const void* p) { return (((uintptr_t)p
 __device__ __forceinline__ void amax_commit(float m, int* slot) {
   if (!slot) return;
   m = warp_max(m);
-  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(slot, __float_as_int(m));
+  // thousands of warps fold into one word: look first, and leave the atomic to the few that
+  // would raise it (a stale read only costs an unnecessary atomic)
+  if ((threadIdx.x & 31) == 0 && m > 0.f && __float_as_int(m) > *(volatile int*)slot)
+    atomicMax(slot, __float_as_int(m));
 }
 __device__ __forceinline__ float amax4(float m, float4 v) {
   return fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
@@ -219,12 +233,12 @@ k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
                    int accumulate, int* amax_slot) {
   ft_pdl_wait();
   ft_pdl_launch();
-  __shared__ float red[32];
+  __shared__ float red[64];
   const int n4 = n >> 2;
   const size_t off = (size_t)blockIdx.x * n;
   const float4 *x4 = (const float4*)(x + off), *g4 = (const float4*)(g + off), *w4 = (const float4*)w;
   float4* o4 = (float4*)(gx + off);
-  float4 xv[NV], gv[NV];   // gv holds g * w
+  float4 xv[NV], gv[NV], pv[NV];   // gv holds g * w, pv what the result is added to
   float ss = 0.f, gwx = 0.f;
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
@@ -233,14 +247,15 @@ k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
       xv[k] = x4[i];
       const float4 b = g4[i], c = w4[i];
       gv[k] = make_float4(b.x * c.x, b.y * c.y, b.z * c.z, b.w * c.w);
+      // in flight during the reductions instead of after them
+      pv[k] = accumulate ? o4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     } else {
-      xv[k] = gv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      xv[k] = gv[k] = pv[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
     gwx += gv[k].x * xv[k].x + gv[k].y * xv[k].y + gv[k].z * xv[k].z + gv[k].w * xv[k].w;
   }
-  ss = block_sum(ss, red);
-  gwx = block_sum(gwx, red);
+  block_sum2(ss, gwx, red);
   const float inv = 1.0f / sqrtf(ss / (float)n + eps);
   const float coef = gwx * inv * inv * inv / (float)n;
   float am = 0.f;
@@ -250,10 +265,7 @@ k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
     if (i >= n4) continue;
     float4 r = make_float4(gv[k].x * inv - xv[k].x * coef, gv[k].y * inv - xv[k].y * coef,
                            gv[k].z * inv - xv[k].z * coef, gv[k].w * inv - xv[k].w * coef);
-    if (accumulate) {
-      const float4 p = o4[i];
-      r.x += p.x; r.y += p.y; r.z += p.z; r.w += p.w;
-    }
+    r.x += pv[k].x; r.y += pv[k].y; r.z += pv[k].z; r.w += pv[k].w;
     o4[i] = r;
     am = amax4(am, r);
   }
@@ -425,6 +437,87 @@ __global__ void k_silu_gate16(const float* __restrict__ a, long long lda,
     am = amax4(amax4(am, x), y);
   }
   amax_commit(am, in_amax);
+}
+
+// The same from f16 gate | up rows (the projection wrote them as f16): 8 columns per thread.
+__global__ void k_silu_gate16h(const __half* __restrict__ a, const __half* __restrict__ b,
+                               long long ldab, __half* __restrict__ out, long long ldo, int rows,
+                               int n, int* in_amax) {
+  ft_pdl_wait();
+  ft_pdl_launch();
+  size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  float am = 0.f;
+  for (; i < total; i += st) {
+    size_t r = i / per_row, c = (i % per_row) * 8;
+    const uint4 xa = *(const uint4*)(a + r * ldab + c), ya = *(const uint4*)(b + r * ldab + c);
+    const __half2* xh = (const __half2*)&xa;
+    const __half2* yh = (const __half2*)&ya;
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = __half22float2(xh[k]), y = __half22float2(yh[k]);
+      const float v0 = x.x / (1.0f + expf(-x.x)) * y.x, v1 = x.y / (1.0f + expf(-x.y)) * y.y;
+      __half2 h = __floats2half2_rn(v0, v1);
+      o[k] = *(uint32_t*)&h;
+      am = fmaxf(am, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(y.x), fabsf(y.y))));
+    }
+    *(uint4*)(out + r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  amax_commit(am, in_amax);
+}
+
+// SwiGLU backward from f16 gate | up rows, see k_silu_gate_bwd16 for the scale.
+__global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* __restrict__ b,
+                                   long long ldab, const float* __restrict__ g, long long ldg,
+                                   __half* __restrict__ out, long long ldo, int rows, int n,
+                                   const int* __restrict__ g_amax, const int* __restrict__ in_amax,
+                                   float* __restrict__ scales_out) {
+  ft_pdl_wait();
+  ft_pdl_launch();
+  float S = 1.0f;
+  {
+    float bound = 1.1f * __int_as_float(*g_amax) * __int_as_float(*in_amax);
+    if (bound > 0.f && isfinite(bound)) {
+      int e;
+      frexpf(bound, &e);
+      S = ldexpf(1.0f, 13 - e);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      scales_out[0] = S;
+      scales_out[1] = 1.0f / S;
+      scales_out[2] = ldexpf(1.0f / S, -11);
+    }
+  }
+  size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += st) {
+    size_t r = i / per_row, c = (i % per_row) * 8;
+    const uint4 xa = *(const uint4*)(a + r * ldab + c), ya = *(const uint4*)(b + r * ldab + c);
+    const float4 g0 = *(const float4*)(g + r * ldg + c), g1 = *(const float4*)(g + r * ldg + c + 4);
+    const __half2* xh = (const __half2*)&xa;
+    const __half2* yh = (const __half2*)&ya;
+    const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    uint32_t oa[4], ob[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = __half22float2(xh[k]), y = __half22float2(yh[k]);
+      const float xs[2] = {x.x, x.y}, ys[2] = {y.x, y.y};
+      float va[2], vb[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float s = 1.0f / (1.0f + expf(-xs[e]));
+        const float gk = gs[2 * k + e] * S;
+        vb[e] = gk * (xs[e] * s);
+        va[e] = gk * ys[e] * (s * (1.0f + xs[e] * (1.0f - s)));
+      }
+      __half2 ha = __floats2half2_rn(va[0], va[1]), hb = __floats2half2_rn(vb[0], vb[1]);
+      oa[k] = *(uint32_t*)&ha;
+      ob[k] = *(uint32_t*)&hb;
+    }
+    *(uint4*)(out + r * ldo + c) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    *(uint4*)(out + r * ldo + n + c) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+  }
 }
 
 // SwiGLU backward straight to f16 tensor-core operands: out16[r, c] = S d(gate), out16[r, n + c]
@@ -888,6 +981,33 @@ int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float*
              "silu_gate16: width and pitches must be multiples of 4");
   FT_LAUNCH_PDL(ctx, k_silu_gate16, ew_grid(ctx, (size_t)rows * n / 4), 256, 0, a, lda, b, ldb, out, ldo,
             rows, n, in_amax);
+  return FT_OK;
+}
+
+int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* out, long long ldo,
+                      int rows, int n, int* in_amax) {
+  FT_REQUIRE((n % 8) == 0 && (ld % 8) == 0 && (ldo % 8) == 0 && (((uintptr_t)gu) & 15) == 0 &&
+                 (((uintptr_t)out) & 15) == 0,
+             "silu_gate16h: width and pitches must be multiples of 8");
+  FT_LAUNCH_PDL(ctx, k_silu_gate16h, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu, gu + n, ld,
+                out, ldo, rows, n, in_amax);
+  return FT_OK;
+}
+
+int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const float* g,
+                          long long ldg, __half* out, long long ldo, int rows, int n,
+                          const int* in_amax, const float** scales_out) {
+  FT_REQUIRE((n % 8) == 0 && (ld % 8) == 0 && (ldg % 4) == 0 && (ldo % 8) == 0 &&
+                 ((((uintptr_t)gu) | ((uintptr_t)g) | ((uintptr_t)out)) & 15) == 0,
+             "silu_gate_bwd16h: width and pitches must be multiples of 8");
+  FT_REQUIRE(ctx->amax_ready && ctx->amax_out && in_amax,
+             "silu_gate_bwd16h: the upstream gradient's amax must have been armed and produced");
+  const int* g_amax = ctx->amax_out;
+  ctx->amax_out = nullptr;
+  ctx->amax_ready = false;
+  FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16h, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu, gu + n,
+                ld, g, ldg, out, ldo, rows, n, g_amax, in_amax, ctx->scale_buf + 4);
+  *scales_out = ctx->scale_buf + 4;
   return FT_OK;
 }
 

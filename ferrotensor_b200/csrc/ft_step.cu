@@ -61,7 +61,7 @@ struct BlockActs {
   float *h1, *qkv, *attn, *stats, *x1, *h2, *gu, *f;
   float *xa_qkv, *xa_o, *xa_gu, *xa_down;
   // fused tensor-core path: GEMM inputs are kept as f16 only
-  __half *h1_16, *qkv16, *attn16, *h2_16, *f_16;
+  __half *h1_16, *qkv16, *attn16, *h2_16, *f_16, *gu16;
   __half *xa16_qkv, *xa16_o, *xa16_gu, *xa16_down;
 };
 
@@ -127,7 +127,7 @@ bool use_fused(const FtLoraModel* m) {
   for (const auto& ly : m->layers)
     for (const Group* g : {&ly.qkv, &ly.o, &ly.gu, &ly.down})
       if (!g->w_nk || (g->R > 0 && !g->tc_lora)) return false;
-  return m->head.w_nk && (m->head.R == 0 || m->head.tc_lora) && (m->cfg.ffn % 4) == 0;
+  return m->head.w_nk && (m->head.R == 0 || m->head.tc_lora) && (m->cfg.ffn % 8) == 0;
 }
 
 void setup_group(Group& g, std::initializer_list<Linear*> lins, int rank) {
@@ -176,7 +176,7 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
       a.stats = b.take<float>((size_t)sequences * c.heads * seq_len * 2);
       a.x1 = b.take<float>(T * c.hidden);
       a.h2_16 = b.take<__half>(T * c.hidden);
-      a.gu = b.take<float>(T * 2 * c.ffn);
+      a.gu16 = b.take<__half>(T * 2 * c.ffn);   // gate | up kept as f16 only
       a.f_16 = b.take<__half>(T * c.ffn);
       a.xa16_qkv = b.take<__half>(T * RP);
       a.xa16_o = b.take<__half>(T * RP);
@@ -464,7 +464,8 @@ int pack_all(FtLoraModel* m) {
 
 // Y[T, n] = X16 . W + (alpha/r)(X16 . A) . B (+ bias) (+ residual); keeps xa16 = (alpha/r) X16 . A
 int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y, long long ldy,
-                     __half* xa16, const float* residual, long long ldr, int T) {
+                     __half* xa16, const float* residual, long long ldr, int T,
+                     __half* Y16 = nullptr) {
   FtContext* ctx = m->ctx;
   if (g.R > 0) {
     FtGemmArgs a;
@@ -477,7 +478,8 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
   a.a = X16; a.lda = g.in; a.b = g.w_nk; a.ldb = g.in;
   a.M = T; a.N = g.n; a.K = g.in;
   if (g.R > 0) { a.a2 = xa16; a.lda2 = RP; a.b2 = g.b_bdT16; a.ldb2 = RP; a.K2 = RP; }
-  a.c = Y; a.ldc = ldy; a.bias = g.bias_cat; a.residual = residual; a.ldr = ldr;
+  a.c = Y; a.ldc = ldy; a.c16 = Y16; a.ldc16 = ldy;   // Y16: the result as f16 (pitch ldy)
+  a.bias = g.bias_cat; a.residual = residual; a.ldr = ldr;
   return ft_gemm_tc_ex(ctx, a);
 }
 
@@ -601,8 +603,8 @@ int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, 
   // x1 = x_in + o(attn): the residual rides in the GEMM epilogue
   FT_TRY(linear_fwd_fused(m, ly.o, a.attn16, a.x1, h, a.xa16_o, x_in, h, T));
   FT_TRY(ft_k_rms_norm16(ctx, a.x1, ly.norm2, nullptr, a.h2_16, T, h, c.eps));
-  FT_TRY(linear_fwd_fused(m, ly.gu, a.h2_16, a.gu, 2 * F, a.xa16_gu, nullptr, 0, T));
-  FT_TRY(ft_k_silu_gate16(ctx, a.gu, 2 * F, a.gu + F, 2 * F, a.f_16, F, T, F, m->gu_amax + l));
+  FT_TRY(linear_fwd_fused(m, ly.gu, a.h2_16, nullptr, 2 * F, a.xa16_gu, nullptr, 0, T, a.gu16));
+  FT_TRY(ft_k_silu_gate16h(ctx, a.gu16, 2 * F, a.f_16, F, T, F, m->gu_amax + l));
   FT_TRY(linear_fwd_fused(m, ly.down, a.f_16, x_out, h, a.xa16_down, a.x1, h, T));
   return FT_OK;
 }
@@ -618,8 +620,8 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, m->dx, h, a.xa16_down, m->df, F, nullptr, 0, T,
                           nullptr, nullptr, true));
   const float* gu_scales = nullptr;
-  FT_TRY(ft_k_silu_gate_bwd16(ctx, a.gu, 2 * F, a.gu + F, 2 * F, m->df, F, m->cvt_hi, 2 * F, T, F,
-                              m->gu_amax + l, &gu_scales));
+  FT_TRY(ft_k_silu_gate_bwd16h(ctx, a.gu16, 2 * F, m->df, F, m->cvt_hi, 2 * F, T, F, m->gu_amax + l,
+                               &gu_scales));
   FT_TRY(linear_bwd_fused(m, ly.gu, a.h2_16, nullptr, 2 * F, a.xa16_gu, m->dh, h, nullptr, 0, T,
                           m->cvt_hi, gu_scales));
   FT_TRY(ft_amax_arm(ctx));

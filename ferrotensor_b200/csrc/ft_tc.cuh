@@ -14,7 +14,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;            // 64 x 16-bit = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 320; // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
-constexpr uint32_t SPIN_LIMIT = 1u << 26;  // ~ seconds of polling at most
+constexpr uint32_t SPIN_LIMIT = 1u << 26;  // attempts
+constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // four seconds: no legitimate wait is near it
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -40,13 +41,34 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (and raises the abort flag) when it gave up.
+// The waiting form: the thread may be suspended by the hardware until the phase completes or a
+// system-chosen time limit passes, so a waiting warp does not compete for issue slots.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after WAIT_LIMIT_NS (or SPIN_LIMIT attempts, whichever comes first).
+// Returns false (and raises the abort flag) when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int where) {
+  if (mbar_try(bar, parity)) return true;
   if (*abort_flag) return false;
+  const uint64_t t0 = global_ns();
   uint32_t spins = 0;
-  while (!mbar_test(bar, parity)) {
-    if (++spins > SPIN_LIMIT || *abort_flag) {
+  while (!mbar_try(bar, parity)) {
+    if (*abort_flag || ++spins > SPIN_LIMIT || global_ns() - t0 > WAIT_LIMIT_NS) {
       if (!*abort_flag) {
         *abort_flag = 1;
         // the status word lives in pinned host memory: plain stores, first writer wins
@@ -60,7 +82,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
       return false;
     }
-    if ((spins & 1023u) == 0) __nanosleep(64);
   }
   return true;
 }

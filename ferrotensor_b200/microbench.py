@@ -1,0 +1,116 @@
+"""Kernel micro-benchmarks through the public engine calls, at shapes chosen on the command line.
+
+    python -m ferrotensor_b200.microbench gemm --m 8192 --n 8192 --k 2048
+    python -m ferrotensor_b200.microbench attention --batch 8 --seq 1024 --heads 32 --kv-heads 32
+
+Each case holds a few hundred MB on the device at most, which makes it the right target for a
+profiler capture of one kernel (the training step keeps tens of GB resident).  Times come from
+the library's per-kernel CUDA-event profiler, one line per kernel name.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+import torch
+
+from .engine import AttentionOptions, ComputeEngine, CudaContext, DType, GemmMode, UnifiedTensor
+
+
+def _dev_f32(ctx, shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    t = torch.randn(int(np.prod(shape)), device="cuda", generator=g) * scale
+    return UnifiedTensor(t.view(torch.uint8), list(shape), DType.F32)
+
+
+def _report(ctx, what, extra):
+    rep = ctx.profile_report()
+    ctx.profile(0)
+    out = {"case": what, **extra, "kernels": {}}
+    for name, (launches, ms) in rep.items():
+        out["kernels"][name] = {"launches": launches, "ms_per_launch": ms / max(launches, 1)}
+    print(json.dumps(out))
+    return out
+
+
+def gemm(args):
+    ctx = CudaContext(0)
+    eng = ComputeEngine(ctx)
+    ctx.set_gemm_mode(GemmMode.F16)
+    a = _dev_f32(ctx, [args.m, args.k], 1.0, 1)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    b = UnifiedTensor((torch.randn(args.n * args.k, device="cuda", generator=g) * 0.05).half()
+                      .view(torch.uint8), [args.n, args.k], DType.FP16)
+    out = UnifiedTensor.empty(ctx, [args.m, args.n])
+    for _ in range(args.warmup):
+        eng.matmul_bt_f16b(ctx, a, b, out)
+    ctx.profile(2)
+    for _ in range(args.iters):
+        eng.matmul_bt_f16b(ctx, a, b, out)
+    ctx.synchronize()
+    rep = _report(ctx, "gemm", {"m": args.m, "n": args.n, "k": args.k})
+    for name, v in rep["kernels"].items():
+        if name.startswith("k_gemm_tc"):
+            tf = 2.0 * args.m * args.n * args.k / (v["ms_per_launch"] * 1e-3) / 1e12
+            print(f"{name}: {v['ms_per_launch'] * 1e3:.1f} us, {tf:.0f} TFLOP/s")
+
+
+def attention(args):
+    ctx = CudaContext(0)
+    eng = ComputeEngine(ctx)
+    ctx.set_gemm_mode(GemmMode.F16)
+    b, s, h, hk, d = args.batch, args.seq, args.heads, args.kv_heads, 64
+    q = _dev_f32(ctx, [b, s, h, d], 1.0, 1)
+    k = _dev_f32(ctx, [b, s, hk, d], 1.0, 2)
+    v = _dev_f32(ctx, [b, s, hk, d], 1.0, 3)
+    go = _dev_f32(ctx, [b, s, h, d], 1e-3, 4)
+    out = UnifiedTensor.empty(ctx, [b, s, h, d])
+    stats = UnifiedTensor.empty(ctx, [b * h * s * 2])
+    gq = UnifiedTensor.empty(ctx, [b, s, h, d])
+    gk = UnifiedTensor.empty(ctx, [b, s, hk, d])
+    gv = UnifiedTensor.empty(ctx, [b, s, hk, d])
+    opts = AttentionOptions(causal=True)
+
+    def once():
+        eng.flash_attention_v2_with_stats(ctx, q, k, v, out, stats, opts)
+        if not args.forward_only:
+            eng.flash_attention_v2_backward_with_stats(ctx, q, k, v, out, go, gq, gk, gv, stats, opts)
+
+    for _ in range(args.warmup):
+        once()
+    ctx.profile(2)
+    for _ in range(args.iters):
+        once()
+    ctx.synchronize()
+    rep = _report(ctx, "attention", {"batch": b, "seq": s, "heads": h, "kv_heads": hk})
+    fwd_flop = 4.0 * b * h * s * s * d / 2          # causal: half of the score matrix
+    for name, mult in (("k_attn_fwd_tc", 1.0), ("k_attn_bwd_dq_tc", 1.5), ("k_attn_bwd_dkv_tc", 2.0)):
+        if name in rep["kernels"]:
+            ms = rep["kernels"][name]["ms_per_launch"]
+            print(f"{name}: {ms * 1e3:.1f} us, {fwd_flop * mult / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    sub = ap.add_subparsers(dest="case", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192)
+    g.add_argument("--n", type=int, default=8192)
+    g.add_argument("--k", type=int, default=2048)
+    a = sub.add_parser("attention")
+    a.add_argument("--batch", type=int, default=8)
+    a.add_argument("--seq", type=int, default=1024)
+    a.add_argument("--heads", type=int, default=32)
+    a.add_argument("--kv-heads", type=int, default=32)
+    a.add_argument("--forward-only", action="store_true")
+    for p in (g, a):
+        p.add_argument("--iters", type=int, default=5)
+        p.add_argument("--warmup", type=int, default=2)
+    args = ap.parse_args()
+    {"gemm": gemm, "attention": attention}[args.case](args)
+
+
+if __name__ == "__main__":
+    main()
