@@ -64,6 +64,7 @@ extern "C" int ft_ctx_create(int device, void* stream, FtContext** out) {
   if (const char* pd = getenv("FT_PDL")) ctx->pdl = atoi(pd) != 0;
   FT_CUDA(cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
   FT_CUDA(cudaMalloc((void**)&ctx->scale_buf, 8 * sizeof(float)));
+  FT_CUDA(cudaMalloc((void**)&ctx->pre_flags, FT_PRE_FLAGS * sizeof(int)));
   {
     const float init[8] = {0.f, 1.0f / 2048.0f, 0.f, 0.f, 1.f, 1.f, 1.0f / 2048.0f, 0.f};
     FT_CUDA(cudaMemcpy(ctx->scale_buf, init, sizeof(init), cudaMemcpyHostToDevice));
@@ -82,6 +83,7 @@ extern "C" int ft_ctx_destroy(FtContext* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->scale_buf) cudaFree(ctx->scale_buf);
+  if (ctx->pre_flags) cudaFree(ctx->pre_flags);
   for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);

@@ -34,6 +34,7 @@ struct FtContext {
   // of what they write into scale_buf[0] (atomicMax), and the next auto-scaled conversion
   // uses it instead of making its own pass over the tensor.
   bool pdl = true;   // programmatic dependent launch for the kernels that support it
+  int* pre_flags = nullptr;   // FT_PRE_FLAGS per-row-block flags of the adapter pre-tiles
   int* amax_out = nullptr;
   bool amax_ready = false;
   int tile_m_override = 0;   // FT_GEMM_TILE_M: 128 or 256 forces the GEMM tile height
@@ -77,6 +78,8 @@ int ft_cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 
 void ft_prof_begin(FtContext* ctx, const char* name);
 void ft_prof_end(FtContext* ctx);
+
+constexpr int FT_PRE_FLAGS = 4096;
 
 // Launch on the context's stream, count the launch and surface launch errors.
 #define FT_LAUNCH(ctx, kernel, grid, block, smem, ...)                          \
@@ -174,6 +177,12 @@ struct FtGemmArgs {
   const float* bias = nullptr;
   const float* residual = nullptr; long long ldr = 0;
   bool want_amax = false;   // contribute the output's largest magnitude to an armed amax slot
+  // adapter pre-tiles: when pre_b is set, the launch first computes
+  //   pre_c16[M, 64] (f16, pitch pre_ldc16) = pre_alpha * A . pre_b^T   (pre_b [64, K], f16)
+  // which is normally the very buffer a2 points at (the K-concatenated tail operand)
+  const void* pre_b = nullptr; long long pre_ldb = 0;
+  __half* pre_c16 = nullptr; long long pre_ldc16 = 0;
+  float pre_alpha = 1.f;
 };
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g);
 // Token-reduction product P[M, N<=64] = sum_t A[t,m] B[t,n] (A [T,M], B [T,N], f16) as K-split

@@ -62,6 +62,47 @@ struct Epilogue {
   int* amax_slot;   // when set, the largest |v| written is folded into it (atomicMax)
 };
 
+// Adapter pre-tiles.  When the K-concatenated tail operand A2 (= alpha/r * A . Bpre^T, 64 columns)
+// does not exist yet, the same launch computes it: `tiles` extra tiles of TM rows x 64 columns,
+// handed to the CTAs in reverse order (the CTAs with the fewest output tiles take them first),
+// each streaming A against Bpre over the whole of K and writing f16 rows to c16.  A finished
+// pre-tile raises flags[m tile] by one per epilogue warp; an output tile reads its tail
+// k-blocks only after its flag reached 8.  Pre-tiles wait for nothing, so they always finish.
+struct PreTile {
+  int tiles;          // 0: no pre-tiles in this launch
+  __half* c16;        // [M, 64]
+  long long ldc16;
+  float alpha;
+  int* flags;         // one per m tile, zero at launch
+  uint32_t idesc;     // instruction descriptor for N = 64
+};
+
+__device__ __forceinline__ bool flag_wait(const int* flag, int target, volatile int* abort_flag,
+                                          int* status, int where) {
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= target) break;
+    if (*abort_flag || global_ns() - t0 > WAIT_LIMIT_NS) {
+      if (!*abort_flag) {
+        *abort_flag = 1;
+        volatile int* st = status;
+        if (st[0] == 0) {
+          st[1] = (int)blockIdx.x;
+          st[2] = v;
+          st[0] = 100 + where;
+        }
+      }
+      return false;
+    }
+    __nanosleep(200);
+  }
+  // what other SMs wrote with ordinary stores is read next by TMA (the async proxy)
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
+}
+
 // KOUTER = false:  C[M,N] = A[M,K] . B[N,K]^T (+ A2[M,K2] . B2[N,K2]^T), operands K-contiguous.
 // KOUTER = true :  C[M,N] = sum_t A[t,m] B[t,n], operands given as [T, M] and [T, N] (the
 //                  token-reduction products of the adapter gradients); BN = 64, the tile list
@@ -70,8 +111,8 @@ template <int BN, int STAGES, bool KOUTER, int MH = 1>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
           const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
-          Epilogue ep, int M, int N, int K, int K2, int splits, uint32_t idesc, int* status,
-          int* dbg) {
+          const __grid_constant__ CUtensorMap map_b3, Epilogue ep, PreTile pre, int M, int N, int K,
+          int K2, int splits, uint32_t idesc, int* status, int* dbg) {
   using L = SmemLayout<BN, STAGES, MH>;
   static_assert(MH == 1 || (BN == 256 && !KOUTER), "the 256-row tile exists for BN = 256 only");
   constexpr int TM = MH * BM;  // rows of an output tile
@@ -132,12 +173,32 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
+      if constexpr (!KOUTER) {
+        for (int p = (int)gridDim.x - 1 - (int)blockIdx.x; p < pre.tiles; p += gridDim.x) {
+          for (int kb = 0; kb < kb_main; ++kb) {
+            if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, status, 5)) break;
+            const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+            const uint32_t bar = bar_full + stage * 8;
+            mbar_expect_tx(bar, L::A_BYTES + 64 * BK * 2);
+            tma_load_2d(sa, &map_a, bar, kb * BK, p * TM);
+            tma_load_2d(sb, &map_b3, bar, kb * BK, 0);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (*abort_flag) break;
+        }
+      }
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
         const int kb0 = KOUTER ? nt * kb_per_split : 0;
         const int kb1 = KOUTER ? min(kb_main, kb0 + kb_per_split) : kb_total;
         for (int kb = kb0; kb < kb1; ++kb) {
           FT_MARK(7, 20);
+          if constexpr (!KOUTER) {
+            // the tail operand of this row block comes from a pre-tile of this same launch
+            if (kb == kb_main && pre.tiles > 0 &&
+                !flag_wait(pre.flags + (tile % tiles_m), 8, abort_flag, status, 6))
+              break;
+          }
           if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, status, 1)) break;
           const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
           const uint32_t bar = bar_full + stage * 8;
@@ -167,7 +228,34 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       int local = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      if constexpr (!KOUTER) {
+        for (int p = (int)gridDim.x - 1 - (int)blockIdx.x; p < pre.tiles; p += gridDim.x, ++local) {
+          const uint32_t buf = MH == 1 ? (local & 1) : 0;
+          const uint32_t acc_phase = MH == 1 ? ((local >> 1) & 1) : (local & 1);
+          if (!mbar_wait(bar_tempty + buf * 8, acc_phase ^ 1, abort_flag, status, 7)) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          for (int kb = 0; kb < kb_main; ++kb) {
+            if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, status, 8)) break;
+            tc_fence_after();
+            const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+            const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sb);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              tc_mma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), pre.idesc,
+                         (kb > 0 || k > 0) ? 1u : 0u);
+              if constexpr (MH == 2)
+                tc_mma_f16(d_tmem + BN, da + (uint64_t)(1024 + k * 2), db + (uint64_t)(k * 2),
+                           pre.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(bar_empty + stage * 8);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (*abort_flag) break;
+          tc_commit(bar_tfull + buf * 8);
+        }
+      }
+      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local) {
         const int nt = tile / tiles_m;
         const int kb0 = KOUTER ? nt * kb_per_split : 0;
         const int kb1 = KOUTER ? min(kb_main, kb0 + kb_per_split) : kb_total;
@@ -231,7 +319,53 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     const float alpha = (ep.alpha_ptr ? *ep.alpha_ptr : 1.0f) * ep.alpha;
     float amax_seen = 0.f;
     constexpr int NCH = MH * (BN / 32);
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+    if constexpr (!KOUTER) {
+      for (int p = (int)gridDim.x - 1 - (int)blockIdx.x; p < pre.tiles; p += gridDim.x, ++local) {
+        const uint32_t buf = MH == 1 ? (local & 1) : 0;
+        const uint32_t acc_phase = MH == 1 ? ((local >> 1) & 1) : (local & 1);
+        if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 9)) break;
+        tc_fence_after();
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+        // 64 columns: the two warps of a lane quadrant take 32 each, per 128-row half
+#pragma unroll 1
+        for (int half = 0; half < MH; ++half) {
+          uint32_t r[32];
+          tc_ld32(t_lane + (buf + half) * BN + grp * 32, r);
+          tc_wait_ld();
+          uint8_t* st = stage_base + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *(float4*)(st + ((j ^ (lane & 7)) << 4)) = make_float4(
+                pre.alpha * __uint_as_float(r[4 * j]), pre.alpha * __uint_as_float(r[4 * j + 1]),
+                pre.alpha * __uint_as_float(r[4 * j + 2]), pre.alpha * __uint_as_float(r[4 * j + 3]));
+          __syncwarp();
+          const int row_base = p * TM + half * BM + quad * 32;
+          const int j = lane & 7;
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const int rr = 4 * t + (lane >> 3);
+            const int grow = row_base + rr;
+            const float4 v4 = *(const float4*)(stage_base + rr * 128 + ((j ^ (rr & 7)) << 4));
+            if (grow < M) {
+              __half2 h0 = __floats2half2_rn(v4.x, v4.y), h1 = __floats2half2_rn(v4.z, v4.w);
+              *(uint2*)(pre.c16 + (long long)grow * pre.ldc16 + grp * 32 + 4 * j) =
+                  make_uint2(*(uint32_t*)&h0, *(uint32_t*)&h1);
+            }
+          }
+          __syncwarp();
+        }
+        tc_fence_before();
+        // publish: the rows are read by other CTAs' TMA loads once the flag shows all 8 warps
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          atomicAdd(pre.flags + p, 1);
+          mbar_arrive(bar_tempty + buf * 8);
+        }
+      }
+    }
+    for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local) {
       const int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
       const int n0 = KOUTER ? 0 : nt * BN;
       const uint32_t buf = MH == 1 ? (local & 1) : 0;
@@ -523,7 +657,12 @@ __global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __
 template <int BN, int STAGES, bool KOUTER, int MH = 1>
 int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2,
               const CUtensorMap& mb2, const Epilogue& ep, int M, int N, int K, int K2, int splits,
-              uint32_t idesc, double flops) {
+              uint32_t idesc, double flops, const CUtensorMap* mb3 = nullptr,
+              const PreTile* pre_in = nullptr) {
+  PreTile pre;
+  memset(&pre, 0, sizeof(pre));
+  if (pre_in) pre = *pre_in;
+  const CUtensorMap& map3 = mb3 ? *mb3 : mb;
   using L = SmemLayout<BN, STAGES, MH>;
   static bool configured = false;
   if (!configured) {
@@ -554,8 +693,8 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
     if (pa) ft_prof_begin(ctx, nm);
     ctx->profile_all = false;
     cudaError_t le = ft_launch_ex(ctx, k_gemm_tc<BN, STAGES, KOUTER, MH>, grid, GEMM_THREADS,
-                                  L::DYN_BYTES, ma, mb, ma2, mb2, ep, M, N, K, K2, splits, idesc,
-                                  ctx->status_dev, dbg);
+                                  L::DYN_BYTES, ma, mb, ma2, mb2, map3, ep, pre, M, N, K, K2, splits,
+                                  idesc, ctx->status_dev, dbg);
     ctx->profile_all = pa;
     if (pa) ft_prof_end(ctx);
     ctx->launches++;
@@ -680,13 +819,34 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
     ep.amax_slot = ctx->amax_out;
     ctx->amax_ready = true;
   }
-  const double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
+  double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
+  // adapter pre-tiles: the tail operand A2 = pre_alpha * A . pre_b^T is made by this launch
+  CUtensorMap mb3;
+  PreTile pre;
+  memset(&pre, 0, sizeof(pre));
+  const bool with_pre = g.pre_b != nullptr;
+  if (with_pre) {
+    const int tiles_m = ft_cdiv(g.M, MH * BM);
+    if (!tail || !tma_ok(g.pre_b, g.pre_ldb, g.K) || !g.pre_c16 || (g.pre_ldc16 % 4) ||
+        (((uintptr_t)g.pre_c16) & 7) || tiles_m > FT_PRE_FLAGS)
+      return FT_ERR_UNSUPPORTED;
+    FT_TRY(make_map(ctx, &mb3, g.pre_b, dt, (uint64_t)g.K, 64, (uint64_t)g.pre_ldb, BK, 64));
+    if (!ctx->pre_flags) FT_CUDA(cudaMalloc(&ctx->pre_flags, FT_PRE_FLAGS * sizeof(int)));
+    FT_CUDA(cudaMemsetAsync(ctx->pre_flags, 0, (size_t)tiles_m * sizeof(int), ctx->stream));
+    pre.tiles = tiles_m;
+    pre.c16 = g.pre_c16; pre.ldc16 = g.pre_ldc16; pre.alpha = g.pre_alpha;
+    pre.flags = ctx->pre_flags;
+    pre.idesc = make_idesc(BM, 64, fmt, fmt);
+    flops += 2.0 * g.M * 64.0 * (double)g.K;
+  }
+  const CUtensorMap* p3 = with_pre ? &mb3 : nullptr;
+  const PreTile* pp = with_pre ? &pre : nullptr;
   if (MH == 2)
-    return launch_tc<256, 3, false, 2>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
+    return launch_tc<256, 3, false, 2>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops, p3, pp);
   switch (BN) {
-    case 256: return launch_tc<256, 4, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
-    case 128: return launch_tc<128, 6, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
-    default: return launch_tc<64, 8, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops);
+    case 256: return launch_tc<256, 4, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops, p3, pp);
+    case 128: return launch_tc<128, 6, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops, p3, pp);
+    default: return launch_tc<64, 8, false>(ctx, ma, mb, ma2, mb2, ep, g.M, g.N, g.K, g.K2, 1, idesc, flops, p3, pp);
   }
 }
 

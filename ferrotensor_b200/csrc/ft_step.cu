@@ -467,17 +467,14 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
                      __half* xa16, const float* residual, long long ldr, int T,
                      __half* Y16 = nullptr) {
   FtContext* ctx = m->ctx;
-  if (g.R > 0) {
-    FtGemmArgs a;
-    a.a = X16; a.lda = g.in; a.b = g.a_catT16; a.ldb = g.in;
-    a.M = T; a.N = RP; a.K = g.in;
-    a.c16 = xa16; a.ldc16 = RP; a.alpha = m->scale;
-    FT_TRY(ft_gemm_tc_ex(ctx, a));
-  }
   FtGemmArgs a;
   a.a = X16; a.lda = g.in; a.b = g.w_nk; a.ldb = g.in;
   a.M = T; a.N = g.n; a.K = g.in;
-  if (g.R > 0) { a.a2 = xa16; a.lda2 = RP; a.b2 = g.b_bdT16; a.ldb2 = RP; a.K2 = RP; }
+  if (g.R > 0) {
+    // xa16 = (alpha/r) X16 . A is made by pre-tiles of the same launch
+    a.a2 = xa16; a.lda2 = RP; a.b2 = g.b_bdT16; a.ldb2 = RP; a.K2 = RP;
+    a.pre_b = g.a_catT16; a.pre_ldb = g.in; a.pre_c16 = xa16; a.pre_ldc16 = RP; a.pre_alpha = m->scale;
+  }
   a.c = Y; a.ldc = ldy; a.c16 = Y16; a.ldc16 = ldy;   // Y16: the result as f16 (pitch ldy)
   a.bias = g.bias_cat; a.residual = residual; a.ldr = ldr;
   return ft_gemm_tc_ex(ctx, a);
@@ -503,7 +500,7 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     dY16 = m->cvt_hi;
   }
   const float* inv_s = scales + 1;
-  if (g.R > 0) {
+  if (g.R > 0 && !dX) {
     FtGemmArgs a;   // G16 = (alpha/r) * (S dY) . B^T
     a.a = dY16; a.lda = np; a.b = g.b_bd16; a.ldb = g.n;
     a.M = T; a.N = RP; a.K = g.n;
@@ -514,7 +511,11 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     FtGemmArgs a;
     a.a = dY16; a.lda = np; a.b = g.w_kn; a.ldb = g.n;
     a.M = T; a.N = g.in; a.K = g.n;
-    if (g.R > 0) { a.a2 = m->g16; a.lda2 = RP; a.b2 = g.a_cat16; a.ldb2 = RP; a.K2 = RP; }
+    if (g.R > 0) {
+      // G16 = (alpha/r) * (S dY) . B^T is made by pre-tiles of the same launch
+      a.a2 = m->g16; a.lda2 = RP; a.b2 = g.a_cat16; a.ldb2 = RP; a.K2 = RP;
+      a.pre_b = g.b_bd16; a.pre_ldb = g.n; a.pre_c16 = m->g16; a.pre_ldc16 = RP; a.pre_alpha = m->scale;
+    }
     a.c = dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
     if (amax_on_dx) {
       FT_TRY(ft_amax_arm(ctx));
