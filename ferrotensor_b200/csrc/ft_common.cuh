@@ -185,6 +185,25 @@ struct FtGemmArgs {
   float pre_alpha = 1.f;
 };
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g);
+// One problem of a token-reduction launch: P[M, N<=64] = sum_t A[t, m] B[t, n]; the reduction
+// launch adds it into up to three segments out[(m - m0) * som + (n - n0) * son].
+struct FtKoSeg {
+  float* out = nullptr;
+  int m0 = 0, mcount = 0, n0 = 0, ncount = 0;
+  long long som = 0, son = 0;
+};
+struct FtKoProblem {
+  const void* a = nullptr; long long lda = 0;
+  const void* b = nullptr; long long ldb = 0;
+  int M = 0, N = 0;
+  int nseg = 0;
+  FtKoSeg seg[3];
+  float* slabs = nullptr;   // set by the call: [nslabs][M][64]
+  int nslabs = 0;
+};
+int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T);
+int ft_slab_reduce_problems(FtContext* ctx, int nprob, const FtKoProblem* prob,
+                            const float* alpha_ptr, float alpha, bool accumulate);
 // Token-reduction product P[M, N<=64] = sum_t A[t,m] B[t,n] (A [T,M], B [T,N], f16) as K-split
 // f32 slabs [nslabs][M][64] in context scratch; ft_slab_reduce adds the slabs in order into a
 // strided sub-block: out[(m-m0)*som + (n-n0)*son] (=|+=) alpha_dev*alpha*sum.

@@ -11,6 +11,9 @@
 // Every mbarrier wait is bounded: when a wait runs out the CTA raises a sticky abort flag,
 // records a status word the host reads, lets all roles fall through, waits out its
 // in-flight copies, frees its tensor memory and returns.  Nothing traps.
+#include <map>
+#include <string>
+#include <stdlib.h>
 #include "ft_tc.cuh"
 
 namespace {
@@ -103,6 +106,34 @@ __device__ __forceinline__ bool flag_wait(const int* flag, int target, volatile 
   return true;
 }
 
+// Token-reduction launches (KOUTER) carry up to two problems that share T and N = 64: problem q
+// is P_q[M_q, 64] = sum_t A_q[t, m] B_q[t, n] with A_q = map_a / map_a2 and B_q = map_b / map_b2.
+// The tile list is (problem, m tile, K split); every split writes its own f32 slab and a small
+// second launch sums the slabs in split order.
+struct KoProblem {
+  int M, splits, per;   // rows, K splits, k-blocks per split
+  float* slabs;         // [splits][M][64]
+};
+struct KoPair {
+  KoProblem p[2];       // p[1].M == 0: one problem only
+};
+struct KoTile { int q, mt, sp, kb0, kb1; };
+__device__ __forceinline__ int ko_tiles(const KoPair& ko) {
+  return ((ko.p[0].M + BM - 1) / BM) * ko.p[0].splits + ((ko.p[1].M + BM - 1) / BM) * ko.p[1].splits;
+}
+__device__ __forceinline__ KoTile ko_decode(const KoPair& ko, int tile, int kb_main) {
+  const int tm0 = (ko.p[0].M + BM - 1) / BM, n0 = tm0 * ko.p[0].splits;
+  KoTile t;
+  t.q = tile >= n0 ? 1 : 0;
+  const int r = t.q ? tile - n0 : tile;
+  const int tm = t.q ? (ko.p[1].M + BM - 1) / BM : tm0;
+  t.mt = r % tm;
+  t.sp = r / tm;
+  t.kb0 = t.sp * ko.p[t.q].per;
+  t.kb1 = min(kb_main, t.kb0 + ko.p[t.q].per);
+  return t;
+}
+
 // KOUTER = false:  C[M,N] = A[M,K] . B[N,K]^T (+ A2[M,K2] . B2[N,K2]^T), operands K-contiguous.
 // KOUTER = true :  C[M,N] = sum_t A[t,m] B[t,n], operands given as [T, M] and [T, N] (the
 //                  token-reduction products of the adapter gradients); BN = 64, the tile list
@@ -111,8 +142,8 @@ template <int BN, int STAGES, bool KOUTER, int MH = 1>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
           const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
-          const __grid_constant__ CUtensorMap map_b3, Epilogue ep, PreTile pre, int M, int N, int K,
-          int K2, int splits, uint32_t idesc, int* status, int* dbg) {
+          const __grid_constant__ CUtensorMap map_b3, Epilogue ep, PreTile pre, KoPair ko, int M,
+          int N, int K, int K2, int splits, uint32_t idesc, int* status, int* dbg) {
   using L = SmemLayout<BN, STAGES, MH>;
   static_assert(MH == 1 || (BN == 256 && !KOUTER), "the 256-row tile exists for BN = 256 only");
   constexpr int TM = MH * BM;  // rows of an output tile
@@ -131,10 +162,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + TM - 1) / TM;
   const int tiles_n = KOUTER ? splits : (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = KOUTER ? ko_tiles(ko) : tiles_m * tiles_n;
   const int kb_main = (K + BK - 1) / BK;
   const int kb_total = kb_main + (KOUTER ? 0 : (K2 + BK - 1) / BK);
-  const int kb_per_split = KOUTER ? (kb_main + splits - 1) / splits : kb_total;
   // MH = 1: two accumulators of BN columns (epilogue of one overlaps the products of the
   // other); MH = 2: one pair of 256-column accumulators, all of tensor memory
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -188,9 +218,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         }
       }
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
-        const int kb0 = KOUTER ? nt * kb_per_split : 0;
-        const int kb1 = KOUTER ? min(kb_main, kb0 + kb_per_split) : kb_total;
+        int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
+        int kb0 = 0, kb1 = kb_total, prob = 0;
+        if constexpr (KOUTER) {
+          const KoTile kt = ko_decode(ko, tile, kb_main);
+          m0 = kt.mt * BM; nt = kt.sp; kb0 = kt.kb0; kb1 = kt.kb1; prob = kt.q;
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           FT_MARK(7, 20);
           if constexpr (!KOUTER) {
@@ -205,9 +238,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
           mbar_expect_tx(bar, L::STAGE_BYTES);
           if constexpr (KOUTER) {
             // {x = M/N index (64 wide), y = token row}
-            tma_load_2d(sa, &map_a, bar, m0, kb * BK);
-            tma_load_2d(sa + 64 * 128, &map_a, bar, m0 + 64, kb * BK);
-            tma_load_2d(sb, &map_b, bar, 0, kb * BK);
+            const CUtensorMap* pa = prob ? &map_a2 : &map_a;
+            tma_load_2d(sa, pa, bar, m0, kb * BK);
+            tma_load_2d(sa + 64 * 128, pa, bar, m0 + 64, kb * BK);
+            tma_load_2d(sb, prob ? &map_b2 : &map_b, bar, 0, kb * BK);
           } else if (kb < kb_main) {
             tma_load_2d(sa, &map_a, bar, kb * BK, m0);
             tma_load_2d(sb, &map_b, bar, kb * BK, nt * BN);
@@ -256,9 +290,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         }
       }
       for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local) {
-        const int nt = tile / tiles_m;
-        const int kb0 = KOUTER ? nt * kb_per_split : 0;
-        const int kb1 = KOUTER ? min(kb_main, kb0 + kb_per_split) : kb_total;
+        int kb0 = 0, kb1 = kb_total;
+        if constexpr (KOUTER) {
+          const KoTile kt = ko_decode(ko, tile, kb_main);
+          kb0 = kt.kb0; kb1 = kt.kb1;
+        }
         const uint32_t buf = MH == 1 ? (local & 1) : 0;
         const uint32_t acc_phase = MH == 1 ? ((local >> 1) & 1) : (local & 1);
         FT_MARK(8, 30);
@@ -366,15 +402,22 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       }
     }
     for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local) {
-      const int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
+      int m0 = (tile % tiles_m) * TM, nt = tile / tiles_m;
       const int n0 = KOUTER ? 0 : nt * BN;
       const uint32_t buf = MH == 1 ? (local & 1) : 0;
       const uint32_t acc_phase = MH == 1 ? ((local >> 1) & 1) : (local & 1);
       if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 4)) break;
       tc_fence_after();
       if (warp == 2 && lane == 0) FT_MARK(9, 41);
-      // a K split of the token-reduction product writes its own slab
-      float* cbase = ep.c ? ep.c + (KOUTER ? (long long)nt * M * ep.ldc : 0) : nullptr;
+      float* cbase = ep.c;
+      KoTile kt = {0, 0, 0, 0, 0};
+      if constexpr (KOUTER) {
+        // a K split of the token-reduction product writes its own slab
+        kt = ko_decode(ko, tile, kb_main);
+        m0 = kt.mt * BM;
+        M = ko.p[kt.q].M;
+        cbase = ko.p[kt.q].slabs + (long long)kt.sp * M * 64;
+      }
       const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
       uint32_t r[32];
       // chunk c of the tile: half c / (BN/32) (a 128-row half), 32 columns from (c % (BN/32)) * 32
@@ -499,22 +542,26 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   }
 }
 
-// Up to three sub-blocks of one slab set in a single launch (the adapters of a q|k|v group).
+// Up to six sub-blocks in a single launch (the adapters of a q|k|v group, B and A gradients),
+// each from its own slab set part[s][M][ldp].
 struct SlabSegs {
   int count;
-  float* out[3];
-  int m0[3], mcount[3], n0[3], ncount[3];
-  long long som[3], son[3];
+  float* out[6];
+  const float* part[6];
+  int M[6];
+  int m0[6], mcount[6], n0[6], ncount[6];
+  long long som[6], son[6];
 };
-__global__ void k_slab_reduce_multi(const float* __restrict__ part, int slabs, int M, int ldp,
-                                    SlabSegs sg, const float* __restrict__ alpha_ptr, float alpha,
+__global__ void k_slab_reduce_multi(int slabs, int ldp, SlabSegs sg,
+                                    const float* __restrict__ alpha_ptr, float alpha,
                                     int accumulate) {
   ft_pdl_wait();
   ft_pdl_launch();
   const float a = (alpha_ptr ? *alpha_ptr : 1.0f) * alpha;
   const int seg = blockIdx.y;
   if (seg >= sg.count) return;
-  const int ncount = sg.ncount[seg];
+  const int ncount = sg.ncount[seg], M = sg.M[seg];
+  const float* __restrict__ part = sg.part[seg];
   size_t total = (size_t)sg.mcount[seg] * ncount;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += st) {
@@ -654,14 +701,33 @@ __global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __
   }
 }
 
+// profile name of a token-reduction launch; FT_PROFILE_SHAPES=1 appends the problem sizes
+static const char* ko_name(const KoPair& ko) {
+  static const bool shapes = getenv("FT_PROFILE_SHAPES") != nullptr;
+  if (!shapes) return "k_gemm_tc<64,token-reduction>";
+  static std::map<std::pair<int, int>, std::string> names;
+  auto key = std::make_pair(ko.p[0].M, ko.p[1].M);
+  auto it = names.find(key);
+  if (it == names.end()) {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "k_gemm_tc<64,token-reduction>[%d+%d,s%d]", ko.p[0].M, ko.p[1].M,
+             ko.p[0].splits);
+    it = names.emplace(key, buf).first;
+  }
+  return it->second.c_str();
+}
+
 template <int BN, int STAGES, bool KOUTER, int MH = 1>
 int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2,
               const CUtensorMap& mb2, const Epilogue& ep, int M, int N, int K, int K2, int splits,
               uint32_t idesc, double flops, const CUtensorMap* mb3 = nullptr,
-              const PreTile* pre_in = nullptr) {
+              const PreTile* pre_in = nullptr, const KoPair* ko_in = nullptr, int ko_tiles_host = 0) {
   PreTile pre;
   memset(&pre, 0, sizeof(pre));
   if (pre_in) pre = *pre_in;
+  KoPair ko;
+  memset(&ko, 0, sizeof(ko));
+  if (ko_in) ko = *ko_in;
   const CUtensorMap& map3 = mb3 ? *mb3 : mb;
   using L = SmemLayout<BN, STAGES, MH>;
   static bool configured = false;
@@ -670,7 +736,7 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
     configured = true;
   }
-  int tiles = ft_cdiv(M, MH * BM) * (KOUTER ? splits : ft_cdiv(N, BN));
+  int tiles = KOUTER ? ko_tiles_host : ft_cdiv(M, MH * BM) * ft_cdiv(N, BN);
   int grid = std::min(tiles, ctx->sm_count);
   int* dbg = ctx->debug_markers ? ctx->status_dev : nullptr;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -686,14 +752,14 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
   }
   {
     // by-name profiling: one name per instantiation
-    const char* nm = KOUTER ? "k_gemm_tc<64,token-reduction>"
+    const char* nm = KOUTER ? ko_name(ko)
                             : (BN == 256 ? (MH == 2 ? "k_gemm_tc<256x256>" : "k_gemm_tc<128x256>")
                                          : (BN == 128 ? "k_gemm_tc<128x128>" : "k_gemm_tc<128x64>"));
     const bool pa = ctx->profile_all;
     if (pa) ft_prof_begin(ctx, nm);
     ctx->profile_all = false;
     cudaError_t le = ft_launch_ex(ctx, k_gemm_tc<BN, STAGES, KOUTER, MH>, grid, GEMM_THREADS,
-                                  L::DYN_BYTES, ma, mb, ma2, mb2, map3, ep, pre, M, N, K, K2, splits,
+                                  L::DYN_BYTES, ma, mb, ma2, mb2, map3, ep, pre, ko, M, N, K, K2, splits,
                                   idesc, ctx->status_dev, dbg);
     ctx->profile_all = pa;
     if (pa) ft_prof_end(ctx);
@@ -861,32 +927,76 @@ int ft_gemm_tc(FtContext* ctx, const void* a, long long lda, const void* b, FtDT
   return ft_gemm_tc_ex(ctx, g);
 }
 
-// P[M, N<=64] (slabs) = sum_t A[t, m] B[t, n] on the tensor cores, then a deterministic
-// reduction of the K-split slabs.  A is [T, M] (lda), B is [T, N] (ldb), both f16.
-int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* b, long long ldb,
-                      int M, int N, int T, float** slabs_out, int* nslabs_out) {
-  if (N > 64 || !tma_ok(a, lda, M) || !tma_ok(b, ldb, N) || (M % 8) || (N % 8)) return FT_ERR_UNSUPPORTED;
-  CUtensorMap ma, mb;
+// Token-reduction products on the tensor cores: P_q[M_q, 64] = sum_t A_q[t, m] B_q[t, n] for one or
+// two problems that share T (A_q is [T, M_q], B_q is [T, <=64], both f16), K-split into f32
+// slabs prob[q].slabs[nslabs][M_q][64] that the caller reduces (ft_slab_reduce_problems).
+static void ko_pick_splits(int sms, int tm0, int tm1, int kb, int* splits_out, int* per_out) {
+  // cost of a choice = waves x (k-blocks per split + a fixed per-tile cost of about 6 k-blocks)
+  double best = 1e30;
+  int bs = 1;
+  for (int sp = 1; sp <= std::min(kb, 32); ++sp) {
+    const int per = ft_cdiv(kb, sp), real = ft_cdiv(kb, per);
+    const int tiles = (tm0 + tm1) * real;
+    const double cost = (double)ft_cdiv(tiles, sms) * (per + 6.0);
+    if (cost < best - 1e-9) { best = cost; bs = real; }
+  }
+  *splits_out = bs;
+  *per_out = ft_cdiv(kb, bs);
+}
+
+int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T) {
+  if (nprob < 1 || nprob > 2) return FT_ERR_UNSUPPORTED;
+  CUtensorMap ma[2], mb[2];
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  // inner dimension = M/N index, outer = token row; box = 64 x 64
-  FT_TRY(make_map(ctx, &ma, a, dt, (uint64_t)M, (uint64_t)T, (uint64_t)lda, 64, BK));
-  FT_TRY(make_map(ctx, &mb, b, dt, (uint64_t)N, (uint64_t)T, (uint64_t)ldb, 64, BK));
-  const int tiles_m = ft_cdiv(M, BM), kb = ft_cdiv(T, BK);
-  int splits = std::max(1, std::min(std::min(kb, 32), ft_cdiv(2 * ctx->sm_count, tiles_m)));
-  const int per = ft_cdiv(kb, splits);
-  splits = ft_cdiv(kb, per);
+  const int kb = ft_cdiv(T, BK);
+  int tm[2] = {0, 0};
+  for (int q = 0; q < nprob; ++q) {
+    const FtKoProblem& P = prob[q];
+    if (P.N > 64 || !tma_ok(P.a, P.lda, P.M) || !tma_ok(P.b, P.ldb, P.N) || (P.M % 8) || (P.N % 8) ||
+        P.nseg > 3)
+      return FT_ERR_UNSUPPORTED;
+    // inner dimension = M/N index, outer = token row; box = 64 x 64
+    FT_TRY(make_map(ctx, &ma[q], P.a, dt, (uint64_t)P.M, (uint64_t)T, (uint64_t)P.lda, 64, BK));
+    FT_TRY(make_map(ctx, &mb[q], P.b, dt, (uint64_t)P.N, (uint64_t)T, (uint64_t)P.ldb, 64, BK));
+    tm[q] = ft_cdiv(P.M, BM);
+  }
+  if (nprob == 1) { ma[1] = ma[0]; mb[1] = mb[0]; }
+  int splits = 1, per = kb;
+  ko_pick_splits(ctx->sm_count, tm[0], tm[1], kb, &splits, &per);
+  size_t slab_floats = 0;
+  for (int q = 0; q < nprob; ++q) slab_floats += (size_t)splits * prob[q].M * 64;
   void* s = nullptr;
-  FT_TRY(ft_scratch(ctx, (size_t)splits * M * 64 * sizeof(float), &s));
+  FT_TRY(ft_scratch(ctx, slab_floats * sizeof(float), &s));
+  KoPair ko;
+  memset(&ko, 0, sizeof(ko));
+  float* slab = (float*)s;
+  double flops = 0;
+  for (int q = 0; q < nprob; ++q) {
+    KoProblem& K = ko.p[q];
+    K.M = prob[q].M; K.splits = splits; K.per = per; K.slabs = slab;
+    prob[q].slabs = slab;
+    prob[q].nslabs = splits;
+    slab += (size_t)splits * prob[q].M * 64;
+    flops += 2.0 * prob[q].M * 64.0 * T;
+  }
   Epilogue ep;
   ep.c = (float*)s; ep.ldc = 64; ep.c16 = nullptr; ep.ldc16 = 0;
   ep.alpha_ptr = nullptr; ep.alpha = 1.f; ep.bias = nullptr; ep.residual = nullptr; ep.ldr = 0;
   ep.amax_slot = nullptr;
   // both operands M/N-major: bits 15 and 16 of the instruction descriptor
   const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
-  *slabs_out = (float*)s;
-  *nslabs_out = splits;
-  return launch_tc<64, 8, true>(ctx, ma, mb, ma, mb, ep, M, 64, T, 0, splits, idesc,
-                                2.0 * M * 64.0 * T);
+  return launch_tc<64, 8, true>(ctx, ma[0], mb[0], ma[1], mb[1], ep, prob[0].M, 64, T, 0, splits, idesc,
+                                flops, nullptr, nullptr, &ko, (tm[0] + tm[1]) * splits);
+}
+
+int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* b, long long ldb,
+                      int M, int N, int T, float** slabs_out, int* nslabs_out) {
+  FtKoProblem P;
+  P.a = a; P.lda = lda; P.b = b; P.ldb = ldb; P.M = M; P.N = N;
+  FT_TRY(ft_gemm_tc_kouter_pair(ctx, 1, &P, T));
+  *slabs_out = P.slabs;
+  *nslabs_out = P.nslabs;
+  return FT_OK;
 }
 
 int ft_slab_reduce_multi(FtContext* ctx, const float* slabs, int nslabs, int M, int count,
@@ -896,20 +1006,44 @@ int ft_slab_reduce_multi(FtContext* ctx, const float* slabs, int nslabs, int M, 
                          bool accumulate) {
   if (count <= 0) return FT_OK;
   SlabSegs sg;
+  memset(&sg, 0, sizeof(sg));
   sg.count = count;
   size_t most = 0;
-  for (int i = 0; i < 3; ++i) {
-    const bool on = i < count;
-    sg.out[i] = on ? out[i] : nullptr;
-    sg.m0[i] = on ? m0[i] : 0; sg.mcount[i] = on ? mcount[i] : 0;
-    sg.n0[i] = on ? n0[i] : 0; sg.ncount[i] = on ? ncount[i] : 0;
-    sg.som[i] = on ? som[i] : 0; sg.son[i] = on ? son[i] : 0;
-    if (on) most = std::max(most, (size_t)mcount[i] * ncount[i]);
+  for (int i = 0; i < count; ++i) {
+    sg.out[i] = out[i]; sg.part[i] = slabs; sg.M[i] = M;
+    sg.m0[i] = m0[i]; sg.mcount[i] = mcount[i]; sg.n0[i] = n0[i]; sg.ncount[i] = ncount[i];
+    sg.som[i] = som[i]; sg.son[i] = son[i];
+    most = std::max(most, (size_t)mcount[i] * ncount[i]);
   }
   if (!most) return FT_OK;
   dim3 grid((unsigned)std::min<size_t>((most + 255) / 256, (size_t)ctx->sm_count * 4), count);
-  FT_LAUNCH_PDL(ctx, k_slab_reduce_multi, grid, 256, 0, slabs, nslabs, M, 64, sg, alpha_ptr, alpha,
-            accumulate ? 1 : 0);
+  FT_LAUNCH_PDL(ctx, k_slab_reduce_multi, grid, 256, 0, nslabs, 64, sg, alpha_ptr, alpha,
+                accumulate ? 1 : 0);
+  return FT_OK;
+}
+
+// The segments of every problem of a token-reduction launch, reduced in one launch.
+int ft_slab_reduce_problems(FtContext* ctx, int nprob, const FtKoProblem* prob,
+                            const float* alpha_ptr, float alpha, bool accumulate) {
+  SlabSegs sg;
+  memset(&sg, 0, sizeof(sg));
+  size_t most = 0;
+  int nslabs = 0;
+  for (int q = 0; q < nprob; ++q) {
+    nslabs = prob[q].nslabs;
+    for (int i = 0; i < prob[q].nseg && sg.count < 6; ++i) {
+      const FtKoSeg& S = prob[q].seg[i];
+      const int k = sg.count++;
+      sg.out[k] = S.out; sg.part[k] = prob[q].slabs; sg.M[k] = prob[q].M;
+      sg.m0[k] = S.m0; sg.mcount[k] = S.mcount; sg.n0[k] = S.n0; sg.ncount[k] = S.ncount;
+      sg.som[k] = S.som; sg.son[k] = S.son;
+      most = std::max(most, (size_t)S.mcount * S.ncount);
+    }
+  }
+  if (!most) return FT_OK;
+  dim3 grid((unsigned)std::min<size_t>((most + 255) / 256, (size_t)ctx->sm_count * 4), sg.count);
+  FT_LAUNCH_PDL(ctx, k_slab_reduce_multi, grid, 256, 0, nslabs, 64, sg, alpha_ptr, alpha,
+                accumulate ? 1 : 0);
   return FT_OK;
 }
 

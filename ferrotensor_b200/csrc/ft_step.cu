@@ -9,6 +9,7 @@
 // Linears that share an input are computed as a group into one wide buffer
 // (q|k|v -> [T, nq+2nkv], gate|up -> [T, 2F]); attention, RoPE and SwiGLU read their slices
 // through leading dimensions, so no slice is ever copied.
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -524,34 +525,26 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     FT_TRY(ft_gemm_tc_ex(ctx, a));
   }
   if (g.R > 0) {
-    float* slabs = nullptr;
-    int ns = 0;
-    // dB^T [n, 64] = (S dY)^T . xa16, reduced over tokens
-    FT_TRY(ft_gemm_tc_kouter(ctx, dY16, np, xa16, RP, g.n, RP, T, &slabs, &ns));
-    float* outs[3];
-    int m0[3], mc[3], n0[3], nc[3], cnt = 0;
-    long long som[3], son[3];
+    // one launch for both adapter gradients, each reduced over tokens:
+    //   dB^T [n, 64] = (S dY)^T . xa16      dA [in, 64] = X16^T . G16
+    // the slabs of the K splits are summed inside the launch and added to the flat buffer
+    FtKoProblem pr[2];
+    pr[0].a = dY16; pr[0].lda = np; pr[0].b = xa16; pr[0].ldb = RP; pr[0].M = g.n; pr[0].N = RP;
+    pr[1].a = X16; pr[1].lda = g.in; pr[1].b = m->g16; pr[1].ldb = RP; pr[1].M = g.in; pr[1].N = RP;
     for (int j = 0; j < g.nlin; ++j) {
       const Linear& l = *g.lin[j];
       if (!l.lora) continue;
-      outs[cnt] = m->grads + l.b_off; m0[cnt] = g.col_off[j]; mc[cnt] = l.out;
-      n0[cnt] = g.r_off[j]; nc[cnt] = r; som[cnt] = 1; son[cnt] = l.out;
-      ++cnt;
+      FtKoSeg& sb = pr[0].seg[pr[0].nseg++];   // lora_b [r, out]
+      sb.out = m->grads + l.b_off; sb.m0 = g.col_off[j]; sb.mcount = l.out;
+      sb.n0 = g.r_off[j]; sb.ncount = r; sb.som = 1; sb.son = l.out;
+      FtKoSeg& sa = pr[1].seg[pr[1].nseg++];   // lora_a [in, r]
+      sa.out = m->grads + l.a_off; sa.m0 = 0; sa.mcount = l.in;
+      sa.n0 = g.r_off[j]; sa.ncount = r; sa.som = r; sa.son = 1;
     }
-    FT_TRY(ft_slab_reduce_multi(ctx, slabs, ns, g.n, cnt, outs, m0, mc, n0, nc, som, son, inv_s, 1.f,
-                                true));
-    // dA [in, 64] = X16^T . G16
-    FT_TRY(ft_gemm_tc_kouter(ctx, X16, g.in, m->g16, RP, g.in, RP, T, &slabs, &ns));
-    cnt = 0;
-    for (int j = 0; j < g.nlin; ++j) {
-      const Linear& l = *g.lin[j];
-      if (!l.lora) continue;
-      outs[cnt] = m->grads + l.a_off; m0[cnt] = 0; mc[cnt] = l.in;
-      n0[cnt] = g.r_off[j]; nc[cnt] = r; som[cnt] = r; son[cnt] = 1;
-      ++cnt;
-    }
-    FT_TRY(ft_slab_reduce_multi(ctx, slabs, ns, g.in, cnt, outs, m0, mc, n0, nc, som, son, inv_s, 1.f,
-                                true));
+    // (summing the slabs inside the launch, by the last warp to finish each piece, was
+    // measured slower than this second small launch: a long serial tail on few warps)
+    FT_TRY(ft_gemm_tc_kouter_pair(ctx, 2, pr, T));
+    FT_TRY(ft_slab_reduce_problems(ctx, 2, pr, inv_s, 1.f, true));
   }
   return FT_OK;
 }
