@@ -275,6 +275,9 @@ int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const floa
                        float* gb, long long ldgb, int rows, int n);
 // y[t, j] += bias[j]
 int ft_k_add_bias(FtContext* ctx, float* y, long long ld, const float* bias, int rows, int n);
+int ft_k_masked_ce16(FtContext* ctx, const float* logits, const uint32_t* targets,
+                     const float* weights, __half* g16, long long ld16, float* row_loss, int rows,
+                     int vocab, float grad_scale, const float** scales_out);
 int ft_k_masked_ce(FtContext* ctx, const float* logits, const uint32_t* targets,
                    const float* weights, float* grad, float* row_loss, int rows, int vocab,
                    float grad_scale);

@@ -623,7 +623,8 @@ __global__ void k_silu_gate_bwd4(const float* __restrict__ a, long long lda,
 __global__ void __launch_bounds__(kRowThreads)
 k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
             const float* __restrict__ weights, float* grad, float* __restrict__ row_loss,
-            int vocab, float grad_scale, int* amax_slot) {
+            int vocab, float grad_scale, int* amax_slot, __half* __restrict__ g16 = nullptr,
+            long long ld16 = 0, const float* __restrict__ scales16 = nullptr) {
   // `grad` may alias `logits` (in-place use by the fused step): every element is read for
   // the last time by the thread that then overwrites it, after both reductions are done.
   __shared__ float red[32];
@@ -632,7 +633,12 @@ k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
   float* gz = grad ? grad + (size_t)row * vocab : nullptr;
   uint32_t tgt = targets[row];
   bool vec = (vocab & 3) == 0 && aligned16(z) && (!gz || aligned16(gz));
+  // optional f16 copy of the gradient, times the power of two scales16[0] (vocab % 4 == 0)
+  __half* hz = g16 ? g16 + (size_t)row * ld16 : nullptr;
+  const float S16 = hz ? scales16[0] : 1.0f;
   if (tgt == FT_MASKED_CE_SKIP) {
+    if (hz)
+      for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) ((uint2*)hz)[i] = make_uint2(0u, 0u);
     if (gz) {
       if (vec) {
         float4* g4 = (float4*)gz;
@@ -673,6 +679,23 @@ k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
   float inv = weights[row] * grad_scale;
   // |(softmax - onehot) * inv| <= |inv|: a tight bound serves as this row's amax
   if (amax_slot && threadIdx.x == 0 && inv != 0.f) atomicMax(amax_slot, __float_as_int(fabsf(inv)));
+  if (hz) {
+    const float4* z4 = (const float4*)z;
+    const float invs = inv * S16;
+    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+      float4 v = z4[i];
+      float4 r = make_float4(expf(v.x - log_z) * invs, expf(v.y - log_z) * invs,
+                             expf(v.z - log_z) * invs, expf(v.w - log_z) * invs);
+      uint32_t base = (uint32_t)i * 4u;
+      if (tgt - base < 4u) {
+        uint32_t k = tgt - base;
+        if (k == 0) r.x -= invs; else if (k == 1) r.y -= invs;
+        else if (k == 2) r.z -= invs; else r.w -= invs;
+      }
+      __half2 h0 = __floats2half2_rn(r.x, r.y), h1 = __floats2half2_rn(r.z, r.w);
+      ((uint2*)hz)[i] = make_uint2(*(uint32_t*)&h0, *(uint32_t*)&h1);
+    }
+  }
   if (gz) {
     if (vec) {
       const float4* z4 = (const float4*)z;
@@ -1054,7 +1077,48 @@ int ft_k_masked_ce(FtContext* ctx, const float* logits, const uint32_t* targets,
   int* am = ctx->amax_out;
   if (am) ctx->amax_ready = true;
   FT_LAUNCH(ctx, k_masked_ce, rows, kRowThreads, 0, logits, targets, weights, grad, row_loss,
-            vocab, grad_scale, am);
+            vocab, grad_scale, am, (__half*)nullptr, 0ll, (const float*)nullptr);
+  return FT_OK;
+}
+
+// {S, 1/S, 2^-11/S} with S the power of two that brings max_r |weights[r] * grad_scale| - a bound
+// on every element of the loss gradient, since |softmax - onehot| <= 1 - into [2^7, 2^8)
+__global__ void __launch_bounds__(kRowThreads)
+k_ce_scale(const float* __restrict__ weights, const uint32_t* __restrict__ targets, int rows,
+           float grad_scale, float* __restrict__ scales) {
+  ft_pdl_wait();
+  __shared__ float red[32];
+  float m = 0.f;
+  for (int i = threadIdx.x; i < rows; i += blockDim.x)
+    if (targets[i] != FT_MASKED_CE_SKIP) m = fmaxf(m, fabsf(weights[i] * grad_scale));
+  m = block_max(m, red);
+  if (threadIdx.x == 0) {
+    float S = 1.0f;
+    if (m > 0.f && isfinite(m)) {
+      int e;
+      frexpf(m, &e);
+      S = ldexpf(1.0f, 8 - e);
+    }
+    scales[0] = S;
+    scales[1] = 1.0f / S;
+    scales[2] = ldexpf(1.0f / S, -11);
+  }
+}
+
+// Loss rows and the gradient as scaled f16 operands [rows, ld16] (no f32 gradient is written);
+// *scales_out points at {S, 1/S, 2^-11/S} on the device.
+int ft_k_masked_ce16(FtContext* ctx, const float* logits, const uint32_t* targets,
+                     const float* weights, __half* g16, long long ld16, float* row_loss, int rows,
+                     int vocab, float grad_scale, const float** scales_out) {
+  FT_REQUIRE((vocab % 4) == 0 && (ld16 % 4) == 0 && ld16 >= vocab && (((uintptr_t)logits) & 15) == 0 &&
+                 (((uintptr_t)g16) & 7) == 0,
+             "masked_ce16: vocabulary and pitch must be multiples of 4");
+  ctx->amax_out = nullptr;
+  ctx->amax_ready = false;
+  FT_LAUNCH(ctx, k_ce_scale, 1, kRowThreads, 0, weights, targets, rows, grad_scale, ctx->scale_buf + 4);
+  FT_LAUNCH(ctx, k_masked_ce, rows, kRowThreads, 0, logits, targets, weights, (float*)nullptr, row_loss,
+            vocab, grad_scale, (int*)nullptr, g16, ld16, (const float*)(ctx->scale_buf + 4));
+  *scales_out = ctx->scale_buf + 4;
   return FT_OK;
 }
 

@@ -964,11 +964,21 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
       const __half* X16 = m->hN16 + (size_t)r0 * h;
       __half* xa16 = m->xa16_head + (size_t)r0 * RP;
       FT_TRY(linear_fwd_fused(m, m->head, X16, z, V, xa16, nullptr, 0, rows));
-      FT_TRY(ft_amax_arm(ctx));   // the loss kernel reports the gradient's amax
-      FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, m->logit_chunk, row_loss + r0, rows,
-                            V, seed));
-      FT_TRY(linear_bwd_fused(m, m->head, X16, m->logit_chunk, V, xa16, m->dh + (size_t)r0 * h, h,
-                              nullptr, 0, rows));
+      if ((V % 8) == 0) {
+        // the loss kernel writes its gradient as scaled f16 operands: its magnitude is bounded
+        // by the row weights, so the scale is known before the first element is written
+        const float* ce_scales = nullptr;
+        FT_TRY(ft_k_masked_ce16(ctx, z, targets + r0, weights + r0, m->cvt_hi, V, row_loss + r0, rows,
+                                V, seed, &ce_scales));
+        FT_TRY(linear_bwd_fused(m, m->head, X16, nullptr, V, xa16, m->dh + (size_t)r0 * h, h,
+                                nullptr, 0, rows, m->cvt_hi, ce_scales));
+      } else {
+        FT_TRY(ft_amax_arm(ctx));   // the loss kernel reports the gradient's amax
+        FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, m->logit_chunk, row_loss + r0, rows,
+                              V, seed));
+        FT_TRY(linear_bwd_fused(m, m->head, X16, m->logit_chunk, V, xa16, m->dh + (size_t)r0 * h, h,
+                                nullptr, 0, rows));
+      }
     } else {
       const float* X = m->hN + (size_t)r0 * h;
       float* xa = m->xa_head + (size_t)r0 * std::max(1, m->head.R);
