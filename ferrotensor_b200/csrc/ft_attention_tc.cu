@@ -6,12 +6,16 @@
 // Forward, one CTA per (128 queries, head), over 64-key blocks:
 //   S = Q K^T      tcgen05.mma 128 x 64 x 64 into one of two tensor-memory accumulators
 //   softmax        4 warps, thread t owns query row t (= TMEM lane t): tcgen05.ld the row,
-//                  online max/sum in the exp2 domain, P written to shared memory as f16 in the
-//                  128-byte-swizzled K-major form the next product wants
-//   O_j = P V_j    tcgen05.mma 128 x 64 x 64, V used in place as an N-major operand
-//   O = sum_j corr * O_j accumulated in registers, normalised at the end.
+//                  exp2 against a lazily raised maximum, P written to shared memory as f16 in
+//                  the 128-byte-swizzled K-major form the next product wants
+//   O += P [V|1]   tcgen05.mma 128 x 80 x 64, V used in place as an N-major operand; the
+//                  ones column makes column 64 of the accumulator the softmax denominator
 // One extra warp issues all TMA loads and MMAs; the S product of block j+1 is issued as soon
 // as the softmax warps have read block j, so it overlaps with their arithmetic and with P V.
+// (Measured and not kept: eight softmax warps with a half-row maximum exchange; paired f16
+// exponentials; releasing S / dP to the next product before the arithmetic in the backward
+// kernels - per block the time goes to the hand-offs between the warps and the tensor pipe,
+// not to the arithmetic.)
 // All waits are bounded (see ft_tc.cuh).
 #include <math.h>
 #include <stdlib.h>
@@ -59,8 +63,7 @@ struct AttnSmem {
 // exactly as the numerator is.  The running maximum is only raised (and the accumulator
 // rescaled, by the softmax warps themselves) when a block exceeds it by more than 2^8: until
 // then exp2(s - m) <= 256 is harmless in f16 and the final O / l is unchanged.  Exponentials
-// are taken two at a time in f16 (P is rounded to f16 for the product anyway).
-template <int VARIANT>
+// use the f32 special-function unit; the scale-and-shift before them is a packed pair FMA.
 __global__ void __launch_bounds__(AT_THREADS, 2)
 k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constant__ CUtensorMap map_kv64,
               __half* __restrict__ out16, long long ldo16, float* __restrict__ out32,
@@ -257,26 +260,16 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
           m_st = m_new;
         }
       }
-      // P = exp2(s * scale - m), two at a time in f16
+      // P = exp2(s * scale - m)
       const float nm = -m_st;
       uint32_t packed[32];
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
         float x0, x1, y0, y1;
-        if (VARIANT & 1) {
-          x0 = fmaf(__uint_as_float(r0[c]), scale_log2e, nm); x1 = fmaf(__uint_as_float(r0[c + 1]), scale_log2e, nm);
-          y0 = fmaf(__uint_as_float(r1[c]), scale_log2e, nm); y1 = fmaf(__uint_as_float(r1[c + 1]), scale_log2e, nm);
-        } else {
-          ffma2(x0, x1, __uint_as_float(r0[c]), __uint_as_float(r0[c + 1]), scale_log2e, scale_log2e, nm, nm);
-          ffma2(y0, y1, __uint_as_float(r1[c]), __uint_as_float(r1[c + 1]), scale_log2e, scale_log2e, nm, nm);
-        }
-        if (VARIANT & 2) {
-          packed[c >> 1] = pack_h2(ex2(x0), ex2(x1));
-          packed[16 + (c >> 1)] = pack_h2(ex2(y0), ex2(y1));
-        } else {
-          packed[c >> 1] = ex2_h2(pack_h2(x0, x1));
-          packed[16 + (c >> 1)] = ex2_h2(pack_h2(y0, y1));
-        }
+        ffma2(x0, x1, __uint_as_float(r0[c]), __uint_as_float(r0[c + 1]), scale_log2e, scale_log2e, nm, nm);
+        ffma2(y0, y1, __uint_as_float(r1[c]), __uint_as_float(r1[c + 1]), scale_log2e, scale_log2e, nm, nm);
+        packed[c >> 1] = pack_h2(ex2(x0), ex2(x1));
+        packed[16 + (c >> 1)] = pack_h2(ex2(y0), ex2(y1));
       }
       // this P buffer was last read by P V(j-2)
       if (j >= 2) {
@@ -883,28 +876,16 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
   FT_TRY(ft_tc::make_map(ctx, &kv64, qkv16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)ld,
                          (uint64_t)batch * seq, (uint64_t)ld, 64, 64));
   static bool configured = false;
-  static int variant = 0;
   if (!configured) {
-    if (const char* v = getenv("FT_ATTN_VARIANT")) variant = atoi(v) & 3;
-    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::DYN_BYTES));
-    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::DYN_BYTES));
-    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::DYN_BYTES));
-    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem::DYN_BYTES));
+    FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 AttnSmem::DYN_BYTES));
     configured = true;
   }
   dim3 grid(ft_cdiv(seq, AT_Q), batch * heads);
   const float scale_log2e = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
-#define FT_FWD_LAUNCH(V)                                                                          \
-  FT_LAUNCH_PDL(ctx, k_attn_fwd_tc<V>, grid, AT_THREADS, AttnSmem::DYN_BYTES, q128, kv64, out16, \
-                ldo16, out32, ldo32, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0,        \
-                scale_log2e, ctx->status_dev)
-  switch (variant) {
-    case 1: FT_FWD_LAUNCH(1); break;
-    case 2: FT_FWD_LAUNCH(2); break;
-    case 3: FT_FWD_LAUNCH(3); break;
-    default: FT_FWD_LAUNCH(0); break;
-  }
-#undef FT_FWD_LAUNCH
+  FT_LAUNCH_PDL(ctx, k_attn_fwd_tc, grid, AT_THREADS, AttnSmem::DYN_BYTES, q128, kv64, out16, ldo16,
+                out32, ldo32, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale_log2e,
+                ctx->status_dev);
   return FT_OK;
 }
 
