@@ -201,7 +201,8 @@ extern "C" int ft_ctx_set_gemm_mode(FtContext* ctx, int mode) {
 
 extern "C" int ft_ctx_set_gemm_tile_m(FtContext* ctx, int rows) {
   FT_REQUIRE(ctx, "ft_ctx_set_gemm_tile_m: ctx is NULL");
-  FT_REQUIRE(rows == 0 || rows == 128 || rows == 256, "ft_ctx_set_gemm_tile_m: 0, 128 or 256");
+  FT_REQUIRE(rows == 0 || rows == 128 || rows == 256 || rows == 512,
+             "ft_ctx_set_gemm_tile_m: 0, 128, 256 or 512 (CTA pairs)");
   ctx->tile_m_override = rows;
   return FT_OK;
 }

@@ -542,6 +542,346 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   }
 }
 
+// =========================================================================================
+// The same product on CTA pairs (tcgen05 cta_group::2): a cluster of two CTAs owns a 256 x 256
+// output tile.  Each CTA loads its own 128 rows of A and HALF of the B tile (128 of the 256
+// weight rows) - a third less operand traffic per FLOP than the 128 x 256 single-CTA tile - and
+// keeps a 128 x 256 accumulator per buffer, so both accumulator buffers fit in tensor memory
+// and the epilogue stays hidden behind the next tile's products.  One thread of the even CTA
+// (the leader) issues the MMAs for both; barriers:
+//   full[s]   in the leader: one arrival (its producer, expecting both CTAs' bytes); both CTAs'
+//             TMA loads complete their transaction bytes there
+//   empty[s]  in each CTA: one arrival, from the leader's tcgen05.commit multicast
+//   tfull[b]  in each CTA: one arrival, commit multicast
+//   tempty[b] in the leader: 16 arrivals, the 8 epilogue warps of each CTA (remote for the odd one)
+// Pre-tiles (see PreTile) cover 256 rows per pair, 64 columns split 32 + 32.
+// =========================================================================================
+template <int STAGES>
+struct Smem2 {
+  static constexpr int A_BYTES = BM * BK * 2;          // this CTA's 128 rows
+  static constexpr int B_BYTES = 128 * BK * 2;         // this CTA's half of the 256 weight rows
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + 8 * 4096;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+           const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
+           const __grid_constant__ CUtensorMap map_b3, Epilogue ep, PreTile pre, int M, int N, int K,
+           int K2, uint32_t idesc, int* status) {
+  using L = Smem2<STAGES>;
+  constexpr int BN = 256, TM = 256;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+
+  const uint32_t bar_full = base + L::BAR_OFFSET;
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;
+  const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  uint32_t* tmem_slot = (uint32_t*)(gbase + L::BAR_OFFSET + (2 * STAGES + 4) * 8);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();      // 0: leader
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int tiles_m = (M + TM - 1) / TM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kb_main = (K + BK - 1) / BK;
+  const int kb_total = kb_main + (K2 + BK - 1) / BK;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + b * 8, 1);
+      mbar_init(bar_tempty + b * 8, 16);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  ft_pdl_wait();
+  ft_pdl_launch();
+
+  // the leader's copies of the barriers this CTA signals remotely
+  const uint32_t lead_full = mapa_shared(bar_full, 0);
+  const uint32_t lead_tempty = mapa_shared(bar_tempty, 0);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int p = npairs - 1 - pair; p < pre.tiles; p += npairs) {
+        for (int kb = 0; kb < kb_main; ++kb) {
+          if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, status, 5)) break;
+          const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+          if (rank == 0) mbar_expect_tx(bar_full + stage * 8, 2 * (L::A_BYTES + 32 * BK * 2));
+          tma_load_2d_pair(sa, &map_a, lead_full + stage * 8, kb * BK, p * TM + (int)rank * BM);
+          tma_load_2d_pair(sb, &map_b3, lead_full + stage * 8, kb * BK, (int)rank * 32);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (*abort_flag) break;
+      }
+      for (int tile = pair; tile < num_tiles && !*abort_flag; tile += npairs) {
+        const int m0 = (tile % tiles_m) * TM + (int)rank * BM, nt = tile / tiles_m;
+        const int nrow = nt * BN + (int)rank * 128;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (kb == kb_main && pre.tiles > 0 &&
+              !flag_wait(pre.flags + (tile % tiles_m), 16, abort_flag, status, 6))
+            break;
+          if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, abort_flag, status, 1)) break;
+          const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+          if (rank == 0) mbar_expect_tx(bar_full + stage * 8, 2 * L::STAGE_BYTES);
+          if (kb < kb_main) {
+            tma_load_2d_pair(sa, &map_a, lead_full + stage * 8, kb * BK, m0);
+            tma_load_2d_pair(sb, &map_b, lead_full + stage * 8, kb * BK, nrow);
+          } else {
+            tma_load_2d_pair(sa, &map_a2, lead_full + stage * 8, (kb - kb_main) * BK, m0);
+            tma_load_2d_pair(sb, &map_b2, lead_full + stage * 8, (kb - kb_main) * BK, nrow);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0;
+      int local = 0;
+      for (int p = npairs - 1 - pair; p < pre.tiles; p += npairs, ++local) {
+        const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(bar_tempty + buf * 8, acc_phase ^ 1, abort_flag, status, 7)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < kb_main; ++kb) {
+          if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, status, 8)) break;
+          tc_fence_after();
+          const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+          const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma_f16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), pre.idesc,
+                            (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit_pair(bar_empty + stage * 8, 3);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (*abort_flag) break;
+        tc_commit_pair(bar_tfull + buf * 8, 3);
+      }
+      for (int tile = pair; tile < num_tiles && !*abort_flag; tile += npairs, ++local) {
+        const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(bar_tempty + buf * 8, acc_phase ^ 1, abort_flag, status, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, status, 3)) break;
+          tc_fence_after();
+          const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+          const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma_f16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                            (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit_pair(bar_empty + stage * 8, 3);  // frees the stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (*abort_flag) break;
+        tc_commit_pair(bar_tfull + buf * 8, 3);      // accumulator complete, both CTAs
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quad = warp & 3;               // TMEM lanes [32*quad, 32*quad+32)
+    const int grp = (warp - 2) >> 2;
+    int local = 0;
+    uint8_t* stage_base = gbase + L::EPI_OFFSET + (warp - 2) * 4096;   // 32 x 128 bytes per warp
+    const bool vec_c = ep.c && ((ep.ldc & 3) == 0) && ((((uintptr_t)ep.c) & 15) == 0);
+    const bool vec_r = !ep.residual || (((ep.ldr & 3) == 0) && ((((uintptr_t)ep.residual) & 15) == 0));
+    const bool vec_h = ep.c16 && ((ep.ldc16 & 3) == 0) && ((((uintptr_t)ep.c16) & 7) == 0);
+    const float alpha = (ep.alpha_ptr ? *ep.alpha_ptr : 1.0f) * ep.alpha;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float amax_seen = 0.f;
+    constexpr int NCH = BN / 32;
+    for (int p = npairs - 1 - pair; p < pre.tiles; p += npairs, ++local) {
+      const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 9)) break;
+      tc_fence_after();
+      {
+        uint32_t r[32];
+        tc_ld32(t_lane + buf * BN + grp * 32, r);
+        tc_wait_ld();
+        uint8_t* st = stage_base + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *(float4*)(st + ((j ^ (lane & 7)) << 4)) = make_float4(
+              pre.alpha * __uint_as_float(r[4 * j]), pre.alpha * __uint_as_float(r[4 * j + 1]),
+              pre.alpha * __uint_as_float(r[4 * j + 2]), pre.alpha * __uint_as_float(r[4 * j + 3]));
+        __syncwarp();
+        const int row_base = p * TM + (int)rank * BM + quad * 32;
+        const int j = lane & 7;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const int rr = 4 * t + (lane >> 3);
+          const int grow = row_base + rr;
+          const float4 v4 = *(const float4*)(stage_base + rr * 128 + ((j ^ (rr & 7)) << 4));
+          if (grow < M) {
+            __half2 h0 = __floats2half2_rn(v4.x, v4.y), h1 = __floats2half2_rn(v4.z, v4.w);
+            *(uint2*)(pre.c16 + (long long)grow * pre.ldc16 + grp * 32 + 4 * j) =
+                make_uint2(*(uint32_t*)&h0, *(uint32_t*)&h1);
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        atomicAdd(pre.flags + p, 1);
+        mbar_arrive_cluster(lead_tempty + buf * 8);
+      }
+    }
+    for (int tile = pair; tile < num_tiles && !*abort_flag; tile += npairs, ++local) {
+      const int m0 = (tile % tiles_m) * TM + (int)rank * BM, nt = tile / tiles_m;
+      const int n0 = nt * BN;
+      const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 4)) break;
+      tc_fence_after();
+      float* cbase = ep.c;
+      uint32_t r[32];
+      tc_ld32(t_lane + buf * BN + grp * 32, r);
+#pragma unroll 1
+      for (int cb = grp; cb < NCH; cb += 2) {
+        tc_wait_ld();
+        const int col0 = n0 + cb * 32;
+        {
+          uint8_t* st = stage_base + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *(float4*)(st + ((j ^ (lane & 7)) << 4)) =
+                make_float4(alpha * __uint_as_float(r[4 * j]), alpha * __uint_as_float(r[4 * j + 1]),
+                            alpha * __uint_as_float(r[4 * j + 2]), alpha * __uint_as_float(r[4 * j + 3]));
+        }
+        if (cb + 2 < NCH) tc_ld32(t_lane + buf * BN + (cb + 2) * 32, r);
+        __syncwarp();
+        const int row_base = m0 + quad * 32;
+        const int j = lane & 7, gcol = col0 + 4 * j;
+        if (row_base < M && gcol < N) {
+          const bool full = gcol + 4 <= N;
+          const bool fast_r = ep.residual && full && vec_r;
+          float4 resv[8];
+          if (fast_r) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              const int grow = row_base + 4 * t + (lane >> 3);
+              resv[t] = grow < M ? *(const float4*)(ep.residual + (long long)grow * ep.ldr + gcol)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+          float bv[4] = {0.f, 0.f, 0.f, 0.f};
+          if (ep.bias) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (gcol + e < N) bv[e] = ep.bias[gcol + e];
+          }
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const int rr = 4 * t + (lane >> 3);
+            const int grow = row_base + rr;
+            float4 v4 = *(const float4*)(stage_base + rr * 128 + ((j ^ (rr & 7)) << 4));
+            if (grow >= M) continue;
+            float v[4] = {v4.x + bv[0], v4.y + bv[1], v4.z + bv[2], v4.w + bv[3]};
+            if (fast_r) {
+              v[0] += resv[t].x; v[1] += resv[t].y; v[2] += resv[t].z; v[3] += resv[t].w;
+            } else if (ep.residual) {
+              const float* rp = ep.residual + (long long)grow * ep.ldr + gcol;
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (gcol + e < N) v[e] += rp[e];
+            }
+            if (ep.amax_slot) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (full || gcol + e < N) amax_seen = fmaxf(amax_seen, fabsf(v[e]));
+            }
+            if (cbase) {
+              float* cp = cbase + (long long)grow * ep.ldc + gcol;
+              if (full && vec_c) {
+                *(float4*)cp = make_float4(v[0], v[1], v[2], v[3]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (gcol + e < N) cp[e] = v[e];
+              }
+            }
+            if (ep.c16) {
+              __half* hp = ep.c16 + (long long)grow * ep.ldc16 + gcol;
+              if (full && vec_h) {
+                __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                *(uint2*)hp = make_uint2(*(uint32_t*)&h0, *(uint32_t*)&h1);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (gcol + e < N) hp[e] = __float2half_rn(v[e]);
+              }
+            }
+          }
+        }
+        __syncwarp();   // the staging tile is reused by the next chunk
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(lead_tempty + buf * 8);
+    }
+    if (ep.amax_slot) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        amax_seen = fmaxf(amax_seen, __shfl_xor_sync(0xffffffffu, amax_seen, o));
+      if (lane == 0 && amax_seen > 0.f && __float_as_int(amax_seen) > *(volatile int*)ep.amax_slot)
+        atomicMax(ep.amax_slot, __float_as_int(amax_seen));
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  // neither CTA may leave while the other can still read its shared memory or signal its barriers
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
 // Up to six sub-blocks in a single launch (the adapters of a q|k|v group, B and A gradients),
 // each from its own slab set part[s][M][ldp].
 struct SlabSegs {
@@ -775,6 +1115,66 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
   return FT_OK;
 }
 
+// CTA-pair launch: `tiles` 256 x 256 output tiles over as many clusters of two as can be
+// resident at once (pre-tiles rely on every cluster making progress).
+template <int STAGES>
+int launch_tc2(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& ma2,
+               const CUtensorMap& mb2, const CUtensorMap& mb3, const Epilogue& ep, const PreTile& pre,
+               int M, int N, int K, int K2, uint32_t idesc, double flops) {
+  using L = Smem2<STAGES>;
+  static bool configured = false;
+  static int max_pairs = 0;
+  if (!configured) {
+    FT_CUDA(cudaFuncSetAttribute(k_gemm_tc2<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 L::DYN_BYTES));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(ctx->sm_count & ~1));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = L::DYN_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    FT_CUDA(cudaOccupancyMaxActiveClusters(&n, k_gemm_tc2<STAGES>, &cfg));
+    max_pairs = std::min(n, ctx->sm_count / 2);
+    configured = true;
+  }
+  if (max_pairs < 1) return FT_ERR_UNSUPPORTED;
+  const int tiles = ft_cdiv(M, 256) * ft_cdiv(N, 256);
+  const int pairs = std::max(1, std::min(tiles, max_pairs));
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (ctx->profile) {
+    while (ctx->prof_events.size() < ctx->prof_used + 2) {
+      cudaEvent_t e;
+      FT_CUDA(cudaEventCreate(&e));
+      ctx->prof_events.push_back(e);
+    }
+    e0 = ctx->prof_events[ctx->prof_used++];
+    e1 = ctx->prof_events[ctx->prof_used++];
+    FT_CUDA(cudaEventRecord(e0, ctx->stream));
+  }
+  {
+    const bool pa = ctx->profile_all;
+    if (pa) ft_prof_begin(ctx, "k_gemm_tc2<pair 256x256>");
+    ctx->profile_all = false;
+    cudaError_t le = ft_launch_ex(ctx, k_gemm_tc2<STAGES>, 2 * pairs, GEMM_THREADS, L::DYN_BYTES, ma, mb,
+                                  ma2, mb2, mb3, ep, pre, M, N, K, K2, idesc, ctx->status_dev);
+    ctx->profile_all = pa;
+    if (pa) ft_prof_end(ctx);
+    ctx->launches++;
+    if (le == cudaSuccess) le = cudaPeekAtLastError();
+    if (le != cudaSuccess) return ft_cuda_fail(le, "k_gemm_tc2", __FILE__, __LINE__);
+  }
+  if (ctx->profile) {
+    FT_CUDA(cudaEventRecord(e1, ctx->stream));
+    ctx->prof_flops += flops;
+    ctx->prof_launches++;
+  }
+  return FT_OK;
+}
+
 }  // namespace
 
 int ft_amax_arm(FtContext* ctx) {
@@ -862,6 +1262,50 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   }
   const CUtensorMapDataType dt = g.ab_type == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  // CTA pairs (256 x 256 tile over two SMs) are the default for wide products: measured
+  // 1340-1480 TFLOP/s against 1150-1280 for the 128-row and 1100-1400 for the 256-row
+  // single-CTA tiles; FT_GEMM_TILE_M=128|256 selects those, 512 the pairs
+  const bool pair = BN == 256 && g.M >= 256 && (ctx->tile_m_override == 512 || ctx->tile_m_override == 0);
+  if (pair) {
+    const int fmt = g.ab_type == FT_F16 ? 0 : 1;
+    FT_TRY(make_map(ctx, &ma, g.a, dt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, 128));
+    FT_TRY(make_map(ctx, &mb, g.b, dt, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, 128));
+    if (tail) {
+      FT_TRY(make_map(ctx, &ma2, g.a2, dt, (uint64_t)g.K2, (uint64_t)g.M, (uint64_t)g.lda2, BK, 128));
+      FT_TRY(make_map(ctx, &mb2, g.b2, dt, (uint64_t)g.K2, (uint64_t)g.N, (uint64_t)g.ldb2, BK, 128));
+    } else {
+      ma2 = ma;
+      mb2 = mb;
+    }
+    Epilogue ep;
+    ep.c = g.c; ep.ldc = g.ldc; ep.c16 = g.c16; ep.ldc16 = g.ldc16;
+    ep.alpha_ptr = g.alpha_ptr; ep.alpha = g.alpha; ep.bias = g.bias;
+    ep.residual = g.residual; ep.ldr = g.ldr;
+    ep.amax_slot = nullptr;
+    if (g.want_amax && ctx->amax_out) {
+      ep.amax_slot = ctx->amax_out;
+      ctx->amax_ready = true;
+    }
+    double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
+    CUtensorMap mb3 = mb;
+    PreTile pre;
+    memset(&pre, 0, sizeof(pre));
+    if (g.pre_b) {
+      const int tiles_m = ft_cdiv(g.M, 256);
+      if (!tail || !tma_ok(g.pre_b, g.pre_ldb, g.K) || !g.pre_c16 || (g.pre_ldc16 % 4) ||
+          (((uintptr_t)g.pre_c16) & 7) || tiles_m > FT_PRE_FLAGS)
+        return FT_ERR_UNSUPPORTED;
+      FT_TRY(make_map(ctx, &mb3, g.pre_b, dt, (uint64_t)g.K, 64, (uint64_t)g.pre_ldb, BK, 32));
+      FT_CUDA(cudaMemsetAsync(ctx->pre_flags, 0, (size_t)tiles_m * sizeof(int), ctx->stream));
+      pre.tiles = tiles_m;
+      pre.c16 = g.pre_c16; pre.ldc16 = g.pre_ldc16; pre.alpha = g.pre_alpha;
+      pre.flags = ctx->pre_flags;
+      pre.idesc = make_idesc(256, 64, fmt, fmt);
+      flops += 2.0 * g.M * 64.0 * (double)g.K;
+    }
+    return launch_tc2<6>(ctx, ma, mb, ma2, mb2, mb3, ep, pre, g.M, g.N, g.K, g.K2,
+                         make_idesc(256, 256, fmt, fmt), flops);
+  }
   const uint32_t a_rows = (uint32_t)(MH * BM);
   FT_TRY(make_map(ctx, &ma, g.a, dt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, a_rows));
   FT_TRY(make_map(ctx, &mb, g.b, dt, (uint64_t)g.K, (uint64_t)g.N, (uint64_t)g.ldb, BK, (uint32_t)BN));

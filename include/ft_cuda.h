@@ -74,7 +74,8 @@ int ft_ctx_profile_report(FtContext* ctx, char* buf, size_t cap);
 int ft_ctx_profile_read(FtContext* ctx, double* gemm_ms, double* gemm_flops,
                         uint64_t* gemm_launches);
 int ft_ctx_set_gemm_mode(FtContext* ctx, int mode);    /* FT_GEMM_*; default FT_GEMM_F32 */
-/* Tuning/diagnostics: force the tensor-core GEMM's output tile height (128 or 256 rows;
+/* Tuning/diagnostics: force the tensor-core GEMM's output tile height (128 or 256 rows, 512 = 256 x 256
+ * tiles on CTA pairs;
  * 0 = choose per shape, the default; FT_GEMM_TILE_M in the environment sets the initial value). */
 int ft_ctx_set_gemm_tile_m(FtContext* ctx, int rows);
 int ft_ctx_launch_count(FtContext* ctx, uint64_t* kernels_launched);

@@ -327,8 +327,8 @@ def test_attention_backward_on_tensor_cores(cuda_ctx, eng, b, s, h, hkv):
 
 # tcgen05 GEMM through ft_matmul_bt_f16b in F16 mode: activations with 8 significant bits times
 # f16 weights give exact products, so only f32 accumulation order separates the result from
-# the f64 product.  Both output tile heights, ragged M/N/K tails.
-@pytest.mark.parametrize("tile_m", [128, 256])
+# the f64 product.  Both output tile heights and CTA pairs (512), ragged M/N/K tails.
+@pytest.mark.parametrize("tile_m", [128, 256, 512])
 @pytest.mark.parametrize("m,n,k", [(128, 64, 64), (256, 256, 128), (384, 320, 192), (1000, 1000, 520),
                                    (2048, 768, 4096), (777, 2048, 264)])
 def test_tensor_core_gemm_shapes(cuda_ctx, eng, tile_m, m, n, k):
