@@ -278,6 +278,66 @@ class Trainer:
             rest = rest[take:]
         return out
 
+    # ---- checkpoint / resume in the reference's file formats (trainer/checkpoint.rs, ----------
+    # ---- cli main.rs:1799-1841: adapter file + `x.state.json` + `x.state.safetensors`) ---------
+    def save_adapter(self, path) -> None:
+        """The adapters as F32 safetensors with rank/alpha/target_modules in the header."""
+        from . import checkpoint as ck
+        lora = self.model.lora
+        meta = ck.LoraMetadata(lora.rank, lora.alpha, list(lora.target_modules))
+        tensors = {ck.reference_tensor_name(n): t.detach().cpu().numpy()
+                   for n, t in self.model.named_lora_params().items()}
+        ck.save_lora_checkpoint(path, tensors, meta)
+
+    def load_adapter(self, path) -> int:
+        """All-or-nothing restore of the adapters (checkpoint.rs:214-297); returns the count."""
+        from . import checkpoint as ck
+        cp = ck.load_lora_checkpoint(path)
+        params = self.model.named_lora_params()
+        expected = {ck.reference_tensor_name(n): list(t.shape) for n, t in params.items()}
+        sources = ck.resolve_checkpoint(cp, expected)
+        adapters = {ck.host_tensor_name(n): torch.from_numpy(np.ascontiguousarray(cp.tensors[key][1]))
+                    for n, key in sources.items()}
+        self.model.load_adapters(adapters)
+        return len(adapters)
+
+    def optimizer_checkpoint(self):
+        """`AdamW::save_state` (autograd/lib.rs:1577-1625): hyper-parameters, t, and both moments
+        of every trainable tensor under its reference name."""
+        from . import checkpoint as ck
+        o = self.optimizer
+        m, v = self.model.named_moments()
+        def states(d):
+            return {ck.reference_tensor_name(n): ck.OptimizerTensorState(list(t.shape), t.detach().cpu().numpy().ravel())
+                    for n, t in d.items()}
+        return ck.AdamWCheckpoint(o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, o.t, states(m), states(v))
+
+    def save_training_checkpoint(self, state_path, training_state) -> None:
+        from . import checkpoint as ck
+        ck.TrainingCheckpoint(training_state, self.optimizer_checkpoint(), None).save(state_path)
+
+    def load_training_checkpoint(self, state_path):
+        """Restores t, the hyper-parameters and the moments; a moment whose shape does not fit is
+        an error and nothing is changed (autograd/lib.rs:1627-1700).  Returns the TrainingState."""
+        from . import checkpoint as ck
+        cp = ck.TrainingCheckpoint.load(state_path)
+        a = cp.optimizer_state
+        if a is not None:
+            m, v = self.model.named_moments()
+            for dst, src, what in ((m, a.m_states, "first"), (v, a.v_states, "second")):
+                for n, t in dst.items():
+                    s = src.get(ck.reference_tensor_name(n))
+                    if s is not None and list(s.shape) != list(t.shape):
+                        raise ck.CheckpointError(f"{what} moment of {n} has shape {list(s.shape)}, expected {list(t.shape)}")
+            for dst, src in ((m, a.m_states), (v, a.v_states)):
+                for n, t in dst.items():
+                    s = src.get(ck.reference_tensor_name(n))
+                    if s is not None:
+                        t.copy_(torch.from_numpy(np.asarray(s.data, np.float32).reshape(s.shape)))
+            o = self.optimizer
+            o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, o.t = a.lr, a.beta1, a.beta2, a.eps, a.weight_decay, a.t
+        return cp.training_state
+
     def train_arrays(self, ids: np.ndarray, tgt: np.ndarray, msk: np.ndarray) -> List[StepStats]:
         """`train_batch` for already rectangular uint32/uint8 arrays [sequences, seq_len]
         whose length is a multiple of the length bucket (the benchmark's input form)."""
