@@ -117,6 +117,7 @@ PROTOTYPES = {
     "ft_model_workspace_bytes": [_P, _I, _I, C.POINTER(_Z)],
     "ft_model_set_workspace": [_P, _P, _Z],
     "ft_model_forward_backward": [_P, _P, _P, _P, _I, _I, _F, _P, _P],
+    "ft_model_forward_loss": [_P, _P, _P, _P, _I, _I, _P, _P],
     "ft_model_zero_grad": [_P],
     "ft_model_apply_gradients": [_P, _F, _F, C.POINTER(FtAdamParams), _P],
 }

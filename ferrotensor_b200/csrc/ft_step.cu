@@ -917,10 +917,26 @@ extern "C" int ft_model_zero_grad(FtLoraModel* m) {
   return FT_OK;
 }
 
+static int step_impl(FtLoraModel* m, const uint32_t* ids, const uint32_t* targets,
+                     const float* weights, int sequences, int seq_len, float seed, float* row_loss,
+                     float* logits, bool backward);
+
 extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
                                          const uint32_t* targets, const float* weights,
                                          int sequences, int seq_len, float seed, float* row_loss,
                                          float* logits) {
+  return step_impl(m, ids, targets, weights, sequences, seq_len, seed, row_loss, logits, true);
+}
+
+extern "C" int ft_model_forward_loss(FtLoraModel* m, const uint32_t* ids, const uint32_t* targets,
+                                     const float* weights, int sequences, int seq_len,
+                                     float* row_loss, float* logits) {
+  return step_impl(m, ids, targets, weights, sequences, seq_len, 0.f, row_loss, logits, false);
+}
+
+static int step_impl(FtLoraModel* m, const uint32_t* ids, const uint32_t* targets,
+                     const float* weights, int sequences, int seq_len, float seed, float* row_loss,
+                     float* logits, bool backward) {
   FT_REQUIRE(m && ids && targets && weights && row_loss, "ft_model_forward_backward: NULL argument");
   FT_REQUIRE(m->prepared, "ft_model_forward_backward: call ft_model_prepare first");
   FT_REQUIRE(sequences > 0 && seq_len > 0, "ft_model_forward_backward: empty batch");
@@ -964,7 +980,9 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
       const __half* X16 = m->hN16 + (size_t)r0 * h;
       __half* xa16 = m->xa16_head + (size_t)r0 * RP;
       FT_TRY(linear_fwd_fused(m, m->head, X16, z, V, xa16, nullptr, 0, rows));
-      if ((V % 8) == 0) {
+      if (!backward) {
+        FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, nullptr, row_loss + r0, rows, V, seed));
+      } else if ((V % 8) == 0) {
         // the loss kernel writes its gradient as scaled f16 operands: its magnitude is bounded
         // by the row weights, so the scale is known before the first element is written
         const float* ce_scales = nullptr;
@@ -983,12 +1001,14 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
       const float* X = m->hN + (size_t)r0 * h;
       float* xa = m->xa_head + (size_t)r0 * std::max(1, m->head.R);
       FT_TRY(linear_fwd(m, m->head, X, h, z, V, xa, rows));
-      FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, m->logit_chunk, row_loss + r0, rows,
-                            V, seed));
-      FT_TRY(linear_bwd(m, m->head, X, h, m->logit_chunk, V, xa, m->dh + (size_t)r0 * h, h, rows,
-                        false));
+      FT_TRY(ft_k_masked_ce(ctx, z, targets + r0, weights + r0, backward ? m->logit_chunk : nullptr,
+                            row_loss + r0, rows, V, seed));
+      if (backward)
+        FT_TRY(linear_bwd(m, m->head, X, h, m->logit_chunk, V, xa, m->dh + (size_t)r0 * h, h, rows,
+                          false));
     }
   }
+  if (!backward) return FT_OK;   // evaluation: the loss rows are all the caller wants
   if (fused) FT_TRY(ft_amax_arm(ctx));   // consumed by the last block's first conversion
   FT_TRY(ft_k_rms_norm_bwd(ctx, m->x[L], m->final_norm, m->dh, m->dx, nullptr, T, h, c.eps, false));
 

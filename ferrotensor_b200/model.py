@@ -171,6 +171,14 @@ class LoraModel:
         call("ft_model_forward_backward", self.handle, _ptr(ids), _ptr(targets), _ptr(weights),
              sequences, seq_len, float(seed), _ptr(row_loss), _ptr(logits))
 
+    def forward_loss(self, ids: torch.Tensor, targets: torch.Tensor, weights: torch.Tensor,
+                     sequences: int, seq_len: int, row_loss: torch.Tensor,
+                     logits: Optional[torch.Tensor] = None) -> None:
+        """The forward half only: row losses (and logits), gradients untouched."""
+        self._ensure_workspace(sequences, seq_len)
+        call("ft_model_forward_loss", self.handle, _ptr(ids), _ptr(targets), _ptr(weights),
+             sequences, seq_len, _ptr(row_loss), _ptr(logits))
+
     def apply_gradients(self, grad_scale: float, max_norm: Optional[float], adam: FtAdamParams) -> None:
         call("ft_model_apply_gradients", self.handle, float(grad_scale),
              float(max_norm) if max_norm else 0.0, C.byref(adam), _ptr(self.norm_out))

@@ -42,6 +42,9 @@ class Batch:
     padded_target_ids: Sequence[Sequence[int]]
     attention_mask: Sequence[Sequence[int]]
     loss_masks: Sequence[Sequence[int]]
+    input_ids: Optional[Sequence[Sequence[int]]] = None     # unpadded, as the data loader read them
+    target_ids: Optional[Sequence[Sequence[int]]] = None
+    max_seq_len: int = 0
 
     @property
     def batch_size(self) -> int:
@@ -277,6 +280,36 @@ class Trainer:
             out.extend(self.train_chunk(rest[:take]))
             rest = rest[take:]
         return out
+
+    # ---- evaluation (ferrotensor-cli/src/main.rs:1111-1137) ---------------------------------
+    def evaluate(self, dataset, limit: Optional[int] = None, chunk: int = 8) -> Tuple[float, int]:
+        """Token-weighted mean loss over (at most `limit`) examples of `dataset` and the number
+        of supervised tokens it covers; (nan, 0) when nothing is supervised.  Forward only:
+        gradients and the accumulation window are untouched."""
+        examples = list(dataset.examples())[:limit] if limit is not None else list(dataset.examples())
+        seqs = [(e.input_ids, e.target_ids, e.loss_mask) for e in examples
+                if min(len(e.input_ids), len(e.target_ids)) >= 1 and any(e.loss_mask)]
+        dev = self.ctx.device
+        loss_sum, tokens_total = 0.0, 0
+        for c0 in range(0, len(seqs), max(chunk, 1)):
+            ids, tgt, msk = pad_chunk(seqs[c0:c0 + chunk], self.length_bucket)
+            n, s = ids.shape
+            row_tgt, row_w, tokens = batch_targets_weights(tgt, msk, self.model.cfg.vocab)
+            d_ids = torch.from_numpy(ids.reshape(-1).view(np.int32)).to(dev)
+            d_tgt = torch.from_numpy(row_tgt.reshape(-1).view(np.int32)).to(dev)
+            d_w = torch.from_numpy(row_w.reshape(-1)).to(dev)
+            row_loss = torch.empty(n * s, device=dev, dtype=torch.float32)
+            self.model.forward_loss(d_ids, d_tgt, d_w, n, s, row_loss)
+            self.ctx.synchronize()
+            per_seq = row_loss.cpu().numpy().reshape(n, s).astype(np.float64).sum(axis=1)
+            for r in range(n):
+                t = int(tokens[r])
+                if t > 0:
+                    loss_sum += float(np.float32(per_seq[r] / t)) * t
+                    tokens_total += t
+        if tokens_total == 0:
+            return float("nan"), 0
+        return float(np.float32(loss_sum / tokens_total)), tokens_total
 
     # ---- checkpoint / resume in the reference's file formats (trainer/checkpoint.rs, ----------
     # ---- cli main.rs:1799-1841: adapter file + `x.state.json` + `x.state.safetensors`) ---------

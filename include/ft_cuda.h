@@ -266,6 +266,12 @@ int ft_model_set_workspace(FtLoraModel* m, void* dev_ptr, size_t bytes);
 int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids, const uint32_t* targets,
                               const float* weights, int sequences, int seq_len, float seed,
                               float* row_loss, float* logits);
+/* The forward half of ft_model_forward_backward: row losses (and logits when asked for) with
+ * the same arguments, gradients untouched - what the reference's `evaluate` computes under
+ * `no_grad` (ferrotensor-cli/src/main.rs:1111-1137). */
+int ft_model_forward_loss(FtLoraModel* m, const uint32_t* ids, const uint32_t* targets,
+                          const float* weights, int sequences, int seq_len, float* row_loss,
+                          float* logits);
 int ft_model_zero_grad(FtLoraModel* m);
 /* After the (optional) cross-rank sum of the gradient buffer: g *= grad_scale (1/world),
  * global L2 norm on the device (4096-element f32 partials, summed in f64), skip when
