@@ -105,6 +105,7 @@ PROTOTYPES = {
     "ft_clip_grad_by_norm": [_P, _P, _Z, _F],
     "ft_adamw_update": [_P, _P, _P, _P, _P, _Z, C.POINTER(FtAdamParams)],
     "ft_embedding_gather": [_P, _P, _P, _P, _I, _I, _I],
+    "ft_argmax_rows": [_P, _P, _P, _I, _I],
     "ft_model_create": [_P, C.POINTER(FtModelConfig), C.POINTER(_P)],
     "ft_model_destroy": [_P],
     "ft_model_trainable_count": [_P, C.POINTER(_Z)],

@@ -356,6 +356,10 @@ static int check_mm(const char* who, FtContext* ctx, const void* a, const void* 
 static int mm_dispatch(FtContext* ctx, const float* a, long long sam, long long sak,
                        const void* b, FtDType bt, long long sbk, long long sbn, float* out, int M,
                        int N, int K) {
+  // one row against a row-major [K, N] matrix: the matrix-vector kernel, as the reference
+  // routes it (matmul.rs:328-331)
+  if (M == 1 && sak == 1 && sbn == 1 && sbk == N && (((uintptr_t)b) & 15) == 0)
+    return ft_k_matvec(ctx, a, b, bt, out, K, N);
   if (ctx->gemm_mode != FT_GEMM_F32 && sak == 1 && sbk == 1 && bt == FT_F16 && (K % 8) == 0 &&
       M >= 128 && N >= 64 && K >= 64) {
     // A[M,K] row-major f32 -> f16 scratch (auto-scaled: the caller's data may be gradients);
@@ -502,6 +506,8 @@ extern "C" int ft_flash_attention_v2(FtContext* ctx, const float* q, const float
                                      const FtAttnParams* p) {
   FT_REQUIRE(ctx && q && k && v && out, "ft_flash_attention_v2: NULL argument");
   FT_TRY(check_attn("ft_flash_attention_v2", p, mask));
+  // one query and no stats: the decode kernel, whose blocks split the keys (attention.rs:205-224)
+  if (p->seq_q == 1 && !stats && p->head_dim <= 128) return ft_k_attention_decode(ctx, q, k, v, out, *p);
   if (ctx->gemm_mode == FT_GEMM_F16 && p->head_dim == 64 && p->causal && !p->causal_offset &&
       !p->window && p->seq_q == p->seq_k && p->seq_q >= 64) {
     // tensor-core form: q, k, v are rounded to f16 side by side, one row per token
@@ -586,6 +592,11 @@ extern "C" int ft_adamw_update(FtContext* ctx, float* w, const float* g, float* 
                                size_t n, const FtAdamParams* p) {
   FT_REQUIRE(ctx && p && (n == 0 || (w && g && m && v)), "ft_adamw_update: NULL argument");
   return n ? ft_k_adamw(ctx, w, g, m, v, n, p) : FT_OK;
+}
+
+extern "C" int ft_argmax_rows(FtContext* ctx, const float* x, uint32_t* out_idx, int rows, int len) {
+  FT_REQUIRE(ctx && x && out_idx, "ft_argmax_rows: NULL argument");
+  return ft_k_argmax_rows(ctx, x, out_idx, rows, len);
 }
 
 extern "C" int ft_embedding_gather(FtContext* ctx, const float* table, const uint32_t* ids,

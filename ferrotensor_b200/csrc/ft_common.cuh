@@ -275,6 +275,11 @@ int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const floa
                        float* gb, long long ldgb, int rows, int n);
 // y[t, j] += bias[j]
 int ft_k_add_bias(FtContext* ctx, float* y, long long ld, const float* bias, int rows, int n);
+// decode-time kernels                                               (ft_infer.cu)
+int ft_k_matvec(FtContext* ctx, const float* x, const void* w, FtDType w_type, float* out, int K, int N);
+int ft_k_attention_decode(FtContext* ctx, const float* q, const float* k, const float* v, float* out,
+                          const FtAttnParams& p);
+int ft_k_argmax_rows(FtContext* ctx, const float* x, uint32_t* out, int rows, int len);
 int ft_k_masked_ce16(FtContext* ctx, const float* logits, const uint32_t* targets,
                      const float* weights, __half* g16, long long ld16, float* row_loss, int rows,
                      int vocab, float grad_scale, const float** scales_out);

@@ -398,6 +398,14 @@ class ComputeEngine:
         call("ft_masked_cross_entropy_weighted", ctx.handle, logits.ptr, targets.ptr, weights.ptr,
              grad.ptr, row_loss.ptr, rows, vocab)
 
+    # ---- misc.rs:20-34
+    def argmax_rows(self, ctx, input, out_idx):
+        n = input.shape[-1] if input.shape else 1
+        n = max(n, 1)
+        rows = input.numel() // n
+        _require(out_idx.numel() == rows, "argmax_rows: one index per row")
+        call("ft_argmax_rows", ctx.handle, input.ptr, out_idx.ptr, rows, n)
+
     def sum_squares_partial(self, ctx, x, out, offset) -> int:
         n = C.c_size_t()
         call("ft_sum_squares_partial", ctx.handle, x.ptr, x.numel(), out.ptr, offset, C.byref(n))

@@ -2,6 +2,8 @@
 
     python -m ferrotensor_b200.microbench gemm --m 8192 --n 8192 --k 2048
     python -m ferrotensor_b200.microbench attention --batch 8 --seq 1024 --heads 32 --kv-heads 32
+    python -m ferrotensor_b200.microbench matvec --k 2048 --n 8192
+    python -m ferrotensor_b200.microbench decode --batch 8 --seq 4096
 
 Each case holds a few hundred MB on the device at most, which makes it the right target for a
 profiler capture of one kernel (the training step keeps tens of GB resident).  Times come from
@@ -92,6 +94,48 @@ def attention(args):
             print(f"{name}: {ms * 1e3:.1f} us, {fwd_flop * mult / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
 
 
+def matvec(args):
+    ctx = CudaContext(0)
+    eng = ComputeEngine(ctx)
+    k, n = args.k, args.n
+    x = _dev_f32(ctx, [1, k], 1.0, 1)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    # a few different weight matrices in turn so that the 126 MB L2 does not serve the reads
+    ws = [UnifiedTensor((torch.randn(k * n, device="cuda", generator=g) * 0.05).half().view(torch.uint8),
+                        [k, n], DType.FP16) for _ in range(args.copies)]
+    out = UnifiedTensor.empty(ctx, [1, n])
+    for i in range(args.warmup):
+        eng.matmul_f16b(ctx, x, ws[i % len(ws)], out)
+    ctx.profile(2)
+    for i in range(args.iters):
+        eng.matmul_f16b(ctx, x, ws[i % len(ws)], out)
+    ctx.synchronize()
+    rep = _report(ctx, "matvec", {"k": k, "n": n})
+    ms = sum(v["ms_per_launch"] for v in rep["kernels"].values())
+    print(f"matvec f16 weights {k} x {n}: {ms * 1e3:.1f} us, {k * n * 2 / (ms * 1e-3) / 1e9:.0f} GB/s of weights")
+
+
+def decode(args):
+    ctx = CudaContext(0)
+    eng = ComputeEngine(ctx)
+    b, s, h, hk, d = args.batch, args.seq, args.heads, args.kv_heads, 64
+    q = _dev_f32(ctx, [b, 1, h, d], 1.0, 1)
+    caches = [(_dev_f32(ctx, [b, s, hk, d], 1.0, 2 + 2 * i), _dev_f32(ctx, [b, s, hk, d], 1.0, 3 + 2 * i))
+              for i in range(args.copies)]
+    out = UnifiedTensor.empty(ctx, [b, 1, h, d])
+    opts = AttentionOptions(causal=True, causal_offset=s - 1)
+    for i in range(args.warmup):
+        eng.flash_attention_v2_with(ctx, q, *caches[i % len(caches)], out, opts)
+    ctx.profile(2)
+    for i in range(args.iters):
+        eng.flash_attention_v2_with(ctx, q, *caches[i % len(caches)], out, opts)
+    ctx.synchronize()
+    rep = _report(ctx, "decode", {"batch": b, "seq": s, "heads": h, "kv_heads": hk})
+    ms = sum(v["ms_per_launch"] for v in rep["kernels"].values())
+    byts = 2.0 * b * s * hk * d * 4
+    print(f"decode attention: {ms * 1e3:.1f} us, {byts / (ms * 1e-3) / 1e9:.0f} GB/s of K and V")
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -105,11 +149,21 @@ def main():
     a.add_argument("--heads", type=int, default=32)
     a.add_argument("--kv-heads", type=int, default=32)
     a.add_argument("--forward-only", action="store_true")
-    for p in (g, a):
+    mv = sub.add_parser("matvec")
+    mv.add_argument("--k", type=int, default=2048)
+    mv.add_argument("--n", type=int, default=8192)
+    mv.add_argument("--copies", type=int, default=8)
+    dc = sub.add_parser("decode")
+    dc.add_argument("--batch", type=int, default=8)
+    dc.add_argument("--seq", type=int, default=4096)
+    dc.add_argument("--heads", type=int, default=32)
+    dc.add_argument("--kv-heads", type=int, default=32)
+    dc.add_argument("--copies", type=int, default=3)
+    for p in (g, a, mv, dc):
         p.add_argument("--iters", type=int, default=5)
         p.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args()
-    {"gemm": gemm, "attention": attention}[args.case](args)
+    {"gemm": gemm, "attention": attention, "matvec": matvec, "decode": decode}[args.case](args)
 
 
 if __name__ == "__main__":

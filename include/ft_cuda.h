@@ -193,6 +193,10 @@ int ft_clip_grad_by_norm(FtContext* ctx, float* g, size_t n, float scale);
 int ft_adamw_update(FtContext* ctx, float* w, const float* g, float* m, float* v, size_t n,
                     const FtAdamParams* p);
 
+/* engine/misc.rs:20-34 argmax_rows: for each of `rows` rows of `len` f32 values, the index of
+ * the largest in f32::total_cmp order, the last index winning ties (a greedy token). */
+int ft_argmax_rows(FtContext* ctx, const float* x, uint32_t* out_idx, int rows, int len);
+
 /* ---- embedding rows: ferrotensor-autograd/src/lib.rs:1159-1179 (a host loop in the
  * reference).  out[t,:] = table[ids[t],:]; ids[t] >= vocab gives a zero row. */
 int ft_embedding_gather(FtContext* ctx, const float* table, const uint32_t* ids, float* out,

@@ -194,3 +194,36 @@ def embedding(table, ids):
     ok = ids < table.shape[0]
     out[ok] = table[ids[ok]]
     return out
+
+
+def attention_decode(q, k, v, b, sk, h, hkv, d, causal=True, causal_offset=0, window=0, dtype=torch.float64):
+    """One query per (batch, head) against a KV cache (flash_attention_v2.wgsl:284-382): the query
+    sits at position `causal_offset`; key kp is visible when kp < sk, (not causal or kp <= qa) and
+    (no window or |qa - kp| < window) (`fa_visible`, :106-116).  A row with no visible key is 0."""
+    q = _t(q, dtype).view(b, 1, h, d).transpose(1, 2)
+    k = _t(k, dtype).view(b, sk, hkv, d).transpose(1, 2).repeat_interleave(h // hkv, dim=1)
+    v = _t(v, dtype).view(b, sk, hkv, d).transpose(1, 2).repeat_interleave(h // hkv, dim=1)
+    s = q @ k.transpose(-1, -2) * (1.0 / math.sqrt(d))
+    kp = torch.arange(sk)
+    vis = torch.ones(sk, dtype=torch.bool)
+    if causal:
+        vis &= kp <= causal_offset
+    if window > 0:
+        vis &= (kp - causal_offset).abs() < window
+    s = s.masked_fill(~vis, float("-inf"))
+    if not vis.any():
+        return np.zeros((b, 1, h, d), dtype=np.float32)
+    p = torch.softmax(s, dim=-1)
+    return (p @ v).transpose(1, 2).contiguous().to(torch.float32).numpy()
+
+
+def argmax_rows(x):
+    """Index of the largest value per row in `f32::total_cmp` order, the last index winning ties
+    (kernels.wgsl:251-296): compare the bit patterns mapped to an order-preserving unsigned key."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    bits = x.view(np.uint32)
+    key = np.where(bits & np.uint32(0x80000000), ~bits, bits | np.uint32(0x80000000)).astype(np.uint64)
+    n = x.shape[-1]
+    # larger index wins ties: combine (key, index) into one sortable integer
+    combined = key * np.uint64(n) + np.arange(n, dtype=np.uint64)
+    return combined.argmax(axis=-1).astype(np.uint32)
