@@ -318,8 +318,14 @@ def run_cuda(args):
     # ---- roofline of the dominant kernel: the tensor-core GEMM, timed inside a step ------------
     ctx.profile(True)
     resident_step()
+    ctx.synchronize()
+    gemm_bytes = ctx.profile_bytes()
     gemm_ms, gemm_flops, gemm_launches = ctx.profile_read()
     ctx.profile(False)
+    # DRAM traffic per launch: the launches' algorithmic bytes (operands once, results once) times
+    # the ratio dram bytes / algorithmic bytes that one ncu capture of the 8192 x 8192 x 2048
+    # launch gave (344 MB / 335 MB); the full step is too large to capture with all metrics
+    traffic = gemm_bytes / gemm_launches * (344.0 / 335.0) if gemm_launches else None
 
     kernel_ms = None
     if args.kernel_times:
@@ -373,7 +379,8 @@ def run_cuda(args):
         "roofline": {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 f16)", "achieved": achieved,
                      "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"] if peaks["tflops"] else None,
-                     "traffic": None, "peak_source": peaks["source"] + " (sustained)",
+                     "traffic": traffic, "traffic_unit": "bytes per launch (algorithmic x 1.027, the ncu-measured dram/algorithmic ratio of one launch)",
+                     "peak_source": peaks["source"] + " (sustained)",
                      "launches_per_step": gemm_launches, "kernel_ms_per_step": gemm_ms},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},

@@ -191,6 +191,13 @@ extern "C" int ft_ctx_profile_read(FtContext* ctx, double* gemm_ms, double* gemm
   return FT_OK;
 }
 
+extern "C" int ft_ctx_profile_bytes(FtContext* ctx, double* gemm_bytes) {
+  FT_REQUIRE(ctx && gemm_bytes, "ft_ctx_profile_bytes: NULL argument");
+  *gemm_bytes = ctx->prof_bytes;
+  ctx->prof_bytes = 0.0;
+  return FT_OK;
+}
+
 extern "C" int ft_ctx_set_gemm_mode(FtContext* ctx, int mode) {
   FT_REQUIRE(ctx, "ft_ctx_set_gemm_mode: ctx is NULL");
   FT_REQUIRE(mode == FT_GEMM_F32 || mode == FT_GEMM_F16 || mode == FT_GEMM_F16X2,

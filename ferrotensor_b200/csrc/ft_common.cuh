@@ -43,6 +43,8 @@ struct FtContext {
   std::vector<cudaEvent_t> prof_events;  // start/stop pairs, reused
   size_t prof_used = 0;                  // events handed out since the last read
   double prof_flops = 0.0;
+  double next_launch_bytes = 0.0;
+  double prof_bytes = 0.0;   // algorithmic bytes (operands once, results once) of the timed GEMM launches
   uint64_t prof_launches = 0;
   // optional timing of EVERY launch by kernel name (ft_ctx_profile(ctx, 2))
   bool profile_all = false;
@@ -204,19 +206,6 @@ struct FtKoProblem {
 int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T);
 int ft_slab_reduce_problems(FtContext* ctx, int nprob, const FtKoProblem* prob,
                             const float* alpha_ptr, float alpha, bool accumulate);
-// Token-reduction product P[M, N<=64] = sum_t A[t,m] B[t,n] (A [T,M], B [T,N], f16) as K-split
-// f32 slabs [nslabs][M][64] in context scratch; ft_slab_reduce adds the slabs in order into a
-// strided sub-block: out[(m-m0)*som + (n-n0)*son] (=|+=) alpha_dev*alpha*sum.
-int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* b, long long ldb,
-                      int M, int N, int T, float** slabs_out, int* nslabs_out);
-int ft_slab_reduce(FtContext* ctx, const float* slabs, int nslabs, int M, float* out, int m0,
-                   int mcount, int n0, int ncount, long long som, long long son,
-                   const float* alpha_ptr, float alpha, bool accumulate);
-int ft_slab_reduce_multi(FtContext* ctx, const float* slabs, int nslabs, int M, int count,
-                         float* const out[3], const int m0[3], const int mcount[3],
-                         const int n0[3], const int ncount[3], const long long som[3],
-                         const long long son[3], const float* alpha_ptr, float alpha,
-                         bool accumulate);
 // f32 [rows, cols] (ld) -> f16 [rows, ldo]; `lo` (optional) receives the rounding remainder
 // x 2^11.  auto_scale first multiplies by the power of two that brings the largest magnitude
 // to [2^11, 2^12) (gradients are far below f16's normal range otherwise); *scales_out then
@@ -260,16 +249,11 @@ int ft_k_scale(FtContext* ctx, float* x, size_t n, float s);
 // 2-D SwiGLU: out[t, j] = silu(a[t*lda + j]) * b[t*ldb + j], j < n
 int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
                    float* out, long long ldo, int rows, int n);
-int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
-                     __half* out, long long ldo, int rows, int n, int* in_amax = nullptr);
 int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* out, long long ldo,
                       int rows, int n, int* in_amax);
 int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const float* g,
                           long long ldg, __half* out, long long ldo, int rows, int n,
                           const int* in_amax, const float** scales_out);
-int ft_k_silu_gate_bwd16(FtContext* ctx, const float* a, long long lda, const float* b,
-                         long long ldb, const float* g, long long ldg, __half* out, long long ldo,
-                         int rows, int n, const int* in_amax, const float** scales_out);
 int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const float* b,
                        long long ldb, const float* g, long long ldg, float* ga, long long ldga,
                        float* gb, long long ldgb, int rows, int n);

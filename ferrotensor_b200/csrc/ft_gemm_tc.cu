@@ -914,24 +914,6 @@ __global__ void k_slab_reduce_multi(int slabs, int ldp, SlabSegs sg,
   }
 }
 
-// out[(m - m0) * som + (n - n0) * son] (=|+=) alpha * sum over slabs of part[s][m][n],
-// slabs added in index order.
-__global__ void k_slab_reduce(const float* __restrict__ part, int slabs, int M, int ldp,
-                              float* __restrict__ out, int m0, int mcount, int n0, int ncount,
-                              long long som, long long son, const float* __restrict__ alpha_ptr,
-                              float alpha, int accumulate) {
-  const float a = (alpha_ptr ? *alpha_ptr : 1.0f) * alpha;
-  size_t total = (size_t)mcount * ncount;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
-  for (; i < total; i += st) {
-    int m = (int)(i / ncount), n = (int)(i % ncount);
-    float acc = 0.f;
-    for (int s = 0; s < slabs; ++s)
-      acc += part[((size_t)s * M + (m0 + m)) * ldp + (n0 + n)];
-    float* o = out + (long long)m * som + (long long)n * son;
-    *o = accumulate ? *o + a * acc : a * acc;
-  }
-}
 
 // ------------------------------------------------------------------------------ f32 -> f16
 // Largest magnitude of a strided matrix, as the bit pattern of a non-negative float (which
@@ -1110,6 +1092,7 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
   if (ctx->profile) {
     FT_CUDA(cudaEventRecord(e1, ctx->stream));
     ctx->prof_flops += flops;
+    ctx->prof_bytes += ctx->next_launch_bytes;
     ctx->prof_launches++;
   }
   return FT_OK;
@@ -1170,6 +1153,7 @@ int launch_tc2(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, con
   if (ctx->profile) {
     FT_CUDA(cudaEventRecord(e1, ctx->stream));
     ctx->prof_flops += flops;
+    ctx->prof_bytes += ctx->next_launch_bytes;
     ctx->prof_launches++;
   }
   return FT_OK;
@@ -1235,7 +1219,18 @@ static bool tma_ok(const void* p, long long ld, int k) {
   return p && (((uintptr_t)p) & 15) == 0 && (ld % 8) == 0 && ld >= k;
 }
 
+// operands read once, results written once (what a launch must move at least)
+static double gemm_algorithmic_bytes(const FtGemmArgs& g) {
+  double b = 2.0 * g.M * (double)(g.K + g.K2) + 2.0 * g.N * (double)(g.K + g.K2);
+  if (g.c) b += 4.0 * g.M * (double)g.N;
+  if (g.c16) b += 2.0 * g.M * (double)g.N;
+  if (g.residual) b += 4.0 * g.M * (double)g.N;
+  if (g.pre_b) b += 2.0 * 64.0 * g.K + 2.0 * g.M * 64.0;
+  return b;
+}
+
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
+  ctx->next_launch_bytes = gemm_algorithmic_bytes(g);
   if (g.ab_type != FT_F16 && g.ab_type != FT_BF16) return FT_ERR_UNSUPPORTED;
   if (!tma_ok(g.a, g.lda, g.K) || !tma_ok(g.b, g.ldb, g.K) || g.K < 8) return FT_ERR_UNSUPPORTED;
   const bool tail = g.K2 > 0;
@@ -1423,6 +1418,9 @@ int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T) 
     slab += (size_t)splits * prob[q].M * 64;
     flops += 2.0 * prob[q].M * 64.0 * T;
   }
+  ctx->next_launch_bytes = 0.0;
+  for (int q = 0; q < nprob; ++q)
+    ctx->next_launch_bytes += 2.0 * T * (double)prob[q].M + 2.0 * T * 64.0 + 4.0 * splits * (double)prob[q].M * 64.0;
   Epilogue ep;
   ep.c = (float*)s; ep.ldc = 64; ep.c16 = nullptr; ep.ldc16 = 0;
   ep.alpha_ptr = nullptr; ep.alpha = 1.f; ep.bias = nullptr; ep.residual = nullptr; ep.ldr = 0;
@@ -1433,38 +1431,7 @@ int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T) 
                                 flops, nullptr, nullptr, &ko, (tm[0] + tm[1]) * splits);
 }
 
-int ft_gemm_tc_kouter(FtContext* ctx, const void* a, long long lda, const void* b, long long ldb,
-                      int M, int N, int T, float** slabs_out, int* nslabs_out) {
-  FtKoProblem P;
-  P.a = a; P.lda = lda; P.b = b; P.ldb = ldb; P.M = M; P.N = N;
-  FT_TRY(ft_gemm_tc_kouter_pair(ctx, 1, &P, T));
-  *slabs_out = P.slabs;
-  *nslabs_out = P.nslabs;
-  return FT_OK;
-}
 
-int ft_slab_reduce_multi(FtContext* ctx, const float* slabs, int nslabs, int M, int count,
-                         float* const out[3], const int m0[3], const int mcount[3],
-                         const int n0[3], const int ncount[3], const long long som[3],
-                         const long long son[3], const float* alpha_ptr, float alpha,
-                         bool accumulate) {
-  if (count <= 0) return FT_OK;
-  SlabSegs sg;
-  memset(&sg, 0, sizeof(sg));
-  sg.count = count;
-  size_t most = 0;
-  for (int i = 0; i < count; ++i) {
-    sg.out[i] = out[i]; sg.part[i] = slabs; sg.M[i] = M;
-    sg.m0[i] = m0[i]; sg.mcount[i] = mcount[i]; sg.n0[i] = n0[i]; sg.ncount[i] = ncount[i];
-    sg.som[i] = som[i]; sg.son[i] = son[i];
-    most = std::max(most, (size_t)mcount[i] * ncount[i]);
-  }
-  if (!most) return FT_OK;
-  dim3 grid((unsigned)std::min<size_t>((most + 255) / 256, (size_t)ctx->sm_count * 4), count);
-  FT_LAUNCH_PDL(ctx, k_slab_reduce_multi, grid, 256, 0, nslabs, 64, sg, alpha_ptr, alpha,
-                accumulate ? 1 : 0);
-  return FT_OK;
-}
 
 // The segments of every problem of a token-reduction launch, reduced in one launch.
 int ft_slab_reduce_problems(FtContext* ctx, int nprob, const FtKoProblem* prob,
@@ -1491,16 +1458,6 @@ int ft_slab_reduce_problems(FtContext* ctx, int nprob, const FtKoProblem* prob,
   return FT_OK;
 }
 
-int ft_slab_reduce(FtContext* ctx, const float* slabs, int nslabs, int M, float* out, int m0,
-                   int mcount, int n0, int ncount, long long som, long long son,
-                   const float* alpha_ptr, float alpha, bool accumulate) {
-  size_t total = (size_t)mcount * ncount;
-  if (!total) return FT_OK;
-  int grid = (int)std::min<size_t>((total + 255) / 256, (size_t)ctx->sm_count * 8);
-  FT_LAUNCH(ctx, k_slab_reduce, grid, 256, 0, slabs, nslabs, M, 64, out, m0, mcount, n0, ncount, som,
-            son, alpha_ptr, alpha, accumulate ? 1 : 0);
-  return FT_OK;
-}
 
 // C (=|+=) A(f32, rounded to f16 with optional auto scale) . B(f16)^T, single or split pass.
 int ft_gemm_tc_f32a(FtContext* ctx, const float* a, long long lda_f32, __half* stage_hi,

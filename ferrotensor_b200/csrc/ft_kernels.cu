@@ -415,31 +415,9 @@ __global__ void k_silu_gate(const float* __restrict__ a, long long lda,
     out[r * ldo + c] = x * s * b[r * ldb + c];
   }
 }
-// SwiGLU forward with an f16 result (the down projection's tensor-core operand); 4 columns
-// per thread, n and the pitches multiples of 4.  With in_amax the largest |gate| or |up| seen
-// is folded into that slot: the backward pass bounds its output with it.
-__global__ void k_silu_gate16(const float* __restrict__ a, long long lda,
-                              const float* __restrict__ b, long long ldb,
-                              __half* __restrict__ out, long long ldo, int rows, int n,
-                              int* in_amax) {
-  ft_pdl_wait();
-  ft_pdl_launch();
-  size_t per_row = (size_t)n / 4, total = (size_t)rows * per_row;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
-  float am = 0.f;
-  for (; i < total; i += st) {
-    size_t r = i / per_row, c = (i % per_row) * 4;
-    float4 x = *(const float4*)(a + r * lda + c), y = *(const float4*)(b + r * ldb + c);
-    float v0 = x.x / (1.0f + expf(-x.x)) * y.x, v1 = x.y / (1.0f + expf(-x.y)) * y.y;
-    float v2 = x.z / (1.0f + expf(-x.z)) * y.z, v3 = x.w / (1.0f + expf(-x.w)) * y.w;
-    __half2 h0 = __floats2half2_rn(v0, v1), h1 = __floats2half2_rn(v2, v3);
-    *(uint2*)(out + r * ldo + c) = make_uint2(*(uint32_t*)&h0, *(uint32_t*)&h1);
-    am = amax4(amax4(am, x), y);
-  }
-  amax_commit(am, in_amax);
-}
-
-// The same from f16 gate | up rows (the projection wrote them as f16): 8 columns per thread.
+// SwiGLU forward from f16 gate | up rows (the projection wrote them as f16) to the f16 operand
+// of the down projection: 8 columns per thread.  With in_amax the largest |gate| or |up| seen is
+// folded into that slot: the backward pass bounds its output with it.
 __global__ void k_silu_gate16h(const __half* __restrict__ a, const __half* __restrict__ b,
                                long long ldab, __half* __restrict__ out, long long ldo, int rows,
                                int n, int* in_amax) {
@@ -467,7 +445,11 @@ __global__ void k_silu_gate16h(const __half* __restrict__ a, const __half* __res
   amax_commit(am, in_amax);
 }
 
-// SwiGLU backward from f16 gate | up rows, see k_silu_gate_bwd16 for the scale.
+// SwiGLU backward from f16 gate | up rows straight to f16 tensor-core operands: out[r, c] =
+// S d(gate), out[r, n + c] = S d(up).  No pass over the result is needed to choose S: with
+// |silu(x)| <= |x| and |silu'(x)| < 1.1, every result is at most 1.1 * max|g| * max(|gate|, |up|),
+// both factors left behind by the kernels that produced those tensors; S is the power of two
+// that brings this bound under 2^13.  One thread publishes {S, 1/S, 2^-11/S}.
 __global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* __restrict__ b,
                                    long long ldab, const float* __restrict__ g, long long ldg,
                                    __half* __restrict__ out, long long ldo, int rows, int n,
@@ -517,55 +499,6 @@ __global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* _
     }
     *(uint4*)(out + r * ldo + c) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
     *(uint4*)(out + r * ldo + n + c) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
-  }
-}
-
-// SwiGLU backward straight to f16 tensor-core operands: out16[r, c] = S d(gate), out16[r, n + c]
-// = S d(up).  No pass over the result is needed to choose S: with |silu(x)| <= |x| and
-// |silu'(x)| < 1.1, every result is at most 1.1 * max|g| * max(|gate|, |up|), both factors left
-// behind by the kernels that produced those tensors; S is the power of two that brings this
-// bound under 2^13.  One thread publishes {S, 1/S, 2^-11/S} for the products that follow.
-__global__ void k_silu_gate_bwd16(const float* __restrict__ a, long long lda,
-                                  const float* __restrict__ b, long long ldb,
-                                  const float* __restrict__ g, long long ldg,
-                                  __half* __restrict__ out, long long ldo, int rows, int n,
-                                  const int* __restrict__ g_amax, const int* __restrict__ in_amax,
-                                  float* __restrict__ scales_out) {
-  ft_pdl_wait();
-  ft_pdl_launch();
-  float S = 1.0f;
-  {
-    float bound = 1.1f * __int_as_float(*g_amax) * __int_as_float(*in_amax);
-    if (bound > 0.f && isfinite(bound)) {
-      int e;
-      frexpf(bound, &e);
-      S = ldexpf(1.0f, 13 - e);
-    }
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-      scales_out[0] = S;
-      scales_out[1] = 1.0f / S;
-      scales_out[2] = ldexpf(1.0f / S, -11);
-    }
-  }
-  size_t per_row = (size_t)n / 4, total = (size_t)rows * per_row;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
-  for (; i < total; i += st) {
-    size_t r = i / per_row, c = (i % per_row) * 4;
-    float4 x = *(const float4*)(a + r * lda + c), y = *(const float4*)(b + r * ldb + c);
-    float4 go = *(const float4*)(g + r * ldg + c);
-    float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w}, gs[4] = {go.x, go.y, go.z, go.w};
-    float va[4], vb[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float s = 1.0f / (1.0f + expf(-xs[k]));
-      float gk = gs[k] * S;
-      vb[k] = gk * (xs[k] * s);
-      va[k] = gk * ys[k] * (s * (1.0f + xs[k] * (1.0f - s)));
-    }
-    __half2 a0 = __floats2half2_rn(va[0], va[1]), a1 = __floats2half2_rn(va[2], va[3]);
-    __half2 b0 = __floats2half2_rn(vb[0], vb[1]), b1 = __floats2half2_rn(vb[2], vb[3]);
-    *(uint2*)(out + r * ldo + c) = make_uint2(*(uint32_t*)&a0, *(uint32_t*)&a1);
-    *(uint2*)(out + r * ldo + n + c) = make_uint2(*(uint32_t*)&b0, *(uint32_t*)&b1);
   }
 }
 
@@ -997,16 +930,6 @@ int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b
   return FT_OK;
 }
 
-int ft_k_silu_gate16(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
-                     __half* out, long long ldo, int rows, int n, int* in_amax) {
-  FT_REQUIRE((n % 4) == 0 && (lda % 4) == 0 && (ldb % 4) == 0 && (ldo % 4) == 0 &&
-                 ((((uintptr_t)a) | ((uintptr_t)b)) & 15) == 0 && (((uintptr_t)out) & 7) == 0,
-             "silu_gate16: width and pitches must be multiples of 4");
-  FT_LAUNCH_PDL(ctx, k_silu_gate16, ew_grid(ctx, (size_t)rows * n / 4), 256, 0, a, lda, b, ldb, out, ldo,
-            rows, n, in_amax);
-  return FT_OK;
-}
-
 int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* out, long long ldo,
                       int rows, int n, int* in_amax) {
   FT_REQUIRE((n % 8) == 0 && (ld % 8) == 0 && (ldo % 8) == 0 && (((uintptr_t)gu) & 15) == 0 &&
@@ -1017,6 +940,8 @@ int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* ou
   return FT_OK;
 }
 
+// Consumes the armed amax of g (left by the product that wrote it) and in_amax (left by
+// ft_k_silu_gate16h); *scales_out points at {S, 1/S, 2^-11/S} on the device.
 int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const float* g,
                           long long ldg, __half* out, long long ldo, int rows, int n,
                           const int* in_amax, const float** scales_out) {
@@ -1030,26 +955,6 @@ int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const 
   ctx->amax_ready = false;
   FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16h, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu, gu + n,
                 ld, g, ldg, out, ldo, rows, n, g_amax, in_amax, ctx->scale_buf + 4);
-  *scales_out = ctx->scale_buf + 4;
-  return FT_OK;
-}
-
-// Consumes the armed amax of g (left by the product that wrote it) and in_amax (left by
-// ft_k_silu_gate16); *scales_out points at {S, 1/S, 2^-11/S} on the device.
-int ft_k_silu_gate_bwd16(FtContext* ctx, const float* a, long long lda, const float* b,
-                         long long ldb, const float* g, long long ldg, __half* out, long long ldo,
-                         int rows, int n, const int* in_amax, const float** scales_out) {
-  FT_REQUIRE((n % 4) == 0 && (lda % 4) == 0 && (ldb % 4) == 0 && (ldg % 4) == 0 && (ldo % 4) == 0 &&
-                 ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)g)) & 15) == 0 &&
-                 (((uintptr_t)out) & 7) == 0,
-             "silu_gate_bwd16: width and pitches must be multiples of 4");
-  FT_REQUIRE(ctx->amax_ready && ctx->amax_out && in_amax,
-             "silu_gate_bwd16: the upstream gradient's amax must have been armed and produced");
-  const int* g_amax = ctx->amax_out;
-  ctx->amax_out = nullptr;
-  ctx->amax_ready = false;
-  FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16, ew_grid(ctx, (size_t)rows * n / 4, 256, 2), 256, 0, a, lda, b,
-            ldb, g, ldg, out, ldo, rows, n, g_amax, in_amax, ctx->scale_buf + 4);
   *scales_out = ctx->scale_buf + 4;
   return FT_OK;
 }

@@ -94,6 +94,12 @@ class CudaContext:
         call("ft_ctx_profile_read", self.handle, C.byref(ms), C.byref(fl), C.byref(n))
         return ms.value, fl.value, n.value
 
+    def profile_bytes(self) -> float:
+        """Algorithmic bytes of the GEMM launches timed so far (read before `profile_read`)."""
+        b = C.c_double()
+        call("ft_ctx_profile_bytes", self.handle, C.byref(b))
+        return b.value
+
     def launch_count(self) -> int:
         n = C.c_uint64()
         call("ft_ctx_launch_count", self.handle, C.byref(n))

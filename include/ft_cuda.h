@@ -73,6 +73,9 @@ int ft_ctx_profile(FtContext* ctx, int enable);   /* 0 off, 1 GEMM launches, 2 e
 int ft_ctx_profile_report(FtContext* ctx, char* buf, size_t cap);
 int ft_ctx_profile_read(FtContext* ctx, double* gemm_ms, double* gemm_flops,
                         uint64_t* gemm_launches);
+/* Algorithmic bytes (operands read once, results written once) of the GEMM launches timed since
+ * the last call; call it before ft_ctx_profile_read, which closes the same interval. */
+int ft_ctx_profile_bytes(FtContext* ctx, double* gemm_bytes);
 int ft_ctx_set_gemm_mode(FtContext* ctx, int mode);    /* FT_GEMM_*; default FT_GEMM_F32 */
 /* Tuning/diagnostics: force the tensor-core GEMM's output tile height (128 or 256 rows, 512 = 256 x 256
  * tiles on CTA pairs;
