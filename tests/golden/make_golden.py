@@ -124,6 +124,8 @@ def qwen2_family(ref: Path):
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to a checkout of the reference repository>")
+    ref = Path(sys.argv[1])
     gradient_parity(ref)
     qwen2_family(ref)
