@@ -167,6 +167,14 @@ class Trainer:
         self.world_size, self.rank = world_size, rank
         return self
 
+    def set_optimizer_steps(self, steps: int) -> None:
+        """Restore the optimizer-step counter on resume and advance the LR schedule to match
+        (lib.rs:204-213)."""
+        if self.lr_scheduler is not None:
+            while self.lr_scheduler.current_step() < steps:
+                self.lr_scheduler.step()
+        self.optimizer_step_count = steps
+
     # ---- one forward/backward over a chunk of sequences -----------------------------------
     def _run_chunk(self, ids: np.ndarray, tgt: np.ndarray, msk: np.ndarray) -> None:
         n, s = ids.shape
