@@ -33,6 +33,7 @@ class FtAttnParams(C.Structure):
         ("seq_k", C.c_uint32), ("head_dim", C.c_uint32), ("kv_heads", C.c_uint32),
         ("causal", C.c_uint32), ("causal_offset", C.c_uint32), ("window", C.c_uint32),
         ("scale", C.c_float), ("dropout_prob", C.c_float), ("lse_saved", C.c_uint32),
+        ("seed_lo", C.c_uint32), ("seed_hi", C.c_uint32), ("mask_stride", C.c_uint32 * 4),
     ]
 
 
@@ -50,7 +51,7 @@ class FtModelConfig(C.Structure):
         ("eps", C.c_float), ("theta", C.c_float),
         ("qkv_bias", C.c_int), ("lora_rank", C.c_int), ("lora_alpha", C.c_float),
         ("lora_mask", C.c_int), ("lora_head", C.c_int), ("f16_base", C.c_int),
-        ("checkpoint_blocks", C.c_int),
+        ("checkpoint_blocks", C.c_int), ("attention_dropout", C.c_float),
     ]
 
 
@@ -120,6 +121,7 @@ PROTOTYPES = {
     "ft_model_set_workspace": [_P, _P, _Z],
     "ft_model_forward_backward": [_P, _P, _P, _P, _I, _I, _F, _P, _P],
     "ft_model_forward_loss": [_P, _P, _P, _P, _I, _I, _P, _P],
+    "ft_model_set_dropout_seed": [_P, C.c_uint64],
     "ft_model_zero_grad": [_P],
     "ft_model_apply_gradients": [_P, _F, _F, C.POINTER(FtAdamParams), _P],
 }

@@ -39,6 +39,7 @@ class ModelConfig:
     head_dim: Optional[int] = None
     tied: bool = False
     qkv_bias: bool = False
+    attention_dropout: float = 0.0   # applied to attention weights in training passes only
 
     def __post_init__(self):
         if self.head_dim is None:

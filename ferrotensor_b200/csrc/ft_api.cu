@@ -501,11 +501,14 @@ static int check_attn(const char* who, const FtAttnParams* p, const float* mask)
              p->heads, p->kv_heads);
   FT_REQUIRE(p->head_dim >= 4 && p->head_dim <= 128 && p->head_dim % 4 == 0,
              "%s: head_dim %u must be a multiple of 4 in [4,128]", who, p->head_dim);
-  if (mask != nullptr || p->dropout_prob != 0.f) {
-    ft_set_error("%s: additive masks and attention dropout are outside this library", who);
-    return FT_ERR_UNSUPPORTED;
-  }
+  FT_REQUIRE(p->dropout_prob >= 0.f && p->dropout_prob < 1.f, "%s: dropout_prob %g is outside [0, 1)",
+             who, (double)p->dropout_prob);
+  (void)mask;
   return FT_OK;
+}
+// masks and dropout are served by the exact f32 kernels only
+static inline bool attn_plain(const FtAttnParams* p, const float* mask) {
+  return mask == nullptr && p->dropout_prob == 0.f;
 }
 
 extern "C" int ft_flash_attention_v2(FtContext* ctx, const float* q, const float* k,
@@ -514,8 +517,9 @@ extern "C" int ft_flash_attention_v2(FtContext* ctx, const float* q, const float
   FT_REQUIRE(ctx && q && k && v && out, "ft_flash_attention_v2: NULL argument");
   FT_TRY(check_attn("ft_flash_attention_v2", p, mask));
   // one query and no stats: the decode kernel, whose blocks split the keys (attention.rs:205-224)
-  if (p->seq_q == 1 && !stats && p->head_dim <= 128) return ft_k_attention_decode(ctx, q, k, v, out, *p);
-  if (ctx->gemm_mode == FT_GEMM_F16 && p->head_dim == 64 && p->causal && !p->causal_offset &&
+  const bool plain = attn_plain(p, mask);
+  if (plain && p->seq_q == 1 && !stats && p->head_dim <= 128) return ft_k_attention_decode(ctx, q, k, v, out, *p);
+  if (plain && ctx->gemm_mode == FT_GEMM_F16 && p->head_dim == 64 && p->causal && !p->causal_offset &&
       !p->window && p->seq_q == p->seq_k && p->seq_q >= 64) {
     // tensor-core form: q, k, v are rounded to f16 side by side, one row per token
     const int nq = p->heads * 64, nkv = p->kv_heads * 64, ld = nq + 2 * nkv;
@@ -531,7 +535,7 @@ extern "C" int ft_flash_attention_v2(FtContext* ctx, const float* q, const float
     if (r != FT_ERR_UNSUPPORTED) return r;
   }
   FtAttnLaunch a;
-  a.q = q; a.k = k; a.v = v; a.out = out; a.stats = stats; a.p = *p;
+  a.q = q; a.k = k; a.v = v; a.out = out; a.stats = stats; a.mask = mask; a.p = *p;
   a.ldq = a.ldo = (long long)p->heads * p->head_dim;
   a.ldk = a.ldv = (long long)p->kv_heads * p->head_dim;
   return ft_k_attention_fwd(ctx, a);
@@ -545,7 +549,7 @@ extern "C" int ft_flash_attention_v2_backward(FtContext* ctx, const float* q, co
   FT_REQUIRE(ctx && q && k && v && out && dout && dq && dk && dv,
              "ft_flash_attention_v2_backward: NULL argument");
   FT_TRY(check_attn("ft_flash_attention_v2_backward", p, mask));
-  if (ctx->gemm_mode == FT_GEMM_F16 && p->head_dim == 64 && p->causal && !p->causal_offset &&
+  if (attn_plain(p, mask) && ctx->gemm_mode == FT_GEMM_F16 && p->head_dim == 64 && p->causal && !p->causal_offset &&
       !p->window && p->seq_q == p->seq_k && p->seq_q >= 64 && stats && p->lse_saved) {
     // tensor-core form: operands rounded to f16 (dout after a power-of-two scale)
     const int nq = p->heads * 64, nkv = p->kv_heads * 64, ld = nq + 2 * nkv;
@@ -570,7 +574,7 @@ extern "C" int ft_flash_attention_v2_backward(FtContext* ctx, const float* q, co
   }
   FtAttnBwdLaunch a;
   a.q = q; a.k = k; a.v = v; a.out = out; a.dout = dout; a.dq = dq; a.dk = dk; a.dv = dv;
-  a.stats = stats; a.p = *p;
+  a.stats = stats; a.mask = mask; a.p = *p;
   a.ldq = a.ldo = a.lddo = a.lddq = (long long)p->heads * p->head_dim;
   a.ldk = a.ldv = a.lddk = a.lddv = (long long)p->kv_heads * p->head_dim;
   return ft_k_attention_bwd(ctx, a);

@@ -285,6 +285,7 @@ struct FtAttnLaunch {
   float* out;
   long long ldo;
   float* stats;             // [b*h*sq*2] or nullptr
+  const float* mask = nullptr;   // additive, strides in p.mask_stride
   FtAttnParams p;
 };
 int ft_k_attention_fwd(FtContext* ctx, const FtAttnLaunch& a);
@@ -294,6 +295,7 @@ struct FtAttnBwdLaunch {
   float *dq, *dk, *dv;
   long long lddq, lddk, lddv;
   float* stats;
+  const float* mask = nullptr;
   FtAttnParams p;
 };
 int ft_k_attention_bwd(FtContext* ctx, const FtAttnBwdLaunch& a);

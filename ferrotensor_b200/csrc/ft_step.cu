@@ -112,6 +112,8 @@ struct FtLoraModel {
   __half *hN16 = nullptr, *xa16_head = nullptr, *g16 = nullptr;
   bool packs_dirty = true;         // adapter operand forms must be rebuilt before use
   bool tc_attention = false;       // head_dim 64: attention and RoPE take the tensor-core route
+  uint64_t dropout_step_seed = 0;  // seed of the coming forward pass (ft_model_set_dropout_seed)
+  bool dropout_on = false;         // training pass of a model with attention dropout
   float* rope_table = nullptr;     // {cos, sin} [seq_len, 32] in the workspace
   int table_seq = 0;
   int* gu_amax = nullptr;          // per layer: largest |gate| or |up| of the forward pass
@@ -155,8 +157,9 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   const int L = c.layers;
   const int nqkv = m->nq + 2 * m->nkv;
   const bool fused = use_fused(m);
+  // (attention dropout is served by the exact f32 kernels only)
   const bool tc_attention = fused && c.head_dim == 64 && (nqkv % 8) == 0 && (m->nq % 64) == 0 &&
-                            (long long)sequences * c.heads <= 65535;
+                            (long long)sequences * c.heads <= 65535 && c.attention_dropout == 0.f;
   std::vector<float*> x(L + 1);
   for (int l = 0; l <= L; ++l) x[l] = b.take<float>(T * c.hidden);
   // with attention on the tensor cores only the f16 q|k|v rows are kept per block: the f32
@@ -329,6 +332,28 @@ int linear_bwd(FtLoraModel* m, const Group& g, const float* X, long long ldx, co
   return FT_OK;
 }
 
+// SplitMix64's finaliser and the seed of layer l for one forward pass
+// (ferrotensor-graph/src/dropout.rs:17-38): derive_seed([step_seed, l]).
+inline uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+inline uint64_t layer_seed(uint64_t step_seed, int l) {
+  uint64_t acc = mix64(2);
+  acc = mix64(acc ^ mix64(step_seed));
+  return mix64(acc ^ mix64((uint64_t)l));
+}
+// training passes of a model with attention dropout: the layer's probability and seed
+inline void fill_dropout(const FtLoraModel* m, int l, FtAttnParams& p) {
+  if (!m->dropout_on) return;
+  const uint64_t s = layer_seed(m->dropout_step_seed, l);
+  p.dropout_prob = m->cfg.attention_dropout;
+  p.seed_lo = (uint32_t)s;
+  p.seed_hi = (uint32_t)(s >> 32);
+}
+
 int block_forward(FtLoraModel* m, int l, const float* x_in, float* x_out, BlockActs& a) {
   FtContext* ctx = m->ctx;
   const FtModelConfig& c = m->cfg;
@@ -345,6 +370,7 @@ int block_forward(FtLoraModel* m, int l, const float* x_in, float* x_out, BlockA
   memset(&at.p, 0, sizeof(at.p));
   at.p.batch = m->sequences; at.p.heads = c.heads; at.p.kv_heads = c.kv_heads;
   at.p.seq_q = at.p.seq_k = m->seq_len; at.p.head_dim = c.head_dim; at.p.causal = 1;
+  fill_dropout(m, l, at.p);
   FT_TRY(ft_k_attention_fwd(ctx, at));
   FT_TRY(linear_fwd(m, ly.o, a.attn, nq, a.x1, h, a.xa_o, T));
   FT_TRY(ft_k_add(ctx, x_in, a.x1, a.x1, (size_t)T * h));
@@ -381,6 +407,7 @@ int block_backward(FtLoraModel* m, int l, const float* x_in, BlockActs& a) {
   ab.p.batch = m->sequences; ab.p.heads = c.heads; ab.p.kv_heads = c.kv_heads;
   ab.p.seq_q = ab.p.seq_k = m->seq_len; ab.p.head_dim = c.head_dim; ab.p.causal = 1;
   ab.p.lse_saved = 1;
+  fill_dropout(m, l, ab.p);
   FT_TRY(ft_k_attention_bwd(ctx, ab));
   FT_TRY(ft_k_rope(ctx, m->dqkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, true));
   FT_TRY(ft_k_rope(ctx, m->dqkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, true));
@@ -549,13 +576,14 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
   return FT_OK;
 }
 
-int attention_launch(FtLoraModel* m, BlockActs& a, bool backward) {
+int attention_launch(FtLoraModel* m, int l, BlockActs& a, bool backward) {
   const FtModelConfig& c = m->cfg;
   const int nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv;
   FtAttnParams p;
   memset(&p, 0, sizeof(p));
   p.batch = m->sequences; p.heads = c.heads; p.kv_heads = c.kv_heads;
   p.seq_q = p.seq_k = m->seq_len; p.head_dim = c.head_dim; p.causal = 1;
+  fill_dropout(m, l, p);
   if (!backward) {
     FtAttnLaunch at;
     at.q = a.qkv; at.k = a.qkv + nq; at.v = a.qkv + nq + nkv;
@@ -591,7 +619,7 @@ int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, 
   } else {
     FT_TRY(ft_k_rope(ctx, a.qkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, false));
     FT_TRY(ft_k_rope(ctx, a.qkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, false));
-    FT_TRY(attention_launch(m, a, false));
+    FT_TRY(attention_launch(m, l, a, false));
     FT_TRY(ft_to_f16(ctx, a.attn, nq, a.attn16, nullptr, nq, T, nq, false, nullptr));
   }
   // x1 = x_in + o(attn): the residual rides in the GEMM epilogue
@@ -641,7 +669,7 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
                             h, nullptr, 0, T, m->cvt_hi, scales));
   } else {
     FT_TRY(linear_bwd_fused(m, ly.o, a.attn16, m->dx, h, a.xa16_o, m->dattn, nq, nullptr, 0, T));
-    FT_TRY(attention_launch(m, a, true));
+    FT_TRY(attention_launch(m, l, a, true));
     FT_TRY(ft_k_rope(ctx, m->dqkv, nqkv, T, c.heads, c.head_dim, m->seq_len, 0, c.theta, true));
     FT_TRY(ft_k_rope(ctx, m->dqkv + nq, nqkv, T, c.kv_heads, c.head_dim, m->seq_len, 0, c.theta, true));
     FT_TRY(linear_bwd_fused(m, ly.qkv, a.h1_16, m->dqkv, nqkv, a.xa16_qkv, need_dx ? m->dh : nullptr,
@@ -747,6 +775,8 @@ extern "C" int ft_model_create(FtContext* ctx, const FtModelConfig* cfg, FtLoraM
   FT_REQUIRE(cfg->head_dim % 4 == 0 && cfg->head_dim <= 128,
              "ft_model_create: head_dim must be a multiple of 4, at most 128");
   FT_REQUIRE(cfg->lora_rank >= 0, "ft_model_create: negative rank");
+  FT_REQUIRE(cfg->attention_dropout >= 0.f && cfg->attention_dropout < 1.f,
+             "ft_model_create: attention_dropout %g is outside [0, 1)", (double)cfg->attention_dropout);
   FtLoraModel* m = new FtLoraModel();
   m->ctx = ctx;
   m->cfg = *cfg;
@@ -928,6 +958,12 @@ extern "C" int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids,
   return step_impl(m, ids, targets, weights, sequences, seq_len, seed, row_loss, logits, true);
 }
 
+extern "C" int ft_model_set_dropout_seed(FtLoraModel* m, uint64_t step_seed) {
+  FT_REQUIRE(m, "ft_model_set_dropout_seed: NULL model");
+  m->dropout_step_seed = step_seed;
+  return FT_OK;
+}
+
 extern "C" int ft_model_forward_loss(FtLoraModel* m, const uint32_t* ids, const uint32_t* targets,
                                      const float* weights, int sequences, int seq_len,
                                      float* row_loss, float* logits) {
@@ -953,6 +989,7 @@ static int step_impl(FtLoraModel* m, const uint32_t* ids, const uint32_t* target
   }
   const int T = m->T, h = c.hidden, L = c.layers, V = c.vocab;
   const bool ckpt = c.checkpoint_blocks != 0;
+  m->dropout_on = backward && c.attention_dropout > 0.f;   // evaluation drops nothing
   if (fused && m->packs_dirty) FT_TRY(pack_all(m));
   if (fused && m->tc_attention && m->table_seq != seq_len) {
     FT_TRY(ft_k_rope_table(ctx, m->rope_table, seq_len, c.head_dim, c.theta));

@@ -357,34 +357,49 @@ class ComputeEngine:
 
     # ---- attention.rs:139-441
     @staticmethod
-    def _attn_params(q, k, opts: AttentionOptions, lse_saved=False) -> FtAttnParams:
+    def _attn_params(q, k, opts: AttentionOptions, lse_saved=False, mask=None) -> FtAttnParams:
         _require(len(q.shape) == 4 and len(k.shape) == 4, "attention: q and k must be 4-D")
         b, sq, h, d = q.shape
         _, sk, hkv, _ = k.shape
+        seed = int(opts.seed) & 0xFFFFFFFFFFFFFFFF
+        strides = [0, 0, 0, 0]
+        if mask is not None and len(mask.shape) == 4:
+            # broadcast strides of a [batch, heads, seq_q, seq_k] mask: size-1 dimensions get 0
+            mb, mh, mq, mk = mask.shape
+            for dim, want, name in ((mb, b, "batch"), (mh, h, "heads"), (mq, sq, "seq_q"), (mk, sk, "seq_k")):
+                _require(dim in (1, want), f"attention mask: {name} dimension is {dim}, expected 1 or {want}")
+            strides = [mk * mq * mh if mb > 1 else 0, mk * mq if mh > 1 else 0, mk if mq > 1 else 0,
+                       1 if mk > 1 else 0]
         return FtAttnParams(b, h, sq, sk, d, hkv, 1 if opts.causal else 0, opts.causal_offset,
-                            opts.window, 0.0, float(opts.dropout_prob), 1 if lse_saved else 0)
+                            opts.window, 0.0, float(opts.dropout_prob), 1 if lse_saved else 0,
+                            seed & 0xFFFFFFFF, seed >> 32, (C.c_uint32 * 4)(*strides))
+
+    def flash_attention_v2(self, ctx, q, k, v, out, causal, dropout_prob=0.0, seed=0, mask=None):
+        """attention.rs:112-135: the positional form."""
+        self.flash_attention_v2_with(ctx, q, k, v, out,
+                                     AttentionOptions(causal=causal, dropout_prob=dropout_prob, seed=seed), mask)
 
     def flash_attention_v2_with(self, ctx, q, k, v, out, opts, mask=None):
-        p = self._attn_params(q, k, opts)
+        p = self._attn_params(q, k, opts, mask=mask)
         call("ft_flash_attention_v2", ctx.handle, q.ptr, k.ptr, v.ptr, out.ptr, None,
              mask.ptr if mask is not None else None, C.byref(p))
 
     def flash_attention_v2_with_stats(self, ctx, q, k, v, out, stats, opts, mask=None):
-        p = self._attn_params(q, k, opts)
+        p = self._attn_params(q, k, opts, mask=mask)
         _require(stats.numel() == p.batch * p.heads * p.seq_q * 2, "attention: stats size")
         call("ft_flash_attention_v2", ctx.handle, q.ptr, k.ptr, v.ptr, out.ptr, stats.ptr,
              mask.ptr if mask is not None else None, C.byref(p))
 
     def flash_attention_v2_backward_with(self, ctx, q, k, v, out, grad_out, grad_q, grad_k,
                                          grad_v, opts, mask=None):
-        p = self._attn_params(q, k, opts)
+        p = self._attn_params(q, k, opts, mask=mask)
         call("ft_flash_attention_v2_backward", ctx.handle, q.ptr, k.ptr, v.ptr, out.ptr,
              grad_out.ptr, grad_q.ptr, grad_k.ptr, grad_v.ptr, None,
              mask.ptr if mask is not None else None, C.byref(p))
 
     def flash_attention_v2_backward_with_stats(self, ctx, q, k, v, out, grad_out, grad_q, grad_k,
                                                grad_v, stats, opts, mask=None):
-        p = self._attn_params(q, k, opts, lse_saved=True)
+        p = self._attn_params(q, k, opts, lse_saved=True, mask=mask)
         call("ft_flash_attention_v2_backward", ctx.handle, q.ptr, k.ptr, v.ptr, out.ptr,
              grad_out.ptr, grad_q.ptr, grad_k.ptr, grad_v.ptr, stats.ptr,
              mask.ptr if mask is not None else None, C.byref(p))

@@ -344,6 +344,7 @@ def train(args: TrainArgs) -> TrainSummary:
             start_step, args.seed = ts.step, ts.seed
             trainer.set_optimizer_steps(start_step)
         _log(f"resume: {resume} ({n} tensors), continuing at step {start_step}")
+    trainer.dropout_seed = args.seed     # attention-dropout masks follow the run seed (restored on resume)
 
     _log(f"data:   {len(dataset)} examples ({args.task} task), {supervised_tokens(dataset)} supervised tokens, "
          f"seq-len {args.seq_len}")

@@ -98,7 +98,8 @@ def model_config_from_json(config: dict) -> ModelConfig:
     return ModelConfig(vocab=vocab, hidden=hidden, layers=layers, heads=heads, kv_heads=int(kv), ffn=ffn,
                        eps=float(np.float32(1e-5 if eps is None else eps)),
                        theta=float(np.float32(10000.0 if theta is None else theta)), head_dim=int(head_dim),
-                       tied=bool(config.get("tie_word_embeddings") or False))
+                       tied=bool(config.get("tie_word_embeddings") or False),
+                       attention_dropout=float(config.get("attention_dropout") or 0.0))
 
 
 class WeightsContext:

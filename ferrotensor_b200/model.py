@@ -43,7 +43,7 @@ class LoraModel:
         c = FtModelConfig(cfg.vocab, cfg.hidden, cfg.layers, cfg.heads, cfg.kv_heads, cfg.head_dim,
                           cfg.ffn, cfg.eps, cfg.theta, int(cfg.qkv_bias), lora.rank, lora.alpha,
                           mask, int(lora_head and lora.rank > 0), int(f16_base),
-                          int(checkpoint_blocks))
+                          int(checkpoint_blocks), float(cfg.attention_dropout))
         handle = C.c_void_p()
         call("ft_model_create", ctx.handle, C.byref(c), C.byref(handle))
         self.handle = handle
@@ -170,6 +170,10 @@ class LoraModel:
         self._ensure_workspace(sequences, seq_len)
         call("ft_model_forward_backward", self.handle, _ptr(ids), _ptr(targets), _ptr(weights),
              sequences, seq_len, float(seed), _ptr(row_loss), _ptr(logits))
+
+    def set_dropout_seed(self, step_seed: int) -> None:
+        """Seed of the next training pass's attention-dropout masks (no effect at dropout 0)."""
+        call("ft_model_set_dropout_seed", self.handle, C.c_uint64(step_seed & 0xFFFFFFFFFFFFFFFF))
 
     def forward_loss(self, ids: torch.Tensor, targets: torch.Tensor, weights: torch.Tensor,
                      sequences: int, seq_len: int, row_loss: torch.Tensor,

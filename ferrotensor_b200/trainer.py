@@ -147,6 +147,7 @@ class Trainer:
         self.last_logits: Optional[torch.Tensor] = None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.dropout_seed = 0                  # run seed of the attention-dropout masks
         self._pending: List[Tuple[torch.Tensor, np.ndarray, int, int]] = []  # pinned row losses
 
     # builder-style setters, as the reference's `with_*`
@@ -161,6 +162,17 @@ class Trainer:
     def with_lr_scheduler(self, s: WarmupCosineScheduler) -> "Trainer":
         self.lr_scheduler = s
         return self
+
+    def with_dropout_seed(self, seed: int) -> "Trainer":
+        self.dropout_seed = int(seed)
+        return self
+
+    def attention_dropout_seed(self) -> int:
+        """The seed of the next forward pass's dropout masks: run seed, rank, optimizer step and
+        position in the accumulation window (lib.rs:185-197); layers derive their own from it."""
+        from .dropout import attention_dropout_seed
+        return attention_dropout_seed(self.dropout_seed, self.rank if self.world_size > 1 else 0,
+                                      self.optimizer_step_count, self.step_in_accum)
 
     def with_distributed(self, world_size: int, rank: int) -> "Trainer":
         """Average gradients over `world_size` ranks (torch.distributed must be initialised)."""
@@ -195,6 +207,8 @@ class Trainer:
         seed = 1.0 / self.grad_accum_steps
         if self.step_in_accum == 0:
             self.model.zero_grad()
+        if self.model.cfg.attention_dropout > 0.0:
+            self.model.set_dropout_seed(self.attention_dropout_seed())
         self.model.forward_backward(d_ids, d_tgt, d_w, n, s, seed, row_loss, logits)
         self.last_logits = logits
         # row losses travel to pinned host memory asynchronously; they are summed per

@@ -159,15 +159,25 @@ int ft_silu_gate_backward(FtContext* ctx, const float* a, const float* b, const 
  * [batch, seq_q, heads, head_dim]; k, v, dk, dv are [batch, seq_k, kv_heads, head_dim].
  * stats (may be NULL) has 2 f32 per (batch, head, query) row: element 2*row+1 receives
  * the row's log-sum-exp in the forward pass, element 2*row is backward scratch (Delta).
- * The backward pass recomputes the log-sum-exp when stats is NULL or lse_saved == 0. */
+ * The backward pass recomputes the log-sum-exp when stats is NULL or lse_saved == 0.
+ * mask (may be NULL) is added to the scaled score of every visible (query, key) pair:
+ * element b*mask_stride[0] + h*mask_stride[1] + q*mask_stride[2] + k*mask_stride[3], a stride
+ * of 0 broadcasting that dimension (attention.rs:596-620); a score at or below -1e30 after the
+ * addition counts as hidden (flash_attention_v2.wgsl:32-33).
+ * dropout_prob > 0 multiplies the weight of pair (b*heads + h, q, k) by 0 or 1/(1 - p), decided
+ * by the hash of flash_attention_v2.wgsl:68-104 on the 64-bit seed; the log-sum-exp stays that
+ * of the undropped scores and the backward pass regenerates the same decisions.  Masks and
+ * dropout run on the exact f32 kernels whatever the GEMM mode. */
 typedef struct FtAttnParams {
   uint32_t batch, heads, seq_q, seq_k, head_dim, kv_heads;
   uint32_t causal;        /* hide keys after the query's absolute position           */
   uint32_t causal_offset; /* absolute position of query 0                            */
   uint32_t window;        /* sliding window in tokens; 0 = unlimited                 */
   float scale;            /* 0 => 1/sqrt(head_dim)                                   */
-  float dropout_prob;     /* must be 0: attention dropout is outside this library    */
+  float dropout_prob;     /* 0 = none                                                */
   uint32_t lse_saved;     /* backward only: stats already holds the forward's LSE    */
+  uint32_t seed_lo, seed_hi;   /* the two halves of the 64-bit dropout seed           */
+  uint32_t mask_stride[4];     /* elements per step of batch, head, query, key        */
 } FtAttnParams;
 int ft_flash_attention_v2(FtContext* ctx, const float* q, const float* k, const float* v,
                           float* out, float* stats, const float* mask, const FtAttnParams* p);
@@ -228,6 +238,8 @@ typedef struct FtModelConfig {
   int lora_head;         /* lm_head carries an adapter                                 */
   int f16_base;          /* frozen linears and the head are stored as f16              */
   int checkpoint_blocks; /* keep only block inputs, replay each block in backward      */
+  float attention_dropout; /* config.json attention_dropout (model_builder.rs:541); > 0
+                            * keeps attention on the exact f32 kernels                  */
 } FtModelConfig;
 
 int ft_model_create(FtContext* ctx, const FtModelConfig* cfg, FtLoraModel** out);
@@ -273,6 +285,11 @@ int ft_model_set_workspace(FtLoraModel* m, void* dev_ptr, size_t bytes);
 int ft_model_forward_backward(FtLoraModel* m, const uint32_t* ids, const uint32_t* targets,
                               const float* weights, int sequences, int seq_len, float seed,
                               float* row_loss, float* logits);
+/* The seed of the next training pass's attention-dropout masks (models with
+ * attention_dropout > 0; ferrotensor-trainer/src/lib.rs:185-197, :452-456).  Layer l draws its
+ * masks from derive_seed([step_seed, l]) (ferrotensor-graph/src/dropout.rs:28-38); the backward
+ * pass and a checkpointed block's replay regenerate them.  Evaluation applies no dropout. */
+int ft_model_set_dropout_seed(FtLoraModel* m, uint64_t step_seed);
 /* The forward half of ft_model_forward_backward: row losses (and logits when asked for) with
  * the same arguments, gradients untouched - what the reference's `evaluate` computes under
  * `no_grad` (ferrotensor-cli/src/main.rs:1111-1137). */

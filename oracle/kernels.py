@@ -227,3 +227,96 @@ def argmax_rows(x):
     # larger index wins ties: combine (key, index) into one sortable integer
     combined = key * np.uint64(n) + np.arange(n, dtype=np.uint64)
     return combined.argmax(axis=-1).astype(np.uint32)
+
+
+# ---- attention with an additive mask, offset/window visibility and dropout -------------------
+_U32 = np.uint32
+
+
+def _fmix32(h):
+    """Murmur3's 32-bit finaliser (flash_attention_v2.wgsl:84-92)."""
+    h = np.asarray(h, dtype=_U32)
+    h = h ^ (h >> _U32(16))
+    h = h * _U32(0x85EBCA6B)
+    h = h ^ (h >> _U32(13))
+    h = h * _U32(0xC2B2AE35)
+    return h ^ (h >> _U32(16))
+
+
+def _hash3(x, y, z):
+    """flash_attention_v2.wgsl:70-82 (CPU copy: backend/tests/gpu_kernels.rs:2261-2281): three LCG
+    steps, a round of cross-multiplication, a shift-xor each, the wrapped sum scaled by 2^-32 in
+    f32 (so the value can round up to 1.0)."""
+    with np.errstate(over="ignore"):
+        a, b, c = (np.asarray(t, dtype=_U32) * _U32(1664525) + _U32(1013904223) for t in (x, y, z))
+        a = a + b * c
+        b = b + c * a
+        c = c + a * b
+        a, b, c = (t ^ (t >> _U32(16)) for t in (a, b, c))
+        return (a + b + c).astype(np.float32) * np.float32(2.3283064365386963e-10)
+
+
+def dropout_keep(prob, seed, bh, q_idx, k_idx):
+    """Keep decision of attention weight (bh, q, k) under the 64-bit `seed`
+    (flash_attention_v2.wgsl:94-104): both seed halves are mixed into one key that enters the
+    hash xor-ed with bh.  Broadcasts over numpy index arrays."""
+    if prob <= 0.0:
+        return np.ones(np.broadcast(bh, q_idx, k_idx).shape, dtype=bool)
+    with np.errstate(over="ignore"):
+        lo, hi = _U32(seed & 0xFFFFFFFF), _U32((seed >> 32) & 0xFFFFFFFF)
+        key = _fmix32(lo ^ _fmix32(hi ^ _U32(0x9E3779B9)))
+        r = _hash3(np.asarray(bh, dtype=_U32) ^ key, q_idx, k_idx)
+    return r >= np.float32(prob)
+
+
+def _visibility(sq, sk, causal, causal_offset, window):
+    """`fa_visible` (flash_attention_v2.wgsl:106-116) for every (query, key) pair."""
+    qa = np.arange(sq)[:, None] + causal_offset
+    kp = np.arange(sk)[None, :]
+    vis = np.ones((sq, sk), dtype=bool)
+    if causal:
+        vis &= kp <= qa
+    if window > 0:
+        vis &= np.abs(qa - kp) < window
+    return vis
+
+
+def attention_general(q, k, v, b, sq, sk, h, hkv, d, causal=True, causal_offset=0, window=0, mask=None,
+                      dropout_prob=0.0, seed=0, dout=None, dtype=torch.float64):
+    """Forward (and, given `dout`, backward) of the general attention call: q/out [b,sq,h,d],
+    k/v [b,sk,hkv,d]; `mask` broadcastable to [b,h,sq,sk] is added to the scaled scores of visible
+    pairs and a score at or below -1e30 is then hidden; P = softmax over what is left, a row with
+    nothing visible gives 0 and LSE 3e38; M = 0 or 1/(1-p) per pair;
+    O = (P*M) V;  dV = (P*M)^T dO;  dS = P * (M * dO V^T - Delta), Delta = rowsum(dO * O);
+    dQ = scale dS K;  dK = scale dS^T Q  (flash_attention_v2_backward.wgsl:5-15).
+    Returns (out, lse) or (out, lse, dq, dk, dv) as float32 numpy arrays."""
+    grp = h // hkv
+    scale = 1.0 / math.sqrt(d)
+    qh = _t(q, dtype).view(b, sq, h, d).transpose(1, 2)
+    kh = _t(k, dtype).view(b, sk, hkv, d).transpose(1, 2).repeat_interleave(grp, dim=1)
+    vh = _t(v, dtype).view(b, sk, hkv, d).transpose(1, 2).repeat_interleave(grp, dim=1)
+    s = qh @ kh.transpose(-1, -2) * scale
+    vis = torch.as_tensor(_visibility(sq, sk, causal, causal_offset, window)).expand(b, h, sq, sk).clone()
+    if mask is not None:
+        s = s + _t(np.broadcast_to(np.asarray(mask, dtype=np.float32), (b, h, sq, sk)).copy(), dtype)
+        vis &= s > -1.0e30
+    s = s.masked_fill(~vis, float("-inf"))
+    any_vis = vis.any(-1)
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.where(any_vis[..., None], torch.exp(s - lse[..., None]), torch.zeros_like(s))
+    lse = torch.where(any_vis, lse, torch.full_like(lse, 3.0e38))
+    bh = (np.arange(b)[:, None] * h + np.arange(h)[None, :])[:, :, None, None]
+    keep = dropout_keep(dropout_prob, seed, bh, np.arange(sq)[None, None, :, None], np.arange(sk)[None, None, None, :])
+    m = _t(keep.astype(np.float64) * (1.0 / (1.0 - np.float32(dropout_prob)) if dropout_prob > 0 else 1.0), dtype)
+    pm = p * m
+    out = pm @ vh
+    res = [out.transpose(1, 2).contiguous().to(torch.float32).numpy(), lse.to(torch.float32).numpy()]
+    if dout is None:
+        return tuple(res)
+    do = _t(dout, dtype).view(b, sq, h, d).transpose(1, 2)
+    delta = (do * out).sum(-1, keepdim=True)
+    ds = p * (m * (do @ vh.transpose(-1, -2)) - delta) * scale
+    dq = (ds @ kh).transpose(1, 2).contiguous()
+    dk = (ds.transpose(-1, -2) @ qh).view(b, hkv, grp, sk, d).sum(2).transpose(1, 2).contiguous()
+    dv = (pm.transpose(-1, -2) @ do).view(b, hkv, grp, sk, d).sum(2).transpose(1, 2).contiguous()
+    return tuple(res + [t.to(torch.float32).numpy() for t in (dq, dk, dv)])

@@ -64,6 +64,7 @@ class OracleConfig:
     # ferrotensor-graph/src/model_builder.rs:426-446 does
     lora_targets: Tuple[str, ...] = ()
     f16_base: bool = False  # frozen linears (and the head) rounded to f16
+    attention_dropout: float = 0.0  # config.json attention_dropout (model_builder.rs:541)
 
     def __post_init__(self):
         if self.head_dim is None:
@@ -137,7 +138,25 @@ def rope(x, heads: int, head_dim: int, theta: float):
     return torch.cat([x1 * cos - x2 * sin, x1 * sin + x2 * cos], dim=-1).view(b, s, heads * head_dim)
 
 
-def attention(cfg: OracleConfig, q, k, v):
+def _mix64(z: int) -> int:
+    m = (1 << 64) - 1
+    z = (z + 0x9E3779B97F4A7C15) & m
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+    return z ^ (z >> 31)
+
+
+def derive_seed(parts: Sequence[int]) -> int:
+    """ferrotensor-graph/src/dropout.rs:25-32: fold of SplitMix64 finalisers over the list."""
+    acc = _mix64(len(parts))
+    for part in parts:
+        acc = _mix64(acc ^ _mix64(part & ((1 << 64) - 1)))
+    return acc
+
+
+def attention(cfg: OracleConfig, q, k, v, dropout_seed: Optional[int] = None):
+    """`dropout_seed` (the layer's seed) multiplies the softmax weights by the keep mask of
+    flash_attention_v2.wgsl:94-104 scaled by 1/(1-p); None = evaluation, no dropout."""
     b, s, _ = q.shape
     h, hk, d = cfg.heads, cfg.kv_heads, cfg.head_dim
     q = q.view(b, s, h, d).transpose(1, 2)
@@ -146,13 +165,24 @@ def attention(cfg: OracleConfig, q, k, v):
     scores = q @ k.transpose(-1, -2) / math.sqrt(d)
     causal = torch.ones(s, s, dtype=torch.bool).tril()
     scores = scores.masked_fill(~causal, float("-inf"))
-    out = scores.softmax(-1) @ v
+    weights = scores.softmax(-1)
+    if dropout_seed is not None and cfg.attention_dropout > 0.0:
+        import numpy as np
+        from .kernels import dropout_keep
+        bh = (np.arange(b)[:, None] * h + np.arange(h)[None, :])[:, :, None, None]
+        keep = dropout_keep(cfg.attention_dropout, dropout_seed, bh, np.arange(s)[None, None, :, None],
+                            np.arange(s)[None, None, None, :])
+        scale = 1.0 / (1.0 - float(np.float32(cfg.attention_dropout)))
+        weights = weights * torch.as_tensor(keep.astype(np.float64) * scale, dtype=weights.dtype)
+    out = weights @ v
     return out.transpose(1, 2).reshape(b, s, h * d)
 
 
-def forward(cfg: OracleConfig, p, ids: torch.Tensor, return_hidden: bool = False):
+def forward(cfg: OracleConfig, p, ids: torch.Tensor, return_hidden: bool = False,
+            dropout_seed: Optional[int] = None):
     """ids [B, S] int64 -> logits [B, S, V].  Out-of-range ids embed as zero rows
-    (ferrotensor-autograd/src/lib.rs:1163-1168)."""
+    (ferrotensor-autograd/src/lib.rs:1163-1168).  `dropout_seed` is the forward pass's seed;
+    layer l draws its masks from derive_seed([dropout_seed, l]) (lfm.rs:568)."""
     emb = p["model.embed_tokens.weight"]
     in_range = ids < cfg.vocab
     x = emb[ids.clamp(max=cfg.vocab - 1)] * in_range[..., None].to(emb.dtype)
@@ -162,7 +192,8 @@ def forward(cfg: OracleConfig, p, ids: torch.Tensor, return_hidden: bool = False
         q = rope(linear(cfg, p, f"{pre}.self_attn.q_proj", h), cfg.heads, cfg.head_dim, cfg.theta)
         k = rope(linear(cfg, p, f"{pre}.self_attn.k_proj", h), cfg.kv_heads, cfg.head_dim, cfg.theta)
         v = linear(cfg, p, f"{pre}.self_attn.v_proj", h)
-        x = x + linear(cfg, p, f"{pre}.self_attn.o_proj", attention(cfg, q, k, v))
+        layer_seed = None if dropout_seed is None else derive_seed([dropout_seed, l])
+        x = x + linear(cfg, p, f"{pre}.self_attn.o_proj", attention(cfg, q, k, v, layer_seed))
         h = rms_norm(x, p[f"{pre}.post_attention_layernorm.weight"], cfg.eps)
         gate = linear(cfg, p, f"{pre}.mlp.gate_proj", h)
         up = linear(cfg, p, f"{pre}.mlp.up_proj", h)
@@ -311,7 +342,8 @@ class StepResult:
 
 
 def forward_backward(cfg: OracleConfig, p, ids, targets, masks, seed_scale: float = 1.0,
-                     train: Optional[Sequence[str]] = None, dtype=torch.float32) -> StepResult:
+                     train: Optional[Sequence[str]] = None, dtype=torch.float32,
+                     dropout_seed: Optional[int] = None) -> StepResult:
     """One micro-batch: forward, loss, autograd backward seeded with `seed_scale`
     (the trainer's 1/grad_accum_steps).  Returns grads of the LoRA factors (or `train`)."""
     q = {n: t.detach().to(dtype).clone() for n, t in p.items()}
@@ -321,7 +353,7 @@ def forward_backward(cfg: OracleConfig, p, ids, targets, masks, seed_scale: floa
     ids = torch.as_tensor(ids, dtype=torch.long)
     targets = torch.as_tensor(targets, dtype=torch.long)
     masks = torch.as_tensor(masks, dtype=torch.long)
-    logits = forward(cfg, q, ids)
+    logits = forward(cfg, q, ids, dropout_seed=dropout_seed)
     loss = loss_fn(logits, targets, masks)
     (loss * seed_scale).backward()
     vocab = logits.shape[-1]

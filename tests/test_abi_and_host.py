@@ -42,11 +42,23 @@ def test_every_prototype_is_declared_in_header(lib):
         assert n in declared, f"{n} bound in python but missing from ft_cuda.h"
 
 
-def test_struct_layouts_match_header():
+def test_struct_layouts_match_header(tmp_path):
+    """ctypes mirrors against the header itself: sizes and a few offsets printed by a C program."""
+    import subprocess
     from ferrotensor_b200 import _lib
     assert ctypes.sizeof(_lib.FtAdamParams) == 32       # training.rs:15-32: 6 floats + 2 pad
-    assert ctypes.sizeof(_lib.FtAttnParams) == 48
-    assert ctypes.sizeof(_lib.FtModelConfig) == 16 * 4
+    src = tmp_path / "sizes.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "ft_cuda.h"\n'
+                   'int main(void) { printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(FtAdamParams), sizeof(FtAttnParams), '
+                   'sizeof(FtModelConfig), offsetof(FtAttnParams, seed_lo), offsetof(FtAttnParams, mask_stride), '
+                   'offsetof(FtModelConfig, attention_dropout)); return 0; }\n')
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    A, M = _lib.FtAttnParams, _lib.FtModelConfig
+    assert got == [ctypes.sizeof(_lib.FtAdamParams), ctypes.sizeof(A), ctypes.sizeof(M), A.seed_lo.offset,
+                   A.mask_stride.offset, M.attention_dropout.offset]
+    assert ctypes.sizeof(A) == 18 * 4 and ctypes.sizeof(M) == 17 * 4
 
 
 def test_build_info_lists_the_tensor_core_kernel(lib):

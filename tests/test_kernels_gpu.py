@@ -190,14 +190,10 @@ def test_attention_forward_backward(cuda_ctx, eng, b, sq, sk, h, hkv, d, causal)
     assert np.array_equal(dk2.to_vec(cuda_ctx), dk.to_vec(cuda_ctx))
 
 
-def test_attention_rejects_mask_and_dropout(cuda_ctx, eng):
-    from ferrotensor_b200._lib import FtError
+def test_attention_rejects_a_mask_of_another_shape(cuda_ctx, eng):
     from ferrotensor_b200.engine import AttentionOptions
     q = _ut(cuda_ctx, np.zeros((1, 4, 1, 8), dtype=np.float32))
-    with pytest.raises(FtError):
-        eng.flash_attention_v2_with(cuda_ctx, q, q, q, _empty(cuda_ctx, (1, 4, 1, 8)),
-                                    AttentionOptions(causal=True, dropout_prob=0.1))
-    with pytest.raises(FtError):
+    with pytest.raises(Exception, match="attention mask"):
         eng.flash_attention_v2_with(cuda_ctx, q, q, q, _empty(cuda_ctx, (1, 4, 1, 8)),
                                     AttentionOptions(causal=True), mask=q)
 

@@ -20,7 +20,7 @@ def _oracle_cfg(cfg, lora, f16_base=False, lora_head=False):
                            kv_heads=cfg.kv_heads, ffn=cfg.ffn, eps=cfg.eps, theta=cfg.theta,
                            head_dim=cfg.head_dim, tied=cfg.tied, qkv_bias=cfg.qkv_bias,
                            lora_rank=lora.rank, lora_alpha=lora.alpha, lora_targets=targets,
-                           f16_base=f16_base)
+                           f16_base=f16_base, attention_dropout=getattr(cfg, "attention_dropout", 0.0))
 
 
 def _oracle_params(cfg, weights, adapters, f16_base):
