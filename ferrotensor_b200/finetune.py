@@ -15,8 +15,7 @@ trains on its shard of the data (distributed.rs:222-227) and the gradients are a
 NCCL all-reduce per optimizer step, where the reference exchanges them through files.
 
 Not carried over, each an error rather than a silent difference: `--q4-weights`,
-`--train-modules` other than `lora`, `--memory-report`, `--profile`, `--sample-prompt`
-(generation is a separate path).  One flag is added: `--gemm f16|f16x2|f32`, the arithmetic of
+`--train-modules` other than `lora`, `--memory-report`, `--profile`.  One flag is added: `--gemm f16|f16x2|f32`, the arithmetic of
 the matrix products (f16 operands with f32 accumulation on the tensor cores by default; `f32`
 is the exact f32 path, which `--f32-weights` always takes).
 """
@@ -177,6 +176,7 @@ class TrainArgs:
     seed: int = 0
     lite: bool = False
     json: bool = False
+    sample_prompt: Optional[str] = None
     checkpoint_blocks: bool = False
     gemm: str = "f16"
     device: int = 0
@@ -296,7 +296,10 @@ def train(args: TrainArgs) -> TrainSummary:
                       checkpoint_blocks=args.checkpoint_blocks)
     if args.checkpoint_blocks:
         _log("block checkpointing: on")
-    del weights
+    if args.sample_prompt is None:
+        del weights
+    elif tokenizer is None:
+        raise Unmet("--sample-prompt needs a tokenizer.json in the model directory")
     n_params = sum(t.numel() for t in model.named_lora_params().values())
     if n_params == 0:
         raise Unmet(f"--lora-targets {','.join(args.lora_targets)} matches no linear of the model")
@@ -448,6 +451,21 @@ def train(args: TrainArgs) -> TrainSummary:
         _log(f"metrics: {out_dir / 'metrics.jsonl'}")
     eval_after = evaluate("after", step)
     metrics.close()
+    if args.sample_prompt is not None:
+        # a quick sanity check: a greedy reply of up to 96 tokens to the prompt in the ChatML template
+        from . import generate as gen
+        adapters_now = {n: t.detach().clone() for n, t in model.named_lora_params().items()}
+        infer = gen.InferenceModel(ctx, cfg, weights, lora, adapters_now, f16_base=not args.f32_weights)
+        prompt = gen.Prompt.chatml(tokenizer, _raw, tokenizer.encode_chat(None, args.sample_prompt))
+        _log(f"sample ({args.sample_prompt!r}):")
+        out_stream = sys.stderr if args.json else sys.stdout
+
+        def emit(text: str) -> None:
+            out_stream.write(text)
+            out_stream.flush()
+        gen.generate_tokens(infer, prompt, 96, gen.Sampler(0.0, 0, 1.0), gen.DecodeCache(infer, len(prompt.ids) + 96),
+                            tokenizer.decode, emit)
+        emit("\n")
     peak_mib = -(-torch.cuda.max_memory_allocated(device) // (1 << 20))
     model.close()
     return TrainSummary(step, first_loss, last_loss, eval_before, eval_after, int(peak_mib), elapsed, str(out_dir),
@@ -489,6 +507,7 @@ def parse_args(argv=None) -> TrainArgs:
     ap.add_argument("--eval-every", type=int, default=d.eval_every)
     ap.add_argument("--eval-samples", type=int, default=d.eval_samples)
     ap.add_argument("--seed", type=int, default=d.seed)
+    ap.add_argument("--sample-prompt", default=None, help="generate from this prompt after training")
     ap.add_argument("--lite", action="store_true", help="seq-len 128, rank 4, grad-accum 8 unless set")
     ap.add_argument("--checkpoint-blocks", action="store_true",
                     help="recompute each decoder block during backward instead of keeping its activations")

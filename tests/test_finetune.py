@@ -182,7 +182,7 @@ class _Stop(Exception):
 
 
 @pytest.mark.gpu
-def test_run_saves_resumes_and_lands_on_the_same_bits(cuda_ctx, tmp_path, monkeypatch):
+def test_run_saves_resumes_and_lands_on_the_same_bits(cuda_ctx, tmp_path, monkeypatch, capsys):
     from ferrotensor_b200 import checkpoint as ck
     from ferrotensor_b200 import trainer as tr_mod
     model_dir = _model_dir(tmp_path)
@@ -192,7 +192,8 @@ def test_run_saves_resumes_and_lands_on_the_same_bits(cuda_ctx, tmp_path, monkey
                             seq_len=96, lr=5e-3, warmup_steps=2, max_steps=6, batch_size=2, grad_accum=2,
                             lora_targets=["q_proj", "v_proj", "down_proj"], log_every=1, seed=3, **kw)
 
-    whole = ft.train(args("whole", eval_data=str(tmp_path / "eval.jsonl"), eval_every=4))
+    whole = ft.train(args("whole", eval_data=str(tmp_path / "eval.jsonl"), eval_every=4, sample_prompt="colour 2?"))
+    assert capsys.readouterr().out.endswith("\n")            # the sampled reply went to stdout
     assert whole.steps == 6 and whole.final_loss < whole.first_loss and whole.eval_loss_after < whole.eval_loss_before
     assert whole.measured_peak_mib > 0 and whole.adapter == str(tmp_path / "whole" / "lora_adapters.safetensors")
     lines = [json.loads(l) for l in (tmp_path / "whole" / "metrics.jsonl").read_text().splitlines()]
