@@ -1140,7 +1140,19 @@ int launch_tc2(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, con
   }
   {
     const bool pa = ctx->profile_all;
-    if (pa) ft_prof_begin(ctx, "k_gemm_tc2<pair 256x256>");
+    if (pa) {
+      // FT_PROFILE_SHAPES=1 appends the problem sizes (M x N x K + adapter K, p = with pre-tiles)
+      static const bool shapes = getenv("FT_PROFILE_SHAPES") != nullptr;
+      const char* name = "k_gemm_tc2<pair 256x256>";
+      if (shapes) {
+        static std::map<std::string, std::string> names;
+        char buf[112];
+        snprintf(buf, sizeof(buf), "k_gemm_tc2<pair 256x256>[%dx%dx%d+%d%s]", M, N, K, K2,
+                 pre.tiles > 0 ? ",p" : "");
+        name = names.emplace(buf, buf).first->second.c_str();
+      }
+      ft_prof_begin(ctx, name);
+    }
     ctx->profile_all = false;
     cudaError_t le = ft_launch_ex(ctx, k_gemm_tc2<STAGES>, 2 * pairs, GEMM_THREADS, L::DYN_BYTES, ma, mb,
                                   ma2, mb2, mb3, ep, pre, M, N, K, K2, idesc, ctx->status_dev);

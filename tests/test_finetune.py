@@ -145,6 +145,17 @@ def test_command_line_defaults_and_helpers(tmp_path):
     assert d["final_loss"] is None and d["first_loss"] is None and d["eval_loss_after"] == 1.5 and d["adapter"] is None
 
 
+def test_cli_parses_eval_and_generate_flags():
+    from ferrotensor_b200 import cli
+    a = cli._parser().parse_args(["eval", "--model", "m", "--dataset", "d.jsonl", "--lora", "a.safetensors", "--json"])
+    assert (a.command, a.data, a.lora, a.json, a.task, a.seq_len) == ("eval", "d.jsonl", "a.safetensors", True, "sft", 256)
+    g = cli._parser().parse_args(["infer", "--model", "m"])
+    assert (g.prompt, g.max_new_tokens, g.temperature, g.top_k, g.top_p, g.seed, g.raw) == ("Hello!", 128, 0.7, 50, 0.9, None, False)
+    with pytest.raises(SystemExit):
+        cli._parser().parse_args(["eval", "--model", "m"])
+    assert cli._json_line({"loss": float("nan"), "n": 1}) == '{"loss": null, "n": 1}'
+
+
 def test_requests_that_cannot_be_met(tmp_path):
     base = dict(model=str(tmp_path), data=str(tmp_path / "d.jsonl"))
     with pytest.raises(ft.Unmet, match="must be positive"):
@@ -206,6 +217,26 @@ def test_run_saves_resumes_and_lands_on_the_same_bits(cuda_ctx, tmp_path, monkey
     saved = ck.load_lora_checkpoint(whole.adapter)
     assert (saved.metadata.rank, saved.metadata.alpha, saved.metadata.target_modules) == (8, 16.0, ["q_proj", "v_proj", "down_proj"])
     assert len(saved) == 2 * 2 * 3
+
+    # eval and generate read the adapter's settings from the file the run wrote
+    from ferrotensor_b200 import cli
+    capsys.readouterr()
+    common = ["--model", str(model_dir), "--json"]
+    assert cli.main(["eval", *common, "--data", str(tmp_path / "eval.jsonl"), "--seq-len", "96", "--lora", whole.adapter]) == 0
+    with_lora = json.loads(capsys.readouterr().out)
+    assert with_lora["examples"] == 6 and with_lora["tokens"] > 0
+    assert abs(with_lora["loss"] - whole.eval_loss_after) < 1e-5 and with_lora["perplexity"] == pytest.approx(math.exp(with_lora["loss"]), rel=1e-5)
+    assert cli.main(["eval", *common, "--data", str(tmp_path / "eval.jsonl"), "--seq-len", "96"]) == 0
+    base_only = json.loads(capsys.readouterr().out)
+    assert abs(base_only["loss"] - whole.eval_loss_before) < 1e-5
+    assert cli.main(["generate", *common, "--lora", whole.adapter, "--prompt", "colour 2?", "--temperature", "0",
+                     "--max-new-tokens", "8"]) == 0
+    cap = capsys.readouterr()
+    reply = json.loads(cap.out)
+    assert reply["prompt_tokens"] > 20 and 0 <= reply["new_tokens"] <= 8 and reply["kv_cache"] is True
+    assert reply["text"] + "\n" in cap.err and "prompt +" in cap.err
+    assert cli.main(["eval", *common, "--data", str(tmp_path / "missing.jsonl")]) == 2
+    capsys.readouterr()
 
     # the same run stopped right after the save at step 3 ...
     original = tr_mod.Trainer.save_training_checkpoint
