@@ -4,6 +4,7 @@
     python -m ferrotensor_b200.microbench attention --batch 8 --seq 1024 --heads 32 --kv-heads 32
     python -m ferrotensor_b200.microbench matvec --k 2048 --n 8192
     python -m ferrotensor_b200.microbench decode --batch 8 --seq 4096
+    python -m ferrotensor_b200.microbench sustained --seconds 4       # GEMM under the power cap, beside cuBLAS
 
 Each case holds a few hundred MB on the device at most, which makes it the right target for a
 profiler capture of one kernel (the training step keeps tens of GB resident).  Times come from
@@ -136,6 +137,82 @@ def decode(args):
     print(f"decode attention: {ms * 1e3:.1f} us, {byts / (ms * 1e-3) / 1e9:.0f} GB/s of K and V")
 
 
+def _sample_clocks(stop, acc, device):
+    import subprocess
+    import time
+    while not stop.is_set():
+        out = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,power.draw", "--format=csv,noheader,nounits",
+                              "-i", str(device)], capture_output=True, text=True).stdout.strip().split(",")
+        try:
+            acc.append((float(out[0]), float(out[1])))
+        except (ValueError, IndexError):
+            pass
+        time.sleep(0.2)
+
+
+def sustained(args):
+    """Each product back to back for `--seconds`, long enough for the power cap to settle the clock:
+    this library's tensor-core GEMM (f32 activations rounded to f16 by its conversion kernel, f32
+    result) and torch.matmul on the same f16 operands (cuBLAS, f16 result), with the median SM
+    clock and board power of the second half of each run.  The GEMM's own time comes from the
+    library's per-kernel events, cuBLAS's from events around each batch of launches."""
+    import threading
+    import time
+    ctx = CudaContext(0)
+    eng = ComputeEngine(ctx)
+    ctx.set_gemm_mode(GemmMode.F16)
+    shapes = [(8192, 8192, 2048), (8192, 2048, 8192), (8192, 2048, 2048), (8192, 16384, 2048), (8192, 6144, 2048),
+              (8192, 8192, 8192)] if not args.shape else [tuple(args.shape)]
+    per = 200
+    for m, n, k in shapes:
+        g = torch.Generator(device="cuda").manual_seed(1)
+        a32 = torch.randn(m * k, device="cuda", generator=g)
+        b16 = (torch.randn(n * k, device="cuda", generator=g) * 0.05).half()
+        a = UnifiedTensor(a32.view(torch.uint8), [m, k], DType.F32)
+        b = UnifiedTensor(b16.view(torch.uint8), [n, k], DType.FP16)
+        out = UnifiedTensor.empty(ctx, [m, n])
+        a16, bt = a32.view(m, k).half(), b16.view(n, k)
+        flop = 2.0 * m * n * k
+        row = {"case": "sustained", "m": m, "n": n, "k": k, "seconds": args.seconds}
+
+        def run(batch):
+            acc, stop = [], threading.Event()
+            th = threading.Thread(target=_sample_clocks, args=(stop, acc, 0))
+            th.start()
+            t0, last = time.time(), None
+            while time.time() - t0 < args.seconds:
+                last = batch()
+            stop.set()
+            th.join()
+            tail = acc[len(acc) // 2:] or [(float("nan"), float("nan"))]
+            return last, float(np.median([c for c, _ in tail])), float(np.median([w for _, w in tail]))
+
+        def ours():
+            ctx.profile(2)
+            for _ in range(per):
+                eng.matmul_bt_f16b(ctx, a, b, out)
+            ctx.synchronize()
+            rep = ctx.profile_report()
+            ctx.profile(0)
+            cnt, ms = next((v for name, v in rep.items() if name.startswith("k_gemm_tc")), (0, 0.0))
+            return flop * cnt / (ms * 1e-3) / 1e12 if ms else float("nan")
+
+        def cublas():
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(per):
+                torch.matmul(a16, bt.t())
+            e1.record()
+            torch.cuda.synchronize()
+            return flop * per / (e0.elapsed_time(e1) * 1e-3) / 1e12
+
+        for name, fn in (("library", ours), ("cublas", cublas)):
+            fn()
+            tf, mhz, watts = run(fn)
+            row[name] = {"tflops": round(tf, 1), "sm_mhz": mhz, "watts": watts}
+        print(json.dumps(row), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -159,11 +236,14 @@ def main():
     dc.add_argument("--heads", type=int, default=32)
     dc.add_argument("--kv-heads", type=int, default=32)
     dc.add_argument("--copies", type=int, default=3)
+    su = sub.add_parser("sustained")
+    su.add_argument("--seconds", type=float, default=4.0)
+    su.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None)
     for p in (g, a, mv, dc):
         p.add_argument("--iters", type=int, default=5)
         p.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args()
-    {"gemm": gemm, "attention": attention, "matvec": matvec, "decode": decode}[args.case](args)
+    {"gemm": gemm, "attention": attention, "matvec": matvec, "decode": decode, "sustained": sustained}[args.case](args)
 
 
 if __name__ == "__main__":
