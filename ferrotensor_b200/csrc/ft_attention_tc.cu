@@ -50,8 +50,8 @@ struct AttnSmem {
   static constexpr int ONES_OFF = V_OFF + KV_STAGES * HALF_TILE;    // 64 keys x 64: column 0 = 1
   static constexpr int P_OFF = ONES_OFF + HALF_TILE;                // 2 x (128 q x 64 keys), K-major
   static constexpr int BAR_OFF = P_OFF + 2 * TILE_BYTES;
-  // q_full, kv_full[3], s_full[2], s_free[2], p_full[2], o_full[2]
-  static constexpr int NBAR = 12;
+  // q_full, kv_full[3], s_full[2], s_free[2], p_full[2], o_full[2], o_read
+  static constexpr int NBAR = 13;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -64,29 +64,55 @@ struct AttnSmem {
 // rescaled, by the softmax warps themselves) when a block exceeds it by more than 2^8: until
 // then exp2(s - m) <= 256 is harmless in f16 and the final O / l is unchanged.  Exponentials
 // use the f32 special-function unit; the scale-and-shift before them is a packed pair FMA.
+//
+// The kernel is persistent: a CTA walks the (128-query tile, head) pairs t = blockIdx.x,
+// blockIdx.x + gridDim.x, ..., late (long) query tiles first, and its key/value ring, score
+// and P buffers and barrier phases run on across tile boundaries, counted in blocks since the
+// CTA started.  The loads of the next tile's first key/value blocks are therefore issued two
+// blocks ahead like any others, the next Q tile is fetched as soon as the last S product of
+// the current tile has finished, and S of the next tile's first block is computed while the
+// softmax warps normalise and store the current tile; tensor memory, barriers and the ones
+// block are set up once per CTA instead of once per tile.
+struct FwdTile {
+  int q0, nblk, b, h, kvh, tok0;
+};
+__device__ __forceinline__ bool fwd_tile(int t, int total, int nq, int bh_count, int heads, int kv_heads,
+                                         int seq, FwdTile& w) {
+  if (t >= total) return false;
+  const int qblk = nq - 1 - t / bh_count;   // heavy (late) query tiles first
+  const int bh = t % bh_count;
+  w.b = bh / heads;
+  w.h = bh % heads;
+  w.kvh = w.h / (heads / kv_heads);
+  w.q0 = qblk * AT_Q;
+  w.nblk = min((w.q0 + AT_Q) / 64, (seq + 63) / 64);   // 64-key blocks at or below the diagonal
+  w.tok0 = w.b * seq;
+  return true;
+}
+// a position in the CTA's sequence of (tile, block) pairs
+struct FwdCursor {
+  int it, j;       // tile iteration of this CTA, block within the tile
+  bool has;
+  FwdTile w;
+};
+
 __global__ void __launch_bounds__(AT_THREADS, 2)
 k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constant__ CUtensorMap map_kv64,
               __half* __restrict__ out16, long long ldo16, float* __restrict__ out32,
               long long ldo32, float* __restrict__ stats, int seq, int heads, int kv_heads,
-              int q_col0, int k_col0, int v_col0, float scale_log2e, int* status) {
+              int bh_count, int q_col0, int k_col0, int v_col0, float scale_log2e, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - raw);
   const uint32_t bar0 = base + AttnSmem::BAR_OFF;
   const uint32_t bar_q = bar0, bar_kv = bar0 + 8, bar_sfull = bar0 + 32, bar_sfree = bar0 + 48,
-                 bar_pfull = bar0 + 64, bar_ofull = bar0 + 80;
+                 bar_pfull = bar0 + 64, bar_ofull = bar0 + 80, bar_oread = bar0 + 96;
   uint32_t* tmem_slot = (uint32_t*)(gbase + AttnSmem::BAR_OFF + AttnSmem::NBAR * 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // heavy (late) query blocks first: they have the most key blocks to visit
-  const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;
-  const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
-  const int kvh = h / (heads / kv_heads);
-  const int q0 = qblk * AT_Q;
-  const int nblk = min((q0 + AT_Q) / 64, (seq + 63) / 64);  // 64-key blocks at or below the diagonal
-  const int tok0 = b * seq;
+  const int nq = (seq + AT_Q - 1) / AT_Q, total = nq * bh_count;
   constexpr uint32_t TMEM_COLS = 256;  // S0 [0,64), S1 [64,128), O [128,192), sum of P at 192
   constexpr int O_COLS = 80;           // 64 outputs + the ones column, padded to a multiple of 16
 
@@ -99,6 +125,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
       mbar_init(bar_pfull + s * 8, 4);
       mbar_init(bar_ofull + s * 8, 1);
     }
+    mbar_init(bar_oread, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -129,6 +156,18 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
   ft_pdl_wait();
   ft_pdl_launch();
 
+  auto start_cursor = [&](FwdCursor& c) {
+    c.it = 0;
+    c.j = 0;
+    c.has = fwd_tile((int)blockIdx.x, total, nq, bh_count, heads, kv_heads, seq, c.w);
+  };
+  auto advance = [&](FwdCursor& c) {
+    if (++c.j < c.w.nblk) return;
+    c.j = 0;
+    ++c.it;
+    c.has = fwd_tile((int)blockIdx.x + c.it * (int)gridDim.x, total, nq, bh_count, heads, kv_heads, seq, c.w);
+  };
+
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA + MMA issuer
     if (lane == 0) {
@@ -136,60 +175,89 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
                      sv = base + AttnSmem::V_OFF, sp = base + AttnSmem::P_OFF;
       const uint32_t idesc_s = make_idesc(128, 64, 0, 0);                      // Q, K both K-major
       const uint32_t idesc_o = make_idesc(128, O_COLS, 0, 0) | (1u << 16);     // V is N-major
-      auto load_kv = [&](int j) {
-        const int s = j % 3;
-        mbar_expect_tx(bar_kv + s * 8, 2 * HALF_TILE);
-        tma_load_2d(sk + s * HALF_TILE, &map_kv64, bar_kv + s * 8, k_col0 + kvh * AT_D, tok0 + j * 64);
-        tma_load_2d(sv + s * HALF_TILE, &map_kv64, bar_kv + s * 8, v_col0 + kvh * AT_D, tok0 + j * 64);
+      // three cursors over the same sequence of blocks: loads run two blocks ahead of P V,
+      // S one block ahead; gl, gs, gp count blocks since the CTA started
+      FwdCursor L, S, P;
+      start_cursor(L);
+      start_cursor(S);
+      start_cursor(P);
+      uint32_t gl = 0, gs = 0, gp = 0;
+      bool ok = true;
+      auto load_q = [&](const FwdCursor& c) {
+        mbar_expect_tx(bar_q, TILE_BYTES);
+        tma_load_2d(sq, &map_q128, bar_q, q_col0 + c.w.h * AT_D, c.w.tok0 + c.w.q0);
       };
-      auto mma_s = [&](int j) {
-        const int s = j & 1;
-        const uint64_t da = make_desc_sw128(sq), db = make_desc_sw128(sk + (j % 3) * HALF_TILE);
+      auto load_kv = [&]() {
+        const uint32_t st = gl % 3;
+        mbar_expect_tx(bar_kv + st * 8, 2 * HALF_TILE);
+        tma_load_2d(sk + st * HALF_TILE, &map_kv64, bar_kv + st * 8, k_col0 + L.w.kvh * AT_D,
+                    L.w.tok0 + L.j * 64);
+        tma_load_2d(sv + st * HALF_TILE, &map_kv64, bar_kv + st * 8, v_col0 + L.w.kvh * AT_D,
+                    L.w.tok0 + L.j * 64);
+        advance(L);
+        ++gl;
+      };
+      // S of block gs: its keys must have landed and its accumulator (last used by block gs-2)
+      // must have been read
+      auto issue_s = [&]() -> bool {
+        if (!mbar_wait(bar_kv + (gs % 3) * 8, (gs / 3) & 1, abort_flag, status, 13)) return false;
+        if (gs >= 2 && !mbar_wait(bar_sfree + (gs & 1) * 8, ((gs - 2) >> 1) & 1, abort_flag, status, 14))
+          return false;
+        tc_fence_after();
+        const uint64_t da = make_desc_sw128(sq), db = make_desc_sw128(sk + (gs % 3) * HALF_TILE);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          tc_mma_f16(tmem_base + s * 64, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s,
+          tc_mma_f16(tmem_base + (gs & 1) * 64, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s,
                      k > 0 ? 1u : 0u);
-        tc_commit(bar_sfull + s * 8);
+        tc_commit(bar_sfull + (gs & 1) * 8);
+        advance(S);
+        ++gs;
+        return true;
       };
-      mbar_expect_tx(bar_q, TILE_BYTES);
-      tma_load_2d(sq, &map_q128, bar_q, q_col0 + h * AT_D, tok0 + q0);
-      for (int j = 0; j < 3 && j < nblk; ++j) load_kv(j);
-      bool ok = mbar_wait(bar_q, 0, abort_flag, status, 11) &&
-                mbar_wait(bar_kv, 0, abort_flag, status, 12);
-      if (ok) {
-        tc_fence_after();
-        mma_s(0);
+      if (P.has) {
+        load_q(S);
+        for (int i = 0; i < 3 && L.has; ++i) load_kv();
+        ok = mbar_wait(bar_q, 0, abort_flag, status, 11) && issue_s();
       }
-      for (int j = 0; ok && j < nblk; ++j) {
-        if (j + 1 < nblk) {
-          // S(j+1) goes to the other accumulator, free once block j-1's scores were read
-          const int s = (j + 1) & 1;
-          ok = mbar_wait(bar_kv + ((j + 1) % 3) * 8, ((j + 1) / 3) & 1, abort_flag, status, 13);
-          if (ok && j >= 1) ok = mbar_wait(bar_sfree + s * 8, ((j - 1) >> 1) & 1, abort_flag, status, 14);
+      while (ok && P.has) {
+        // the next S product: at once when it belongs to the same tile; across a tile boundary
+        // the Q buffer is reloaded first, after the current tile's last S product has finished
+        const bool next_tile = S.has && S.j == 0;
+        if (S.has && !next_tile) {
+          ok = issue_s();
           if (!ok) break;
-          tc_fence_after();
-          mma_s(j + 1);
-        }
-        if (j >= 1 && j + 2 < nblk) {
-          // stage (j+2) % 3 held block j-1: free once P V(j-1) has run
-          ok = mbar_wait(bar_ofull + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1, abort_flag, status, 17);
+        } else if (next_tile) {
+          ok = mbar_wait(bar_sfull + ((gs - 1) & 1) * 8, ((gs - 1) >> 1) & 1, abort_flag, status, 16);
           if (!ok) break;
-          load_kv(j + 2);
+          load_q(S);
         }
-        ok = mbar_wait(bar_pfull + (j & 1) * 8, (j >> 1) & 1, abort_flag, status, 15);
+        if (gp >= 1 && L.has) {
+          // stage (gp + 2) % 3 held block gp - 1: free once P V(gp - 1) has run
+          ok = mbar_wait(bar_ofull + ((gp - 1) & 1) * 8, ((gp - 1) >> 1) & 1, abort_flag, status, 17);
+          if (!ok) break;
+          load_kv();
+        }
+        ok = mbar_wait(bar_pfull + (gp & 1) * 8, (gp >> 1) & 1, abort_flag, status, 15);
+        if (ok && P.j == 0 && P.it >= 1)   // the previous tile's output must have left tensor memory
+          ok = mbar_wait(bar_oread, (P.it - 1) & 1, abort_flag, status, 18);
         if (!ok) break;
         tc_fence_after();
         {
           // O += P[128 q x 64 keys] . [V | 1][64 keys x 80]: V in place as an N-major operand,
           // its second 64-column block is the ones block
-          const uint32_t vs = sv + (j % 3) * HALF_TILE;
-          const uint64_t dp = make_desc_sw128(sp + (j & 1) * TILE_BYTES);
+          const uint32_t vs = sv + (gp % 3) * HALF_TILE;
+          const uint64_t dp = make_desc_sw128(sp + (gp & 1) * TILE_BYTES);
           const uint64_t dv = make_desc_mn_sw128(vs, (base + AttnSmem::ONES_OFF) - vs);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             tc_mma_f16(tmem_o, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * 128), idesc_o,
-                       (j > 0 || k > 0) ? 1u : 0u);
-          tc_commit(bar_ofull + (j & 1) * 8);
+                       (P.j > 0 || k > 0) ? 1u : 0u);
+          tc_commit(bar_ofull + (gp & 1) * 8);
+        }
+        advance(P);
+        ++gp;
+        if (next_tile) {
+          ok = mbar_wait(bar_q, S.it & 1, abort_flag, status, 11) && issue_s();
         }
       }
     }
@@ -197,103 +265,115 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
   } else {
     // ------------------------------------------------------------------ softmax warps
     const int row = warp * 32 + lane;          // query row in the tile = TMEM lane
-    const int qi = q0 + row;                   // position in the sequence
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
     uint8_t* rowp = gbase + AttnSmem::P_OFF + (row >> 3) * 1024 + (row & 7) * 128;
-    float m_st = -INFINITY;   // the maximum the exponentials are taken against (log2 domain)
+    uint32_t g0 = 0;                           // blocks of the tiles before this one
     bool ok = true;
-    for (int j = 0; ok && j < nblk; ++j) {
-      const int sb = j & 1;
-      ok = mbar_wait(bar_sfull + sb * 8, (j >> 1) & 1, abort_flag, status, 21);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t r0[32], r1[32];
-      tc_ld32(tmem_base + lane_addr + sb * 64, r0);
-      tc_ld32(tmem_base + lane_addr + sb * 64 + 32, r1);
-      tc_wait_ld();
-      // the scores are in registers: this accumulator may be overwritten
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_sfree + sb * 8);
-      const int key0 = j * 64;
-      if (key0 + 63 > q0) {                     // the block touches the diagonal for some row
-        const int lim = qi - key0;              // keys [0, lim] of the block are visible
+    FwdTile w;
+    for (int it = 0; ok && fwd_tile((int)blockIdx.x + it * (int)gridDim.x, total, nq, bh_count, heads,
+                                    kv_heads, seq, w); ++it) {
+      const int q0 = w.q0, nblk = w.nblk;
+      const int qi = q0 + row;                 // position in the sequence
+      float m_st = -INFINITY;   // the maximum the exponentials are taken against (log2 domain)
+      for (int j = 0; ok && j < nblk; ++j) {
+        const uint32_t g = g0 + (uint32_t)j;
+        const int sb = (int)(g & 1);
+        ok = mbar_wait(bar_sfull + sb * 8, (g >> 1) & 1, abort_flag, status, 21);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t r0[32], r1[32];
+        tc_ld32(tmem_base + lane_addr + sb * 64, r0);
+        tc_ld32(tmem_base + lane_addr + sb * 64 + 32, r1);
+        tc_wait_ld();
+        // the scores are in registers: this accumulator may be overwritten
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sfree + sb * 8);
+        const int key0 = j * 64;
+        if (key0 + 63 > q0) {                     // the block touches the diagonal for some row
+          const int lim = qi - key0;              // keys [0, lim] of the block are visible
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          if (c > lim) r0[c] = 0xff800000u;     // -inf
-          if (c + 32 > lim) r1[c] = 0xff800000u;
+          for (int c = 0; c < 32; ++c) {
+            if (c > lim) r0[c] = 0xff800000u;     // -inf
+            if (c + 32 > lim) r1[c] = 0xff800000u;
+          }
         }
-      }
-      float mx = -INFINITY;
+        float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
-        mx = fmaxf(mx, fmaxf(__uint_as_float(r0[c]), __uint_as_float(r1[c])));
-      const float mxs = mx * scale_log2e;
-      if (j == 0) {
-        m_st = mxs;   // key 0 is visible to every row, so this is finite
-      } else {
-        const bool need = mxs > m_st + 8.0f;
-        if (__any_sync(0xffffffffu, need)) {
-          // raise the maximum and rescale the accumulator (rows that do not need it use 1);
-          // P V(j-1) must have finished, P V(j) cannot start before this warp publishes P(j)
-          const float m_new = need ? mxs : m_st;
-          const float corr = ex2(m_st - m_new);
-          ok = mbar_wait(bar_ofull + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1, abort_flag, status, 22);
-          if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-          tc_fence_after();
-          uint32_t a[32];
+        for (int c = 0; c < 32; ++c)
+          mx = fmaxf(mx, fmaxf(__uint_as_float(r0[c]), __uint_as_float(r1[c])));
+        const float mxs = mx * scale_log2e;
+        if (j == 0) {
+          m_st = mxs;   // key 0 is visible to every row, so this is finite
+        } else {
+          const bool need = mxs > m_st + 8.0f;
+          if (__any_sync(0xffffffffu, need)) {
+            // raise the maximum and rescale the accumulator (rows that do not need it use 1);
+            // P V(j-1) must have finished, P V(j) cannot start before this warp publishes P(j)
+            const float m_new = need ? mxs : m_st;
+            const float corr = ex2(m_st - m_new);
+            ok = mbar_wait(bar_ofull + ((g - 1) & 1) * 8, ((g - 1) >> 1) & 1, abort_flag, status, 22);
+            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t a[32];
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            tc_ld32(tmem_o + lane_addr + hh * 32, a);
+            for (int hh = 0; hh < 2; ++hh) {
+              tc_ld32(tmem_o + lane_addr + hh * 32, a);
+              tc_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * corr);
+              tc_st32(tmem_o + lane_addr + hh * 32, a);
+            }
+            uint32_t s16[16];
+            tc_ld16(tmem_o + lane_addr + 64, s16);
             tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * corr);
-            tc_st32(tmem_o + lane_addr + hh * 32, a);
+            for (int c = 0; c < 16; ++c) s16[c] = __float_as_uint(__uint_as_float(s16[c]) * corr);
+            tc_st16(tmem_o + lane_addr + 64, s16);
+            tc_wait_st();
+            m_st = m_new;
           }
-          uint32_t s16[16];
-          tc_ld16(tmem_o + lane_addr + 64, s16);
-          tc_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 16; ++c) s16[c] = __float_as_uint(__uint_as_float(s16[c]) * corr);
-          tc_st16(tmem_o + lane_addr + 64, s16);
-          tc_wait_st();
-          m_st = m_new;
         }
-      }
-      // P = exp2(s * scale - m)
-      const float nm = -m_st;
-      uint32_t packed[32];
+        // P = exp2(s * scale - m)
+        const float nm = -m_st;
+        uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        float x0, x1, y0, y1;
-        ffma2(x0, x1, __uint_as_float(r0[c]), __uint_as_float(r0[c + 1]), scale_log2e, scale_log2e, nm, nm);
-        ffma2(y0, y1, __uint_as_float(r1[c]), __uint_as_float(r1[c + 1]), scale_log2e, scale_log2e, nm, nm);
-        packed[c >> 1] = pack_h2(ex2(x0), ex2(x1));
-        packed[16 + (c >> 1)] = pack_h2(ex2(y0), ex2(y1));
-      }
-      // this P buffer was last read by P V(j-2)
-      if (j >= 2) {
-        ok = mbar_wait(bar_ofull + sb * 8, ((j - 2) >> 1) & 1, abort_flag, status, 23);
-        if (!ok) break;
-      }
-      uint8_t* rp = rowp + sb * TILE_BYTES;
+        for (int c = 0; c < 32; c += 2) {
+          float x0, x1, y0, y1;
+          ffma2(x0, x1, __uint_as_float(r0[c]), __uint_as_float(r0[c + 1]), scale_log2e, scale_log2e, nm, nm);
+          ffma2(y0, y1, __uint_as_float(r1[c]), __uint_as_float(r1[c + 1]), scale_log2e, scale_log2e, nm, nm);
+          packed[c >> 1] = pack_h2(ex2(x0), ex2(x1));
+          packed[16 + (c >> 1)] = pack_h2(ex2(y0), ex2(y1));
+        }
+        // this P buffer was last read by P V of the block two before (possibly of the last tile)
+        if (g >= 2) {
+          ok = mbar_wait(bar_ofull + sb * 8, ((g - 2) >> 1) & 1, abort_flag, status, 23);
+          if (!ok) break;
+        }
+        uint8_t* rp = rowp + sb * TILE_BYTES;
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        *(uint4*)(rp + ((q ^ (row & 7)) << 4)) =
-            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-      tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull + sb * 8);
-    }
-    if (ok) ok = mbar_wait(bar_ofull + ((nblk - 1) & 1) * 8, ((nblk - 1) >> 1) & 1, abort_flag, status, 24);
-    if (ok) {
+        for (int q = 0; q < 8; ++q)
+          *(uint4*)(rp + ((q ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_pfull + sb * 8);
+      }
+      if (!ok) break;
+      const uint32_t gl_ = g0 + (uint32_t)nblk - 1;   // the tile's last block
+      ok = mbar_wait(bar_ofull + (gl_ & 1) * 8, (gl_ >> 1) & 1, abort_flag, status, 24);
+      if (!ok) break;
       tc_fence_after();
       uint32_t a0[32], a1[32], s16[16];
       tc_ld32(tmem_o + lane_addr, a0);
       tc_ld32(tmem_o + lane_addr + 32, a1);
       tc_ld16(tmem_o + lane_addr + 64, s16);
       tc_wait_ld();
+      // the accumulator is in registers: the next tile's first P V may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_oread);
       if (qi < seq) {
         const float l = __uint_as_float(s16[0]);
         const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -303,26 +383,27 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
           o_acc[c] = __uint_as_float(a0[c]) * inv;
           o_acc[32 + c] = __uint_as_float(a1[c]) * inv;
         }
-        const long long tok = (long long)tok0 + qi;
+        const long long tok = (long long)w.tok0 + qi;
         if (out16) {
-          __half* o = out16 + tok * ldo16 + (long long)h * AT_D;
+          __half* o = out16 + tok * ldo16 + (long long)w.h * AT_D;
 #pragma unroll
           for (int i = 0; i < AT_D; i += 8)
             *(uint4*)(o + i) = make_uint4(pack_h2(o_acc[i], o_acc[i + 1]), pack_h2(o_acc[i + 2], o_acc[i + 3]),
                                           pack_h2(o_acc[i + 4], o_acc[i + 5]), pack_h2(o_acc[i + 6], o_acc[i + 7]));
         }
         if (out32) {
-          float* o = out32 + tok * ldo32 + (long long)h * AT_D;
+          float* o = out32 + tok * ldo32 + (long long)w.h * AT_D;
 #pragma unroll
           for (int i = 0; i < AT_D; i += 4)
             *(float4*)(o + i) = make_float4(o_acc[i], o_acc[i + 1], o_acc[i + 2], o_acc[i + 3]);
         }
         if (stats) {
-          const size_t srow = ((size_t)b * heads + h) * seq + qi;
+          const size_t srow = ((size_t)w.b * heads + w.h) * seq + qi;
           // natural-log LSE of the scaled scores
           stats[2 * srow + 1] = l > 0.f ? (m_st + log2f(l)) * 0.6931471805599453f : 3.0e38f;
         }
       }
+      g0 += (uint32_t)nblk;
     }
   }
 
@@ -881,11 +962,13 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
                                  AttnSmem::DYN_BYTES));
     configured = true;
   }
-  dim3 grid(ft_cdiv(seq, AT_Q), batch * heads);
+  // persistent: two CTAs per SM walk the (query tile, head) pairs
+  const int tiles = ft_cdiv(seq, AT_Q) * batch * heads;
+  const int grid = std::min(tiles, 2 * ctx->sm_count);
   const float scale_log2e = (1.0f / sqrtf((float)head_dim)) * 1.4426950408889634f;
   FT_LAUNCH_PDL(ctx, k_attn_fwd_tc, grid, AT_THREADS, AttnSmem::DYN_BYTES, q128, kv64, out16, ldo16,
-                out32, ldo32, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale_log2e,
-                ctx->status_dev);
+                out32, ldo32, stats, seq, heads, kv_heads, batch * heads, q_col0, k_col0, v_col0,
+                scale_log2e, ctx->status_dev);
   return FT_OK;
 }
 
