@@ -345,11 +345,9 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
           packed[c >> 1] = pack_h2(ex2(x0), ex2(x1));
           packed[16 + (c >> 1)] = pack_h2(ex2(y0), ex2(y1));
         }
-        // this P buffer was last read by P V of the block two before (possibly of the last tile)
-        if (g >= 2) {
-          ok = mbar_wait(bar_ofull + sb * 8, ((g - 2) >> 1) & 1, abort_flag, status, 23);
-          if (!ok) break;
-        }
+        // This P buffer was last read by P V of block g-2.  That product has finished: the issuer
+        // thread issued it before S(g), and the commit that completed sfull(g) above covers every
+        // tcgen05 operation the thread had issued before it.
         uint8_t* rp = rowp + sb * TILE_BYTES;
 #pragma unroll
         for (int q = 0; q < 8; ++q)

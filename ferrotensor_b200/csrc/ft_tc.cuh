@@ -16,6 +16,9 @@ constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 320; // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr uint32_t SPIN_LIMIT = 1u << 26;  // attempts
 constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // four seconds: no legitimate wait is near it
+// the same bound for the barrier waits, counted in SM cycles (reading the cycle counter costs a
+// few cycles, reading the global timer costs hundreds): 2 to 8 seconds over the clock range
+constexpr long long WAIT_LIMIT_CYCLES = 8000000000ll;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -59,16 +62,15 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: gives up after WAIT_LIMIT_NS (or SPIN_LIMIT attempts, whichever comes first).
-// Returns false (and raises the abort flag) when it gave up.
+// Bounded wait: gives up after WAIT_LIMIT_CYCLES (or SPIN_LIMIT attempts, whichever comes
+// first).  Returns false (and raises the abort flag) when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int where) {
-  if (mbar_try(bar, parity)) return true;
-  if (*abort_flag) return false;
-  const uint64_t t0 = global_ns();
+  if (mbar_test(bar, parity)) return true;   // the non-blocking form: a completed phase costs a few cycles
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try(bar, parity)) {
-    if (*abort_flag || ++spins > SPIN_LIMIT || global_ns() - t0 > WAIT_LIMIT_NS) {
+    if (*abort_flag || ++spins > SPIN_LIMIT || clock64() - t0 > WAIT_LIMIT_CYCLES) {
       if (!*abort_flag) {
         *abort_flag = 1;
         // the status word lives in pinned host memory: plain stores, first writer wins
