@@ -15,7 +15,12 @@
 // (Measured and not kept: eight softmax warps with a half-row maximum exchange; paired f16
 // exponentials; releasing S / dP to the next product before the arithmetic in the backward
 // kernels - per block the time goes to the hand-offs between the warps and the tensor pipe,
-// not to the arithmetic.)
+// not to the arithmetic; the backward kernels made persistent like the forward one - the dQ
+// kernel ran as before, the dK / dV kernel 20 % slower.  Cycle counts inside the forward kernel:
+// of about 2600 cycles per 64-key block, 1100 are the exponentials (two CTAs share the SM's
+// special-function unit), the rest are barrier operations of 100-200 cycles each, the
+// shared-memory hand-over of P, and per-tile work; one tcgen05.mma costs the issuing thread
+// about 55 cycles, a TMA load about 75.)
 // All waits are bounded (see ft_tc.cuh).
 #include <math.h>
 #include <stdlib.h>
@@ -73,6 +78,14 @@ struct AttnSmem {
 // the current tile has finished, and S of the next tile's first block is computed while the
 // softmax warps normalise and store the current tile; tensor memory, barriers and the ones
 // block are set up once per CTA instead of once per tile.
+// Tile t of a persistent CTA's round `it`: CTAs take the tiles of even rounds in index order and
+// of odd rounds in reverse, so a CTA that got the heaviest tile of one round (tiles are sorted
+// heavy first) gets the lightest of the next; the per-CTA totals then differ by a few percent
+// instead of the 12 % of plain round-robin.
+__device__ __forceinline__ int snake_tile(int it) {
+  const int c = (it & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+  return it * (int)gridDim.x + c;
+}
 struct FwdTile {
   int q0, nblk, b, h, kvh, tok0;
 };
@@ -165,7 +178,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
     if (++c.j < c.w.nblk) return;
     c.j = 0;
     ++c.it;
-    c.has = fwd_tile((int)blockIdx.x + c.it * (int)gridDim.x, total, nq, bh_count, heads, kv_heads, seq, c.w);
+    c.has = fwd_tile(snake_tile(c.it), total, nq, bh_count, heads, kv_heads, seq, c.w);
   };
 
   if (warp == 4) {
@@ -270,7 +283,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
     uint32_t g0 = 0;                           // blocks of the tiles before this one
     bool ok = true;
     FwdTile w;
-    for (int it = 0; ok && fwd_tile((int)blockIdx.x + it * (int)gridDim.x, total, nq, bh_count, heads,
+    for (int it = 0; ok && fwd_tile(snake_tile(it), total, nq, bh_count, heads,
                                     kv_heads, seq, w); ++it) {
       const int q0 = w.q0, nblk = w.nblk;
       const int qi = q0 + row;                 // position in the sequence
