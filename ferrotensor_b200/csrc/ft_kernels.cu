@@ -326,6 +326,25 @@ __global__ void k_rope_table(float2* __restrict__ table, int seq_len, int half, 
   table[idx] = make_float2(c, s);
 }
 
+// sigmoid with the fast exponential and reciprocal (about 2 ulp): the results are rounded to
+// f16, whose half ulp is 2^-12
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+// A flat index i = r * per_row + c walked with stride st without dividing in the loop:
+// (r, c) advance by (st / per_row, st % per_row) with a carry.
+struct RowWalk {
+  long long r;
+  int c, st_r, st_c, per_row;
+  __device__ __forceinline__ RowWalk(size_t i, size_t st, size_t per_row_)
+      : r((long long)(i / per_row_)), c((int)(i % per_row_)), st_r((int)(st / per_row_)),
+        st_c((int)(st % per_row_)), per_row((int)per_row_) {}
+  __device__ __forceinline__ void next() {
+    r += st_r;
+    c += st_c;
+    if (c >= per_row) { c -= per_row; ++r; }
+  }
+};
+
 // One thread per 8 elements of a q|k|v row with head_dim 64: in the q and k parts the thread
 // owns pairs (i..i+3, i+32..i+35) of one head, in the v part 8 consecutive values.
 // out = f16(scale * rotate(+-angle)(x)).
@@ -340,9 +359,20 @@ __global__ void k_rope_to_f16(const float* __restrict__ src, __half* __restrict_
   const long long total = tokens * per_tok;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long st = (long long)gridDim.x * blockDim.x;
+  // token, unit within the token and position in the sequence advance without dividing in the loop
+  RowWalk w((size_t)idx, (size_t)st, (size_t)per_tok);
+  int pos = (int)(w.r % seq_len);
+  const int st_pos = w.st_r % seq_len;
   for (; idx < total; idx += st) {
-    const long long t = idx / per_tok;
-    const int u = (int)(idx % per_tok);
+    const long long t = w.r;
+    const int u = w.c;
+    const int pos_now = pos;
+    {
+      const long long r_before = w.r;
+      w.next();
+      pos += st_pos + (int)(w.r - r_before - w.st_r);
+      if (pos >= seq_len) pos -= seq_len;
+    }
     const float* row = src + t * ld;
     __half* orow = dst + t * ld;
     const int rot_units = (nq + nkv) / 8;
@@ -350,7 +380,7 @@ __global__ void k_rope_to_f16(const float* __restrict__ src, __half* __restrict_
       const int head = u >> 3, i = (u & 7) * 4;      // 8 threads per 64-wide head
       const int c0 = head * 64 + i;
       const float4 lo = *(const float4*)(row + c0), hi = *(const float4*)(row + c0 + 32);
-      const float2* tb = table + (size_t)(t % seq_len) * 32 + i;
+      const float2* tb = table + (size_t)pos_now * 32 + i;
       const float a[4] = {lo.x, lo.y, lo.z, lo.w}, b[4] = {hi.x, hi.y, hi.z, hi.w};
       float o1[4], o2[4];
 #pragma unroll
@@ -423,26 +453,29 @@ __global__ void k_silu_gate16h(const __half* __restrict__ a, const __half* __res
                                int n, int* in_amax) {
   ft_pdl_wait();
   ft_pdl_launch();
-  size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
-  float am = 0.f;
-  for (; i < total; i += st) {
-    size_t r = i / per_row, c = (i % per_row) * 8;
-    const uint4 xa = *(const uint4*)(a + r * ldab + c), ya = *(const uint4*)(b + r * ldab + c);
+  const size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t st = (size_t)gridDim.x * blockDim.x;
+  RowWalk w(i, st, per_row);
+  __half2 am2 = __float2half2_rn(0.f);
+  for (; i < total; i += st, w.next()) {
+    const size_t c = (size_t)w.c * 8;
+    const uint4 xa = *(const uint4*)(a + w.r * ldab + c), ya = *(const uint4*)(b + w.r * ldab + c);
     const __half2* xh = (const __half2*)&xa;
     const __half2* yh = (const __half2*)&ya;
     uint32_t o[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 x = __half22float2(xh[k]), y = __half22float2(yh[k]);
-      const float v0 = x.x / (1.0f + expf(-x.x)) * y.x, v1 = x.y / (1.0f + expf(-x.y)) * y.y;
+      const float v0 = x.x * fast_sigmoid(x.x) * y.x, v1 = x.y * fast_sigmoid(x.y) * y.y;
       __half2 h = __floats2half2_rn(v0, v1);
       o[k] = *(uint32_t*)&h;
-      am = fmaxf(am, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(y.x), fabsf(y.y))));
+      am2 = __hmax2(am2, __hmax2(__habs2(xh[k]), __habs2(yh[k])));
     }
-    *(uint4*)(out + r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    *(uint4*)(out + w.r * ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
   }
-  amax_commit(am, in_amax);
+  const float2 amf = __half22float2(am2);
+  amax_commit(fmaxf(amf.x, amf.y), in_amax);
 }
 
 // SwiGLU backward from f16 gate | up rows straight to f16 tensor-core operands: out[r, c] =
@@ -471,10 +504,13 @@ __global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* _
       scales_out[2] = ldexpf(1.0f / S, -11);
     }
   }
-  size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
-  for (; i < total; i += st) {
-    size_t r = i / per_row, c = (i % per_row) * 8;
+  const size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t st = (size_t)gridDim.x * blockDim.x;
+  RowWalk w(i, st, per_row);
+  for (; i < total; i += st, w.next()) {
+    const long long r = w.r;
+    const size_t c = (size_t)w.c * 8;
     const uint4 xa = *(const uint4*)(a + r * ldab + c), ya = *(const uint4*)(b + r * ldab + c);
     const float4 g0 = *(const float4*)(g + r * ldg + c), g1 = *(const float4*)(g + r * ldg + c + 4);
     const __half2* xh = (const __half2*)&xa;
@@ -488,7 +524,7 @@ __global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* _
       float va[2], vb[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const float s = 1.0f / (1.0f + expf(-xs[e]));
+        const float s = fast_sigmoid(xs[e]);
         const float gk = gs[2 * k + e] * S;
         vb[e] = gk * (xs[e] * s);
         va[e] = gk * ys[e] * (s * (1.0f + xs[e] * (1.0f - s)));
