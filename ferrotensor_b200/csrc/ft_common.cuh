@@ -278,6 +278,21 @@ int ft_k_apply_fused(FtContext* ctx, float* w, float* g, float* m, float* v, siz
                      float grad_scale, float max_norm, const FtAdamParams* p, float* partials,
                      float* norm_out);
 
+// A flat index i = r * per_row + c walked with stride st without dividing in the loop:
+// (r, c) advance by (st / per_row, st % per_row) with a carry.
+struct RowWalk {
+  long long r;
+  int c, st_r, st_c, per_row;
+  __device__ __forceinline__ RowWalk(size_t i, size_t st, size_t per_row_)
+      : r((long long)(i / per_row_)), c((int)(i % per_row_)), st_r((int)(st / per_row_)),
+        st_c((int)(st % per_row_)), per_row((int)per_row_) {}
+  __device__ __forceinline__ void next() {
+    r += st_r;
+    c += st_c;
+    if (c >= per_row) { c -= per_row; ++r; }
+  }
+};
+
 // attention with token strides (elements between consecutive tokens)   (ft_attention.cu)
 struct FtAttnLaunch {
   const float *q, *k, *v;

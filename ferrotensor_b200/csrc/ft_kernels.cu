@@ -330,21 +330,6 @@ __global__ void k_rope_table(float2* __restrict__ table, int seq_len, int half, 
 // f16, whose half ulp is 2^-12
 __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
-// A flat index i = r * per_row + c walked with stride st without dividing in the loop:
-// (r, c) advance by (st / per_row, st % per_row) with a carry.
-struct RowWalk {
-  long long r;
-  int c, st_r, st_c, per_row;
-  __device__ __forceinline__ RowWalk(size_t i, size_t st, size_t per_row_)
-      : r((long long)(i / per_row_)), c((int)(i % per_row_)), st_r((int)(st / per_row_)),
-        st_c((int)(st % per_row_)), per_row((int)per_row_) {}
-  __device__ __forceinline__ void next() {
-    r += st_r;
-    c += st_c;
-    if (c >= per_row) { c -= per_row; ++r; }
-  }
-};
-
 // One thread per 8 elements of a q|k|v row with head_dim 64: in the q and k parts the thread
 // owns pairs (i..i+3, i+32..i+35) of one head, in the v part 8 consecutive values.
 // out = f16(scale * rotate(+-angle)(x)).
