@@ -65,6 +65,7 @@ extern "C" int ft_ctx_create(int device, void* stream, FtContext** out) {
   FT_CUDA(cudaHostGetDevicePointer((void**)&ctx->status_dev, ctx->status_host, 0));
   FT_CUDA(cudaMalloc((void**)&ctx->scale_buf, 8 * sizeof(float)));
   FT_CUDA(cudaMalloc((void**)&ctx->pre_flags, FT_PRE_FLAGS * sizeof(int)));
+  FT_CUDA(cudaMalloc((void**)&ctx->amax_ring, FT_AMAX_RING * sizeof(int)));
   {
     const float init[8] = {0.f, 1.0f / 2048.0f, 0.f, 0.f, 1.f, 1.f, 1.0f / 2048.0f, 0.f};
     FT_CUDA(cudaMemcpy(ctx->scale_buf, init, sizeof(init), cudaMemcpyHostToDevice));
@@ -77,6 +78,30 @@ extern "C" int ft_ctx_create(int device, void* stream, FtContext** out) {
   return FT_OK;
 }
 
+// Flags and amax slots must be zero when a launch starts to use them.  Instead of one memset in
+// front of every such launch (a stream operation that also keeps the launch from overlapping
+// with its predecessor), launches take consecutive stretches of a larger array that is zeroed as
+// a whole when it has been used up; by stream order every earlier user has finished by then.
+int ft_take_pre_flags(FtContext* ctx, int count, int** flags) {
+  FT_REQUIRE(count > 0 && count <= FT_PRE_FLAGS, "pre-tile flags: %d row blocks exceed %d", count,
+             FT_PRE_FLAGS);
+  if (ctx->pre_flag_pos + count > FT_PRE_FLAGS) {
+    FT_CUDA(cudaMemsetAsync(ctx->pre_flags, 0, FT_PRE_FLAGS * sizeof(int), ctx->stream));
+    ctx->pre_flag_pos = 0;
+  }
+  *flags = ctx->pre_flags + ctx->pre_flag_pos;
+  ctx->pre_flag_pos += count;
+  return FT_OK;
+}
+int ft_take_amax_slot(FtContext* ctx, int** slot) {
+  if (ctx->amax_pos >= FT_AMAX_RING) {
+    FT_CUDA(cudaMemsetAsync(ctx->amax_ring, 0, FT_AMAX_RING * sizeof(int), ctx->stream));
+    ctx->amax_pos = 0;
+  }
+  *slot = ctx->amax_ring + ctx->amax_pos++;
+  return FT_OK;
+}
+
 extern "C" int ft_ctx_destroy(FtContext* ctx) {
   if (!ctx) return FT_OK;
   cudaSetDevice(ctx->device);
@@ -84,6 +109,7 @@ extern "C" int ft_ctx_destroy(FtContext* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->scale_buf) cudaFree(ctx->scale_buf);
   if (ctx->pre_flags) cudaFree(ctx->pre_flags);
+  if (ctx->amax_ring) cudaFree(ctx->amax_ring);
   for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->own_stream) cudaStreamDestroy(ctx->stream);

@@ -34,7 +34,12 @@ struct FtContext {
   // of what they write into scale_buf[0] (atomicMax), and the next auto-scaled conversion
   // uses it instead of making its own pass over the tensor.
   bool pdl = true;   // programmatic dependent launch for the kernels that support it
-  int* pre_flags = nullptr;   // FT_PRE_FLAGS per-row-block flags of the adapter pre-tiles
+  int* pre_flags = nullptr;   // FT_PRE_FLAGS per-row-block flags of the adapter pre-tiles: each
+                              // launch takes the next unused stretch, the array is zeroed again
+                              // (one memset) when it has been used up
+  int pre_flag_pos = 1 << 30; // first unused flag; past the end = zero the array first
+  int* amax_ring = nullptr;   // FT_AMAX_RING slots for armed maxima, handed out and zeroed the same way
+  int amax_pos = 1 << 30;
   int* amax_out = nullptr;
   bool amax_ready = false;
   int tile_m_override = 0;   // FT_GEMM_TILE_M: 128 or 256 forces the GEMM tile height
@@ -82,6 +87,7 @@ void ft_prof_begin(FtContext* ctx, const char* name);
 void ft_prof_end(FtContext* ctx);
 
 constexpr int FT_PRE_FLAGS = 4096;
+constexpr int FT_AMAX_RING = 1024;
 
 // Launch on the context's stream, count the launch and surface launch errors.
 #define FT_LAUNCH(ctx, kernel, grid, block, smem, ...)                          \
@@ -294,6 +300,10 @@ struct RowWalk {
 };
 
 // attention with token strides (elements between consecutive tokens)   (ft_attention.cu)
+// the next `count` zeroed pre-tile flags / the next zeroed amax slot of the context's rings
+int ft_take_pre_flags(FtContext* ctx, int count, int** flags);
+int ft_take_amax_slot(FtContext* ctx, int** slot);
+
 struct FtAttnLaunch {
   const float *q, *k, *v;
   long long ldq, ldk, ldv;  // elements between tokens

@@ -1206,8 +1206,9 @@ int launch_tc2(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, con
 }  // namespace
 
 int ft_amax_arm(FtContext* ctx) {
-  FT_CUDA(cudaMemsetAsync(ctx->scale_buf, 0, 4, ctx->stream));
-  ctx->amax_out = (int*)ctx->scale_buf;
+  int* slot = nullptr;
+  FT_TRY(ft_take_amax_slot(ctx, &slot));
+  ctx->amax_out = slot;
   ctx->amax_ready = false;
   return FT_OK;
 }
@@ -1216,16 +1217,17 @@ int ft_amax_arm(FtContext* ctx) {
 int ft_scales_from_amax_or_pass(FtContext* ctx, const float* src, long long ld, int rows, int cols,
                                 int target_exp, const float** scales_out) {
   const bool ready = ctx->amax_ready && ctx->amax_out;
+  int* slot = ctx->amax_out;
   ctx->amax_out = nullptr;
   ctx->amax_ready = false;
   if (!ready) {
-    FT_CUDA(cudaMemsetAsync(ctx->scale_buf, 0, 4, ctx->stream));
+    FT_TRY(ft_take_amax_slot(ctx, &slot));
     long long n = (long long)rows * cols;
     int g = (int)std::max<long long>(1, std::min<long long>((n + 4095) / 4096,
                                                             (long long)ctx->sm_count * 8));
-    FT_LAUNCH(ctx, k_amax, g, 256, 0, src, ld, rows, cols, (int*)ctx->scale_buf);
+    FT_LAUNCH(ctx, k_amax, g, 256, 0, src, ld, rows, cols, slot);
   }
-  FT_LAUNCH_PDL(ctx, k_scale_from_amax, 1, 1, 0, (const int*)ctx->scale_buf, ctx->scale_buf + 4,
+  FT_LAUNCH_PDL(ctx, k_scale_from_amax, 1, 1, 0, (const int*)slot, ctx->scale_buf + 4,
             target_exp);
   *scales_out = ctx->scale_buf + 4;
   return FT_OK;
@@ -1240,7 +1242,7 @@ int ft_to_f16(FtContext* ctx, const float* src, long long ld, __half* hi, __half
   if (auto_scale) {
     if (ctx->amax_ready && ctx->amax_out) {
       // a producer already left the amax: the conversion derives the scale itself
-      amax_bits = (const int*)ctx->scale_buf;
+      amax_bits = ctx->amax_out;
       ctx->amax_out = nullptr;
       ctx->amax_ready = false;
       if (scales_out) *scales_out = ctx->scale_buf + 4;
@@ -1343,10 +1345,9 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
           (((uintptr_t)g.pre_c16) & 7) || tiles_m > FT_PRE_FLAGS)
         return FT_ERR_UNSUPPORTED;
       FT_TRY(make_map(ctx, &mb3, g.pre_b, dt, (uint64_t)g.K, 64, (uint64_t)g.pre_ldb, BK, 32));
-      FT_CUDA(cudaMemsetAsync(ctx->pre_flags, 0, (size_t)tiles_m * sizeof(int), ctx->stream));
+      FT_TRY(ft_take_pre_flags(ctx, tiles_m, &pre.flags));
       pre.tiles = tiles_m;
       pre.c16 = g.pre_c16; pre.ldc16 = g.pre_ldc16; pre.alpha = g.pre_alpha;
-      pre.flags = ctx->pre_flags;
       pre.idesc = make_idesc(256, 64, fmt, fmt);
       flops += 2.0 * g.M * 64.0 * (double)g.K;
     }
@@ -1388,11 +1389,9 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
         (((uintptr_t)g.pre_c16) & 7) || tiles_m > FT_PRE_FLAGS)
       return FT_ERR_UNSUPPORTED;
     FT_TRY(make_map(ctx, &mb3, g.pre_b, dt, (uint64_t)g.K, 64, (uint64_t)g.pre_ldb, BK, 64));
-    if (!ctx->pre_flags) FT_CUDA(cudaMalloc(&ctx->pre_flags, FT_PRE_FLAGS * sizeof(int)));
-    FT_CUDA(cudaMemsetAsync(ctx->pre_flags, 0, (size_t)tiles_m * sizeof(int), ctx->stream));
+    FT_TRY(ft_take_pre_flags(ctx, tiles_m, &pre.flags));
     pre.tiles = tiles_m;
     pre.c16 = g.pre_c16; pre.ldc16 = g.pre_ldc16; pre.alpha = g.pre_alpha;
-    pre.flags = ctx->pre_flags;
     pre.idesc = make_idesc(BM, 64, fmt, fmt);
     flops += 2.0 * g.M * 64.0 * (double)g.K;
   }
