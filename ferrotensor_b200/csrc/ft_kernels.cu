@@ -574,7 +574,10 @@ __global__ void k_silu_gate_bwd4(const float* __restrict__ a, long long lda,
 // ------------------------------------------------------------------- masked cross-entropy
 // One block per row.  Pass 1 keeps a running (max, sum) per thread; pass 2 writes the
 // gradient.  grad_scale folds the upstream gradient of the loss into the same pass.
-__global__ void __launch_bounds__(kRowThreads)
+// Long rows get 1024 threads: two such blocks per SM keep about 300 rows in flight, which for
+// a 49152-entry vocabulary (192 KiB a row) is 58 MB, so the second pass finds its row in L2.
+constexpr int kCeThreads = 1024;
+__global__ void __launch_bounds__(kCeThreads)
 k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
             const float* __restrict__ weights, float* grad, float* __restrict__ row_loss,
             int vocab, float grad_scale, int* amax_slot, __half* __restrict__ g16 = nullptr,
@@ -607,28 +610,25 @@ k_masked_ce(const float* logits, const uint32_t* __restrict__ targets,
   }
   // read before the gradient pass: in in-place use that pass overwrites the logits
   const float z_target = (threadIdx.x == 0 && tgt < (uint32_t)vocab) ? z[tgt] : 0.f;
-  float m = -3.4e38f;
+  float m = -3.4e38f, se = 0.f;
   if (vec) {
+    // one pass: every thread keeps a running maximum and the sum of exponentials against it
     const float4* z4 = (const float4*)z;
     for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
       float4 v = z4[i];
-      m = fmaxf(m, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+      const float m_new = fmaxf(m, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+      se = se * expf(m - m_new) + (expf(v.x - m_new) + expf(v.y - m_new) + expf(v.z - m_new) + expf(v.w - m_new));
+      m = m_new;
     }
+    const float m_all = block_max(m, red);
+    se = block_sum(se * expf(m - m_all), red);
+    m = m_all;
   } else {
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, z[i]);
-  }
-  m = block_max(m, red);
-  float se = 0.f;
-  if (vec) {
-    const float4* z4 = (const float4*)z;
-    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
-      float4 v = z4[i];
-      se += expf(v.x - m) + expf(v.y - m) + expf(v.z - m) + expf(v.w - m);
-    }
-  } else {
+    m = block_max(m, red);
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) se += expf(z[i] - m);
+    se = block_sum(se, red);
   }
-  se = block_sum(se, red);
   float log_z = m + logf(se);
   float inv = weights[row] * grad_scale;
   // |(softmax - onehot) * inv| <= |inv|: a tight bound serves as this row's amax
@@ -1002,7 +1002,7 @@ int ft_k_masked_ce(FtContext* ctx, const float* logits, const uint32_t* targets,
                    float grad_scale) {
   int* am = ctx->amax_out;
   if (am) ctx->amax_ready = true;
-  FT_LAUNCH(ctx, k_masked_ce, rows, kRowThreads, 0, logits, targets, weights, grad, row_loss,
+  FT_LAUNCH(ctx, k_masked_ce, rows, vocab >= 16384 ? kCeThreads : kRowThreads, 0, logits, targets, weights, grad, row_loss,
             vocab, grad_scale, am, (__half*)nullptr, 0ll, (const float*)nullptr);
   return FT_OK;
 }
@@ -1042,7 +1042,7 @@ int ft_k_masked_ce16(FtContext* ctx, const float* logits, const uint32_t* target
   ctx->amax_out = nullptr;
   ctx->amax_ready = false;
   FT_LAUNCH(ctx, k_ce_scale, 1, kRowThreads, 0, weights, targets, rows, grad_scale, ctx->scale_buf + 4);
-  FT_LAUNCH(ctx, k_masked_ce, rows, kRowThreads, 0, logits, targets, weights, (float*)nullptr, row_loss,
+  FT_LAUNCH(ctx, k_masked_ce, rows, vocab >= 16384 ? kCeThreads : kRowThreads, 0, logits, targets, weights, (float*)nullptr, row_loss,
             vocab, grad_scale, (int*)nullptr, g16, ld16, (const float*)(ctx->scale_buf + 4));
   *scales_out = ctx->scale_buf + 4;
   return FT_OK;
