@@ -34,7 +34,7 @@ using namespace ft_tc;
 constexpr int AT_Q = 128;        // queries per CTA
 constexpr int AT_KV = 128;       // keys per block
 constexpr int AT_D = 64;         // head_dim
-constexpr int AT_THREADS = 160;  // forward: warps 0..3 softmax, warp 4 issuer
+constexpr int AT_THREADS = 192;  // forward: warps 0..3 softmax, warp 4 MMA issuer, warp 5 loads
 constexpr int BW_THREADS = 288;  // backward: warps 0..7 arithmetic, warp 8 issuer
 constexpr int BW_ISSUER = 8;
 constexpr int TILE_BYTES = 128 * 64 * 2;  // one 128 x 64 f16 tile = 16 KiB
@@ -55,8 +55,8 @@ struct AttnSmem {
   static constexpr int ONES_OFF = V_OFF + KV_STAGES * HALF_TILE;    // 64 keys x 64: column 0 = 1
   static constexpr int P_OFF = ONES_OFF + HALF_TILE;                // 2 x (128 q x 64 keys), K-major
   static constexpr int BAR_OFF = P_OFF + 2 * TILE_BYTES;
-  // q_full, kv_full[3], s_full[2], s_free[2], p_full[2], o_full[2], o_read
-  static constexpr int NBAR = 13;
+  // q_full, kv_full[3], s_full[2], s_free[2], p_full[2], o_full[2], o_read, kv_free[3], q_free
+  static constexpr int NBAR = 17;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -120,7 +120,8 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
   uint8_t* gbase = smem_raw + (base - raw);
   const uint32_t bar0 = base + AttnSmem::BAR_OFF;
   const uint32_t bar_q = bar0, bar_kv = bar0 + 8, bar_sfull = bar0 + 32, bar_sfree = bar0 + 48,
-                 bar_pfull = bar0 + 64, bar_ofull = bar0 + 80, bar_oread = bar0 + 96;
+                 bar_pfull = bar0 + 64, bar_ofull = bar0 + 80, bar_oread = bar0 + 96,
+                 bar_kvfree = bar0 + 104, bar_qfree = bar0 + 128;
   uint32_t* tmem_slot = (uint32_t*)(gbase + AttnSmem::BAR_OFF + AttnSmem::NBAR * 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -139,6 +140,8 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
       mbar_init(bar_ofull + s * 8, 1);
     }
     mbar_init(bar_oread, 4);
+    for (int st = 0; st < 3; ++st) mbar_init(bar_kvfree + st * 8, 1);
+    mbar_init(bar_qfree, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -148,7 +151,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
                  "r"(TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  } else {
+  } else if (warp < 4) {
     // the ones block: same swizzled layout as a V tile (row = key, 128 bytes = 64 columns; the
     // 16-byte chunk c of row k sits at chunk c ^ (k & 7)): column 0 of every key row is 1, the
     // rest 0.  Thread t writes half a row.
@@ -181,38 +184,57 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
     c.has = fwd_tile(snake_tile(c.it), total, nq, bh_count, heads, kv_heads, seq, c.w);
   };
 
-  if (warp == 4) {
-    // ------------------------------------------------------------------ TMA + MMA issuer
+  if (warp == 5) {
+    // ------------------------------------------------------------------ TMA loads
+    // One thread keeps the K/V ring and the Q tile filled, so that the thread that issues the
+    // products never spends its time on load instructions (about 75 cycles each) or on waiting
+    // for a stage to come free.
+    if (lane == 0) {
+      const uint32_t sq = base + AttnSmem::Q_OFF, sk = base + AttnSmem::K_OFF, sv = base + AttnSmem::V_OFF;
+      uint32_t gl = 0;     // key/value blocks loaded since the CTA started
+      bool ok = true;
+      FwdTile w;
+      for (int it = 0; ok && fwd_tile(snake_tile(it), total, nq, bh_count, heads, kv_heads, seq, w); ++it) {
+        if (it >= 1) {
+          // the Q tile is free once the previous tile's last S product has finished
+          ok = mbar_wait(bar_qfree, (it - 1) & 1, abort_flag, status, 16);
+          if (!ok) break;
+        }
+        mbar_expect_tx(bar_q, TILE_BYTES);
+        tma_load_2d(sq, &map_q128, bar_q, q_col0 + w.h * AT_D, w.tok0 + w.q0);
+        for (int j = 0; j < w.nblk; ++j, ++gl) {
+          const uint32_t st = gl % 3;
+          if (gl >= 3) {
+            // stage st held block gl - 3: free once P V of that block has run (the stage's own
+            // barrier: its next completion needs this very load, so the phase cannot run ahead)
+            ok = mbar_wait(bar_kvfree + st * 8, (gl / 3 - 1) & 1, abort_flag, status, 17);
+            if (!ok) break;
+          }
+          mbar_expect_tx(bar_kv + st * 8, 2 * HALF_TILE);
+          tma_load_2d(sk + st * HALF_TILE, &map_kv64, bar_kv + st * 8, k_col0 + w.kvh * AT_D, w.tok0 + j * 64);
+          tma_load_2d(sv + st * HALF_TILE, &map_kv64, bar_kv + st * 8, v_col0 + w.kvh * AT_D, w.tok0 + j * 64);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t sq = base + AttnSmem::Q_OFF, sk = base + AttnSmem::K_OFF,
                      sv = base + AttnSmem::V_OFF, sp = base + AttnSmem::P_OFF;
       const uint32_t idesc_s = make_idesc(128, 64, 0, 0);                      // Q, K both K-major
       const uint32_t idesc_o = make_idesc(128, O_COLS, 0, 0) | (1u << 16);     // V is N-major
-      // three cursors over the same sequence of blocks: loads run two blocks ahead of P V,
-      // S one block ahead; gl, gs, gp count blocks since the CTA started
-      FwdCursor L, S, P;
-      start_cursor(L);
+      // two cursors over the same sequence of blocks: S runs one block ahead of P V; gs, gp
+      // count blocks since the CTA started
+      FwdCursor S, P;
       start_cursor(S);
       start_cursor(P);
-      uint32_t gl = 0, gs = 0, gp = 0;
+      uint32_t gs = 0, gp = 0;
       bool ok = true;
-      auto load_q = [&](const FwdCursor& c) {
-        mbar_expect_tx(bar_q, TILE_BYTES);
-        tma_load_2d(sq, &map_q128, bar_q, q_col0 + c.w.h * AT_D, c.w.tok0 + c.w.q0);
-      };
-      auto load_kv = [&]() {
-        const uint32_t st = gl % 3;
-        mbar_expect_tx(bar_kv + st * 8, 2 * HALF_TILE);
-        tma_load_2d(sk + st * HALF_TILE, &map_kv64, bar_kv + st * 8, k_col0 + L.w.kvh * AT_D,
-                    L.w.tok0 + L.j * 64);
-        tma_load_2d(sv + st * HALF_TILE, &map_kv64, bar_kv + st * 8, v_col0 + L.w.kvh * AT_D,
-                    L.w.tok0 + L.j * 64);
-        advance(L);
-        ++gl;
-      };
-      // S of block gs: its keys must have landed and its accumulator (last used by block gs-2)
-      // must have been read
+      // S of block gs: the tile's Q and the block's keys must have landed and its accumulator
+      // (last used by block gs-2) must have been read
       auto issue_s = [&]() -> bool {
+        if (S.j == 0 && !mbar_wait(bar_q, S.it & 1, abort_flag, status, 11)) return false;
         if (!mbar_wait(bar_kv + (gs % 3) * 8, (gs / 3) & 1, abort_flag, status, 13)) return false;
         if (gs >= 2 && !mbar_wait(bar_sfree + (gs & 1) * 8, ((gs - 2) >> 1) & 1, abort_flag, status, 14))
           return false;
@@ -223,32 +245,19 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
           tc_mma_f16(tmem_base + (gs & 1) * 64, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s,
                      k > 0 ? 1u : 0u);
         tc_commit(bar_sfull + (gs & 1) * 8);
+        if (S.j == S.w.nblk - 1) tc_commit(bar_qfree);   // the tile's last S product: Q may be replaced
         advance(S);
         ++gs;
         return true;
       };
-      if (P.has) {
-        load_q(S);
-        for (int i = 0; i < 3 && L.has; ++i) load_kv();
-        ok = mbar_wait(bar_q, 0, abort_flag, status, 11) && issue_s();
-      }
+      if (P.has) ok = issue_s();
       while (ok && P.has) {
-        // the next S product: at once when it belongs to the same tile; across a tile boundary
-        // the Q buffer is reloaded first, after the current tile's last S product has finished
+        // the next S product first when it belongs to the same tile; across a tile boundary the
+        // current tile's last P V goes first (the next Q tile is still on its way)
         const bool next_tile = S.has && S.j == 0;
         if (S.has && !next_tile) {
           ok = issue_s();
           if (!ok) break;
-        } else if (next_tile) {
-          ok = mbar_wait(bar_sfull + ((gs - 1) & 1) * 8, ((gs - 1) >> 1) & 1, abort_flag, status, 16);
-          if (!ok) break;
-          load_q(S);
-        }
-        if (gp >= 1 && L.has) {
-          // stage (gp + 2) % 3 held block gp - 1: free once P V(gp - 1) has run
-          ok = mbar_wait(bar_ofull + ((gp - 1) & 1) * 8, ((gp - 1) >> 1) & 1, abort_flag, status, 17);
-          if (!ok) break;
-          load_kv();
         }
         ok = mbar_wait(bar_pfull + (gp & 1) * 8, (gp >> 1) & 1, abort_flag, status, 15);
         if (ok && P.j == 0 && P.it >= 1)   // the previous tile's output must have left tensor memory
@@ -266,12 +275,11 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
             tc_mma_f16(tmem_o, dp + (uint64_t)(k * 2), dv + (uint64_t)(k * 128), idesc_o,
                        (P.j > 0 || k > 0) ? 1u : 0u);
           tc_commit(bar_ofull + (gp & 1) * 8);
+          tc_commit(bar_kvfree + (gp % 3) * 8);
         }
         advance(P);
         ++gp;
-        if (next_tile) {
-          ok = mbar_wait(bar_q, S.it & 1, abort_flag, status, 11) && issue_s();
-        }
+        if (next_tile) ok = issue_s();
       }
     }
     __syncwarp();
