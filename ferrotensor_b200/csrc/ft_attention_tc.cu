@@ -15,7 +15,8 @@
 // (Measured and not kept: eight softmax warps with a half-row maximum exchange; paired f16
 // exponentials; releasing S / dP to the next product before the arithmetic in the backward
 // kernels - per block the time goes to the hand-offs between the warps and the tensor pipe,
-// not to the arithmetic; the backward kernels made persistent like the forward one - the dQ
+// not to the arithmetic; a separate loader warp in the backward kernels (8 % slower, while the
+// same split made the forward kernel 10 % faster); the backward kernels made persistent like the forward one - the dQ
 // kernel ran as before, the dK / dV kernel 20 % slower.  Cycle counts inside the forward kernel:
 // of about 2600 cycles per 64-key block, 1100 are the exponentials (two CTAs share the SM's
 // special-function unit), the rest are barrier operations of 100-200 cycles each, the
