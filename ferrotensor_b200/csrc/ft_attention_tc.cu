@@ -13,7 +13,7 @@
 // One extra warp issues all TMA loads and MMAs; the S product of block j+1 is issued as soon
 // as the softmax warps have read block j, so it overlaps with their arithmetic and with P V.
 // (Measured and not kept: eight softmax warps with a half-row maximum exchange; paired f16
-// exponentials; releasing S / dP to the next product before the arithmetic in the backward
+// exponentials; a quarter of the exponentials as a polynomial on the FMA pipe; releasing S / dP to the next product before the arithmetic in the backward
 // kernels - per block the time goes to the hand-offs between the warps and the tensor pipe,
 // not to the arithmetic; a separate loader warp in the backward kernels (8 % slower, while the
 // same split made the forward kernel 10 % faster); the backward kernels made persistent like the forward one - the dQ
