@@ -1,0 +1,228 @@
+"""The headline workload at its full size on a B200: the SmolLM2-1.7B architecture (24 blocks,
+hidden 2048, 32 heads of 64, ffn 8192, vocabulary 49152, tied head, f16 frozen base) with
+rank-16 adapters on all seven linears.
+
+Against the CPU oracle the full architecture runs on one sequence of 256 positions, which the
+oracle finishes in seconds; at the benchmark's micro-batch (8 sequences of 1024 positions) the
+step is checked through properties that need no oracle: bit-identical repeats, the same
+gradient whether a batch runs as one micro-batch or two, rows without supervision that change
+nothing, and adapters with B = 0 whose A gradients are exactly zero."""
+
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import lora_step as ol
+
+pytestmark = pytest.mark.gpu
+
+ORACLE_POSITIONS = 256
+
+# Tolerances of the three GEMM modes against the f32 oracle, per gradient tensor and for the
+# logits:  |got - exp| <= atol_rel * max|exp| + rtol * |exp|  on every element, and a bound
+# on the relative L2 error of the tensor.  The f32 and split-f16 modes carry the reference's
+# own rule (1e-4 + 1e-3*|exp|, absolute part relative to the tensor's scale because the
+# gradients of a 24-block model are of order 1e-3 and below); the single-pass f16 mode rounds
+# every activation and activation gradient to 11 significant bits before each product.
+TOLERANCE = {          # atol_rel, rtol, relative L2
+    "F32":   (1e-4, 1e-3, 2e-4),
+    "F16X2": (1e-4, 1e-3, 2e-4),
+    "F16":   (5e-3, 2e-2, 8e-3),
+}
+# Measured on this workload: f32 relative L2 at most 1.3e-5, split f16 1.1e-4, single-pass f16
+# 5.4e-3 (the q and k adapters of the middle blocks, whose gradients pass through the softmax).
+
+
+class _Headline:
+    def __init__(self, ctx):
+        from ferrotensor_b200.config import WORKLOADS, init_adapters, init_weights
+        from ferrotensor_b200.model import LoraModel
+        self.ctx = ctx
+        self.w = copy.deepcopy(WORKLOADS["smollm2-1.7b"])
+        w = self.w
+        weights = init_weights(w.model, w.seed, device="cuda:0", f16_base=True)
+        adapters = init_adapters(w.model, w.lora, w.seed, device="cuda:0", b_std=0.02)
+        self.model = LoraModel(ctx, w.model, w.lora, weights, adapters, f16_base=True)
+        self.weights_cpu = {k: v.cpu() for k, v in weights.items()}
+        self.adapters_cpu = {k: v.cpu() for k, v in adapters.items()}
+        del weights, adapters
+        torch.cuda.empty_cache()
+        self._oracle = None
+
+    def device_rows(self, ids, tg, mk):
+        from ferrotensor_b200.trainer import batch_targets_weights
+        rt, rw, _ = batch_targets_weights(tg, mk, self.w.model.vocab)
+        dev = self.ctx.device
+        return (torch.from_numpy(np.ascontiguousarray(ids).view(np.int32).reshape(-1)).to(dev),
+                torch.from_numpy(rt.view(np.int32).reshape(-1)).to(dev),
+                torch.from_numpy(rw.reshape(-1)).to(dev))
+
+    def gradients(self, chunks, seq_len, seed):
+        """Gradient buffer and row losses after the given micro-batches (each ids, targets,
+        mask as [sequences, seq_len]), starting from zero."""
+        self.model.zero_grad()
+        losses = []
+        for ids, tg, mk in chunks:
+            d_ids, d_tg, d_w = self.device_rows(ids, tg, mk)
+            row_loss = torch.empty(ids.size, device=self.ctx.device, dtype=torch.float32)
+            self.model.forward_backward(d_ids, d_tg, d_w, ids.shape[0], seq_len, seed, row_loss)
+            losses.append(row_loss)
+        self.ctx.synchronize()
+        return self.model.grads.clone(), torch.cat(losses).cpu().numpy()
+
+    def oracle(self):
+        """Loss, logits and gradients of the oracle on the first sequence's first
+        ORACLE_POSITIONS positions (computed once for the three modes)."""
+        if self._oracle is None:
+            from ferrotensor_b200.config import head_weight, synthetic_batch
+            w, c = self.w, self.w.model
+            ids, tg, mk = synthetic_batch(w, 1)
+            ids, tg, mk = (a[:, :ORACLE_POSITIONS].copy() for a in (ids, tg, mk))
+            mk[:, ::7] = 0                      # a loss mask with holes
+            ocfg = ol.OracleConfig(vocab=c.vocab, hidden=c.hidden, layers=c.layers, heads=c.heads,
+                                   kv_heads=c.kv_heads, ffn=c.ffn, eps=c.eps, theta=c.theta,
+                                   head_dim=c.head_dim, tied=c.tied, qkv_bias=c.qkv_bias,
+                                   lora_rank=w.lora.rank, lora_alpha=w.lora.alpha,
+                                   lora_targets=tuple(w.lora.target_modules), f16_base=True)
+            p = dict(self.weights_cpu)
+            p.update(self.adapters_cpu)
+            p["lm_head.weight"] = head_weight(c, self.weights_cpu, True)
+            r = ol.forward_backward(ocfg, p, ids.astype(np.int64), tg.astype(np.int64), mk)
+            self._oracle = (ids, tg, mk, r)
+        return self._oracle
+
+
+@pytest.fixture(scope="module")
+def headline(cuda_ctx):
+    from ferrotensor_b200.engine import GemmMode
+    h = _Headline(cuda_ctx)
+    yield h
+    h.model.close()
+    cuda_ctx.set_gemm_mode(GemmMode.F32)
+
+
+def _errors(got, exp):
+    got = np.asarray(got, dtype=np.float64)
+    exp = np.asarray(exp, dtype=np.float64)
+    scale = np.abs(exp).max()
+    err = np.abs(got - exp)
+    denom = np.linalg.norm(exp)
+    rel = np.linalg.norm(got - exp) / denom if denom > 0 else float(np.linalg.norm(got))
+    return err, scale, rel
+
+
+@pytest.mark.parametrize("mode_name", ["F32", "F16X2", "F16"])
+def test_full_architecture_matches_the_oracle(headline, mode_name):
+    """Loss, logits and all 336 adapter gradients of the full 24-block model against the
+    oracle, in each GEMM mode, with the mode's stated tolerance."""
+    from ferrotensor_b200.engine import GemmMode
+    h = headline
+    h.ctx.set_gemm_mode(GemmMode[mode_name])
+    ids, tg, mk, r = h.oracle()
+    atol_rel, rtol, l2 = TOLERANCE[mode_name]
+    d_ids, d_tg, d_w = h.device_rows(ids, tg, mk)
+    row_loss = torch.empty(ids.size, device=h.ctx.device, dtype=torch.float32)
+    logits = torch.empty((ids.size, h.w.model.vocab), device=h.ctx.device, dtype=torch.float32)
+    h.model.zero_grad()
+    h.model.forward_backward(d_ids, d_tg, d_w, 1, ORACLE_POSITIONS, 1.0, row_loss, logits)
+    h.ctx.synchronize()
+    exp_loss, exp_tokens = r.per_sequence[0]
+    assert exp_tokens == int(mk.sum())
+    loss = float(row_loss.sum().item()) / exp_tokens      # rows carry the unweighted loss
+    print(f"\n  {mode_name}: loss {loss:.6f} (oracle {exp_loss:.6f})")
+    failures = []
+    if abs(loss - exp_loss) > atol_rel + rtol * abs(exp_loss):
+        failures.append(f"loss {loss} vs {exp_loss}")
+    worst_rel, worst_ratio = 0.0, 0.0
+    tensors = {"logits": (logits.cpu().numpy(), r.logits.numpy().reshape(ids.size, -1))}
+    for name, g in h.model.named_grads().items():
+        tensors[f"grad {name}"] = (g.cpu().numpy(), r.grads[name].numpy())
+    assert len(tensors) == 1 + 24 * 7 * 2
+    for what, (got, exp) in tensors.items():
+        err, scale, rel = _errors(got, exp)
+        tol = atol_rel * scale + rtol * np.abs(exp)
+        ratio = float((err / tol).max())
+        worst_rel, worst_ratio = max(worst_rel, rel), max(worst_ratio, ratio)
+        if ratio > 1.0 or rel > l2:
+            failures.append(f"{what}: worst error {ratio:.2f} x tolerance, relative L2 {rel:.2e}")
+    print(f"  {mode_name}: worst element {worst_ratio:.2f} x tolerance, worst relative L2 {worst_rel:.2e}")
+    assert not failures, f"{len(failures)} of {len(tensors) + 1}: " + "; ".join(failures[:8])
+
+
+def test_micro_batch_of_the_benchmark_repeats_bit_for_bit(headline):
+    """8 sequences of 1024 positions (the benchmark's micro-batch), twice: the gradient
+    buffer and the row losses are identical bit for bit (no atomics, no order that varies)."""
+    from ferrotensor_b200.config import synthetic_batch
+    from ferrotensor_b200.engine import GemmMode
+    h = headline
+    h.ctx.set_gemm_mode(GemmMode.F16)
+    ids, tg, mk = synthetic_batch(h.w, 8)
+    g0, l0 = h.gradients([(ids, tg, mk)], h.w.seq_len, 1.0 / 8)
+    g1, l1 = h.gradients([(ids, tg, mk)], h.w.seq_len, 1.0 / 8)
+    assert torch.isfinite(g0).all() and float(g0.abs().max()) > 0.0
+    assert torch.equal(g0.view(torch.int32), g1.view(torch.int32))
+    assert np.array_equal(l0.view(np.uint32), l1.view(np.uint32))
+    # the mean loss of a randomly initialised model over a Zipf stream stays near ln(vocab)
+    mean = float(l0.sum()) / l0.size
+    assert 0.5 * np.log(h.w.model.vocab) < mean < 1.5 * np.log(h.w.model.vocab)
+
+
+def test_one_micro_batch_or_two_give_the_same_gradient(headline):
+    """Linearity of accumulation at full size: 8 sequences as one micro-batch against 4 + 4.
+    The per-tensor f16 scales follow each micro-batch's own maxima, so the two differ by
+    operand rounding only; row losses agree to 2e-3 relative."""
+    from ferrotensor_b200.config import synthetic_batch
+    from ferrotensor_b200.engine import GemmMode
+    h = headline
+    h.ctx.set_gemm_mode(GemmMode.F16)
+    ids, tg, mk = synthetic_batch(h.w, 8)
+    whole, lw = h.gradients([(ids, tg, mk)], h.w.seq_len, 1.0 / 8)
+    halves, lh = h.gradients([(ids[:4], tg[:4], mk[:4]), (ids[4:], tg[4:], mk[4:])], h.w.seq_len, 1.0 / 8)
+    assert np.allclose(lw, lh, rtol=2e-3, atol=1e-6)
+    err, scale, rel = _errors(halves.cpu().numpy(), whole.cpu().numpy())
+    print(f"\n  one micro-batch against two: relative L2 {rel:.2e}, worst {err.max():.2e} of {scale:.2e}")
+    assert rel < 4e-3
+
+
+def test_rows_without_supervision_change_nothing(headline):
+    """Sequences whose loss mask is all zero contribute no loss and no gradient: a batch of
+    4 supervised and 4 unsupervised sequences gives, row for row, the losses of the 4 alone
+    and a gradient within operand rounding of theirs."""
+    from ferrotensor_b200.config import synthetic_batch
+    from ferrotensor_b200.engine import GemmMode
+    h = headline
+    h.ctx.set_gemm_mode(GemmMode.F16)
+    ids, tg, mk = synthetic_batch(h.w, 8)
+    mk = mk.copy()
+    mk[4:] = 0
+    both, lb = h.gradients([(ids, tg, mk)], h.w.seq_len, 0.25)
+    alone, la = h.gradients([(ids[:4], tg[:4], mk[:4])], h.w.seq_len, 0.25)
+    s = h.w.seq_len
+    assert not lb[4 * s:].any()
+    assert np.allclose(lb[:4 * s], la, rtol=2e-3, atol=1e-6)
+    err, scale, rel = _errors(both.cpu().numpy(), alone.cpu().numpy())
+    print(f"\n  with unsupervised rows against without: relative L2 {rel:.2e}")
+    assert rel < 4e-3
+
+
+def test_zero_b_adapters_leave_a_without_gradient(headline):
+    """The reference's initial state, B = 0: the adapter adds nothing, every A gradient is
+    exactly zero (dA = X^T (dY B^T) s) and every B gradient is not."""
+    from ferrotensor_b200.config import init_adapters, synthetic_batch
+    from ferrotensor_b200.engine import GemmMode
+    h = headline
+    h.ctx.set_gemm_mode(GemmMode.F16)
+    zero_b = init_adapters(h.w.model, h.w.lora, h.w.seed, device="cuda:0", b_std=0.0)
+    h.model.load_adapters(zero_b)
+    try:
+        ids, tg, mk = synthetic_batch(h.w, 2)
+        h.gradients([(ids, tg, mk)], h.w.seq_len, 0.5)
+        for name, g in h.model.named_grads().items():
+            if name.endswith("lora_a"):
+                assert not g.any(), name
+            else:
+                assert torch.isfinite(g).all() and float(g.abs().max()) > 0.0, name
+    finally:
+        h.model.load_adapters({k: v.to("cuda:0") for k, v in h.adapters_cpu.items()})
