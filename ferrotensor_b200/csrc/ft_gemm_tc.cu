@@ -1522,8 +1522,19 @@ int ft_gemm_tc_f32a(FtContext* ctx, const float* a, long long lda_f32, __half* s
   // without auto scale: alpha 1 for the high half, 2^-11 (a constant in scale_buf) for the low
   const float* alpha_hi = scales ? scales + 1 : nullptr;
   const float* alpha_lo = scales ? scales + 2 : ctx->scale_buf + 1;
-  int r = ft_gemm_tc(ctx, stage_hi, kp, b_f16, FT_F16, ldb, c, ldc, M, N, K, accumulate, alpha_hi);
-  if (r == FT_OK && split)
-    r = ft_gemm_tc(ctx, stage_lo, kp, b_f16, FT_F16, ldb, c, ldc, M, N, K, true, alpha_lo);
-  return r;
+  if (!split)
+    return ft_gemm_tc(ctx, stage_hi, kp, b_f16, FT_F16, ldb, c, ldc, M, N, K, accumulate, alpha_hi);
+  // The tensor core adds each 16-deep group of products into its f32 accumulator with the
+  // low bits cut off, not rounded: a sum over K shrinks by about K/16 * 2^-25 of its size
+  // (measured 2.3e-4 at K = 151936, the head's input gradient; 1.1e-4 at K = 49152).  The split
+  // mode promises f32 accuracy, so a long K runs in slices that the f32 epilogue adds up.
+  const int kSlice = 2048;
+  const __half* b = (const __half*)b_f16;
+  for (int k0 = 0; k0 < std::max(K, 1); k0 += kSlice) {
+    const int kc = std::min(kSlice, K - k0);
+    FT_TRY(ft_gemm_tc(ctx, stage_hi + k0, kp, b + k0, FT_F16, ldb, c, ldc, M, N, kc,
+                      accumulate || k0 > 0, alpha_hi));
+    FT_TRY(ft_gemm_tc(ctx, stage_lo + k0, kp, b + k0, FT_F16, ldb, c, ldc, M, N, kc, true, alpha_lo));
+  }
+  return FT_OK;
 }
