@@ -266,7 +266,10 @@ def test_shape_errors_raise_instead_of_launching(cuda_ctx, eng):
 # probabilities to f16 before P.V; accumulation and softmax are f32.  Stated tolerance against
 # the f64 oracle: 2e-3 absolute + 1e-2 relative on outputs of O(1) inputs.
 @pytest.mark.parametrize("b,s,h,hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 1024, 3, 3),
-                                       (2, 200, 2, 1), (1, 77, 2, 2), (1, 640, 14, 2)])
+                                       (2, 200, 2, 1), (1, 77, 2, 2), (1, 640, 14, 2),
+                                       # more tiles than resident blocks (each walks several),
+                                       # and Qwen2's 7:1 head sharing at 4096 positions
+                                       (4, 1024, 12, 4), (1, 4096, 7, 1)])
 def test_attention_forward_on_tensor_cores(cuda_ctx, eng, b, s, h, hkv):
     from ferrotensor_b200.engine import AttentionOptions, GemmMode, UnifiedTensor
     d = 64
@@ -292,7 +295,10 @@ def test_attention_forward_on_tensor_cores(cuda_ctx, eng, b, s, h, hkv):
 # scale), P and dS rounded to f16 before the second products, f32 accumulation.  Stated
 # tolerance against the f64 oracle: 2e-3 of the tensor's largest magnitude + 1e-2 relative.
 @pytest.mark.parametrize("b,s,h,hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 1024, 3, 3),
-                                       (2, 200, 2, 1), (1, 77, 2, 2), (1, 640, 14, 2)])
+                                       (2, 200, 2, 1), (1, 77, 2, 2), (1, 640, 14, 2),
+                                       # more tiles than resident blocks (each walks several),
+                                       # and Qwen2's 7:1 head sharing at 4096 positions
+                                       (4, 1024, 12, 4), (1, 4096, 7, 1)])
 def test_attention_backward_on_tensor_cores(cuda_ctx, eng, b, s, h, hkv):
     from ferrotensor_b200.engine import AttentionOptions, GemmMode, UnifiedTensor
     d = 64
