@@ -5,6 +5,7 @@
     python -m ferrotensor_b200.microbench matvec --k 2048 --n 8192
     python -m ferrotensor_b200.microbench decode --batch 8 --seq 4096
     python -m ferrotensor_b200.microbench sustained --seconds 4       # GEMM under the power cap, beside cuBLAS
+    python -m ferrotensor_b200.microbench step --layers 2             # one micro-batch of a cut-down benchmark model
 
 Each case holds a few hundred MB on the device at most, which makes it the right target for a
 profiler capture of one kernel (the training step keeps tens of GB resident).  Times come from
@@ -150,6 +151,48 @@ def _sample_clocks(stop, acc, device):
         time.sleep(0.2)
 
 
+def step(args):
+    """One micro-batch (forward, loss, backward) and the optimizer update of a benchmark
+    workload's architecture cut to `--layers` blocks: every kernel of the training step at the
+    shapes of the full model, with a few GB on the device instead of tens."""
+    import copy
+    from .config import WORKLOADS, init_adapters, init_weights, synthetic_batch
+    from .model import LoraModel
+    from .trainer import AdamW, batch_targets_weights
+    ctx = CudaContext(0)
+    ctx.set_gemm_mode(GemmMode.F16)
+    w = copy.deepcopy(WORKLOADS[args.workload])
+    w.model.layers = args.layers
+    weights = init_weights(w.model, w.seed, device="cuda:0", f16_base=True)
+    adapters = init_adapters(w.model, w.lora, w.seed, device="cuda:0", b_std=w.adapter_b_std)
+    model = LoraModel(ctx, w.model, w.lora, weights, adapters, f16_base=True,
+                      checkpoint_blocks=w.checkpoint_blocks)
+    del weights, adapters
+    torch.cuda.empty_cache()
+    ids, tg, mk = synthetic_batch(w, args.batch)
+    rt, rw, _ = batch_targets_weights(tg, mk, w.model.vocab)
+    d_ids = torch.from_numpy(np.ascontiguousarray(ids).view(np.int32).reshape(-1)).cuda()
+    d_tg = torch.from_numpy(rt.view(np.int32).reshape(-1)).cuda()
+    d_w = torch.from_numpy(rw.reshape(-1)).cuda()
+    row_loss = torch.empty(ids.size, device="cuda", dtype=torch.float32)
+    opt = AdamW(w.lr, weight_decay=w.weight_decay)
+
+    def once():
+        model.zero_grad()
+        model.forward_backward(d_ids, d_tg, d_w, args.batch, w.seq_len, 1.0 / args.batch, row_loss)
+        opt.t += 1.0
+        model.apply_gradients(1.0, w.clip, opt.params())
+    for _ in range(args.warmup):
+        once()
+    ctx.profile(2)
+    for _ in range(args.iters):
+        once()
+    ctx.synchronize()
+    _report(ctx, "step", {"workload": w.name, "layers": args.layers, "sequences": args.batch,
+                          "seq_len": w.seq_len, "loss": float(row_loss.sum().item()) / ids.size})
+    model.close()
+
+
 def sustained(args):
     """Each product back to back for `--seconds`, long enough for the power cap to settle the clock:
     this library's tensor-core GEMM (f32 activations rounded to f16 by its conversion kernel, f32
@@ -239,11 +282,16 @@ def main():
     su = sub.add_parser("sustained")
     su.add_argument("--seconds", type=float, default=4.0)
     su.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=None)
-    for p in (g, a, mv, dc):
+    st = sub.add_parser("step")
+    st.add_argument("--workload", default="smollm2-1.7b")
+    st.add_argument("--layers", type=int, default=2)
+    st.add_argument("--batch", type=int, default=8)
+    for p in (g, a, mv, dc, st):
         p.add_argument("--iters", type=int, default=5)
         p.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args()
-    {"gemm": gemm, "attention": attention, "matvec": matvec, "decode": decode, "sustained": sustained}[args.case](args)
+    {"gemm": gemm, "attention": attention, "matvec": matvec, "decode": decode, "sustained": sustained,
+     "step": step}[args.case](args)
 
 
 if __name__ == "__main__":
