@@ -1009,7 +1009,7 @@ int ft_k_masked_ce(FtContext* ctx, const float* logits, const uint32_t* targets,
 
 // {S, 1/S, 2^-11/S} with S the power of two that brings max_r |weights[r] * grad_scale| - a bound
 // on every element of the loss gradient, since |softmax - onehot| <= 1 - into [2^7, 2^8)
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(1024)
 k_ce_scale(const float* __restrict__ weights, const uint32_t* __restrict__ targets, int rows,
            float grad_scale, float* __restrict__ scales) {
   ft_pdl_wait();
@@ -1041,7 +1041,7 @@ int ft_k_masked_ce16(FtContext* ctx, const float* logits, const uint32_t* target
              "masked_ce16: vocabulary and pitch must be multiples of 4");
   ctx->amax_out = nullptr;
   ctx->amax_ready = false;
-  FT_LAUNCH(ctx, k_ce_scale, 1, kRowThreads, 0, weights, targets, rows, grad_scale, ctx->scale_buf + 4);
+  FT_LAUNCH(ctx, k_ce_scale, 1, 1024, 0, weights, targets, rows, grad_scale, ctx->scale_buf + 4);
   FT_LAUNCH(ctx, k_masked_ce, rows, vocab >= 16384 ? kCeThreads : kRowThreads, 0, logits, targets, weights, (float*)nullptr, row_loss,
             vocab, grad_scale, (int*)nullptr, g16, ld16, (const float*)(ctx->scale_buf + 4));
   *scales_out = ctx->scale_buf + 4;

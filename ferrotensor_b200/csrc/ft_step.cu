@@ -111,6 +111,9 @@ struct FtLoraModel {
   bool plan_fused = false;         // the planned workspace is the fused tensor-core layout
   __half *hN16 = nullptr, *xa16_head = nullptr, *g16 = nullptr;
   bool packs_dirty = true;         // adapter operand forms must be rebuilt before use
+  void* pack_jobs = nullptr;       // device table of the groups' packing jobs (k_pack_adapters)
+  int n_pack_jobs = 0;
+  size_t pack_most = 0;            // elements of the largest operand form
   bool tc_attention = false;       // head_dim 64: attention and RoPE take the tensor-core route
   uint64_t dropout_step_seed = 0;  // seed of the coming forward pass (ft_model_set_dropout_seed)
   bool dropout_on = false;         // training pass of a model with attention dropout
@@ -431,11 +434,18 @@ struct PackMeta {
   unsigned long long a_off[3], b_off[3];
 };
 
-// Writes the four f16 operand forms of a group's adapters (blockIdx.y selects the form).
-__global__ void k_pack_adapters(const float* __restrict__ params, PackMeta g,
-                                __half* __restrict__ a_catT16, __half* __restrict__ b_bdT16,
-                                __half* __restrict__ b_bd16, __half* __restrict__ a_cat16) {
+struct PackJob {
+  PackMeta g;
+  __half* out[4];  // a_catT16, b_bdT16, b_bd16, a_cat16
+};
+
+// Writes the four f16 operand forms of every group's adapters in one launch: blockIdx.z selects
+// the group, blockIdx.y the form.
+__global__ void k_pack_adapters(const float* __restrict__ params, const PackJob* __restrict__ jobs) {
+  const PackJob& job = jobs[blockIdx.z];
+  const PackMeta& g = job.g;
   const int which = blockIdx.y;
+  __half* __restrict__ dst = job.out[which];
   const size_t total = (size_t)RP * (which == 0 || which == 3 ? g.in : g.n);
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += st) {
@@ -453,39 +463,52 @@ __global__ void k_pack_adapters(const float* __restrict__ params, PackMeta g,
             rr >= g.r_off[j] && rr < g.r_off[j] + g.r)
           v = params[g.b_off[j] + (size_t)(rr - g.r_off[j]) * g.out[j] + (other - g.col_off[j])];
     }
-    __half h = __float2half_rn(v);
-    if (which == 0) a_catT16[i] = h;
-    else if (which == 1) b_bdT16[i] = h;
-    else if (which == 2) b_bd16[i] = h;
-    else a_cat16[i] = h;
+    dst[i] = __float2half_rn(v);
   }
 }
 
-int pack_group(FtLoraModel* m, const Group& g) {
-  if (!g.tc_lora) return FT_OK;
-  PackMeta pm;
-  memset(&pm, 0, sizeof(pm));
+void pack_job_of(const FtLoraModel* m, const Group& g, PackJob* job) {
+  memset(job, 0, sizeof(*job));
+  PackMeta& pm = job->g;
   pm.nlin = g.nlin; pm.in = g.in; pm.n = g.n; pm.r = m->cfg.lora_rank;
   for (int j = 0; j < g.nlin; ++j) {
     pm.col_off[j] = g.col_off[j]; pm.out[j] = g.lin[j]->out; pm.r_off[j] = g.r_off[j];
     pm.lora[j] = g.lin[j]->lora ? 1 : 0;
     pm.a_off[j] = g.lin[j]->a_off; pm.b_off[j] = g.lin[j]->b_off;
   }
-  size_t most = (size_t)RP * std::max(g.in, g.n);
-  dim3 grid((unsigned)std::min<size_t>((most + 255) / 256, 1024), 4);
-  FT_LAUNCH(m->ctx, k_pack_adapters, grid, 256, 0, m->params, pm, g.a_catT16, g.b_bdT16, g.b_bd16,
-            g.a_cat16);
+  job->out[0] = g.a_catT16; job->out[1] = g.b_bdT16; job->out[2] = g.b_bd16; job->out[3] = g.a_cat16;
+}
+
+// The job table of all groups that keep f16 adapter forms, on the device (after prepare_group).
+int build_pack_jobs(FtLoraModel* m) {
+  std::vector<PackJob> jobs;
+  size_t most = 0;
+  auto add = [&](const Group& g) {
+    if (!g.tc_lora) return;
+    jobs.emplace_back();
+    pack_job_of(m, g, &jobs.back());
+    most = std::max(most, (size_t)RP * std::max(g.in, g.n));
+  };
+  for (auto& ly : m->layers) { add(ly.qkv); add(ly.o); add(ly.gu); add(ly.down); }
+  add(m->head);
+  m->pack_jobs = nullptr;
+  m->n_pack_jobs = (int)jobs.size();
+  m->pack_most = most;
+  if (jobs.empty()) return FT_OK;
+  FT_REQUIRE(jobs.size() <= 65535, "prepare: too many adapter groups");
+  void* p = nullptr;
+  FT_CUDA(cudaMalloc(&p, jobs.size() * sizeof(PackJob)));
+  m->owned.push_back(p);
+  FT_CUDA(cudaMemcpy(p, jobs.data(), jobs.size() * sizeof(PackJob), cudaMemcpyHostToDevice));
+  m->pack_jobs = p;
   return FT_OK;
 }
 
 int pack_all(FtLoraModel* m) {
-  for (auto& ly : m->layers) {
-    FT_TRY(pack_group(m, ly.qkv));
-    FT_TRY(pack_group(m, ly.o));
-    FT_TRY(pack_group(m, ly.gu));
-    FT_TRY(pack_group(m, ly.down));
+  if (m->n_pack_jobs > 0) {
+    dim3 grid((unsigned)std::min<size_t>((m->pack_most + 255) / 256, 256), 4, (unsigned)m->n_pack_jobs);
+    FT_LAUNCH(m->ctx, k_pack_adapters, grid, 256, 0, m->params, (const PackJob*)m->pack_jobs);
   }
-  FT_TRY(pack_group(m, m->head));
   m->packs_dirty = false;
   return FT_OK;
 }
@@ -908,6 +931,7 @@ extern "C" int ft_model_prepare(FtLoraModel* m) {
     FT_TRY(prepare_group(m, ly.down));
   }
   FT_TRY(prepare_group(m, m->head));
+  FT_TRY(build_pack_jobs(m));
   if (!m->apply_scratch) {
     size_t chunks = (m->trainable + FT_SUM_SQUARES_CHUNK - 1) / FT_SUM_SQUARES_CHUNK;
     FT_CUDA(cudaMalloc((void**)&m->apply_scratch, (chunks + 8) * sizeof(float)));
