@@ -52,6 +52,34 @@ def parse_args():
     return ap.parse_args()
 
 
+PARITY_RULES = {
+    "f16": "|err| <= 5e-3*max|e| + 2e-2*|e| and relative L2 <= 8e-3 per tensor against the f32 CPU "
+           "oracle (f16 tensor-core operands, f32 accumulation)",
+    "f16x2": "1e-4 + 1e-3*|e| against the f32 CPU oracle (the reference's own rule; operands "
+             "split into two f16 halves)",
+    "f32": "1e-4 + 1e-3*|e| against the f32 CPU oracle (the reference's own rule; f32 FMA)",
+}
+
+
+def workload_config(w, world, micro_batch, mode, reduced):
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": w.name, "global_batch": w.global_batch, "seq_len": w.seq_len,
+            "micro_batch_sequences": micro_batch, "parallelism": f"dp{world}",
+            "lora_rank": w.lora.rank, "checkpoint_blocks": w.checkpoint_blocks,
+            "reduced_case": reduced,
+            "l2": "inputs larger than L2 (weights and activations of one step exceed 126 MB)",
+            "gemm_operands": "f16 activations x f16 weights, f32 accumulate" if mode != "f32" else "f32",
+            "parity_rule": PARITY_RULES[mode]}
+
+
+def resolve_mode(args, w):
+    return args.mode if w.f16_base else "f32"
+
+
+def local_micro_batch(args, w, world):
+    return max(1, min(args.micro_batch, w.global_batch // world))
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -121,10 +149,13 @@ class ClockSampler:
 # the reference's CPU restatement, timed on the host cores
 # ---------------------------------------------------------------------------------------
 
-def cpu_step_tokens_per_s(workload, weights_cpu, adapters_cpu, sample_tokens, repeats=1, warmup=0):
+def cpu_step_tokens_per_s(workload, weights_cpu, adapters_cpu, sample_tokens, repeats=1, warmup=0,
+                          budget_s=150.0):
     """One sequence of `sample_tokens` positions of the workload through the CPU oracle
-    (forward, loss, autograd backward, clip, AdamW), all host threads.  Returns
-    (tokens/s, cores, seconds per step)."""
+    (forward, loss, autograd backward, clip, AdamW), all host threads.  At most `repeats`
+    timed steps; after three, no further step starts once `budget_s` seconds of timed work
+    have passed (a slow host must still finish within minutes).  Returns
+    (tokens/s, cores, median seconds per step, steps timed)."""
     import numpy as np
     import torch
     from ferrotensor_b200.config import head_weight, synthetic_batch
@@ -155,17 +186,19 @@ def cpu_step_tokens_per_s(workload, weights_cpu, adapters_cpu, sample_tokens, re
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
+            if len(times) >= 3 and sum(times) > budget_s:
+                break
+    n_timed = len(times)
     times.sort()
     sec = times[len(times) // 2]
-    return sample_tokens / sec, cores, sec
+    return sample_tokens / sec, cores, sec, n_timed
 
 
 def default_cpu_sample(workload):
-    cores = os.cpu_count() or 1
-    big = workload.model.base_parameters() > 1_000_000_000
-    if cores >= 32:
-        return min(workload.seq_len, 1024 if not big else 512)
-    return min(workload.seq_len, 256 if big else 512)
+    """Positions of the one sequence the CPU leg steps through: the whole sequence, capped at
+    1024 positions (a 4096-position sequence of the oracle keeps every layer's [heads, S, S]
+    score matrix for its backward pass, tens of GB).  The same on every box."""
+    return min(workload.seq_len, 1024)
 
 
 def run_reference(args):
@@ -176,23 +209,30 @@ def run_reference(args):
         return
     import torch
     from ferrotensor_b200.config import WORKLOADS, init_adapters, init_weights
-    w = WORKLOADS[args.workload]
+    import copy
+    w = copy.deepcopy(WORKLOADS[args.workload])
+    reduced = bool(args.global_batch) and args.global_batch != w.global_batch
+    if args.global_batch:
+        w.global_batch = args.global_batch
+    world = max(1, args.gpus)
     sample = args.cpu_sample_tokens or default_cpu_sample(w)
     weights = init_weights(w.model, w.seed, device="cpu", f16_base=w.f16_base)
     adapters = init_adapters(w.model, w.lora, w.seed, device="cpu", b_std=w.adapter_b_std)
-    tps, cores, sec = cpu_step_tokens_per_s(w, weights, adapters, sample, repeats=args.steps,
-                                            warmup=min(args.warmup, 1))
-    desc = (f"one sequence of {sample} of {w.seq_len} positions per step, median of {args.steps} "
-            f"steps; tokens/s of the sample (a full {w.global_batch}x{w.seq_len} step is "
-            f"extrapolated linearly)")
+    tps, cores, sec, n_timed = cpu_step_tokens_per_s(w, weights, adapters, sample, repeats=args.steps,
+                                                     warmup=1)
+    desc = (f"one sequence of {sample} of {w.seq_len} positions per step, median of {n_timed} "
+            f"steps after one warm-up step (no further step starts after 150 s of timed work); "
+            f"tokens/s of the sample (a full {w.global_batch}x{w.seq_len} step is that many "
+            f"sequences, extrapolated linearly)")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": w.name, "global_batch": w.global_batch, "seq_len": w.seq_len,
-                   "parallelism": "cpu"},
-        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "config": workload_config(w, world, local_micro_batch(args, w, world), resolve_mode(args, w),
+                                  reduced),
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc,
+                         "steps_timed": n_timed},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -206,8 +246,9 @@ def run_cuda(args):
     import torch
     import torch.distributed as dist
 
-    from ferrotensor_b200.config import (WORKLOADS, init_adapters, init_weights, step_flops,
-                                         synthetic_batch)
+    from ferrotensor_b200.config import (WORKLOADS, gemm_flops, init_adapters, init_weights,
+                                         step_flops, synthetic_batch)
+    from ferrotensor_b200.distributed import Communicator
     from ferrotensor_b200.engine import CudaContext, GemmMode
     from ferrotensor_b200.model import LoraModel
     from ferrotensor_b200.trainer import AdamW, Trainer, batch_targets_weights, shard_indices
@@ -229,10 +270,12 @@ def run_cuda(args):
         w.global_batch = args.global_batch
     assert w.global_batch % world == 0, "global batch must divide over the ranks"
     ctx = CudaContext(local)
-    mode = {"f16": GemmMode.F16, "f16x2": GemmMode.F16X2, "f32": GemmMode.F32}[args.mode]
-    if not w.f16_base:
-        mode = GemmMode.F32
+    mode_name = resolve_mode(args, w)
+    mode = {"f16": GemmMode.F16, "f16x2": GemmMode.F16X2, "f32": GemmMode.F32}[mode_name]
     ctx.set_gemm_mode(mode)
+    # the gradient exchange runs inside the library (NCCL on the context's stream);
+    # torch.distributed only carries the communicator id, the barriers and the max over ranks
+    comm = Communicator.from_torch_distributed(ctx, max_wait_s=120.0) if world > 1 else None
 
     weights = init_weights(w.model, w.seed, device=f"cuda:{local}", f16_base=w.f16_base)
     adapters = init_adapters(w.model, w.lora, w.seed, device=f"cuda:{local}", b_std=w.adapter_b_std)
@@ -251,13 +294,13 @@ def run_cuda(args):
     mine = shard_indices(w.global_batch, world, rank)
     ids, tg, mk = ids[mine], tg[mine], mk[mine]
     n_local = len(mine)
-    mb = max(1, min(args.micro_batch, n_local))
+    mb = local_micro_batch(args, w, world)
     tokens_per_step = w.global_batch * w.seq_len
 
     trainer = Trainer(model, AdamW(w.lr, weight_decay=w.weight_decay)) \
         .with_grad_accum_steps(n_local).with_clip_grad_norm(w.clip)
     if world > 1:
-        trainer.with_distributed(world, rank)
+        trainer.with_distributed(world, rank, comm)
     trainer.max_chunk = mb
 
     # ---- device-resident form of one step --------------------------------------------------
@@ -265,35 +308,39 @@ def run_cuda(args):
     resident = []
     for r0 in range(0, n_local, mb):
         i, t, m = ids[r0:r0 + mb], tg[r0:r0 + mb], mk[r0:r0 + mb]
-        rt, rw, _ = batch_targets_weights(t, m, w.model.vocab)
+        rt, rw, tok = batch_targets_weights(t, m, w.model.vocab)
         resident.append((
             torch.from_numpy(np.ascontiguousarray(i).view(np.int32).reshape(-1)).to(dev),
             torch.from_numpy(rt.view(np.int32).reshape(-1)).to(dev),
             torch.from_numpy(rw.reshape(-1)).to(dev),
-            torch.empty(i.size, device=dev, dtype=torch.float32), i.shape[0]))
+            torch.empty(i.size, device=dev, dtype=torch.float32), i.shape[0],
+            torch.from_numpy(np.maximum(tok, 1).astype(np.float32)).to(dev)))
+    # self-check of the first timed step, kept on the device until the timed region is over:
+    # [sum over this rank's sequences of the sequence loss, pre-clip gradient norm, applied flag]
+    check_dev = torch.zeros(3, device=dev, dtype=torch.float64)
 
-    def resident_step():
+    def resident_step(capture=False):
         model.zero_grad()
-        for d_ids, d_tg, d_w, row_loss, n in resident:
+        for d_ids, d_tg, d_w, row_loss, n, d_tok in resident:
             model.forward_backward(d_ids, d_tg, d_w, n, w.seq_len, 1.0 / n_local, row_loss)
-        scale = 1.0
-        if world > 1:
-            dist.all_reduce(model.grads, op=dist.ReduceOp.SUM)
-            scale = 1.0 / world
+            if capture:
+                check_dev[0] += (row_loss.view(n, -1).sum(dim=1) / d_tok).sum().double()
         trainer.optimizer.t += 1.0
-        model.apply_gradients(scale, w.clip, trainer.optimizer.params())
+        model.allreduce_apply_gradients(comm, w.clip, trainer.optimizer.params())
+        if capture:
+            check_dev[1:3] = model.norm_out[:2].double()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, first=None):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            fn()
+        for k in range(steps):
+            (first if first is not None and k == 0 else fn)()
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -309,18 +356,37 @@ def run_cuda(args):
     if rank == 0:
         sampler.start()
     launches0 = ctx.launch_count()
-    ms_total = timed(resident_step, args.steps)
+    ms_total = timed(resident_step, args.steps, first=lambda: resident_step(True))
     launches = ctx.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     ms_step = ms_total / args.steps
     value = tokens_per_step / (ms_step * 1e-3)
+
+    # ---- the step checks itself: loss and pre-clip norm of the first timed step, and whether
+    # every rank holds the same parameters after the last one -----------------------------------
+    chk = check_dev.clone()
+    words = model.params.view(torch.int32).to(torch.int64)
+    fingerprint = torch.stack([words.sum(), (words * (torch.arange(words.numel(), device=dev) % 8191 + 1)).sum()])
+    fp_min, fp_max = fingerprint.clone(), fingerprint.clone()
+    if world > 1:
+        dist.all_reduce(chk[0:1], op=dist.ReduceOp.SUM)
+        dist.all_reduce(fp_min, op=dist.ReduceOp.MIN)
+        dist.all_reduce(fp_max, op=dist.ReduceOp.MAX)
+    check = {"loss_step1": float(chk[0].item()) / w.global_batch,
+             "grad_norm_step1": float(chk[1].item()),
+             "update_applied_step1": bool(chk[2].item() != 0.0),
+             "params_equal_across_ranks": bool(torch.equal(fp_min, fp_max)),
+             "params_fingerprint": [int(v) for v in fingerprint.tolist()],
+             "what": "mean sequence loss and pre-clip global gradient norm of the first timed "
+                     "step (after the warm-up steps' updates); two integer checksums of the "
+                     "parameter bits after the last step, min == max over ranks"}
 
     # ---- roofline of the dominant kernel: the tensor-core GEMM, timed inside a step ------------
     ctx.profile(True)
     resident_step()
     ctx.synchronize()
     gemm_bytes = ctx.profile_bytes()
-    gemm_ms, gemm_flops, gemm_launches = ctx.profile_read()
+    gemm_ms, gemm_flops_done, gemm_launches = ctx.profile_read()
     ctx.profile(False)
     # DRAM traffic per launch: the launches' algorithmic bytes (operands once, results once) times
     # the ratio dram bytes / algorithmic bytes that one ncu capture of the 8192 x 8192 x 2048
@@ -352,31 +418,37 @@ def run_cuda(args):
     ctx.synchronize()
 
     if rank != 0:
+        if comm is not None:
+            comm.close()
         if world > 1:
             dist.destroy_process_group()
         return
     peaks = measured_peaks()
-    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    executed = gemm_flops_done / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    # algorithmic FLOPs of this rank's share of the step's dense contractions (frozen projections
+    # and head forward + input gradient, adapters forward + two gradients)
+    gemm_alg = gemm_flops(w, tokens_per_step) / world
+    achieved = gemm_alg / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     flops_step = step_flops(w, tokens_per_step)
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None,
-        "dtype": {GemmMode.F16: "f16", GemmMode.F16X2: "f16x2", GemmMode.F32: "f32"}[mode],
+        "dtype": mode_name,
         "data": "synthetic",
-        "config": {"workload": w.name, "global_batch": w.global_batch, "seq_len": w.seq_len,
-                   "micro_batch_sequences": mb, "parallelism": f"dp{world}",
-                   "lora_rank": w.lora.rank, "checkpoint_blocks": w.checkpoint_blocks,
-                   "reduced_case": reduced,
-                   "l2": "inputs larger than L2 (weights and activations of one step exceed 126 MB)",
-                   "gemm_operands": "f16 activations x f16 weights, f32 accumulate"
-                   if mode is not GemmMode.F32 else "f32"},
+        "config": workload_config(w, world, mb, mode_name, reduced),
+        "check": check,
         "step_roofline": {"algorithmic_tflop_per_step": flops_step / 1e12,
                           "achieved_tflops": flops_step / (ms_step * 1e-3) / 1e12 / world,
                           "peak_tflops": peaks["tflops"],
                           "frac": flops_step / (ms_step * 1e-3) / 1e12 / world / peaks["tflops"],
                           "peak_source": peaks["source"]},
         "roofline": {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 f16)", "achieved": achieved,
+                     "achieved_executed": executed,
+                     "flops": "achieved = algorithmic FLOPs (2MNK of the frozen projections and "
+                              "the rank-r adapter products) / summed launch time; "
+                              "achieved_executed counts what the launches ran (adapter tail "
+                              "padded to 64 columns, pre-tiles, checkpoint replays)",
                      "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"] if peaks["tflops"] else None,
                      "traffic": traffic, "traffic_unit": "bytes per launch (algorithmic x 1.027, the ncu-measured dram/algorithmic ratio of one launch)",
@@ -391,12 +463,16 @@ def run_cuda(args):
         out["kernel_ms"] = kernel_ms
     if want_cpu:
         sample = args.cpu_sample_tokens or default_cpu_sample(w)
-        tps, cores, sec = cpu_step_tokens_per_s(w, weights_cpu, adapters_cpu, sample)
+        tps, cores, sec, _ = cpu_step_tokens_per_s(w, weights_cpu, adapters_cpu, sample, repeats=3,
+                                                   warmup=1)
         out["cpu_baseline"] = {
             "value": tps, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"one sequence of {sample} of {w.seq_len} positions, one step "
-                      f"({sec:.1f} s); a full step is extrapolated linearly"}
+            "sample": f"one sequence of {sample} of {w.seq_len} positions per step, median of 3 "
+                      f"steps after one warm-up step ({sec:.1f} s per step); a full step is "
+                      f"extrapolated linearly"}
     print(json.dumps(out))
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -73,7 +73,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                     raise RuntimeError(f"nvcc failed on {src.name}")
     objs = [OBJ / (s.stem + ".o") for s in sources()]
     if jobs or not LIB.exists() or any(o.stat().st_mtime > LIB.stat().st_mtime for o in objs):
-        cmd = [nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
+        cmd = [nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

@@ -17,6 +17,8 @@ FT_MASKED_CE_SKIP = 0xFFFFFFFF
 FT_SUM_SQUARES_CHUNK = 4096
 FT_GEMM_F32, FT_GEMM_F16, FT_GEMM_F16X2 = 0, 1, 2
 FT_LINEARS = 7
+FT_ERR_COMM = 5
+FT_COMM_ID_BYTES = 128
 
 
 class FtError(RuntimeError):
@@ -124,6 +126,13 @@ PROTOTYPES = {
     "ft_model_set_dropout_seed": [_P, C.c_uint64],
     "ft_model_zero_grad": [_P],
     "ft_model_apply_gradients": [_P, _F, _F, C.POINTER(FtAdamParams), _P],
+    "ft_comm_unique_id": [_P],
+    "ft_comm_create": [_P, _I, _I, _P, _I, C.POINTER(_P)],
+    "ft_comm_destroy": [_P],
+    "ft_comm_info": [_P, C.POINTER(_I), C.POINTER(_I)],
+    "ft_comm_allreduce_sum": [_P, _P, _Z],
+    "ft_comm_wait": [_P, _I],
+    "ft_model_allreduce_apply_gradients": [_P, _P, _F, C.POINTER(FtAdamParams), _P],
 }
 STRING_GETTERS = ("ft_last_error", "ft_build_info")
 

@@ -235,6 +235,16 @@ def synthetic_batch(w: Workload, sequences: int, seed: Optional[int] = None, fir
     return ids, tgt, msk
 
 
+def gemm_flops(w: Workload, tokens: int) -> float:
+    """The dense-contraction part of `step_flops`: frozen projections and head (forward +
+    input gradient) and the adapter products (forward + two gradients); no attention."""
+    c, lo = w.model, w.lora
+    p_layer = sum(o * i for o, i in c.linear_shapes().values())
+    base = 2 * 2 * (c.layers * p_layer + c.hidden * c.vocab)
+    lora = 6 * lo.rank * sum(o + i for n, (o, i) in c.linear_shapes().items() if lo.targeted(n)) * c.layers
+    return float(tokens) * (base + lora)
+
+
 def step_flops(w: Workload, tokens: int) -> float:
     """Algorithmic FLOPs of one step over `tokens` positions, in the reference's
     conventions (matmul 2MNK; causal attention forward 2 S^2 D per head and sequence,

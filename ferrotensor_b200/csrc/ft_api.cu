@@ -38,7 +38,8 @@ extern "C" int ft_ctx_create(int device, void* stream, FtContext** out) {
   FT_REQUIRE(out != nullptr, "ft_ctx_create: out is NULL");
   int count = 0;
   FT_CUDA(cudaGetDeviceCount(&count));
-  FT_REQUIRE(device >= 0 && device < count, "ft_ctx_create: device %d of %d", device, count);
+  FT_REQUIRE(device >= 0 && device < count && device < FT_MAX_DEVICES,
+             "ft_ctx_create: device %d of %d", device, count);
   FT_CUDA(cudaSetDevice(device));
   cudaDeviceProp prop;
   FT_CUDA(cudaGetDeviceProperties(&prop, device));

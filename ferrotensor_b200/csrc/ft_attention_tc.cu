@@ -976,11 +976,11 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
                          (uint64_t)batch * seq, (uint64_t)ld, 64, 128));
   FT_TRY(ft_tc::make_map(ctx, &kv64, qkv16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)ld,
                          (uint64_t)batch * seq, (uint64_t)ld, 64, 64));
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[FT_MAX_DEVICES] = {};   // function attributes are per device
+  if (!configured[ctx->device]) {
     FT_CUDA(cudaFuncSetAttribute(k_attn_fwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  AttnSmem::DYN_BYTES));
-    configured = true;
+    configured[ctx->device] = true;
   }
   // persistent: two CTAs per SM walk the (query tile, head) pairs
   const int tiles = ft_cdiv(seq, AT_Q) * batch * heads;
@@ -1014,13 +1014,13 @@ int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
   FT_TRY(ft_tc::make_map(ctx, &kv64, qkv16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)ld, T, (uint64_t)ld, 64, 64));
   FT_TRY(ft_tc::make_map(ctx, &do128, do16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)lddo, T, (uint64_t)lddo, 64, 128));
   FT_TRY(ft_tc::make_map(ctx, &do64, do16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)lddo, T, (uint64_t)lddo, 64, 64));
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[FT_MAX_DEVICES] = {};   // function attributes are per device
+  if (!configured[ctx->device]) {
     FT_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  BwdQSmem::DYN_BYTES));
     FT_CUDA(cudaFuncSetAttribute(k_attn_bwd_dkv_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  BwdKSmem::DYN_BYTES));
-    configured = true;
+    configured[ctx->device] = true;
   }
   const float scale = 1.0f / sqrtf((float)head_dim);
   int* am = ctx->amax_out;   // armed: the gradients' largest magnitude goes to the amax slot

@@ -86,6 +86,7 @@ int ft_cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 void ft_prof_begin(FtContext* ctx, const char* name);
 void ft_prof_end(FtContext* ctx);
 
+constexpr int FT_MAX_DEVICES = 64;   // per-device launch state is kept in arrays of this size
 constexpr int FT_PRE_FLAGS = 4096;
 constexpr int FT_AMAX_RING = 1024;
 
@@ -283,6 +284,11 @@ int ft_k_adamw(FtContext* ctx, float* w, const float* g, float* m, float* v, siz
 int ft_k_apply_fused(FtContext* ctx, float* w, float* g, float* m, float* v, size_t n,
                      float grad_scale, float max_norm, const FtAdamParams* p, float* partials,
                      float* norm_out);
+
+// data parallelism (ft_comm.cu): in-place sum over the ranks on the context's stream
+int ft_comm_allreduce_f32(FtComm* c, float* buf, size_t n);
+int ft_comm_world(const FtComm* c);
+FtContext* ft_comm_ctx(const FtComm* c);
 
 // A flat index i = r * per_row + c walked with stride st without dividing in the loop:
 // (r, c) advance by (st / per_row, st % per_row) with a carry.

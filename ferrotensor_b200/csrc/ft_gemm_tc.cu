@@ -35,9 +35,11 @@ struct SmemLayout {
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack to align the base to 1024 bytes
 };
 
-// Progress markers for fault finding: when `dbg` is set, CTA 0 records how far each role got
-// in pinned host memory (which survives a device fault) and lets asynchronous work land
-// before it moves on, so that the last marker names the instruction that failed.
+// Progress markers for fault finding, compiled in only with -DFT_DEBUG_MARKERS: when `dbg` is
+// set, CTA 0 records how far each role got in pinned host memory (which survives a device
+// fault) and lets asynchronous work land before it moves on, so that the last marker names the
+// instruction that failed.  Release builds carry none of it.
+#ifdef FT_DEBUG_MARKERS
 #define FT_MARK(slot, value)                                  \
   do {                                                        \
     if (dbg && blockIdx.x == 0) {                             \
@@ -49,6 +51,10 @@ struct SmemLayout {
   do {                                                        \
     if (dbg) for (int _i = 0; _i < 200; ++_i) __nanosleep(1000); \
   } while (0)
+#else
+#define FT_MARK(slot, value) do { (void)dbg; } while (0)
+#define FT_SETTLE() do { } while (0)
+#endif
 
 // What the epilogue does with a finished accumulator tile:
 //   v = alpha_dev * alpha * acc (+ bias[col]) (+ residual[row, col]);  c = v;  c16 = f16(v)
@@ -1084,11 +1090,12 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
   if (ko_in) ko = *ko_in;
   const CUtensorMap& map3 = mb3 ? *mb3 : mb;
   using L = SmemLayout<BN, STAGES, MH>;
-  static bool configured = false;
-  if (!configured) {
+  // function attributes are per device: set once on each device that launches this kernel
+  static bool configured[FT_MAX_DEVICES] = {};
+  if (!configured[ctx->device]) {
     FT_CUDA(cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, KOUTER, MH>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-    configured = true;
+    configured[ctx->device] = true;
   }
   int tiles = KOUTER ? ko_tiles_host : ft_cdiv(M, MH * BM) * ft_cdiv(N, BN);
   int grid = std::min(tiles, ctx->sm_count);
@@ -1137,8 +1144,11 @@ int launch_tc2(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, con
                const CUtensorMap& mb2, const CUtensorMap& mb3, const Epilogue& ep, const PreTile& pre,
                int M, int N, int K, int K2, uint32_t idesc, double flops) {
   using L = Smem2<STAGES>;
-  static bool configured = false;
-  static int max_pairs = 0;
+  // function attributes and cluster occupancy are per device
+  static bool configured_dev[FT_MAX_DEVICES] = {};
+  static int max_pairs_dev[FT_MAX_DEVICES] = {};
+  bool& configured = configured_dev[ctx->device];
+  int& max_pairs = max_pairs_dev[ctx->device];
   if (!configured) {
     FT_CUDA(cudaFuncSetAttribute(k_gemm_tc2<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  L::DYN_BYTES));

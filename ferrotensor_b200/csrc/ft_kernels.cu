@@ -4,6 +4,8 @@
 // loads when alignment allows and reduced with warp shuffles.
 #include <algorithm>
 
+#include <atomic>
+
 #include "ft_common.cuh"
 
 namespace {
@@ -716,7 +718,9 @@ __global__ void k_adamw(float* __restrict__ w, const float* __restrict__ g,
 
 // norm_out[0] = norm, [1] = 1 if the step is applied, [2] = factor to apply to the raw
 // gradient (grad_scale, times the clip factor when clipping).  Chunk sums are added in
-// index order in f64, as the reference's host loop does.
+// f64 like the reference's host loop, but not in index order: each thread sums a fixed strided
+// subset and a fixed shared-memory tree joins them, so the result is identical from run to run
+// and can differ from a sequential f64 sum in its last bit.
 __global__ void k_norm_finalize(const float* __restrict__ partials, size_t chunks,
                                 float grad_scale, float max_norm, float* __restrict__ norm_out) {
   __shared__ double sred[kRowThreads];
@@ -846,8 +850,10 @@ static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
 
 // In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address:
 // the address is asked for once per device (with that device current) and cached.
-constexpr int kMaxDevices = 64;
-static float* g_noalloc_ptr[kMaxDevices] = {};
+// (A cached address does not survive cudaDeviceReset: a host that resets a device must not
+// call this entry point on it afterwards.)
+constexpr int kMaxDevices = FT_MAX_DEVICES;
+static std::atomic<float*> g_noalloc_ptr[kMaxDevices];
 
 extern "C" int ft_rms_norm_backward_noalloc(FtContext* ctx, const float* x, const float* w,
                                             const float* g, float* gx, float* gw, int rows,
@@ -863,14 +869,20 @@ extern "C" int ft_rms_norm_backward_noalloc(FtContext* ctx, const float* x, cons
              inv_floats + (size_t)size, kNoAllocFloats);
   FT_REQUIRE(ctx->device >= 0 && ctx->device < kMaxDevices,
              "ft_rms_norm_backward_noalloc: device ordinal %d out of range", ctx->device);
-  float* scratch = g_noalloc_ptr[ctx->device];
+  float* scratch = g_noalloc_ptr[ctx->device].load(std::memory_order_acquire);
   if (!scratch) {
-    // first call on this device: resolve the symbol (do this before any stream capture)
-    FT_CUDA(cudaSetDevice(ctx->device));
+    // first call on this device: resolve the symbol with that device current (do this before
+    // any stream capture), then give the caller its own current device back
+    int prev = -1;
+    FT_CUDA(cudaGetDevice(&prev));
+    if (prev != ctx->device) FT_CUDA(cudaSetDevice(ctx->device));
     void* p = nullptr;
-    FT_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    cudaError_t se = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (prev != ctx->device) cudaSetDevice(prev);
+    if (se != cudaSuccess) return ft_cuda_fail(se, "cudaGetSymbolAddress", __FILE__, __LINE__);
     FT_REQUIRE(p != nullptr, "ft_rms_norm_backward_noalloc: symbol address is NULL");
-    scratch = g_noalloc_ptr[ctx->device] = (float*)p;
+    scratch = (float*)p;
+    g_noalloc_ptr[ctx->device].store(scratch, std::memory_order_release);
   }
   float* inv = nullptr;
   float* partial = nullptr;

@@ -1096,3 +1096,13 @@ extern "C" int ft_model_apply_gradients(FtLoraModel* m, float grad_scale, float 
   return ft_k_apply_fused(m->ctx, m->params, m->grads, m->adam_m, m->adam_v, m->trainable,
                           grad_scale, max_norm, p, partials, nout);
 }
+
+extern "C" int ft_model_allreduce_apply_gradients(FtLoraModel* m, FtComm* comm, float max_norm,
+                                                  const FtAdamParams* p, float* norm_out) {
+  FT_REQUIRE(m && p, "ft_model_allreduce_apply_gradients: NULL argument");
+  FT_REQUIRE(!comm || ft_comm_ctx(comm) == m->ctx,
+             "ft_model_allreduce_apply_gradients: the communicator belongs to another context");
+  const int world = ft_comm_world(comm);
+  if (world > 1 && m->trainable) FT_TRY(ft_comm_allreduce_f32(comm, m->grads, m->trainable));
+  return ft_model_apply_gradients(m, 1.0f / (float)world, max_norm, p, norm_out);
+}

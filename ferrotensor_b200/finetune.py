@@ -36,6 +36,7 @@ import numpy as np
 
 from .data import DataLoader, TextDataset, sft_example_from_tokens, supervised_tokens
 from .tokenizer import Tokenizer
+from .trainer import shard_indices
 
 
 class Unmet(RuntimeError):
@@ -181,6 +182,7 @@ class TrainArgs:
     gemm: str = "f16"
     device: int = 0
     max_chunk: Optional[int] = None     # sequences per device micro-batch; None = all that fit the window
+    dist_timeout: int = 600             # seconds a rank waits for its peers (the reference's max_wait)
 
 
 @dataclass
@@ -236,6 +238,23 @@ def _pick_chunk(model, micro_per_step: int, seq_len: int, bucket: int) -> int:
     return chunk
 
 
+def trainable_example(ex) -> bool:
+    """What `Trainer.train_batch` keeps (ferrotensor-trainer/src/lib.rs:371-422): at least two
+    positions and one supervised token."""
+    return min(len(ex.input_ids), len(ex.target_ids)) >= 2 and any(ex.loss_mask)
+
+
+def equal_shard(examples, world: int, rank: int):
+    """This rank's examples for data-parallel training.  Every rank must close the same number
+    of accumulation windows, since each closed window is one collective: examples the trainer
+    would drop are removed BEFORE sharding (so no rank drops any later), the round-robin shards
+    (distributed.rs:222-227) are cut to the common length, and with that the step count derived
+    from the shard is the same on every rank."""
+    kept = [ex for ex in examples if trainable_example(ex)]
+    per_rank = len(kept) // world
+    return [kept[i] for i in shard_indices(per_rank * world, world, rank)]
+
+
 def train(args: TrainArgs) -> TrainSummary:
     import torch
     from . import checkpoint as ck
@@ -264,10 +283,12 @@ def train(args: TrainArgs) -> TrainSummary:
     is_root = rank == 0
     device = int(os.environ.get("LOCAL_RANK", args.device)) if distributed else args.device
     if distributed:
+        import datetime
         import torch.distributed as dist
         torch.cuda.set_device(device)
         if not dist.is_initialized():
-            dist.init_process_group("nccl", device_id=torch.device("cuda", device))
+            dist.init_process_group("nccl", device_id=torch.device("cuda", device),
+                                    timeout=datetime.timedelta(seconds=args.dist_timeout))
 
     model_dir = Path(args.model)
     cfg, weights, _raw = load_model_dir(model_dir)
@@ -309,10 +330,10 @@ def train(args: TrainArgs) -> TrainSummary:
     adapter_path = Path(args.save_lora) if args.save_lora else out_dir / "lora_adapters.safetensors"
     state_path = state_path_for(adapter_path)
 
-    if distributed:                     # each rank trains on a disjoint slice
+    if distributed:                     # each rank trains on a disjoint slice of equal length
         shard = TextDataset()
-        for i in shard_indices(len(dataset), world, rank):
-            shard.add_example(dataset.examples()[i])
+        for ex in equal_shard(dataset.examples(), world, rank):
+            shard.add_example(ex)
         dataset = shard
 
     micro_per_step = args.batch_size * args.grad_accum
@@ -326,7 +347,9 @@ def train(args: TrainArgs) -> TrainSummary:
                .with_clip_grad_norm(args.grad_clip).with_lr_scheduler(scheduler))
     trainer.max_chunk = args.max_chunk or _pick_chunk(model, micro_per_step, args.seq_len, trainer.length_bucket)
     if distributed:
-        trainer.with_distributed(world, rank)
+        from .distributed import Communicator
+        trainer.with_distributed(world, rank, Communicator.from_torch_distributed(
+            ctx, max_wait_s=float(args.dist_timeout)))
 
     start_step = 0
     if args.resume is not None:
@@ -514,6 +537,8 @@ def parse_args(argv=None) -> TrainArgs:
     ap.add_argument("--gemm", choices=("f16", "f16x2", "f32"), default=d.gemm)
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--max-chunk", type=int, default=None, help="sequences per device micro-batch")
+    ap.add_argument("--dist-timeout", type=int, default=d.dist_timeout,
+                    help="seconds a rank waits for its peers before it fails")
     ap.add_argument("--json", action="store_true", help="print one JSON summary to stdout when the run ends")
     ns = ap.parse_args(argv)
     kw = vars(ns)

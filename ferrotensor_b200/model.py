@@ -187,6 +187,13 @@ class LoraModel:
         call("ft_model_apply_gradients", self.handle, float(grad_scale),
              float(max_norm) if max_norm else 0.0, C.byref(adam), _ptr(self.norm_out))
 
+    def allreduce_apply_gradients(self, comm, max_norm: Optional[float], adam: FtAdamParams) -> None:
+        """Sum of the gradient buffer over the communicator's ranks, then the same update with
+        1/world folded in (`comm` None = a single rank)."""
+        call("ft_model_allreduce_apply_gradients", self.handle,
+             comm.handle if comm is not None else C.c_void_p(None),
+             float(max_norm) if max_norm else 0.0, C.byref(adam), _ptr(self.norm_out))
+
     def close(self) -> None:
         if self.handle:
             call("ft_model_destroy", self.handle)

@@ -2,7 +2,7 @@
 (ferrotensor-trainer/src/lib.rs:113-503), `AdamW` / `WarmupCosineScheduler`
 (ferrotensor-autograd/src/lib.rs:1482-1552,1763-1805) and the data-parallel gradient mean
 (ferrotensor-trainer/src/distributed.rs:107-185, there through files; here one NCCL
-all-reduce of the flat gradient buffer).
+all-reduce of the flat gradient buffer inside the library, `distributed.Communicator`).
 
 Host side = integer bookkeeping only (padding, targets, loss weights); every float of the
 step is computed by libft_cuda kernels.
@@ -142,6 +142,7 @@ class Trainer:
         self.length_bucket = 32
         self.max_chunk: Optional[int] = None   # memory bound on sequences per micro-batch
         self.world_size, self.rank = 1, 0
+        self.comm = None                       # distributed.Communicator when world_size > 1
         self.optimizer_step_count = 0
         self.keep_logits = False
         self.last_logits: Optional[torch.Tensor] = None
@@ -174,9 +175,16 @@ class Trainer:
         return attention_dropout_seed(self.dropout_seed, self.rank if self.world_size > 1 else 0,
                                       self.optimizer_step_count, self.step_in_accum)
 
-    def with_distributed(self, world_size: int, rank: int) -> "Trainer":
-        """Average gradients over `world_size` ranks (torch.distributed must be initialised)."""
-        self.world_size, self.rank = world_size, rank
+    def with_distributed(self, world_size: int, rank: int, comm=None) -> "Trainer":
+        """Average gradients over `world_size` ranks through `comm`
+        (`distributed.Communicator`, one per rank)."""
+        from .distributed import validate_world
+        validate_world(world_size, rank)
+        if world_size > 1 and comm is None:
+            raise ValueError("with_distributed: a communicator is required when world_size > 1")
+        if comm is not None and (comm.world_size, comm.rank) != (world_size, rank):
+            raise ValueError("with_distributed: the communicator was created for another rank/world")
+        self.world_size, self.rank, self.comm = world_size, rank, comm
         return self
 
     def set_optimizer_steps(self, steps: int) -> None:
@@ -232,24 +240,29 @@ class Trainer:
     def apply_gradients(self, stats: StepStats) -> None:
         """Mean over ranks -> global norm -> skip if non-finite -> clip -> LR schedule ->
         AdamW (lib.rs:296-360); norm, skip and clip are decided on the device."""
-        grad_scale = 1.0
-        if self.world_size > 1:
-            import torch.distributed as dist
-            dist.all_reduce(self.model.grads, op=dist.ReduceOp.SUM)
-            grad_scale = 1.0 / self.world_size
+        prev_lr = self.optimizer.lr
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
             lr = self.lr_scheduler.get_lr()
             self.optimizer.set_lr(lr)
             stats.lr = lr
         self.optimizer.t += 1.0
-        self.model.apply_gradients(grad_scale, self.clip_grad_norm, self.optimizer.params())
+        # sum over the ranks (NCCL, inside the library) with 1/world folded into the update
+        self.model.allreduce_apply_gradients(self.comm if self.world_size > 1 else None,
+                                             self.clip_grad_norm, self.optimizer.params())
+        if self.comm is not None and self.world_size > 1:
+            self.comm.wait()   # a peer that never joined ends here as FtError, not as a hang
         norm, applied = self.model.norm_out[:2].tolist()
         self.d2h_bytes += 8
         stats.grad_norm = norm
         if applied == 0.0:
-            # non-finite norm: the device skipped the update; undo the host-side counters
+            # non-finite norm: the device skipped the update.  The reference returns before the
+            # schedule advances (lib.rs:330-352): undo the host-side counters, schedule included.
             self.optimizer.t -= 1.0
+            if self.lr_scheduler is not None:
+                self.lr_scheduler.current -= 1
+                self.optimizer.set_lr(prev_lr)
+            stats.lr = None
             return
         self.optimizer_step_count += 1
         stats.optimizer_step = True

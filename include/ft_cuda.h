@@ -34,6 +34,7 @@ extern "C" {
 #define FT_ERR_CUDA 2      /* a CUDA runtime call failed                            */
 #define FT_ERR_UNSUPPORTED 3
 #define FT_ERR_DEVICE 4    /* a kernel reported a failed bounded wait               */
+#define FT_ERR_COMM 5      /* NCCL missing or failed, or a rank did not answer in time */
 
 /* ferrotensor-backend/src/engine/training.rs:7,11 */
 #define FT_MASKED_CE_SKIP 0xffffffffu
@@ -53,15 +54,17 @@ typedef struct FtContext FtContext;
 /* ---- context: ferrotensor-backend/src/context.rs:164-237 (new), :373-397 (flush,
  * synchronize).  `stream` is a cudaStream_t to enqueue on (cudaStreamLegacy, handle value 1,
  * names the legacy default stream), or NULL for a stream the context creates.  One context
- * per process and device, as in the reference. */
+ * per device, as in the reference; a process may hold contexts on several devices (kernel
+ * attributes and occupancy limits are kept per device). */
 int ft_ctx_create(int device_ordinal, void* stream, FtContext** out);
 int ft_ctx_destroy(FtContext* ctx);
 int ft_ctx_flush(FtContext* ctx);        /* no-op: a stream needs no submit            */
 int ft_ctx_synchronize(FtContext* ctx);  /* waits; returns FT_ERR_DEVICE if a kernel failed */
 int ft_ctx_status(FtContext* ctx, int* device_status); /* non-blocking read of the status word */
 /* Diagnostics: the 16 status words kernels write to pinned host memory ([0..3] status of a
- * failed bounded wait, [4..15] progress markers recorded when FT_GEMM_DEBUG=1 is set in the
- * environment at context creation).  Makes no CUDA call, so it works after a device fault. */
+ * failed bounded wait; [4..15] progress markers, recorded only by a library built with
+ * -DFT_DEBUG_MARKERS and with FT_GEMM_DEBUG=1 in the environment at context creation).
+ * Makes no CUDA call, so it works after a device fault. */
 int ft_ctx_debug_words(FtContext* ctx, int* out16);
 /* Timing of the tensor-core GEMM launches with CUDA events on the launch stream.  While
  * enabled every launch is bracketed by two events; ft_ctx_profile_read waits for the stream,
@@ -130,8 +133,9 @@ int ft_rms_norm_backward(FtContext* ctx, const float* x, const float* w, const f
 
 /* No counterpart in the reference.  ft_rms_norm_backward for hosts that cannot allocate
  * device memory during a call (all memory already handed to their own pool, an embedding
- * program's memory cap, a loop where a cudaMalloc stall is not acceptable): same arguments
- * and results, but the per-row scratch lives in a fixed 2 MiB array inside the library image
+ * program's memory cap, a loop where a cudaMalloc stall is not acceptable): same arguments,
+ * results equal to ft_rms_norm_backward's to rounding (the kernel choice can differ), but the
+ * per-row scratch lives in a fixed 2 MiB array inside the library image
  * (held by every GPU that loads the library until the process exits) and the call makes no
  * cudaMalloc/cudaFree.  Limit: with gw != NULL, rows rounded up to 64 plus size must not
  * exceed 524288 floats; larger shapes are rejected with FT_ERR_INVALID.  The first call on a
@@ -304,6 +308,44 @@ int ft_model_zero_grad(FtLoraModel* m);
  * applied to the raw gradient, unused}. */
 int ft_model_apply_gradients(FtLoraModel* m, float grad_scale, float max_norm,
                              const FtAdamParams* p, float* norm_out);
+
+/* =====================================================================================
+ * Data parallelism: ferrotensor-trainer/src/distributed.rs:17-69 (FileGradSyncConfig: world
+ * size, rank, max_wait), :107-185 (average_grads_file_sync), called from
+ * Trainer::apply_gradients (ferrotensor-trainer/src/lib.rs:318-328) before the norm, the clip
+ * and the optimizer.  The reference exchanges gradient files in a shared directory; here one
+ * NCCL all-reduce of the model's flat gradient buffer runs on the context's stream over
+ * NVLink.  NCCL is bound at run time (libnccl.so.2, or the path in FT_NCCL_LIB); a world of
+ * one needs no NCCL.  Nothing here hangs the host: communicators are non-blocking and every
+ * wait has a deadline, after which the communicator is aborted, the call returns FT_ERR_COMM
+ * and every later call on it fails the same way (the reference returns "timed out waiting
+ * for ..." after max_wait).
+ * ===================================================================================== */
+#define FT_COMM_ID_BYTES 128
+typedef struct FtComm FtComm;
+/* Rank 0 makes the 128-byte identifier of a new communicator and hands it to the other ranks
+ * by any host-side channel (a file in the sync directory, a TCP store, an environment variable). */
+int ft_comm_unique_id(void* id_out);
+/* Joins `rank` of `world_size` (one process per GPU; ctx's device is the rank's GPU).  Rejects
+ * world_size == 0 and rank >= world_size with the reference's messages (distributed.rs:36-44).
+ * timeout_ms bounds this call and each later collective's set-up.  id may be NULL when
+ * world_size == 1. */
+int ft_comm_create(FtContext* ctx, int world_size, int rank, const void* id, int timeout_ms,
+                   FtComm** out);
+int ft_comm_destroy(FtComm* comm);
+int ft_comm_info(FtComm* comm, int* world_size, int* rank);
+/* buf[i] = sum over ranks of buf[i], n f32 on the device, enqueued on the context's stream. */
+int ft_comm_allreduce_sum(FtComm* comm, float* buf, size_t n);
+/* Waits (host) until the last collective enqueued has finished on the device, at most
+ * timeout_ms (0 = the communicator's own limit).  On expiry the communicator is aborted, which
+ * ends the waiting kernel, and FT_ERR_COMM is returned: how a rank learns that a peer never
+ * entered the collective. */
+int ft_comm_wait(FtComm* comm, int timeout_ms);
+/* Trainer::apply_gradients for `world_size` ranks (lib.rs:318-358): sum of the flat gradient
+ * buffer over the ranks, then ft_model_apply_gradients with grad_scale = 1/world_size, so every
+ * rank performs the identical update.  comm == NULL means a single rank. */
+int ft_model_allreduce_apply_gradients(FtLoraModel* m, FtComm* comm, float max_norm,
+                                       const FtAdamParams* p, float* norm_out);
 
 #ifdef __cplusplus
 }

@@ -151,20 +151,36 @@ rank, world = int(sys.argv[1]), 2
 os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT={port!r}, RANK=str(rank), WORLD_SIZE="2")
 dist.init_process_group("gloo", rank=rank, world_size=world)
 
+class GlooComm:
+    # stands in for distributed.Communicator on a machine without GPUs: same protocol
+    # (world_size, rank, allreduce_sum, wait), the sum carried by gloo
+    def __init__(self, world, rank):
+        self.world_size, self.rank, self.waits = world, rank, 0
+    def allreduce_sum(self, t):
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    def wait(self, timeout_s=0.0):
+        self.waits += 1
+
 class FakeModel:
-    # stands in for the device model: a flat gradient buffer and a recorder
+    # stands in for the device model: a flat gradient buffer and a recorder; its
+    # allreduce_apply_gradients does what ft_model_allreduce_apply_gradients does
     def __init__(self):
         self.ctx = None
         self.grads = torch.arange(8, dtype=torch.float32) * (rank + 1)
         self.norm_out = torch.tensor([1.0, 1.0, 0.0, 0.0])
         self.seen = None
-    def apply_gradients(self, grad_scale, max_norm, adam):
-        self.seen = (self.grads * grad_scale).clone()
+    def allreduce_apply_gradients(self, comm, max_norm, adam):
+        world = comm.world_size if comm is not None else 1
+        if world > 1:
+            comm.allreduce_sum(self.grads)
+        self.seen = (self.grads * (1.0 / world)).clone()
 
 m = FakeModel()
-t = Trainer(m, AdamW(1e-3)).with_distributed(world, rank)
+comm = GlooComm(world, rank)
+t = Trainer(m, AdamW(1e-3)).with_distributed(world, rank, comm)
 s = StepStats()
 t.apply_gradients(s)
+assert comm.waits == 1
 expect = torch.arange(8, dtype=torch.float32) * 1.5      # mean of 1x and 2x
 assert torch.equal(m.seen, expect), (m.seen, expect)
 assert s.optimizer_step and t.optimizer.t == 1.0
@@ -187,3 +203,41 @@ def test_gradient_mean_over_two_gloo_ranks(tmp_path):
     outs = [p.communicate(timeout=120)[0].decode() for p in procs]
     for p, o in zip(procs, outs):
         assert p.returncode == 0, o
+
+
+def test_communicator_argument_errors():
+    """ft_comm_create rejects what FileGradSyncConfig::new rejects (distributed.rs:31-44), with
+    the same words, before it touches the context or NCCL."""
+    import ctypes as C
+    from ferrotensor_b200 import _lib
+    lib = _lib.load()
+    out = C.c_void_p()
+    fake_ctx = C.c_void_p(1)   # never dereferenced: the argument checks come first
+    assert lib.ft_comm_create(fake_ctx, 0, 0, None, 1000, C.byref(out)) == 1
+    assert "world_size must be >= 1" in _lib.last_error()
+    assert lib.ft_comm_create(fake_ctx, 2, 2, None, 1000, C.byref(out)) == 1
+    assert "rank 2 is out of range for world_size 2" in _lib.last_error()
+    assert lib.ft_comm_create(fake_ctx, 2, -1, None, 1000, C.byref(out)) == 1
+    assert lib.ft_comm_create(fake_ctx, 2, 1, None, 0, C.byref(out)) == 1
+    assert "timeout_ms" in _lib.last_error()
+    assert lib.ft_comm_create(None, 2, 1, None, 1000, C.byref(out)) == 1
+    assert lib.ft_comm_unique_id(None) == 1
+    assert lib.ft_comm_wait(None, 10) == 1
+    assert lib.ft_comm_allreduce_sum(None, None, 4) == 1
+    assert lib.ft_comm_destroy(None) == 0
+    assert lib.ft_model_allreduce_apply_gradients(None, None, 1.0, None, None) == 1
+
+
+def test_host_side_world_validation():
+    from ferrotensor_b200.distributed import validate_world
+    from ferrotensor_b200.trainer import AdamW, Trainer
+    validate_world(2, 1)
+    with pytest.raises(ValueError, match="world_size must be >= 1"):
+        validate_world(0, 0)
+    with pytest.raises(ValueError, match="rank 2 is out of range for world_size 2"):
+        validate_world(2, 2)
+
+    class M:
+        ctx = None
+    with pytest.raises(ValueError, match="communicator is required"):
+        Trainer(M(), AdamW(1e-3)).with_distributed(2, 0)

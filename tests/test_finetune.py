@@ -268,3 +268,34 @@ def test_run_saves_resumes_and_lands_on_the_same_bits(cuda_ctx, tmp_path, monkey
 def dataclass_replace(obj, **kw):
     import dataclasses
     return dataclasses.replace(obj, **kw)
+
+
+@pytest.mark.parametrize("n,world", [(1007, 2), (1007, 3), (9, 4), (3, 4)])
+def test_equal_shards_close_the_same_number_of_windows(n, world):
+    """Data-parallel ranks must issue the same number of collectives: with an odd dataset,
+    examples the trainer would drop scattered through it, every rank still gets the same
+    number of trainable examples, hence the same number of accumulation windows."""
+    from ferrotensor_b200.data import TrainingExample
+    from ferrotensor_b200.finetune import equal_shard, trainable_example
+    rng = np.random.default_rng(n * 31 + world)
+    examples = []
+    for i in range(n):
+        kind = rng.integers(0, 10)
+        if kind == 0:      # too short
+            ex = TrainingExample([i % 50], [1], [1])
+        elif kind == 1:    # nothing supervised
+            ex = TrainingExample([1, 2, 3], [2, 3, 4], [0, 0, 0])
+        else:
+            ex = TrainingExample([1, 2, 3, i % 50], [2, 3, i % 50, 5], [0, 1, 1, 1])
+        examples.append(ex)
+    shards = [equal_shard(examples, world, r) for r in range(world)]
+    assert len({len(s) for s in shards}) == 1
+    assert all(trainable_example(e) for s in shards for e in s)
+    kept = [e for e in examples if trainable_example(e)]
+    assert sum(len(s) for s in shards) == len(kept) // world * world
+    # disjoint, round-robin over the kept examples
+    for r, s in enumerate(shards):
+        assert [id(e) for e in s] == [id(kept[i]) for i in range(r, len(kept) // world * world, world)]
+    micro_per_step = 8
+    windows = {-(-len(s) // micro_per_step) for s in shards}
+    assert len(windows) == 1

@@ -3,8 +3,10 @@ hidden 2048, 32 heads of 64, ffn 8192, vocabulary 49152, tied head, f16 frozen b
 rank-16 adapters on all seven linears.
 
 Against the CPU oracle the full architecture runs on one sequence of 256 positions, which the
-oracle finishes in seconds; at the benchmark's micro-batch (8 sequences of 1024 positions) the
-step is checked through properties that need no oracle: bit-identical repeats, the same
+oracle finishes in seconds, and once on one sequence of the benchmark's own length (1024
+positions: every query tile of the attention kernels, the whole rotary table at theta 130000);
+at the benchmark's micro-batch (8 sequences of 1024 positions) the step is checked through
+properties that need no oracle: bit-identical repeats, the same
 gradient whether a batch runs as one micro-batch or two, rows without supervision that change
 nothing, and adapters with B = 0 whose A gradients are exactly zero."""
 
@@ -55,7 +57,7 @@ class _FullSize:
         self.adapters_cpu = {k: v.cpu() for k, v in adapters.items()}
         del weights, adapters
         torch.cuda.empty_cache()
-        self._oracle = None
+        self._oracle = {}
 
     def device_rows(self, ids, tg, mk):
         from ferrotensor_b200.trainer import batch_targets_weights
@@ -78,14 +80,15 @@ class _FullSize:
         self.ctx.synchronize()
         return self.model.grads.clone(), torch.cat(losses).cpu().numpy()
 
-    def oracle(self):
+    def oracle(self, positions=None):
         """Loss, logits and gradients of the oracle on the first positions of the first
         sequences of the workload's stream (computed once for the three modes)."""
-        if self._oracle is None:
+        positions = positions or self.positions
+        if positions not in self._oracle:
             from ferrotensor_b200.config import head_weight, synthetic_batch
             w, c = self.w, self.w.model
             short = copy.deepcopy(w)
-            short.seq_len = self.positions      # the workload's own mask rule, on short rows
+            short.seq_len = positions           # the workload's own mask rule, on short rows
             ids, tg, mk = synthetic_batch(short, self.sequences)
             mk[:, ::7] = 0                      # and holes in it
             ocfg = ol.OracleConfig(vocab=c.vocab, hidden=c.hidden, layers=c.layers, heads=c.heads,
@@ -98,8 +101,11 @@ class _FullSize:
             p["lm_head.weight"] = head_weight(c, self.weights_cpu, True)
             r = ol.forward_backward(ocfg, p, ids.astype(np.int64), tg.astype(np.int64), mk,
                                     seed_scale=1.0 / self.sequences)
-            self._oracle = (ids, tg, mk, r)
-        return self._oracle
+            self._oracle[positions] = (ids, tg, mk, r)
+        return self._oracle[positions]
+
+    def forget_oracle(self, positions):
+        self._oracle.pop(positions, None)
 
 
 @pytest.fixture(scope="module")
@@ -133,10 +139,10 @@ def _errors(got, exp):
     return err, scale, rel
 
 
-def _compare_with_oracle(h, mode_name, n_tensors):
+def _compare_with_oracle(h, mode_name, n_tensors, positions=None):
     from ferrotensor_b200.engine import GemmMode
     h.ctx.set_gemm_mode(GemmMode[mode_name])
-    ids, tg, mk, r = h.oracle()
+    ids, tg, mk, r = h.oracle(positions)
     atol_rel, rtol, l2 = TOLERANCE[mode_name]
     d_ids, d_tg, d_w = h.device_rows(ids, tg, mk)
     row_loss = torch.empty(ids.size, device=h.ctx.device, dtype=torch.float32)
@@ -175,6 +181,16 @@ def test_full_architecture_matches_the_oracle(headline, mode_name):
     """Loss, logits and all 336 adapter gradients of the full 24-block model against the
     oracle, in each GEMM mode, with the mode's stated tolerance."""
     _compare_with_oracle(headline, mode_name, 24 * 7 * 2)
+
+
+@pytest.mark.parametrize("mode_name", ["F32", "F16X2", "F16"])
+def test_full_architecture_at_the_benchmark_sequence_length(headline, mode_name):
+    """The same comparison on one sequence of 1024 positions, the benchmark's length: positions
+    256-1023 of the rotary table, eight query tiles per head in the forward attention kernel and
+    eight summed in its key/value-gradient kernel, composed through all 24 blocks."""
+    _compare_with_oracle(headline, mode_name, 24 * 7 * 2, positions=1024)
+    if mode_name == "F16":
+        headline.forget_oracle(1024)   # several hundred MB of logits and gradients
 
 
 @pytest.mark.parametrize("mode_name", ["F32", "F16X2", "F16"])

@@ -230,9 +230,9 @@ def test_block_checkpointing_gives_the_same_gradients(cuda_ctx):
 def test_nonfinite_gradients_skip_the_step(cuda_ctx):
     """lib.rs:330-335: a non-finite norm leaves parameters and moments untouched."""
     from ferrotensor_b200.config import synthetic_batch
-    from ferrotensor_b200.trainer import AdamW, StepStats, Trainer
+    from ferrotensor_b200.trainer import AdamW, StepStats, Trainer, WarmupCosineScheduler
     w, _, _, model = _tiny_setup(cuda_ctx)
-    tr = Trainer(model, AdamW(1e-2))
+    tr = Trainer(model, AdamW(1e-2)).with_lr_scheduler(WarmupCosineScheduler(1e-2, 1e-3, 2, 10))
     before = model.params.clone()
     model.grads.fill_(1.0)
     model.grads[3] = float("nan")
@@ -241,6 +241,15 @@ def test_nonfinite_gradients_skip_the_step(cuda_ctx):
     assert not s.optimizer_step and not np.isfinite(s.grad_norm)
     assert torch.equal(model.params, before) and not model.adam_m.any()
     assert tr.optimizer.t == 0.0
+    # the schedule does not advance on a skipped step and no learning rate is reported
+    assert tr.lr_scheduler.current_step() == tr.optimizer_step_count == 0
+    assert s.lr is None and tr.optimizer.lr == 1e-2
+    # the next good step is step 1 of the schedule
+    model.grads.fill_(1.0)
+    s = StepStats()
+    tr.apply_gradients(s)
+    assert s.optimizer_step and tr.lr_scheduler.current_step() == tr.optimizer_step_count == 1
+    assert abs(s.lr - 5e-3) < 1e-9
     model.close()
 
 

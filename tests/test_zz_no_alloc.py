@@ -1,12 +1,16 @@
-"""The allocation-free RMSNorm backward entry point, checked against the regular one.
+"""The allocation-free RMSNorm backward entry point, checked against the regular one and
+against the CPU oracle.
 
 Collected last on purpose: the entry point shares one fixed device array between all calls,
-so this file runs after every other GPU test and must also pass alone in a fresh process."""
+so this file runs after every other GPU test and must also pass alone in a fresh process.
+`test_this_file_is_collected_last` checks the position instead of trusting the file name."""
 
 import ctypes as C
 
 import numpy as np
 import pytest
+
+from oracle import kernels as ok
 
 pytestmark = pytest.mark.gpu
 
@@ -37,6 +41,10 @@ def test_noalloc_matches_regular_entry_point_twice_in_a_row(cuda_ctx, shapes):
         gx, gw = _run(cuda_ctx, "ft_rms_norm_backward_noalloc", x, w, g)
         assert np.all(np.abs(gx - ref_gx) <= 1e-5 + 1e-4 * np.abs(ref_gx))
         assert np.all(np.abs(gw - ref_gw) <= 1e-4 + 1e-4 * np.abs(ref_gw))
+        # and with the oracle, at the tolerance the kernel tests use for this operator
+        exp_gx, exp_gw = ok.rms_norm_backward(x, w, g, 1e-5)
+        assert np.all(np.abs(gx - exp_gx) <= 1e-5 + 1e-4 * np.abs(exp_gx))
+        assert np.all(np.abs(gw - exp_gw) <= 1e-4 + 1e-4 * np.abs(exp_gw))
         gx2, none = _run(cuda_ctx, "ft_rms_norm_backward_noalloc", x, w, g, want_gw=False)
         assert none is None and np.array_equal(gx2, gx)
 
@@ -47,3 +55,14 @@ def test_noalloc_rejects_shapes_beyond_the_fixed_scratch(cuda_ctx):
     x = np.zeros((rows, size), dtype=np.float32)
     with pytest.raises(FtError, match="exceeds the fixed scratch"):
         _run(cuda_ctx, "ft_rms_norm_backward_noalloc", x, np.ones(size, np.float32), x)
+
+
+def test_this_file_is_collected_last(request):
+    """A run that stops at the first failure must already have run every other test file."""
+    files = []
+    for item in request.session.items:
+        f = item.nodeid.split("::")[0]
+        if not files or files[-1] != f:
+            files.append(f)
+    if len(files) > 1:   # run as part of the suite
+        assert files[-1].endswith("test_zz_no_alloc.py"), files[-3:]
