@@ -57,9 +57,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if force or _stale(src, obj, headers):
             jobs.append((src, obj))
 
+    extra = os.environ.get("FT_NVCC_EXTRA", "").split()   # e.g. -DFT_ATTN_TIMING, -DFT_DEBUG_MARKERS
+
     def compile_one(job):
         src, obj = job
-        cmd = [nvcc(), *NVCC_FLAGS, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc(), *NVCC_FLAGS, *extra, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         return src, r
 

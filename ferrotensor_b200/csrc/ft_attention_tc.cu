@@ -190,7 +190,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
     // One thread keeps the K/V ring and the Q tile filled, so that the thread that issues the
     // products never spends its time on load instructions (about 75 cycles each) or on waiting
     // for a stage to come free.
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t sq = base + AttnSmem::Q_OFF, sk = base + AttnSmem::K_OFF, sv = base + AttnSmem::V_OFF;
       uint32_t gl = 0;     // key/value blocks loaded since the CTA started
       bool ok = true;
@@ -220,7 +220,7 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
     __syncwarp();
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t sq = base + AttnSmem::Q_OFF, sk = base + AttnSmem::K_OFF,
                      sv = base + AttnSmem::V_OFF, sp = base + AttnSmem::P_OFF;
       const uint32_t idesc_s = make_idesc(128, 64, 0, 0);                      // Q, K both K-major
@@ -996,7 +996,7 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
 // gradient times the power-of-two scale whose inverse is *inv_scale (device scalar, may be
 // NULL = 1).  stats holds the forward log-sum-exp at [2*row+1]; [2*row] receives Delta.
 // Writes dq [tokens, lddq] (heads*64 columns from dq), dk and dv [tokens, ldd] (kv_heads*64).
-int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q_col0, int k_col0,
+int ft_attention_bwd_tc_v1(FtContext* ctx, const __half* qkv16, long long ld, int q_col0, int k_col0,
                         int v_col0, const __half* o16, long long ldo, const __half* do16,
                         long long lddo, float* dq, long long lddq, float* dk, float* dv,
                         long long ldd, float* stats, const float* inv_scale, int batch, int seq,

@@ -207,7 +207,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       if constexpr (!KOUTER) {
         for (int p = (int)gridDim.x - 1 - (int)blockIdx.x; p < pre.tiles; p += gridDim.x) {
@@ -265,7 +265,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       int local = 0;
       if constexpr (!KOUTER) {
@@ -636,7 +636,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       for (int p = npairs - 1 - pair; p < pre.tiles; p += npairs) {
         for (int kb = 0; kb < kb_main; ++kb) {
@@ -673,7 +673,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader only)
-    if (lane == 0 && rank == 0) {
+    if (rank == 0 && elect_one()) {
       uint32_t stage = 0, phase = 0;
       int local = 0;
       for (int p = npairs - 1 - pair; p < pre.tiles; p += npairs, ++local) {
