@@ -51,6 +51,11 @@ def _stale(src: Path, obj: Path, headers) -> bool:
 def build(force: bool = False, verbose: bool = False) -> Path:
     OBJ.mkdir(parents=True, exist_ok=True)
     headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(INCLUDE.glob("*.h"))
+    # objects built with other flags (FT_NVCC_EXTRA) are stale whatever their age
+    stamp = OBJ / "flags.txt"
+    flags_now = " ".join(NVCC_FLAGS + os.environ.get("FT_NVCC_EXTRA", "").split())
+    if not stamp.exists() or stamp.read_text() != flags_now:
+        force = True
     jobs = []
     for src in sources():
         obj = OBJ / (src.stem + ".o")
@@ -73,6 +78,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 (OBJ / (src.stem + ".ptxas.log")).write_text(r.stderr)
                 if r.returncode != 0:
                     raise RuntimeError(f"nvcc failed on {src.name}")
+        stamp.write_text(flags_now)
     objs = [OBJ / (s.stem + ".o") for s in sources()]
     if jobs or not LIB.exists() or any(o.stat().st_mtime > LIB.stat().st_mtime for o in objs):
         cmd = [nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-ldl"]

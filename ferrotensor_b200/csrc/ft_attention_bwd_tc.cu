@@ -388,7 +388,9 @@ k_attn_bwd_dq_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_cons
         ++gd;
         TSTAMP(4);
       }
+#ifdef FT_ATTN_TIMING
       _acc[5] = gd;
+#endif
       TSTAMP_FLUSH(8);
     }
     __syncwarp();
@@ -440,6 +442,7 @@ k_attn_bwd_dq_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(c.bar(B_INFO_FREE + (it & 1)));
       const float delta = dl.x, lse2 = dl.y;
+      const bool tile_ragged = w.q0 + BT > seq;   // some rows of the tile lie past the sequence
       TSTAMP(0);
       for (int j = 0; ok && j < w.nblk; ++j, ++g) {
         const uint32_t sb = t_s + (g & 1) * 128 + lane_addr + hc * 64;
@@ -464,22 +467,32 @@ k_attn_bwd_dq_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_cons
           tc_ld32(sb + sub * 32, rs);
           tc_wait_ld();
           TSTAMP(3);
-#ifdef FT_ATTN_NOMATH
+          if (diag || tile_ragged) {
+            // the block on the diagonal, or a tile that runs past the sequence: per-element mask
 #pragma unroll
-          for (int cc = 0; cc < 32; cc += 2) packed[cc >> 1] = rs[cc] ^ rp[sub][cc + 1];
-#else
+            for (int cc = 0; cc < 32; cc += 2) {
+              float v[2];
 #pragma unroll
-          for (int cc = 0; cc < 32; cc += 2) {
-            float v[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              float p = ex2(fmaf(__uint_as_float(rs[cc + e]), c2, -lse2));
-              if (!row_ok || (diag && key0 + sub * 32 + cc + e > qi)) p = 0.f;
-              v[e] = p * (__uint_as_float(rp[sub][cc + e]) - delta);
+              for (int e = 0; e < 2; ++e) {
+                float p = ex2(fmaf(__uint_as_float(rs[cc + e]), c2, -lse2));
+                if (!row_ok || key0 + sub * 32 + cc + e > qi) p = 0.f;
+                v[e] = p * (__uint_as_float(rp[sub][cc + e]) - delta);
+              }
+              packed[cc >> 1] = pack_h2(v[0], v[1]);
             }
-            packed[cc >> 1] = pack_h2(v[0], v[1]);
+          } else {
+            // everything visible: packed pair arithmetic, three instructions for two elements
+            // beside the exponentials and the rounding
+            const float nl = -lse2, nd = -delta;
+#pragma unroll
+            for (int cc = 0; cc < 32; cc += 2) {
+              float x0, x1, t0, t1, v0, v1;
+              ffma2(x0, x1, __uint_as_float(rs[cc]), __uint_as_float(rs[cc + 1]), c2, c2, nl, nl);
+              fadd2(t0, t1, __uint_as_float(rp[sub][cc]), __uint_as_float(rp[sub][cc + 1]), nd, nd);
+              fmul2(v0, v1, ex2(x0), ex2(x1), t0, t1);
+              packed[cc >> 1] = pack_h2(v0, v1);
+            }
           }
-#endif
           // dS replaces the S columns this thread has just read (16 columns per 32 keys)
           tc_st16(sb + sub * 16, packed);
           TSTAMP(4);
@@ -650,7 +663,8 @@ k_attn_bwd_dkv_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
     float am = 0.f;
     // per-query {Delta, LSE in the log2 domain} of this warp's 64 queries: every key row needs
     // the same pairs, so each warp stages its own copy in shared memory (no cross-warp barrier)
-    float2* qi_s = (float2*)(c.gbase + Smem::ROW) + warp * 64;
+    float* nl_s = (float*)(c.gbase + Smem::ROW) + warp * 128;   // -LSE (log2 domain) of 64 queries
+    float* nd_s = nl_s + 64;                                    // -Delta of the same queries
     uint32_t g = 0;
     bool ok = true;
     bool pend = false;
@@ -697,12 +711,15 @@ k_attn_bwd_dkv_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
     for (int it = 0; ok && has; ++it) {
       const int kj = w.k0 + row;
       const bool row_ok = kj < seq;
+      const bool tile_ragged = w.k0 + BT > seq;   // some key rows of the tile lie past the sequence
       const bool has_next = k_tile(snake(it + 1), total, nkt, bk_count, group, kv_heads, seq, wn);
       for (int i = 0; ok && i < w.niter; ++i, ++g) {
         const int qs = w.k0 + (i % w.nqb) * BT;
         __syncwarp();
-        qi_s[lane] = make_float2(na.x, na.y * LOG2E);
-        qi_s[32 + lane] = make_float2(nb.x, nb.y * LOG2E);
+        nd_s[lane] = -na.x;
+        nl_s[lane] = -na.y * LOG2E;
+        nd_s[32 + lane] = -nb.x;
+        nl_s[32 + lane] = -nb.y * LOG2E;
         __syncwarp();
         // the next block's pairs (of the next tile after the last block) travel under this
         // block's arithmetic
@@ -726,20 +743,35 @@ k_attn_bwd_dkv_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
           uint32_t rs[32], pk_p[16], pk_ds[16];
           tc_ld32(sb + sub * 32, rs);
           tc_wait_ld();
+          if (need_mask || tile_ragged) {
 #pragma unroll
-          for (int cc = 0; cc < 32; cc += 2) {
-            float pv[2], dsv[2];
+            for (int cc = 0; cc < 32; cc += 2) {
+              float pv[2], dsv[2];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int qq = qs + hc * 64 + sub * 32 + cc + e;
-              const float2 dl = qi_s[sub * 32 + cc + e];   // x = Delta, y = LSE (log2 domain)
-              float p = ex2(fmaf(__uint_as_float(rs[cc + e]), c2, -dl.y));
-              if (!row_ok || (need_mask && (kj > qq || qq >= seq))) p = 0.f;
-              pv[e] = p;
-              dsv[e] = p * (__uint_as_float(rp[sub][cc + e]) - dl.x);
+              for (int e = 0; e < 2; ++e) {
+                const int qq = qs + hc * 64 + sub * 32 + cc + e;
+                float p = ex2(fmaf(__uint_as_float(rs[cc + e]), c2, nl_s[sub * 32 + cc + e]));
+                if (!row_ok || kj > qq || qq >= seq) p = 0.f;
+                pv[e] = p;
+                dsv[e] = p * (__uint_as_float(rp[sub][cc + e]) + nd_s[sub * 32 + cc + e]);
+              }
+              pk_p[cc >> 1] = pack_h2(pv[0], pv[1]);
+              pk_ds[cc >> 1] = pack_h2(dsv[0], dsv[1]);
             }
-            pk_p[cc >> 1] = pack_h2(pv[0], pv[1]);
-            pk_ds[cc >> 1] = pack_h2(dsv[0], dsv[1]);
+          } else {
+            // everything visible: packed pair arithmetic on two queries at a time
+#pragma unroll
+            for (int cc = 0; cc < 32; cc += 2) {
+              const float2 nl = *(const float2*)(nl_s + sub * 32 + cc);
+              const float2 nd = *(const float2*)(nd_s + sub * 32 + cc);
+              float x0, x1, t0, t1, d0, d1;
+              ffma2(x0, x1, __uint_as_float(rs[cc]), __uint_as_float(rs[cc + 1]), c2, c2, nl.x, nl.y);
+              fadd2(t0, t1, __uint_as_float(rp[sub][cc]), __uint_as_float(rp[sub][cc + 1]), nd.x, nd.y);
+              const float p0 = ex2(x0), p1 = ex2(x1);
+              fmul2(d0, d1, p0, p1, t0, t1);
+              pk_p[cc >> 1] = pack_h2(p0, p1);
+              pk_ds[cc >> 1] = pack_h2(d0, d1);
+            }
           }
           // the 32 S^T columns just read become [P (16) | dS (16)]
           tc_st16(sb + sub * 32, pk_p);
@@ -779,12 +811,6 @@ extern "C" int ft_debug_attn_timing(long long* out64) {
 }
 #endif
 
-int ft_attention_bwd_tc_v1(FtContext* ctx, const __half* qkv16, long long ld, int q_col0, int k_col0,
-                           int v_col0, const __half* o16, long long ldo, const __half* do16,
-                           long long lddo, float* dq, long long lddq, float* dk, float* dv,
-                           long long ldd, float* stats, const float* inv_scale, int batch, int seq,
-                           int heads, int kv_heads, int head_dim);
-
 // Backward on f16 operands: qkv16 rows (RoPE applied), o16 = forward output, do16 = output
 // gradient times the power-of-two scale whose inverse is *inv_scale (device scalar, may be
 // NULL = 1).  stats holds the forward log-sum-exp at [2*row+1]; [2*row] receives Delta.
@@ -800,10 +826,6 @@ int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
       bad32(dq, lddq) || bad32(dk, ldd) || bad32(dv, ldd) || (q_col0 % 8) || (k_col0 % 8) ||
       (v_col0 % 8) || !stats)
     return FT_ERR_UNSUPPORTED;
-  if (getenv("FT_ATTN_BWD_V1"))   // the earlier pair of kernels (64-key blocks through shared memory)
-    return ft_attention_bwd_tc_v1(ctx, qkv16, ld, q_col0, k_col0, v_col0, o16, ldo, do16, lddo, dq,
-                                  lddq, dk, dv, ldd, stats, inv_scale, batch, seq, heads, kv_heads,
-                                  head_dim);
   const uint64_t T = (uint64_t)batch * seq;
   CUtensorMap m_qkv, m_do, m_o;
   FT_TRY(ft_tc::make_map(ctx, &m_qkv, qkv16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)ld, T, (uint64_t)ld, 64, 128));

@@ -1,27 +1,24 @@
-// Causal flash attention on the Blackwell tensor cores (head_dim 64, f16 operands, f32
-// accumulation and softmax), grouped-query.  Operands are read straight from the fused
-// q|k|v buffer [tokens, nq + 2 nkv] (f16, RoPE already applied) with TMA: one 128 x 64 box
-// shape serves the query, key and value tiles.
+// Forward of causal flash attention on the Blackwell tensor cores (head_dim 64, f16 operands,
+// f32 accumulation and softmax), grouped-query; the backward kernels are in
+// ft_attention_bwd_tc.cu.  Operands are read straight from the fused q|k|v buffer
+// [tokens, nq + 2 nkv] (f16, RoPE already applied) with TMA.
 //
-// Forward, one CTA per (128 queries, head), over 64-key blocks:
+// A persistent CTA walks (128 queries, head) tiles over 64-key blocks:
 //   S = Q K^T      tcgen05.mma 128 x 64 x 64 into one of two tensor-memory accumulators
 //   softmax        4 warps, thread t owns query row t (= TMEM lane t): tcgen05.ld the row,
 //                  exp2 against a lazily raised maximum, P written to shared memory as f16 in
 //                  the 128-byte-swizzled K-major form the next product wants
 //   O += P [V|1]   tcgen05.mma 128 x 80 x 64, V used in place as an N-major operand; the
 //                  ones column makes column 64 of the accumulator the softmax denominator
-// One extra warp issues all TMA loads and MMAs; the S product of block j+1 is issued as soon
-// as the softmax warps have read block j, so it overlaps with their arithmetic and with P V.
+// One warp issues the products, another the TMA loads (each behind elect.sync, which keeps
+// descriptors in uniform registers: 13 instead of 71 cycles per tcgen05.mma issued); the S
+// product of block j+1 is issued as soon as the softmax warps have read block j, so it overlaps
+// with their arithmetic and with P V.
 // (Measured and not kept: eight softmax warps with a half-row maximum exchange; paired f16
-// exponentials; a quarter of the exponentials as a polynomial on the FMA pipe; releasing S / dP to the next product before the arithmetic in the backward
-// kernels - per block the time goes to the hand-offs between the warps and the tensor pipe,
-// not to the arithmetic; a separate loader warp in the backward kernels (8 % slower, while the
-// same split made the forward kernel 10 % faster); the backward kernels made persistent like the forward one - the dQ
-// kernel ran as before, the dK / dV kernel 20 % slower.  Cycle counts inside the forward kernel:
-// of about 2600 cycles per 64-key block, 1100 are the exponentials (two CTAs share the SM's
-// special-function unit), the rest are barrier operations of 100-200 cycles each, the
-// shared-memory hand-over of P, and per-tile work; one tcgen05.mma costs the issuing thread
-// about 55 cycles, a TMA load about 75.)
+// exponentials; a quarter of the exponentials as a polynomial on the FMA pipe.  Cycle counts
+// inside this kernel: of about 2600 cycles per 64-key block, 1100 are the exponentials (two
+// CTAs share the SM's special-function unit), the rest are barrier operations of 100-200 cycles
+// each, the shared-memory hand-over of P, and per-tile work.)
 // All waits are bounded (see ft_tc.cuh).
 #include <math.h>
 #include <stdlib.h>
@@ -36,8 +33,6 @@ constexpr int AT_Q = 128;        // queries per CTA
 constexpr int AT_KV = 128;       // keys per block
 constexpr int AT_D = 64;         // head_dim
 constexpr int AT_THREADS = 192;  // forward: warps 0..3 softmax, warp 4 MMA issuer, warp 5 loads
-constexpr int BW_THREADS = 288;  // backward: warps 0..7 arithmetic, warp 8 issuer
-constexpr int BW_ISSUER = 8;
 constexpr int TILE_BYTES = 128 * 64 * 2;  // one 128 x 64 f16 tile = 16 KiB
 
 constexpr int HALF_TILE = 64 * 64 * 2;  // 64 x 64 f16 tile = 8 KiB
@@ -441,524 +436,6 @@ k_attn_fwd_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constan
   }
 }
 
-// =========================================================================================
-// Backward.  Two kernels, no atomics (results are identical from run to run):
-//   k_attn_bwd_dq_tc   one CTA per (128 queries, head): over 64-key blocks,
-//                      S = Q K^T, dP = dO V^T (tensor memory), dS = P (dP - Delta) in registers
-//                      -> f16 shared tile, dQ += dS K accumulated in tensor memory.
-//                      Also computes Delta = dO . O per query row and stores it for pass 2.
-//   k_attn_bwd_dkv_tc  one CTA per (128 keys, KV head): over the query heads of the group and
-//                      64-query blocks at or below the diagonal, S^T = K Q^T, dP^T = V dO^T,
-//                      dV += P^T dO, dK += dS^T Q, both accumulated in tensor memory.
-// dO arrives as f16 after a power-of-two scale S (gradients are far below f16's normal
-// range); everything downstream is linear in dO, so the epilogues multiply by 1/S.
-// =========================================================================================
-
-struct BwdQSmem {
-  static constexpr int Q_OFF = 0;                         // 128 x 64
-  static constexpr int DO_OFF = Q_OFF + TILE_BYTES;       // 128 x 64
-  static constexpr int K_OFF = DO_OFF + TILE_BYTES;       // 2 stages of 64 x 64
-  static constexpr int V_OFF = K_OFF + 2 * HALF_TILE;     // 2 stages of 64 x 64
-  static constexpr int DS_OFF = V_OFF + 2 * HALF_TILE;    // 128 q x 64 keys, K-major
-  static constexpr int BAR_OFF = DS_OFF + TILE_BYTES;
-  static constexpr int NBAR = 8;  // q_full, kv_full[2], sp_full, sp_free, ds_full, dq_done, spare
-  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
-  static constexpr int DYN_BYTES = TOTAL + 1024;
-};
-
-__global__ void __launch_bounds__(BW_THREADS, 2)
-k_attn_bwd_dq_tc(const __grid_constant__ CUtensorMap map_q128, const __grid_constant__ CUtensorMap map_kv64,
-                 const __grid_constant__ CUtensorMap map_do128, const __half* __restrict__ do16,
-                 long long lddo, const __half* __restrict__ o16, long long ldo,
-                 float* __restrict__ dq, long long lddq, float* __restrict__ stats, int seq,
-                 int heads, int kv_heads, int q_col0, int k_col0, int v_col0, float scale,
-                 const float* __restrict__ inv_scale_ptr, int* amax_slot, int* status) {
-  ft_pdl_wait();
-  ft_pdl_launch();
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* gbase = smem_raw + (base - raw);
-  const uint32_t bar0 = base + BwdQSmem::BAR_OFF;
-  const uint32_t bar_q = bar0, bar_kv = bar0 + 8, bar_spfull = bar0 + 24, bar_spfree = bar0 + 32,
-                 bar_dsfull = bar0 + 40, bar_dqdone = bar0 + 48;
-  uint32_t* tmem_slot = (uint32_t*)(gbase + BwdQSmem::BAR_OFF + BwdQSmem::NBAR * 8);
-  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;
-  const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
-  const int kvh = h / (heads / kv_heads);
-  const int q0 = qblk * AT_Q;
-  const int nblk = min((q0 + AT_Q) / 64, (seq + 63) / 64);  // 64-key blocks at or below the diagonal
-  const int tok0 = b * seq;
-  constexpr uint32_t TMEM_COLS = 256;  // S [0,64), dP [64,128), dQ [128,192)
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar_q, 1);
-    mbar_init(bar_kv, 1);
-    mbar_init(bar_kv + 8, 1);
-    mbar_init(bar_spfull, 1);
-    mbar_init(bar_spfree, 8);
-    mbar_init(bar_dsfull, 8);
-    mbar_init(bar_dqdone, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == BW_ISSUER) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 64, tmem_dq = tmem_base + 128;
-
-  if (warp == BW_ISSUER) {
-    if (lane == 0) {
-      const uint32_t sq = base + BwdQSmem::Q_OFF, sdo = base + BwdQSmem::DO_OFF,
-                     sk = base + BwdQSmem::K_OFF, sv = base + BwdQSmem::V_OFF,
-                     sds = base + BwdQSmem::DS_OFF;
-      const uint32_t idesc_kk = make_idesc(128, 64, 0, 0);              // both K-major
-      const uint32_t idesc_kn = make_idesc(128, 64, 0, 0) | (1u << 16); // B N-major
-      auto load_kv = [&](int j) {
-        const int s = j & 1;
-        mbar_expect_tx(bar_kv + s * 8, 2 * HALF_TILE);
-        tma_load_2d(sk + s * HALF_TILE, &map_kv64, bar_kv + s * 8, k_col0 + kvh * AT_D, tok0 + j * 64);
-        tma_load_2d(sv + s * HALF_TILE, &map_kv64, bar_kv + s * 8, v_col0 + kvh * AT_D, tok0 + j * 64);
-      };
-      auto mma_sp = [&](int j) {
-        const int s = j & 1;
-        const uint64_t dq_ = make_desc_sw128(sq), ddo = make_desc_sw128(sdo);
-        const uint64_t dk_ = make_desc_sw128(sk + s * HALF_TILE), dv_ = make_desc_sw128(sv + s * HALF_TILE);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_f16(tmem_s, dq_ + (uint64_t)(k * 2), dk_ + (uint64_t)(k * 2), idesc_kk, k > 0 ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_f16(tmem_dp, ddo + (uint64_t)(k * 2), dv_ + (uint64_t)(k * 2), idesc_kk, k > 0 ? 1u : 0u);
-        tc_commit(bar_spfull);
-      };
-      mbar_expect_tx(bar_q, 2 * TILE_BYTES);
-      tma_load_2d(sq, &map_q128, bar_q, q_col0 + h * AT_D, tok0 + q0);
-      tma_load_2d(sdo, &map_do128, bar_q, h * AT_D, tok0 + q0);
-      load_kv(0);
-      if (nblk > 1) load_kv(1);
-      bool ok = mbar_wait(bar_q, 0, abort_flag, status, 31) &&
-                mbar_wait(bar_kv, 0, abort_flag, status, 32);
-      if (ok) {
-        tc_fence_after();
-        mma_sp(0);
-      }
-      for (int j = 0; ok && j < nblk; ++j) {
-        if (j + 1 < nblk) {
-          ok = mbar_wait(bar_kv + ((j + 1) & 1) * 8, ((j + 1) >> 1) & 1, abort_flag, status, 33) &&
-               mbar_wait(bar_spfree, j & 1, abort_flag, status, 34);
-          if (!ok) break;
-          tc_fence_after();
-          mma_sp(j + 1);
-        }
-        ok = mbar_wait(bar_dsfull, j & 1, abort_flag, status, 35);
-        if (!ok) break;
-        tc_fence_after();
-        {
-          // dQ += dS[128 q x 64 keys] . K[64 keys x 64 d]: K tile in place as an N-major operand
-          const uint64_t da = make_desc_sw128(sds);
-          const uint64_t db = make_desc_mn_sw128(sk + (j & 1) * HALF_TILE, HALF_TILE);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma_f16(tmem_dq, da + (uint64_t)(k * 2), db + (uint64_t)(k * 128), idesc_kn,
-                       (j > 0 || k > 0) ? 1u : 0u);
-          tc_commit(bar_dqdone);
-        }
-        if (j + 2 < nblk) {
-          ok = mbar_wait(bar_dqdone, j & 1, abort_flag, status, 36);
-          if (!ok) break;
-          load_kv(j + 2);
-        }
-      }
-    }
-    __syncwarp();
-  } else {
-    // eight warps: warp w works on the 32 query rows of TMEM quadrant w % 4 and on the 32-key
-    // half w / 4 of every block
-    const int quad = warp & 3, hc = warp >> 2;
-    const int row = quad * 32 + lane;
-    const int qi = q0 + row;
-    const bool row_ok = qi < seq;
-    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    uint8_t* ds_smem = gbase + BwdQSmem::DS_OFF;
-    const size_t srow = ((size_t)b * heads + h) * seq + (row_ok ? qi : 0);
-    // Delta = dO . O for this row (both f16 in global memory)
-    float delta = 0.f, lse2 = 0.f;
-    if (row_ok) {
-      const long long tok = (long long)tok0 + qi;
-      const uint4* pd = (const uint4*)(do16 + tok * lddo + (long long)h * AT_D);
-      const uint4* po = (const uint4*)(o16 + tok * ldo + (long long)h * AT_D);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        uint4 a = pd[i], c = po[i];
-        const __half2* ha = (const __half2*)&a;
-        const __half2* hc = (const __half2*)&c;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float2 fa = __half22float2(ha[t]), fc = __half22float2(hc[t]);
-          delta += fa.x * fc.x + fa.y * fc.y;
-        }
-      }
-      lse2 = stats[2 * srow + 1] * 1.4426950408889634f;
-      if (hc == 0) stats[2 * srow] = delta;
-    }
-    const float c2 = scale * 1.4426950408889634f;
-    bool ok = true;
-    for (int j = 0; ok && j < nblk; ++j) {
-      ok = mbar_wait(bar_spfull, j & 1, abort_flag, status, 41);
-      if (!ok) break;
-      tc_fence_after();
-      const bool need_mask = (j * 64 + 63) > q0;  // block touches the diagonal
-      uint32_t packed[16];
-      {
-        uint32_t rs[32], rp[32];
-        tc_ld32(tmem_s + lane_addr + hc * 32, rs);
-        tc_ld32(tmem_dp + lane_addr + hc * 32, rp);
-        tc_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float v[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int key = j * 64 + hc * 32 + c + e;
-            float p = ex2(fmaf(__uint_as_float(rs[c + e]), c2, -lse2));
-            if (!row_ok || (need_mask && key > qi)) p = 0.f;
-            v[e] = p * (__uint_as_float(rp[c + e]) - delta);
-          }
-          packed[c >> 1] = pack_h2(v[0], v[1]);
-        }
-      }
-      // S and dP are in registers: the next pair of products may overwrite them
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_spfree);
-      // the previous dQ product must have finished reading the dS tile
-      if (j > 0) {
-        ok = mbar_wait(bar_dqdone, (j - 1) & 1, abort_flag, status, 42);
-        if (!ok) break;
-      }
-      uint8_t* rowp = ds_smem + (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        *(uint4*)(rowp + (((hc * 4 + q) ^ (row & 7)) << 4)) =
-            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_dsfull);
-    }
-    if (ok) ok = mbar_wait(bar_dqdone, (nblk - 1) & 1, abort_flag, status, 43);
-    if (ok) {
-      tc_fence_after();
-      const float alpha = scale * (inv_scale_ptr ? *inv_scale_ptr : 1.0f);
-      float am = 0.f;
-      {
-        const int cb = hc;
-        uint32_t r[32];
-        tc_ld32(tmem_dq + lane_addr + cb * 32, r);
-        tc_wait_ld();
-        if (row_ok) {
-          float* o = dq + ((long long)tok0 + qi) * lddq + (long long)h * AT_D + cb * 32;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float4 v = make_float4(alpha * __uint_as_float(r[i]), alpha * __uint_as_float(r[i + 1]),
-                                   alpha * __uint_as_float(r[i + 2]), alpha * __uint_as_float(r[i + 3]));
-            *(float4*)(o + i) = v;
-            am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-          }
-        }
-      }
-      if (amax_slot) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        if (lane == 0 && am > 0.f && __float_as_int(am) > *(volatile int*)amax_slot)
-          atomicMax(amax_slot, __float_as_int(am));
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (*abort_flag) {
-    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == BW_ISSUER) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(TMEM_COLS)
-                 : "memory");
-  }
-}
-
-struct BwdKSmem {
-  static constexpr int K_OFF = 0;                         // 128 keys x 64
-  static constexpr int V_OFF = K_OFF + TILE_BYTES;        // 128 keys x 64
-  static constexpr int Q_OFF = V_OFF + TILE_BYTES;        // 2 stages of 64 q x 64
-  static constexpr int DO_OFF = Q_OFF + 2 * HALF_TILE;    // 2 stages of 64 q x 64
-  static constexpr int PT_OFF = DO_OFF + 2 * HALF_TILE;   // 128 keys x 64 q, K-major
-  static constexpr int DST_OFF = PT_OFF + TILE_BYTES;     // 128 keys x 64 q, K-major
-  static constexpr int ROW_OFF = DST_OFF + TILE_BYTES;    // per warp: 32 x {delta, lse2}
-  static constexpr int BAR_OFF = ROW_OFF + 8 * 32 * 2 * 4;
-  static constexpr int NBAR = 8;  // kv_full, qd_full[2], sp_full, sp_free, ds_full, acc_done, spare
-  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
-  static constexpr int DYN_BYTES = TOTAL + 1024;
-};
-
-__global__ void __launch_bounds__(BW_THREADS, 2)
-k_attn_bwd_dkv_tc(const __grid_constant__ CUtensorMap map_kv128, const __grid_constant__ CUtensorMap map_q64,
-                  const __grid_constant__ CUtensorMap map_do64, float* __restrict__ dk,
-                  float* __restrict__ dv, long long ldd, const float* __restrict__ stats, int seq,
-                  int heads, int kv_heads, int q_col0, int k_col0, int v_col0, float scale,
-                  const float* __restrict__ inv_scale_ptr, int* amax_slot, int* status) {
-  ft_pdl_wait();
-  ft_pdl_launch();
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* gbase = smem_raw + (base - raw);
-  const uint32_t bar0 = base + BwdKSmem::BAR_OFF;
-  const uint32_t bar_kv = bar0, bar_qd = bar0 + 8, bar_spfull = bar0 + 24, bar_spfree = bar0 + 32,
-                 bar_dsfull = bar0 + 40, bar_acc = bar0 + 48;
-  uint32_t* tmem_slot = (uint32_t*)(gbase + BwdKSmem::BAR_OFF + BwdKSmem::NBAR * 8);
-  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kblk = blockIdx.x;  // early key blocks see the most queries and run first
-  const int bk = blockIdx.y, b = bk / kv_heads, kvh = bk % kv_heads;
-  const int group = heads / kv_heads;
-  const int k0 = kblk * AT_KV;
-  const int nqb = (seq - k0 + 63) / 64;    // 64-query blocks from the diagonal to the end
-  const int niter = group * nqb;
-  const int tok0 = b * seq;
-  constexpr uint32_t TMEM_COLS = 256;  // S^T [0,64), dP^T [64,128), dK [128,192), dV [192,256)
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar_kv, 1);
-    mbar_init(bar_qd, 1);
-    mbar_init(bar_qd + 8, 1);
-    mbar_init(bar_spfull, 1);
-    mbar_init(bar_spfree, 8);
-    mbar_init(bar_dsfull, 8);
-    mbar_init(bar_acc, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == BW_ISSUER) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_st = tmem_base, tmem_dpt = tmem_base + 64, tmem_dk = tmem_base + 128,
-                 tmem_dv = tmem_base + 192;
-
-  if (warp == BW_ISSUER) {
-    if (lane == 0) {
-      const uint32_t sk = base + BwdKSmem::K_OFF, sv = base + BwdKSmem::V_OFF,
-                     sq = base + BwdKSmem::Q_OFF, sdo = base + BwdKSmem::DO_OFF,
-                     spt = base + BwdKSmem::PT_OFF, sdst = base + BwdKSmem::DST_OFF;
-      const uint32_t idesc_kk = make_idesc(128, 64, 0, 0);
-      const uint32_t idesc_kn = make_idesc(128, 64, 0, 0) | (1u << 16);
-      auto load_qd = [&](int it) {
-        const int s = it & 1, g = it / nqb, i = it % nqb, h = kvh * group + g;
-        mbar_expect_tx(bar_qd + s * 8, 2 * HALF_TILE);
-        tma_load_2d(sq + s * HALF_TILE, &map_q64, bar_qd + s * 8, q_col0 + h * AT_D, tok0 + k0 + i * 64);
-        tma_load_2d(sdo + s * HALF_TILE, &map_do64, bar_qd + s * 8, h * AT_D, tok0 + k0 + i * 64);
-      };
-      auto mma_sp = [&](int it) {
-        const int s = it & 1;
-        const uint64_t dk_ = make_desc_sw128(sk), dv_ = make_desc_sw128(sv);
-        const uint64_t dq_ = make_desc_sw128(sq + s * HALF_TILE), ddo = make_desc_sw128(sdo + s * HALF_TILE);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_f16(tmem_st, dk_ + (uint64_t)(k * 2), dq_ + (uint64_t)(k * 2), idesc_kk, k > 0 ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_f16(tmem_dpt, dv_ + (uint64_t)(k * 2), ddo + (uint64_t)(k * 2), idesc_kk, k > 0 ? 1u : 0u);
-        tc_commit(bar_spfull);
-      };
-      mbar_expect_tx(bar_kv, 2 * TILE_BYTES);
-      tma_load_2d(sk, &map_kv128, bar_kv, k_col0 + kvh * AT_D, tok0 + k0);
-      tma_load_2d(sv, &map_kv128, bar_kv, v_col0 + kvh * AT_D, tok0 + k0);
-      load_qd(0);
-      if (niter > 1) load_qd(1);
-      bool ok = mbar_wait(bar_kv, 0, abort_flag, status, 51) &&
-                mbar_wait(bar_qd, 0, abort_flag, status, 52);
-      if (ok) {
-        tc_fence_after();
-        mma_sp(0);
-      }
-      for (int it = 0; ok && it < niter; ++it) {
-        if (it + 1 < niter) {
-          ok = mbar_wait(bar_qd + ((it + 1) & 1) * 8, ((it + 1) >> 1) & 1, abort_flag, status, 53) &&
-               mbar_wait(bar_spfree, it & 1, abort_flag, status, 54);
-          if (!ok) break;
-          tc_fence_after();
-          mma_sp(it + 1);
-        }
-        ok = mbar_wait(bar_dsfull, it & 1, abort_flag, status, 55);
-        if (!ok) break;
-        tc_fence_after();
-        {
-          const int s = it & 1;
-          const uint64_t dpt = make_desc_sw128(spt), ddst = make_desc_sw128(sdst);
-          const uint64_t bdo = make_desc_mn_sw128(sdo + s * HALF_TILE, HALF_TILE);
-          const uint64_t bq = make_desc_mn_sw128(sq + s * HALF_TILE, HALF_TILE);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)   // dV += P^T[128 keys x 64 q] . dO[64 q x 64 d]
-            tc_mma_f16(tmem_dv, dpt + (uint64_t)(k * 2), bdo + (uint64_t)(k * 128), idesc_kn,
-                       (it > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)   // dK += dS^T . Q
-            tc_mma_f16(tmem_dk, ddst + (uint64_t)(k * 2), bq + (uint64_t)(k * 128), idesc_kn,
-                       (it > 0 || k > 0) ? 1u : 0u);
-          tc_commit(bar_acc);
-        }
-        if (it + 2 < niter) {
-          ok = mbar_wait(bar_acc, it & 1, abort_flag, status, 56);
-          if (!ok) break;
-          load_qd(it + 2);
-        }
-      }
-    }
-    __syncwarp();
-  } else {
-    // eight warps: warp w works on the 32 key rows of TMEM quadrant w % 4 and on the 32-query
-    // half w / 4 of every block
-    const int quad = warp & 3, hc = warp >> 2;
-    const int row = quad * 32 + lane;       // key row in the tile
-    const int kj = k0 + row;
-    const bool row_ok = kj < seq;
-    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    uint8_t* pt_smem = gbase + BwdKSmem::PT_OFF;
-    uint8_t* dst_smem = gbase + BwdKSmem::DST_OFF;
-    const float c2 = scale * 1.4426950408889634f;
-    bool ok = true;
-    for (int it = 0; ok && it < niter; ++it) {
-      const int g = it / nqb, i = it % nqb, h = kvh * group + g;
-      const int qs = k0 + i * 64;
-      // per-query {Delta, LSE in the log2 domain} of this warp's 32 queries: every key row needs
-      // the same pairs, so each warp stages its own copy in shared memory (no cross-warp barrier)
-      float2* qi_s = (float2*)(gbase + BwdKSmem::ROW_OFF) + warp * 32;
-      {
-        const float2* qinfo = (const float2*)(stats + 2 * (((size_t)b * heads + h) * seq));
-        __syncwarp();
-        float2 dl = qinfo[min(qs + hc * 32 + lane, seq - 1)];
-        dl.y *= 1.4426950408889634f;
-        qi_s[lane] = dl;
-        __syncwarp();
-      }
-      ok = mbar_wait(bar_spfull, it & 1, abort_flag, status, 61);
-      if (!ok) break;
-      tc_fence_after();
-      const bool need_mask = qs < k0 + AT_KV - 1 || qs + 64 > seq;
-      uint32_t pk_p[16], pk_ds[16];
-      {
-        uint32_t rs[32], rp[32];
-        tc_ld32(tmem_st + lane_addr + hc * 32, rs);
-        tc_ld32(tmem_dpt + lane_addr + hc * 32, rp);
-        tc_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int qq = qs + hc * 32 + c + e;
-            const float2 dl = qi_s[c + e];   // x = Delta, y = LSE (log2 domain)
-            float p = ex2(fmaf(__uint_as_float(rs[c + e]), c2, -dl.y));
-            if (!row_ok || (need_mask && (kj > qq || qq >= seq))) p = 0.f;
-            pv[e] = p;
-            dsv[e] = p * (__uint_as_float(rp[c + e]) - dl.x);
-          }
-          pk_p[c >> 1] = pack_h2(pv[0], pv[1]);
-          pk_ds[c >> 1] = pack_h2(dsv[0], dsv[1]);
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_spfree);
-      if (it > 0) {
-        ok = mbar_wait(bar_acc, (it - 1) & 1, abort_flag, status, 62);
-        if (!ok) break;
-      }
-      const int off = (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int sw = (((hc * 4 + q) ^ (row & 7)) << 4);
-        *(uint4*)(pt_smem + off + sw) = make_uint4(pk_p[4 * q], pk_p[4 * q + 1], pk_p[4 * q + 2], pk_p[4 * q + 3]);
-        *(uint4*)(dst_smem + off + sw) = make_uint4(pk_ds[4 * q], pk_ds[4 * q + 1], pk_ds[4 * q + 2], pk_ds[4 * q + 3]);
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_dsfull);
-    }
-    if (ok) ok = mbar_wait(bar_acc, (niter - 1) & 1, abort_flag, status, 63);
-    if (ok) {
-      tc_fence_after();
-      const float inv_s = inv_scale_ptr ? *inv_scale_ptr : 1.0f;
-      const float ak = scale * inv_s, av = inv_s;
-      float am = 0.f;
-      {
-        const int cb = hc;
-        uint32_t rk[32], rv[32];
-        tc_ld32(tmem_dk + lane_addr + cb * 32, rk);
-        tc_ld32(tmem_dv + lane_addr + cb * 32, rv);
-        tc_wait_ld();
-        if (row_ok) {
-          const long long tok = (long long)tok0 + kj;
-          float* ok_ = dk + tok * ldd + (long long)kvh * AT_D + cb * 32;
-          float* ov_ = dv + tok * ldd + (long long)kvh * AT_D + cb * 32;
-#pragma unroll
-          for (int i2 = 0; i2 < 32; i2 += 4) {
-            *(float4*)(ok_ + i2) = make_float4(ak * __uint_as_float(rk[i2]), ak * __uint_as_float(rk[i2 + 1]),
-                                               ak * __uint_as_float(rk[i2 + 2]), ak * __uint_as_float(rk[i2 + 3]));
-            *(float4*)(ov_ + i2) = make_float4(av * __uint_as_float(rv[i2]), av * __uint_as_float(rv[i2 + 1]),
-                                               av * __uint_as_float(rv[i2 + 2]), av * __uint_as_float(rv[i2 + 3]));
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              am = fmaxf(am, fmaxf(fabsf(ak * __uint_as_float(rk[i2 + e])), fabsf(av * __uint_as_float(rv[i2 + e]))));
-          }
-        }
-      }
-      if (amax_slot) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        if (lane == 0 && am > 0.f && __float_as_int(am) > *(volatile int*)amax_slot)
-          atomicMax(amax_slot, __float_as_int(am));
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (*abort_flag) {
-    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == BW_ISSUER) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(TMEM_COLS)
-                 : "memory");
-  }
-}
-
 }  // namespace
 
 // Forward on f16 q|k|v rows (RoPE applied): writes f16 and/or f32 output rows [tokens, heads*64]
@@ -989,53 +466,5 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
   FT_LAUNCH_PDL(ctx, k_attn_fwd_tc, grid, AT_THREADS, AttnSmem::DYN_BYTES, q128, kv64, out16, ldo16,
                 out32, ldo32, stats, seq, heads, kv_heads, batch * heads, q_col0, k_col0, v_col0,
                 scale_log2e, ctx->status_dev);
-  return FT_OK;
-}
-
-// Backward on f16 operands: qkv16 rows (RoPE applied), o16 = forward output, do16 = output
-// gradient times the power-of-two scale whose inverse is *inv_scale (device scalar, may be
-// NULL = 1).  stats holds the forward log-sum-exp at [2*row+1]; [2*row] receives Delta.
-// Writes dq [tokens, lddq] (heads*64 columns from dq), dk and dv [tokens, ldd] (kv_heads*64).
-int ft_attention_bwd_tc_v1(FtContext* ctx, const __half* qkv16, long long ld, int q_col0, int k_col0,
-                        int v_col0, const __half* o16, long long ldo, const __half* do16,
-                        long long lddo, float* dq, long long lddq, float* dk, float* dv,
-                        long long ldd, float* stats, const float* inv_scale, int batch, int seq,
-                        int heads, int kv_heads, int head_dim) {
-  auto bad16 = [](const void* p, long long l) { return (l % 8) || (((uintptr_t)p) & 15); };
-  auto bad32 = [](const void* p, long long l) { return (l % 4) || (((uintptr_t)p) & 15); };
-  if (head_dim != AT_D || bad16(qkv16, ld) || bad16(o16, ldo) || bad16(do16, lddo) ||
-      bad32(dq, lddq) || bad32(dk, ldd) || bad32(dv, ldd) || (q_col0 % 8) || (k_col0 % 8) ||
-      (v_col0 % 8) || !stats)
-    return FT_ERR_UNSUPPORTED;
-  FT_REQUIRE((long long)batch * heads <= 65535, "attention: batch*heads exceeds 65535");
-  const uint64_t T = (uint64_t)batch * seq;
-  CUtensorMap q128, kv64, do128, do64;
-  FT_TRY(ft_tc::make_map(ctx, &q128, qkv16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)ld, T, (uint64_t)ld, 64, 128));
-  FT_TRY(ft_tc::make_map(ctx, &kv64, qkv16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)ld, T, (uint64_t)ld, 64, 64));
-  FT_TRY(ft_tc::make_map(ctx, &do128, do16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)lddo, T, (uint64_t)lddo, 64, 128));
-  FT_TRY(ft_tc::make_map(ctx, &do64, do16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (uint64_t)lddo, T, (uint64_t)lddo, 64, 64));
-  static bool configured[FT_MAX_DEVICES] = {};   // function attributes are per device
-  if (!configured[ctx->device]) {
-    FT_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 BwdQSmem::DYN_BYTES));
-    FT_CUDA(cudaFuncSetAttribute(k_attn_bwd_dkv_tc, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 BwdKSmem::DYN_BYTES));
-    configured[ctx->device] = true;
-  }
-  const float scale = 1.0f / sqrtf((float)head_dim);
-  int* am = ctx->amax_out;   // armed: the gradients' largest magnitude goes to the amax slot
-  if (am) ctx->amax_ready = true;
-  {
-    dim3 grid(ft_cdiv(seq, AT_Q), batch * heads);
-    FT_LAUNCH_PDL(ctx, k_attn_bwd_dq_tc, grid, BW_THREADS, BwdQSmem::DYN_BYTES, q128, kv64, do128, do16,
-              lddo, o16, ldo, dq, lddq, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale,
-              inv_scale, am, ctx->status_dev);
-  }
-  {
-    dim3 grid(ft_cdiv(seq, AT_KV), batch * kv_heads);
-    FT_LAUNCH_PDL(ctx, k_attn_bwd_dkv_tc, grid, BW_THREADS, BwdKSmem::DYN_BYTES, q128, kv64, do64, dk, dv,
-              ldd, stats, seq, heads, kv_heads, q_col0, k_col0, v_col0, scale, inv_scale, am,
-              ctx->status_dev);
-  }
   return FT_OK;
 }

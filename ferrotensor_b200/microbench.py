@@ -90,8 +90,7 @@ def attention(args):
     ctx.synchronize()
     rep = _report(ctx, "attention", {"batch": b, "seq": s, "heads": h, "kv_heads": hk})
     fwd_flop = 4.0 * b * h * s * s * d / 2          # causal: half of the score matrix
-    for name, mult in (("k_attn_fwd_tc", 1.0), ("k_attn_bwd_dq_tc", 1.5), ("k_attn_bwd_dkv_tc", 2.0),
-                       ("k_attn_bwd_dq_tc2", 1.5), ("k_attn_bwd_dkv_tc2", 2.0)):
+    for name, mult in (("k_attn_fwd_tc", 1.0), ("k_attn_bwd_dq_tc2", 1.5), ("k_attn_bwd_dkv_tc2", 2.0)):
         if name in rep["kernels"]:
             ms = rep["kernels"][name]["ms_per_launch"]
             print(f"{name}: {ms * 1e3:.1f} us, {fwd_flop * mult / (ms * 1e-3) / 1e12:.0f} TFLOP/s")

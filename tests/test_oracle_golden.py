@@ -206,3 +206,47 @@ def test_f16_packing_layout():
     # round to nearest even at the f16 grid
     assert ok.f16_round([1.0 + 2.0 ** -11])[0] == 1.0
     assert ok.f16_round([1.0 + 3 * 2.0 ** -11])[0] == np.float32(1.0 + 2.0 ** -9)
+
+
+def test_dropout_hash_building_blocks_against_published_algorithms():
+    """The attention-dropout hash (flash_attention_v2.wgsl:68-104, CPU copy in
+    backend/tests/gpu_kernels.rs:2261-2287) is made of two published pieces; the reference holds
+    no output vector of it, so the oracle's restatement is pinned piece by piece instead:
+    * `fmix32` is MurmurHash3's 32-bit finaliser.  MurmurHash3_x86_32 of an EMPTY key is
+      fmix32(seed), so scikit-learn's independent implementation gives known answers.
+    * the three steps `v * 1664525 + 1013904223` are the Numerical Recipes generator, whose
+      sequence from 0 is published.
+    * the cross-multiplication round is checked against exact integer arithmetic reduced mod
+      2^32 (guards the wrap-around of the numpy form)."""
+    from sklearn.utils import murmurhash3_32
+    seeds = [0, 1, 2, 0x9E3779B9, 0x7FFFFFFF, 0x80000000, 0xFFFFFFFF, 123456789, 0xDEADBEEF]
+    for s_ in seeds:
+        assert int(ok._fmix32(np.uint32(s_))) == murmurhash3_32(b"", seed=s_, positive=True), hex(s_)
+    assert int(ok._fmix32(np.uint32(1))) == 0x514E28B7 and int(ok._fmix32(np.uint32(0xFFFFFFFF))) == 0x81F16F39
+    # Numerical Recipes LCG from 0
+    x, seq = 0, []
+    for _ in range(4):
+        x = (x * 1664525 + 1013904223) % (1 << 32)
+        seq.append(x)
+    assert seq == [1013904223, 1196435762, 3519870697, 2868466484]
+
+    def hash3_exact(x, y, z):
+        m = 1 << 32
+        a, b, c = ((v * 1664525 + 1013904223) % m for v in (x, y, z))
+        a = (a + b * c) % m
+        b = (b + c * a) % m
+        c = (c + a * b) % m
+        a, b, c = (v ^ (v >> 16) for v in (a, b, c))
+        return np.float32((a + b + c) % m) * np.float32(2.3283064365386963e-10)
+
+    rng = np.random.default_rng(7)
+    for x, y, z in rng.integers(0, 1 << 32, size=(200, 3), dtype=np.uint64):
+        got = ok._hash3(np.uint32(x), np.uint32(y), np.uint32(z))
+        assert np.float32(got) == hash3_exact(int(x), int(y), int(z)), (x, y, z)
+    # the keep decision: key = fmix32(lo ^ fmix32(hi ^ golden ratio)), hash3(bh ^ key, q, k) >= p
+    seed = 0x0123456789ABCDEF
+    key = murmurhash3_32(b"", seed=(seed & 0xFFFFFFFF) ^ murmurhash3_32(
+        b"", seed=(seed >> 32) ^ 0x9E3779B9, positive=True), positive=True)
+    for bh, q, k in [(0, 0, 0), (3, 17, 5), (31, 1023, 4095)]:
+        expect = hash3_exact(bh ^ key, q, k) >= np.float32(0.3)
+        assert bool(ok.dropout_keep(0.3, seed, bh, q, k)) == bool(expect)
