@@ -18,7 +18,18 @@
 // exponentials; a quarter of the exponentials as a polynomial on the FMA pipe.  Cycle counts
 // inside this kernel: of about 2600 cycles per 64-key block, 1100 are the exponentials (two
 // CTAs share the SM's special-function unit), the rest are barrier operations of 100-200 cycles
-// each, the shared-memory hand-over of P, and per-tile work.)
+// each, the shared-memory hand-over of P, and per-tile work.
+// Also built and measured against this kernel, on 8 x 1024 x 32 heads / 8 x 4096 x 14:2 heads
+// (this kernel: 92.6 / 412 us): one CTA per SM with 128-key blocks and P kept in tensor memory as
+// the A operand of P V, as the backward kernels do it - (a) two query tiles per CTA sharing K/V,
+// P over the tile's single S buffer: 105 / 440 us, the tile's next scores wait for its P V;
+// (b) one tile, S double-buffered, four softmax warps with the row in registers: 98 / 466 us, one
+// warp per scheduler reaches 10 of the SM's 16 exponentials per cycle; (c) the same with eight
+// warps and a half-row maximum exchange: 97 / 461 us - 1150 of 2100 cycles per block are the
+// exponentials at 14 per cycle, the rest (loads, maxima, waits, stores) does not overlap with
+// them because the two warps of a scheduler move in step.  Halving the K/V bytes loaded changed
+// nothing: L2 bandwidth is not the limit.  Two CTAs per SM, whose warps drift apart, remain the
+// better way to keep the special-function unit busy.)
 // All waits are bounded (see ft_tc.cuh).
 #include <math.h>
 #include <stdlib.h>
