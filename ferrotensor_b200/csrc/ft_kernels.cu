@@ -274,6 +274,49 @@ k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
   amax_commit(am, amax_slot);
 }
 
+// Warp-per-row forms for rows of up to 32 * 4 * NV elements (16-byte aligned, n % 4 == 0), eight
+// rows per CTA: no block-wide barrier, so the eight warps of a CTA have their loads in flight
+// independently.  Serves the forward norm of the narrow models (hidden 576, 896, 960): 4.6
+// against 6.5 ms per step on the 360M workload.  (The backward norm in the same form, three
+// register-resident rows per lane, was slower than the two-pass kernel and is not kept.)
+constexpr int kWarpRows = 8;
+template <int NV>
+__global__ void __launch_bounds__(kWarpRows * 32)
+k_rms_norm_warp(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ out,
+                __half* __restrict__ out16, int rows, int n, float eps) {
+  ft_pdl_wait();
+  ft_pdl_launch();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpRows + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int n4 = n >> 2;
+  const float4* x4 = (const float4*)(x + (size_t)row * n);
+  float4 xv[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = lane + k * 32;
+    xv[k] = i < n4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += xv[k].x * xv[k].x + xv[k].y * xv[k].y + xv[k].z * xv[k].z + xv[k].w * xv[k].w;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  const float4* w4 = (const float4*)w;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = lane + k * 32;
+    if (i >= n4) continue;
+    const float4 g = w4[i];
+    const float4 r = make_float4(xv[k].x * inv * g.x, xv[k].y * inv * g.y, xv[k].z * inv * g.z,
+                                 xv[k].w * inv * g.w);
+    if (out) ((float4*)(out + (size_t)row * n))[i] = r;
+    if (out16) {
+      __half2 a = __floats2half2_rn(r.x, r.y), b = __floats2half2_rn(r.z, r.w);
+      ((uint2*)(out16 + (size_t)row * n))[i] = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+    }
+  }
+}
+
 // partial[c, i] = sum over the rows of chunk c of g*x*inv ; one thread per feature
 __global__ void k_rms_gw_partial(const float* __restrict__ x, const float* __restrict__ g,
                                  const float* __restrict__ inv, float* __restrict__ partial,
@@ -790,6 +833,14 @@ int ft_k_rms_norm16(FtContext* ctx, const float* x, const float* w, float* out, 
       FT_LAUNCH_PDL(ctx, k_rms_norm_reg<2>, rows, kRowThreads, 0, x, w, out, out16, n, eps);
     else
       FT_LAUNCH_PDL(ctx, k_rms_norm_reg<4>, rows, kRowThreads, 0, x, w, out, out16, n, eps);
+    return FT_OK;
+  }
+  if (al && n >= 128 && n < 1024) {
+    const int grid = ft_cdiv(rows, kWarpRows);
+    if (n <= 512)
+      FT_LAUNCH_PDL(ctx, k_rms_norm_warp<4>, grid, kWarpRows * 32, 0, x, w, out, out16, rows, n, eps);
+    else
+      FT_LAUNCH_PDL(ctx, k_rms_norm_warp<8>, grid, kWarpRows * 32, 0, x, w, out, out16, rows, n, eps);
     return FT_OK;
   }
   int block = n >= 1024 ? kRowThreads : (n >= 256 ? 128 : 32);
