@@ -278,7 +278,8 @@ k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
 // rows per CTA: no block-wide barrier, so the eight warps of a CTA have their loads in flight
 // independently.  Serves the forward norm of the narrow models (hidden 576, 896, 960): 4.6
 // against 6.5 ms per step on the 360M workload.  (The backward norm in the same form, three
-// register-resident rows per lane, was slower than the two-pass kernel and is not kept.)
+// register-resident rows per lane, was slower than the two-pass kernel and is not kept; so was
+// this forward form at 2048 elements per row against one CTA per row, 11.2 against 10.0 ms.)
 constexpr int kWarpRows = 8;
 template <int NV>
 __global__ void __launch_bounds__(kWarpRows * 32)
