@@ -208,6 +208,97 @@ __device__ __forceinline__ void fold_amax(float am, int* amax_slot, int lane) {
   if (lane == 0 && am > 0.f) atomicMax(amax_slot, __float_as_int(am));
 }
 
+// Optional f16 form of the results: rows [tokens, ld] of S * (dq | dk | dv) with the inverse
+// rotary rotation applied to dq and dk (angles from `table`, {cos, sin} [seq, 32]); S is the
+// power of two carried from *carry_amax (the largest magnitude of the same gradient in the block
+// processed before this one).  When `rows` is set the f32 results are not written.
+struct Out16 {
+  __half* rows;
+  long long ld;
+  const float2* table;
+  const int* carry_amax;
+  int carry_exp;
+  float* carry_scales;
+};
+
+__device__ __forceinline__ void prefetch_l1_256(const void* p) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+  asm volatile("prefetch.global.L1 [%0];" ::"l"((const char*)p + 128));
+}
+
+// Sixteen of a thread's 32 components of a gradient row (half `hc` of the 64), rotated back by
+// the angles of one position and scaled: ra = raw accumulator words of components c..c+15,
+// rb = of components 32+c..32+c+15, f their factor, trow = the position's {cos, sin} pairs from
+// component c on; writes 16 halves to dst.
+__device__ __forceinline__ void store_rot16(__half* dst, const uint32_t (&ra)[16], const uint32_t (&rb)[16],
+                                            float f, int hc, const float2* __restrict__ trow, float S,
+                                            float& am) {
+  uint32_t w[8];
+  const float fs = f * S;   // S is a power of two: exact
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const float4 cs = *(const float4*)(trow + i);   // {cos_i, sin_i, cos_i+1, sin_i+1}
+    const float a0 = __uint_as_float(ra[i]), a1 = __uint_as_float(ra[i + 1]);
+    const float b0 = __uint_as_float(rb[i]), b1 = __uint_as_float(rb[i + 1]);
+    float o0, o1;
+    if (hc == 0) {   // first half: a cos + b sin
+      o0 = a0 * cs.x + b0 * cs.y;
+      o1 = a1 * cs.z + b1 * cs.w;
+      am = fmaxf(am, fmaxf(fabsf(a0), fabsf(a1)));
+    } else {         // second half: b cos - a sin
+      o0 = b0 * cs.x - a0 * cs.y;
+      o1 = b1 * cs.z - a1 * cs.w;
+      am = fmaxf(am, fmaxf(fabsf(b0), fabsf(b1)));
+    }
+    w[i >> 1] = pack_h2(o0 * fs, o1 * fs);
+  }
+  *(uint4*)dst = make_uint4(w[0], w[1], w[2], w[3]);
+  *(uint4*)(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+__device__ __forceinline__ void store_plain16(__half* dst, const uint32_t (&r)[16], float f, float S,
+                                              float& am) {
+  uint32_t w[8];
+  const float fs = f * S;
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const float v0 = __uint_as_float(r[i]), v1 = __uint_as_float(r[i + 1]);
+    am = fmaxf(am, fmaxf(fabsf(v0), fabsf(v1)));
+    w[i >> 1] = pack_h2(v0 * fs, v1 * fs);
+  }
+  *(uint4*)dst = make_uint4(w[0], w[1], w[2], w[3]);
+  *(uint4*)(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// The dK/dV kernel's f16 epilogue of one thread (kept out of line: the kernel's main loop
+// needs every register it can have, and this runs once per tile).  dK rotated back (component
+// i pairs with i + 32), then dV, sixteen components at a time; arrives on `bar_read` once the
+// accumulators have been read; returns the largest magnitude written, before the carried scale.
+__device__ __noinline__ float dkv_store16(uint32_t t_dk_lane, uint32_t t_dv_half, int hc, __half* k16,
+                                          __half* v16, const float2* __restrict__ trow, float ak,
+                                          float av, float s16, uint32_t bar_read, int lane) {
+  float amk = 0.f, amv = 0.f;
+  uint32_t ra[16], rb[16];
+  tc_ld16(t_dk_lane, ra);
+  tc_ld16(t_dk_lane + 32, rb);
+  tc_wait_ld();
+  if (k16) store_rot16(k16, ra, rb, ak, hc, trow, s16, amk);
+  tc_ld16(t_dk_lane + 16, ra);
+  tc_ld16(t_dk_lane + 48, rb);
+  tc_wait_ld();
+  if (k16) store_rot16(k16 + 16, ra, rb, ak, hc, trow + 16, s16, amk);
+  tc_ld16(t_dv_half, ra);
+  tc_ld16(t_dv_half + 16, rb);
+  tc_wait_ld();
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_read);
+  if (v16) {
+    store_plain16(v16, ra, av, s16, amv);
+    store_plain16(v16 + 16, rb, av, s16, amv);
+  }
+  return fmaxf(ak * amk, av * amv);
+}
+
 // =========================================================================================
 // dQ
 // =========================================================================================
@@ -233,7 +324,7 @@ k_attn_bwd_dq_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_cons
                   const __grid_constant__ CUtensorMap map_o, float* __restrict__ dq, long long lddq,
                   float* __restrict__ stats, int seq, int heads, int kv_heads, int bh_count, int q_col0,
                   int k_col0, int v_col0, float scale, const float* __restrict__ inv_scale_ptr,
-                  int* amax_slot, int* status) {
+                  int* amax_slot, int* status, Out16 o16) {
   extern __shared__ uint8_t smem_raw[];
   Common c;
   cta_setup(c, smem_raw, status, 2);
@@ -410,11 +501,38 @@ k_attn_bwd_dq_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_cons
     bool pend = false;
     int pend_it = 0;
     float* pend_out = nullptr;
+    __half* pend16 = nullptr;
+    int pend_pos = 0;
+    float s16 = 1.0f;
+    if (o16.rows) {
+      s16 = ft_scale_from_amax_bits(*o16.carry_amax, o16.carry_exp);
+      if (blockIdx.x == 0 && threadIdx.x == 0) ft_publish_scales(o16.carry_scales, s16);
+    }
     auto flush = [&]() -> bool {
       if (!pend) return true;
       pend = false;
       if (!c.wait(B_ACC_DONE, (uint32_t)pend_it, 83)) return false;
       tc_fence_after();
+      if (o16.rows) {
+        // the rotation pairs component i with i + 32: sixteen components of either half at a
+        // time (magnitudes are folded raw and scaled by alpha once)
+        float amr = 0.f;
+        const float2* trow = o16.table + (size_t)pend_pos * 32;
+        uint32_t ra[16], rb[16];
+        tc_ld16(t_dq + lane_addr, ra);
+        tc_ld16(t_dq + lane_addr + 32, rb);
+        tc_wait_ld();
+        if (pend16) store_rot16(pend16, ra, rb, alpha, hc, trow, s16, amr);
+        tc_ld16(t_dq + lane_addr + 16, ra);
+        tc_ld16(t_dq + lane_addr + 48, rb);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(c.bar(B_ACC_READ));
+        if (pend16) store_rot16(pend16 + 16, ra, rb, alpha, hc, trow + 16, s16, amr);
+        am = fmaxf(am, alpha * amr);
+        return true;
+      }
       uint32_t r[32];
       tc_ld32(t_dq + lane_addr + hc * 32, r);
       tc_wait_ld();
@@ -512,7 +630,15 @@ k_attn_bwd_dq_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_cons
       if (!ok) break;
       pend = true;
       pend_it = it;
-      pend_out = row_ok ? dq + ((long long)w.tok0 + qi) * lddq + (long long)w.h * BD + hc * 32 : nullptr;
+      if (o16.rows) {
+        pend16 = row_ok ? o16.rows + ((long long)w.tok0 + qi) * o16.ld + q_col0 + (long long)w.h * BD + hc * 32
+                        : nullptr;
+        pend_pos = qi;
+        // the row's angles are wanted one key block from now: bring them close meanwhile
+        if (row_ok) prefetch_l1_256(o16.table + (size_t)qi * 32);
+      } else {
+        pend_out = row_ok ? dq + ((long long)w.tok0 + qi) * lddq + (long long)w.h * BD + hc * 32 : nullptr;
+      }
       TSTAMP(7);
     }
     if (ok) ok = flush();
@@ -547,7 +673,7 @@ k_attn_bwd_dkv_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
                    float* __restrict__ dk, float* __restrict__ dv, long long ldd,
                    const float* __restrict__ stats, int seq, int heads, int kv_heads, int bk_count,
                    int q_col0, int k_col0, int v_col0, float scale,
-                   const float* __restrict__ inv_scale_ptr, int* amax_slot, int* status) {
+                   const float* __restrict__ inv_scale_ptr, int* amax_slot, int* status, Out16 o16) {
   extern __shared__ uint8_t smem_raw[];
   Common c;
   cta_setup(c, smem_raw, status, 1);
@@ -670,11 +796,20 @@ k_attn_bwd_dkv_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
     bool pend = false;
     int pend_it = 0;
     float *pend_k = nullptr, *pend_v = nullptr;
+    __half *pend_k16 = nullptr, *pend_v16 = nullptr;
+    int pend_pos = 0;
+    const float s16 = o16.rows ? ft_scale_from_amax_bits(*o16.carry_amax, o16.carry_exp) : 1.0f;
     auto flush = [&]() -> bool {
       if (!pend) return true;
       pend = false;
       if (!c.wait(B_ACC_DONE, (uint32_t)pend_it, 103)) return false;
       tc_fence_after();
+      if (o16.rows) {
+        am = fmaxf(am, dkv_store16(t_dk + lane_addr, t_dv + lane_addr + hc * 32, hc, pend_k16, pend_v16,
+                                   o16.table + (size_t)pend_pos * 32, ak, av, s16, c.bar(B_ACC_READ),
+                                   lane));
+        return true;
+      }
       uint32_t rk[32], rv[32];
       tc_ld32(t_dk + lane_addr + hc * 32, rk);
       tc_ld32(t_dv + lane_addr + hc * 32, rv);
@@ -789,8 +924,15 @@ k_attn_bwd_dkv_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
       pend = true;
       pend_it = it;
       const long long tok = (long long)w.tok0 + kj;
-      pend_k = row_ok ? dk + tok * ldd + (long long)w.kvh * BD + hc * 32 : nullptr;
-      pend_v = row_ok ? dv + tok * ldd + (long long)w.kvh * BD + hc * 32 : nullptr;
+      if (o16.rows) {
+        pend_k16 = row_ok ? o16.rows + tok * o16.ld + k_col0 + (long long)w.kvh * BD + hc * 32 : nullptr;
+        pend_v16 = row_ok ? o16.rows + tok * o16.ld + v_col0 + (long long)w.kvh * BD + hc * 32 : nullptr;
+        pend_pos = kj;
+        if (row_ok) prefetch_l1_256(o16.table + (size_t)kj * 32);
+      } else {
+        pend_k = row_ok ? dk + tok * ldd + (long long)w.kvh * BD + hc * 32 : nullptr;
+        pend_v = row_ok ? dv + tok * ldd + (long long)w.kvh * BD + hc * 32 : nullptr;
+      }
       w = wn;
       has = has_next;
     }
@@ -819,12 +961,23 @@ int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
                         int v_col0, const __half* o16, long long ldo, const __half* do16,
                         long long lddo, float* dq, long long lddq, float* dk, float* dv,
                         long long ldd, float* stats, const float* inv_scale, int batch, int seq,
-                        int heads, int kv_heads, int head_dim) {
+                        int heads, int kv_heads, int head_dim, const FtAttnBwdOut16* out16) {
   auto bad16 = [](const void* p, long long l) { return (l % 8) || (((uintptr_t)p) & 15); };
   auto bad32 = [](const void* p, long long l) { return (l % 4) || (((uintptr_t)p) & 15); };
+  Out16 o;
+  memset(&o, 0, sizeof(o));
+  if (out16 && out16->rows) {
+    // the f16 rows share the q|k|v column layout of the operands
+    if (bad16(out16->rows, out16->ld) || !out16->table || !out16->carry_amax || !out16->carry_scales ||
+        (((uintptr_t)out16->table) & 15))
+      return FT_ERR_UNSUPPORTED;
+    o.rows = out16->rows; o.ld = out16->ld; o.table = (const float2*)out16->table;
+    o.carry_amax = out16->carry_amax; o.carry_exp = out16->carry_exp; o.carry_scales = out16->carry_scales;
+  } else if (bad32(dq, lddq) || bad32(dk, ldd) || bad32(dv, ldd)) {
+    return FT_ERR_UNSUPPORTED;
+  }
   if (head_dim != BD || bad16(qkv16, ld) || bad16(o16, ldo) || bad16(do16, lddo) ||
-      bad32(dq, lddq) || bad32(dk, ldd) || bad32(dv, ldd) || (q_col0 % 8) || (k_col0 % 8) ||
-      (v_col0 % 8) || !stats)
+      (q_col0 % 8) || (k_col0 % 8) || (v_col0 % 8) || !stats)
     return FT_ERR_UNSUPPORTED;
   const uint64_t T = (uint64_t)batch * seq;
   CUtensorMap m_qkv, m_do, m_o;
@@ -848,14 +1001,14 @@ int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
     const int grid = std::min(tiles, ctx->sm_count);
     FT_LAUNCH_PDL(ctx, k_attn_bwd_dq_tc2, grid, DQ_THREADS, Smem::DYN_BYTES, m_qkv, m_do, m_o, dq, lddq,
                   stats, seq, heads, kv_heads, batch * heads, q_col0, k_col0, v_col0, scale, inv_scale,
-                  am, ctx->status_dev);
+                  am, ctx->status_dev, o);
   }
   {
     const int tiles = ntile * batch * kv_heads;
     const int grid = std::min(tiles, ctx->sm_count);
     FT_LAUNCH_PDL(ctx, k_attn_bwd_dkv_tc2, grid, DKV_THREADS, Smem::DYN_BYTES, m_qkv, m_do, dk, dv, ldd,
                   stats, seq, heads, kv_heads, batch * kv_heads, q_col0, k_col0, v_col0, scale,
-                  inv_scale, am, ctx->status_dev);
+                  inv_scale, am, ctx->status_dev, o);
   }
   return FT_OK;
 }

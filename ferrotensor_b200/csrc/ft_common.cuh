@@ -186,6 +186,15 @@ struct FtGemmArgs {
   const float* bias = nullptr;
   const float* residual = nullptr; long long ldr = 0;
   bool want_amax = false;   // contribute the output's largest magnitude to an armed amax slot
+  int* amax_slot = nullptr; // ... or to this slot (zero before the launch), armed or not
+  // carried scale: the f16 result is multiplied by the power of two that would bring
+  // *carry_amax (the largest magnitude of an EARLIER tensor of the same kind, e.g. the same
+  // gradient one block later in the backward pass) into [2^(carry_exp-1), 2^carry_exp); one
+  // thread publishes {S, 1/S, 2^-11/S} to carry_scales.  CTA-pair launches only
+  // (ft_gemm_tc_pair_eligible); amax_slot still receives the UNSCALED magnitude.
+  const int* carry_amax = nullptr;
+  int carry_exp = 0;
+  float* carry_scales = nullptr;
   // adapter pre-tiles: when pre_b is set, the launch first computes
   //   pre_c16[M, 64] (f16, pitch pre_ldc16) = pre_alpha * A . pre_b^T   (pre_b [64, K], f16)
   // which is normally the very buffer a2 points at (the K-concatenated tail operand)
@@ -194,6 +203,23 @@ struct FtGemmArgs {
   float pre_alpha = 1.f;
 };
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g);
+// whether a product of this size runs on CTA pairs (the kernel with the carried-scale epilogue)
+bool ft_gemm_tc_pair_eligible(const FtContext* ctx, int M, int N);
+// S = 2^(target_exp - e) for amax = f * 2^e, f in [0.5, 1); 1 when amax is zero or not finite
+#ifdef __CUDACC__
+__device__ __forceinline__ float ft_scale_from_amax_bits(int bits, int target_exp) {
+  const float amax = __int_as_float(bits);
+  if (!(amax > 0.f) || !isfinite(amax)) return 1.0f;
+  int e;
+  frexpf(amax, &e);
+  return ldexpf(1.0f, target_exp - e);
+}
+__device__ __forceinline__ void ft_publish_scales(float* scales, float S) {
+  scales[0] = S;
+  scales[1] = 1.0f / S;
+  scales[2] = ldexpf(1.0f / S, -11);
+}
+#endif
 // One problem of a token-reduction launch: P[M, N<=64] = sum_t A[t, m] B[t, n]; the reduction
 // launch adds it into up to three segments out[(m - m0) * som + (n - n0) * son].
 struct FtKoSeg {
@@ -240,6 +266,18 @@ int ft_k_rms_norm16(FtContext* ctx, const float* x, const float* w, float* out, 
                     int rows, int n, float eps);
 int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const float* g, float* gx,
                       float* gw, int rows, int n, float eps, bool accumulate_gx);
+// A carried scale (see FtGemmArgs::carry_amax) for a kernel that also writes its result as f16.
+struct FtCarry {
+  const int* amax_in = nullptr;   // largest magnitude of the earlier tensor
+  int exp = 0;
+  float* scales = nullptr;        // {S, 1/S, 2^-11/S} published by one thread
+  int* amax_out = nullptr;        // receives this result's largest magnitude (zero before)
+};
+// frozen-norm backward (gw == NULL, gx accumulated) that also writes gx16 = f16(S gx); rows of
+// 1024..4096 elements, 16-byte aligned.  Returns FT_ERR_UNSUPPORTED for other shapes.
+int ft_k_rms_norm_bwd_carry(FtContext* ctx, const float* x, const float* w, const float* g,
+                            float* gx, __half* gx16, int rows, int n, float eps,
+                            const FtCarry& carry);
 // in place on x[t*ld + h*head_dim + i]; position of token t = pos + t % seq_len
 int ft_k_rope(FtContext* ctx, float* x, long long ld, int tokens, int heads, int head_dim,
               int seq_len, int pos, float theta, bool inverse);
@@ -261,6 +299,12 @@ int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* ou
 int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const float* g,
                           long long ldg, __half* out, long long ldo, int rows, int n,
                           const int* in_amax, const float** scales_out);
+// the same with the upstream gradient as f16 rows carrying the scale g_scales[0]; g_amax is the
+// largest magnitude of the UNSCALED upstream gradient
+int ft_k_silu_gate_bwd16hh(FtContext* ctx, const __half* gu, long long ld, const __half* g16,
+                           long long ldg, const float* g_scales, const int* g_amax, __half* out,
+                           long long ldo, int rows, int n, const int* in_amax,
+                           const float** scales_out);
 int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const float* b,
                        long long ldb, const float* g, long long ldg, float* ga, long long ldga,
                        float* gb, long long ldgb, int rows, int n);
@@ -341,8 +385,18 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
 // Backward: o16 = forward output (f16), do16 = output gradient (f16, times the power-of-two
 // scale whose inverse is the device scalar *inv_scale, NULL = 1); stats must hold the forward
 // log-sum-exp at [2*row+1] and receives Delta at [2*row].  dq [tokens, lddq]; dk, dv [tokens, ldd].
+// With out16 the results are written instead as f16 rows in the operands' q|k|v column layout,
+// dq and dk rotated back by the rotary angles of `table` ({cos, sin} [seq, 32] f32) and all
+// times the power of two carried from *carry_amax (see FtGemmArgs::carry_amax); the armed amax
+// slot still receives the largest unrotated, unscaled magnitude.
+struct FtAttnBwdOut16 {
+  __half* rows = nullptr; long long ld = 0;
+  const float* table = nullptr;
+  const int* carry_amax = nullptr; int carry_exp = 0;
+  float* carry_scales = nullptr;
+};
 int ft_attention_bwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q_col0, int k_col0,
                         int v_col0, const __half* o16, long long ldo, const __half* do16,
                         long long lddo, float* dq, long long lddq, float* dk, float* dv,
                         long long ldd, float* stats, const float* inv_scale, int batch, int seq,
-                        int heads, int kv_heads, int head_dim);
+                        int heads, int kv_heads, int head_dim, const FtAttnBwdOut16* out16 = nullptr);

@@ -58,6 +58,7 @@ struct SmemLayout {
 
 // What the epilogue does with a finished accumulator tile:
 //   v = alpha_dev * alpha * acc (+ bias[col]) (+ residual[row, col]);  c = v;  c16 = f16(v)
+// (pair kernel, with carry_amax: c16 = f16(S v), S the carried power of two)
 struct Epilogue {
   float* c;
   long long ldc;
@@ -69,6 +70,9 @@ struct Epilogue {
   const float* residual;
   long long ldr;
   int* amax_slot;   // when set, the largest |v| written is folded into it (atomicMax)
+  const int* carry_amax;   // see FtGemmArgs::carry_amax
+  int carry_exp;
+  float* carry_scales;
 };
 
 // Adapter pre-tiles.  When the K-concatenated tail operand A2 (= alpha/r * A . Bpre^T, 64 columns)
@@ -739,6 +743,12 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     const bool vec_r = !ep.residual || (((ep.ldr & 3) == 0) && ((((uintptr_t)ep.residual) & 15) == 0));
     const bool vec_h = ep.c16 && ((ep.ldc16 & 3) == 0) && ((((uintptr_t)ep.c16) & 7) == 0);
     const float alpha = (ep.alpha_ptr ? *ep.alpha_ptr : 1.0f) * ep.alpha;
+    // carried scale of the f16 result (a power of two from an earlier tensor's amax)
+    float s16 = 1.0f;
+    if (ep.carry_amax) {
+      s16 = ft_scale_from_amax_bits(*ep.carry_amax, ep.carry_exp);
+      if (blockIdx.x == 0 && warp == 2 && lane == 0) ft_publish_scales(ep.carry_scales, s16);
+    }
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     float amax_seen = 0.f;
     constexpr int NCH = BN / 32;
@@ -859,12 +869,13 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             if (ep.c16) {
               __half* hp = ep.c16 + (long long)grow * ep.ldc16 + gcol;
               if (full && vec_h) {
-                __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                __half2 h0 = __floats2half2_rn(v[0] * s16, v[1] * s16),
+                        h1 = __floats2half2_rn(v[2] * s16, v[3] * s16);
                 *(uint2*)hp = make_uint2(*(uint32_t*)&h0, *(uint32_t*)&h1);
               } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                  if (gcol + e < N) hp[e] = __float2half_rn(v[e]);
+                  if (gcol + e < N) hp[e] = __float2half_rn(v[e] * s16);
               }
             }
           }
@@ -961,13 +972,6 @@ __global__ void k_amax(const float* __restrict__ src, long long ld, int rows, in
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax_bits, __float_as_int(m));
 }
 
-__device__ __forceinline__ float scale_from_amax_bits(int bits, int target_exp) {
-  float amax = __int_as_float(bits);
-  if (!(amax > 0.f) || !isfinite(amax)) return 1.0f;
-  int e;
-  frexpf(amax, &e);           // amax = f * 2^e, f in [0.5, 1)
-  return ldexpf(1.0f, target_exp - e);
-}
 
 // scales[0] = S (power of two bringing the largest magnitude into [2^(t-1), 2^t), t =
 // target_exp), scales[1] = 1/S, scales[2] = 2^-11/S (the factor of the low half in split mode)
@@ -1001,7 +1005,7 @@ __global__ void k_to_f16(const float* __restrict__ src, long long ld, __half* __
   // one thread also publishes {S, 1/S, 2^-11/S} for the products that follow)
   float S = scales ? scales[0] : 1.0f;
   if (amax_bits) {
-    S = scale_from_amax_bits(*amax_bits, target_exp);
+    S = ft_scale_from_amax_bits(*amax_bits, target_exp);
     if (blockIdx.x == 0 && threadIdx.x == 0) {
       scales_out[0] = S;
       scales_out[1] = 1.0f / S;
@@ -1052,7 +1056,7 @@ __global__ void k_to_f16_v8(const float* __restrict__ src, long long ld, __half*
   ft_pdl_launch();
   float S = scales ? scales[0] : 1.0f;
   if (amax_bits) {
-    S = scale_from_amax_bits(*amax_bits, target_exp);
+    S = ft_scale_from_amax_bits(*amax_bits, target_exp);
     if (blockIdx.x == 0 && threadIdx.x == 0) {
       scales_out[0] = S;
       scales_out[1] = 1.0f / S;
@@ -1306,6 +1310,13 @@ static double gemm_algorithmic_bytes(const FtGemmArgs& g) {
   return b;
 }
 
+// CTA pairs (256 x 256 tile over two SMs) are the default for wide products: measured
+// 1340-1480 TFLOP/s against 1150-1280 for the 128-row and 1100-1400 for the 256-row
+// single-CTA tiles; FT_GEMM_TILE_M=128|256 selects those, 512 the pairs
+bool ft_gemm_tc_pair_eligible(const FtContext* ctx, int M, int N) {
+  return N > 128 && M >= 256 && (ctx->tile_m_override == 512 || ctx->tile_m_override == 0);
+}
+
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   ctx->next_launch_bytes = gemm_algorithmic_bytes(g);
   if (g.ab_type != FT_F16 && g.ab_type != FT_BF16) return FT_ERR_UNSUPPORTED;
@@ -1334,10 +1345,11 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   }
   const CUtensorMapDataType dt = g.ab_type == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  // CTA pairs (256 x 256 tile over two SMs) are the default for wide products: measured
-  // 1340-1480 TFLOP/s against 1150-1280 for the 128-row and 1100-1400 for the 256-row
-  // single-CTA tiles; FT_GEMM_TILE_M=128|256 selects those, 512 the pairs
-  const bool pair = BN == 256 && g.M >= 256 && (ctx->tile_m_override == 512 || ctx->tile_m_override == 0);
+  const bool pair = ft_gemm_tc_pair_eligible(ctx, g.M, g.N);
+  if (g.carry_amax) {
+    FT_REQUIRE(pair && g.c16 && g.carry_scales,
+               "gemm: a carried scale needs a CTA-pair launch with an f16 result");
+  }
   if (pair) {
     const int fmt = g.ab_type == FT_F16 ? 0 : 1;
     FT_TRY(make_map(ctx, &ma, g.a, dt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, 128));
@@ -1353,11 +1365,12 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
     ep.c = g.c; ep.ldc = g.ldc; ep.c16 = g.c16; ep.ldc16 = g.ldc16;
     ep.alpha_ptr = g.alpha_ptr; ep.alpha = g.alpha; ep.bias = g.bias;
     ep.residual = g.residual; ep.ldr = g.ldr;
-    ep.amax_slot = nullptr;
-    if (g.want_amax && ctx->amax_out) {
+    ep.amax_slot = g.amax_slot;
+    if (!ep.amax_slot && g.want_amax && ctx->amax_out) {
       ep.amax_slot = ctx->amax_out;
       ctx->amax_ready = true;
     }
+    ep.carry_amax = g.carry_amax; ep.carry_exp = g.carry_exp; ep.carry_scales = g.carry_scales;
     double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
     CUtensorMap mb3 = mb;
     PreTile pre;
@@ -1395,11 +1408,12 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   ep.c = g.c; ep.ldc = g.ldc; ep.c16 = g.c16; ep.ldc16 = g.ldc16;
   ep.alpha_ptr = g.alpha_ptr; ep.alpha = g.alpha; ep.bias = g.bias;
   ep.residual = g.residual; ep.ldr = g.ldr;
-  ep.amax_slot = nullptr;
-  if (g.want_amax && ctx->amax_out) {
+  ep.amax_slot = g.amax_slot;
+  if (!ep.amax_slot && g.want_amax && ctx->amax_out) {
     ep.amax_slot = ctx->amax_out;
     ctx->amax_ready = true;
   }
+  ep.carry_amax = nullptr; ep.carry_exp = 0; ep.carry_scales = nullptr;
   double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
   // adapter pre-tiles: the tail operand A2 = pre_alpha * A . pre_b^T is made by this launch
   CUtensorMap mb3;
@@ -1499,6 +1513,7 @@ int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T) 
   ep.c = (float*)s; ep.ldc = 64; ep.c16 = nullptr; ep.ldc16 = 0;
   ep.alpha_ptr = nullptr; ep.alpha = 1.f; ep.bias = nullptr; ep.residual = nullptr; ep.ldr = 0;
   ep.amax_slot = nullptr;
+  ep.carry_amax = nullptr; ep.carry_exp = 0; ep.carry_scales = nullptr;
   // both operands M/N-major: bits 15 and 16 of the instruction descriptor
   const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
   return launch_tc<64, 8, true>(ctx, ma[0], mb[0], ma[1], mb[1], ep, prob[0].M, 64, T, 0, splits, idesc,

@@ -232,12 +232,20 @@ template <int NV>
 __global__ void __launch_bounds__(kRowThreads)
 k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
                    const float* __restrict__ g, float* __restrict__ gx, int n, float eps,
-                   int accumulate, int* amax_slot) {
+                   int accumulate, int* amax_slot, __half* __restrict__ gx16 = nullptr,
+                   const int* __restrict__ carry_amax = nullptr, int carry_exp = 0,
+                   float* __restrict__ carry_scales = nullptr) {
   ft_pdl_wait();
   ft_pdl_launch();
   __shared__ float red[64];
   const int n4 = n >> 2;
   const size_t off = (size_t)blockIdx.x * n;
+  // gx16 = f16(S gx) with S carried from the amax of the previous version of this gradient
+  float s16 = 1.0f;
+  if (gx16) {
+    s16 = ft_scale_from_amax_bits(*carry_amax, carry_exp);
+    if (blockIdx.x == 0 && threadIdx.x == 0) ft_publish_scales(carry_scales, s16);
+  }
   const float4 *x4 = (const float4*)(x + off), *g4 = (const float4*)(g + off), *w4 = (const float4*)w;
   float4* o4 = (float4*)(gx + off);
   float4 xv[NV], gv[NV], pv[NV];   // gv holds g * w, pv what the result is added to
@@ -269,6 +277,10 @@ k_rms_norm_bwd_reg(const float* __restrict__ x, const float* __restrict__ w,
                            gv[k].z * inv - xv[k].z * coef, gv[k].w * inv - xv[k].w * coef);
     r.x += pv[k].x; r.y += pv[k].y; r.z += pv[k].z; r.w += pv[k].w;
     o4[i] = r;
+    if (gx16) {
+      __half2 a = __floats2half2_rn(r.x * s16, r.y * s16), b = __floats2half2_rn(r.z * s16, r.w * s16);
+      ((uint2*)(gx16 + off))[i] = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+    }
     am = amax4(am, r);
   }
   amax_commit(am, amax_slot);
@@ -557,6 +569,61 @@ __global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* _
       for (int e = 0; e < 2; ++e) {
         const float s = fast_sigmoid(xs[e]);
         const float gk = gs[2 * k + e] * S;
+        vb[e] = gk * (xs[e] * s);
+        va[e] = gk * ys[e] * (s * (1.0f + xs[e] * (1.0f - s)));
+      }
+      __half2 ha = __floats2half2_rn(va[0], va[1]), hb = __floats2half2_rn(vb[0], vb[1]);
+      oa[k] = *(uint32_t*)&ha;
+      ob[k] = *(uint32_t*)&hb;
+    }
+    *(uint4*)(out + r * ldo + c) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    *(uint4*)(out + r * ldo + n + c) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+  }
+}
+
+// The same with the upstream gradient as f16 rows g16 = f16(Sg g) (the down projection's input
+// gradient written with a carried scale): g_scales = {Sg, 1/Sg, ..}, g_amax the largest |g|.
+__global__ void k_silu_gate_bwd16hh(const __half* __restrict__ a, const __half* __restrict__ b,
+                                    long long ldab, const __half* __restrict__ g16, long long ldg,
+                                    const float* __restrict__ g_scales,
+                                    __half* __restrict__ out, long long ldo, int rows, int n,
+                                    const int* __restrict__ g_amax, const int* __restrict__ in_amax,
+                                    float* __restrict__ scales_out) {
+  ft_pdl_wait();
+  ft_pdl_launch();
+  float S = 1.0f;
+  {
+    float bound = 1.1f * __int_as_float(*g_amax) * __int_as_float(*in_amax);
+    if (bound > 0.f && isfinite(bound)) {
+      int e;
+      frexpf(bound, &e);
+      S = ldexpf(1.0f, 13 - e);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) ft_publish_scales(scales_out, S);
+  }
+  const float SG = S * g_scales[1];   // powers of two: exact
+  const size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t st = (size_t)gridDim.x * blockDim.x;
+  RowWalk w(i, st, per_row);
+  for (; i < total; i += st, w.next()) {
+    const long long r = w.r;
+    const size_t c = (size_t)w.c * 8;
+    const uint4 xa = *(const uint4*)(a + r * ldab + c), ya = *(const uint4*)(b + r * ldab + c);
+    const uint4 ga = *(const uint4*)(g16 + r * ldg + c);
+    const __half2* xh = (const __half2*)&xa;
+    const __half2* yh = (const __half2*)&ya;
+    const __half2* gh = (const __half2*)&ga;
+    uint32_t oa[4], ob[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = __half22float2(xh[k]), y = __half22float2(yh[k]), gg = __half22float2(gh[k]);
+      const float xs[2] = {x.x, x.y}, ys[2] = {y.x, y.y}, gs[2] = {gg.x, gg.y};
+      float va[2], vb[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float s = fast_sigmoid(xs[e]);
+        const float gk = gs[e] * SG;
         vb[e] = gk * (xs[e] * s);
         va[e] = gk * ys[e] * (s * (1.0f + xs[e] * (1.0f - s)));
       }
@@ -872,10 +939,10 @@ int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const floa
   if (!gw && al && n >= 1024 && n <= 4096) {
     if (n <= 2048)
       FT_LAUNCH_PDL(ctx, k_rms_norm_bwd_reg<2>, rows, kRowThreads, 0, x, w, g, gx, n, eps,
-                accumulate_gx ? 1 : 0, am);
+                accumulate_gx ? 1 : 0, am, (__half*)nullptr, (const int*)nullptr, 0, (float*)nullptr);
     else
       FT_LAUNCH_PDL(ctx, k_rms_norm_bwd_reg<4>, rows, kRowThreads, 0, x, w, g, gx, n, eps,
-                accumulate_gx ? 1 : 0, am);
+                accumulate_gx ? 1 : 0, am, (__half*)nullptr, (const int*)nullptr, 0, (float*)nullptr);
     return FT_OK;
   }
   FT_LAUNCH(ctx, k_rms_norm_bwd, rows, block, 0, x, w, g, gx, inv, n, eps, accumulate_gx ? 1 : 0, am);
@@ -884,6 +951,21 @@ int ft_k_rms_norm_bwd(FtContext* ctx, const float* x, const float* w, const floa
     FT_LAUNCH(ctx, k_rms_gw_partial, grid, 128, 0, x, g, inv, partial, rows, n, rows_per_chunk);
     FT_LAUNCH(ctx, k_rms_gw_final, ft_cdiv(n, 128), 128, 0, partial, gw, n, chunks);
   }
+  return FT_OK;
+}
+
+int ft_k_rms_norm_bwd_carry(FtContext* ctx, const float* x, const float* w, const float* g,
+                            float* gx, __half* gx16, int rows, int n, float eps,
+                            const FtCarry& carry) {
+  const bool al = (n % 4) == 0 && (((uintptr_t)gx16) & 7) == 0 &&
+                  ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)g) | ((uintptr_t)gx)) & 15) == 0;
+  if (!al || n < 1024 || n > 4096 || !carry.amax_in || !carry.scales) return FT_ERR_UNSUPPORTED;
+  if (n <= 2048)
+    FT_LAUNCH_PDL(ctx, k_rms_norm_bwd_reg<2>, rows, kRowThreads, 0, x, w, g, gx, n, eps, 1,
+                  carry.amax_out, gx16, carry.amax_in, carry.exp, carry.scales);
+  else
+    FT_LAUNCH_PDL(ctx, k_rms_norm_bwd_reg<4>, rows, kRowThreads, 0, x, w, g, gx, n, eps, 1,
+                  carry.amax_out, gx16, carry.amax_in, carry.exp, carry.scales);
   return FT_OK;
 }
 
@@ -1040,6 +1122,21 @@ int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const 
   ctx->amax_ready = false;
   FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16h, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu, gu + n,
                 ld, g, ldg, out, ldo, rows, n, g_amax, in_amax, ctx->scale_buf + 4);
+  *scales_out = ctx->scale_buf + 4;
+  return FT_OK;
+}
+
+int ft_k_silu_gate_bwd16hh(FtContext* ctx, const __half* gu, long long ld, const __half* g16,
+                           long long ldg, const float* g_scales, const int* g_amax, __half* out,
+                           long long ldo, int rows, int n, const int* in_amax,
+                           const float** scales_out) {
+  FT_REQUIRE((n % 8) == 0 && (ld % 8) == 0 && (ldg % 8) == 0 && (ldo % 8) == 0 &&
+                 ((((uintptr_t)gu) | ((uintptr_t)g16) | ((uintptr_t)out)) & 15) == 0,
+             "silu_gate_bwd16hh: width and pitches must be multiples of 8");
+  FT_REQUIRE(g_scales && g_amax && in_amax, "silu_gate_bwd16hh: scales and maxima are required");
+  FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16hh, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu,
+                gu + n, ld, g16, ldg, g_scales, out, ldo, rows, n, g_amax, in_amax,
+                ctx->scale_buf + 4);
   *scales_out = ctx->scale_buf + 4;
   return FT_OK;
 }

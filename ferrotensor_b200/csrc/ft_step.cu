@@ -120,7 +120,27 @@ struct FtLoraModel {
   float* rope_table = nullptr;     // {cos, sin} [seq_len, 32] in the workspace
   int table_seq = 0;
   int* gu_amax = nullptr;          // per layer: largest |gate| or |up| of the forward pass
+  // Carried scales of the backward pass.  A gradient that a kernel writes as f16 needs its
+  // power-of-two scale BEFORE its largest magnitude is known; it takes the scale from the
+  // largest magnitude of the same gradient one step earlier in the pass (the residual-stream
+  // gradient from its previous version, a block's df / dattn / dq|dk|dv from the block above),
+  // which leaves 2^(16 - kCarryExp) of growth before f16 overflows (an overflow makes the
+  // gradient norm non-finite and the step is skipped, never silently wrong).  The first of
+  // each kind takes the two-pass route (f32 result, conversion with its own amax).
+  // Slots: amax ints and {S, 1/S, 2^-11/S} floats, zeroed at the start of every backward pass.
+  int* carry_amax = nullptr;
+  float* carry_scales = nullptr;
+  int carry_mask = 0;              // FT_CARRY bits: 1 residual stream, 2 df, 4 dattn, 8 dq|dk|dv
+  __half *dx16 = nullptr, *df16 = nullptr, *dattn16 = nullptr;
+  int carry_slots() const { return 5 * cfg.layers + 1; }
+  int slot_dx(int k) const { return k; }                                  // k = 0 .. 2L
+  int slot_df(int l) const { return 2 * cfg.layers + 1 + l; }
+  int slot_dattn(int l) const { return 3 * cfg.layers + 1 + l; }
+  int slot_dqkv(int l) const { return 4 * cfg.layers + 1 + l; }
+  int* camax(int slot) const { return carry_amax + slot; }
+  float* cscales(int slot) const { return carry_scales + 4 * (size_t)slot; }
 };
+constexpr int kCarryExp = 7;   // carried scales aim the earlier amax at [2^6, 2^7)
 
 namespace {
 
@@ -232,7 +252,25 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   __half* xa16_head = fused ? b.take<__half>(T * RP) : nullptr;
   __half* g16 = fused ? b.take<__half>(T * RP) : nullptr;
   int* gu_amax = fused ? b.take<int>((size_t)L) : nullptr;
+  int carry_mask = 0;
+  if (tc_attention) {
+    // FT_CARRY=<bits> (read whenever a workspace is planned) switches kinds off: 0 = every
+    // gradient takes the two-pass route
+    const char* env = getenv("FT_CARRY");
+    const int env_mask = env ? atoi(env) : 15;
+    if (c.hidden >= 1024 && c.hidden <= 4096 && (c.hidden % 8) == 0) carry_mask |= 1;
+    if (ft_gemm_tc_pair_eligible(m->ctx, (int)T, c.ffn)) carry_mask |= 2;
+    if (ft_gemm_tc_pair_eligible(m->ctx, (int)T, m->nq)) carry_mask |= 4 | 8;
+    carry_mask &= env_mask;
+  }
+  int* carry_amax = fused ? b.take<int>((size_t)m->carry_slots()) : nullptr;
+  float* carry_scales = fused ? b.take<float>(4 * (size_t)m->carry_slots()) : nullptr;
+  __half* dx16 = (carry_mask & 1) ? b.take<__half>(T * c.hidden) : nullptr;
+  __half* df16 = (carry_mask & 2) ? b.take<__half>(T * c.ffn) : nullptr;
+  __half* dattn16 = (carry_mask & 4) ? b.take<__half>(T * m->nq) : nullptr;
   if (!dry) {
+    m->carry_amax = carry_amax; m->carry_scales = carry_scales; m->carry_mask = carry_mask;
+    m->dx16 = dx16; m->df16 = df16; m->dattn16 = dattn16;
     m->gu_amax = gu_amax;
     m->plan_fused = fused; m->hN16 = hN16; m->xa16_head = xa16_head; m->g16 = g16;
     m->rope_table = rope_table; m->table_seq = 0;
@@ -536,10 +574,25 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
 // carried through G and removed by the epilogues (1/S is a device scalar).
 // When dY16 is given, dY has already been converted (pitch lddy, scale in scales16).  With
 // amax_on_dx the dX product also reports its largest magnitude for the conversion that follows.
+// Where the input gradient's largest magnitude goes, and (with dX16) the f16 form that
+// replaces the f32 result, written with a carried scale.
+struct DxOut {
+  int* amax_out = nullptr;
+  __half* dX16 = nullptr; long long ld16 = 0;
+  const int* carry_in = nullptr;
+  float* carry_scales = nullptr;
+};
+// the next producer's largest magnitude goes to `slot` (zero since the pass began)
+void arm_at(FtContext* ctx, int* slot) {
+  ctx->amax_out = slot;
+  ctx->amax_ready = false;
+}
+
 int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const float* dY,
                      long long lddy, const __half* xa16, float* dX, long long lddx,
                      const float* residual, long long ldr, int T, const __half* dY16 = nullptr,
-                     const float* scales16 = nullptr, bool amax_on_dx = false) {
+                     const float* scales16 = nullptr, bool amax_on_dx = false,
+                     const DxOut* dxo = nullptr) {
   FtContext* ctx = m->ctx;
   const int r = m->cfg.lora_rank;
   long long np = (long long)ft_align_up((size_t)g.n, 8);
@@ -551,14 +604,14 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     dY16 = m->cvt_hi;
   }
   const float* inv_s = scales + 1;
-  if (g.R > 0 && !dX) {
+  if (g.R > 0 && !dX && !(dxo && dxo->dX16)) {
     FtGemmArgs a;   // G16 = (alpha/r) * (S dY) . B^T
     a.a = dY16; a.lda = np; a.b = g.b_bd16; a.ldb = g.n;
     a.M = T; a.N = RP; a.K = g.n;
     a.c16 = m->g16; a.ldc16 = RP; a.alpha = m->scale;
     FT_TRY(ft_gemm_tc_ex(ctx, a));
   }
-  if (dX) {
+  if (dX || (dxo && dxo->dX16)) {
     FtGemmArgs a;
     a.a = dY16; a.lda = np; a.b = g.w_kn; a.ldb = g.n;
     a.M = T; a.N = g.in; a.K = g.n;
@@ -568,7 +621,14 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
       a.pre_b = g.b_bd16; a.pre_ldb = g.n; a.pre_c16 = m->g16; a.pre_ldc16 = RP; a.pre_alpha = m->scale;
     }
     a.c = dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
-    if (amax_on_dx) {
+    if (dxo) {
+      a.amax_slot = dxo->amax_out;
+      if (dxo->dX16) {
+        a.c = nullptr;
+        a.c16 = dxo->dX16; a.ldc16 = dxo->ld16;
+        a.carry_amax = dxo->carry_in; a.carry_exp = kCarryExp; a.carry_scales = dxo->carry_scales;
+      }
+    } else if (amax_on_dx) {
       FT_TRY(ft_amax_arm(ctx));
       a.want_amax = true;
     }
@@ -659,35 +719,100 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   const FtModelConfig& c = m->cfg;
   Layer& ly = m->layers[l];
   const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
-  // On entry an armed amax of m->dx is pending (left by the norm backward that produced it).
+  const int L = c.layers;
+  const bool top = l == L - 1;
+  // m->dx is version k0 of the residual-stream gradient (0 = what the final norm left).  With
+  // carried scales every later version also exists as f16 rows in m->dx16; version 0 is
+  // converted by a pass of its own, from the amax its producer left in slot_dx(0).
+  const int k0 = 2 * (L - 1 - l);
+  const bool cdx = (m->carry_mask & 1) != 0;
+  const bool cdf = (m->carry_mask & 2) != 0 && !top;
+  const bool cda = (m->carry_mask & 4) != 0 && !top && m->tc_attention;
+  auto dx16_of = [&](int k) { return cdx && k > 0 ? m->dx16 : nullptr; };
+  auto dxs_of = [&](int k) { return cdx && k > 0 ? m->cscales(m->slot_dx(k)) : nullptr; };
+  // norm backward producing version k + 1 from version k
+  auto norm_bwd = [&](const float* x, const float* w, int k) -> int {
+    if (cdx) {
+      FtCarry cy;
+      cy.amax_in = m->camax(m->slot_dx(k)); cy.exp = kCarryExp;
+      cy.scales = m->cscales(m->slot_dx(k + 1)); cy.amax_out = m->camax(m->slot_dx(k + 1));
+      return ft_k_rms_norm_bwd_carry(ctx, x, w, m->dh, m->dx, m->dx16, T, h, c.eps, cy);
+    }
+    arm_at(ctx, m->camax(m->slot_dx(k + 1)));
+    return ft_k_rms_norm_bwd(ctx, x, w, m->dh, m->dx, nullptr, T, h, c.eps, true);
+  };
   // The down projection's input gradient reports its amax; SwiGLU's backward bounds its own
   // output with it and writes the gate|up gradient as f16 operands in the same pass.
-  FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, m->dx, h, a.xa16_down, m->df, F, nullptr, 0, T,
-                          nullptr, nullptr, true));
+  DxOut od;
+  od.amax_out = m->camax(m->slot_df(l));
+  if (cdf) {
+    od.dX16 = m->df16; od.ld16 = F;
+    od.carry_in = m->camax(m->slot_df(l + 1)); od.carry_scales = m->cscales(m->slot_df(l));
+  }
+  FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, dx16_of(k0) ? nullptr : m->dx, h, a.xa16_down, m->df, F,
+                          nullptr, 0, T, dx16_of(k0), dxs_of(k0), false, &od));
   const float* gu_scales = nullptr;
-  FT_TRY(ft_k_silu_gate_bwd16h(ctx, a.gu16, 2 * F, m->df, F, m->cvt_hi, 2 * F, T, F, m->gu_amax + l,
-                               &gu_scales));
+  if (cdf) {
+    FT_TRY(ft_k_silu_gate_bwd16hh(ctx, a.gu16, 2 * F, m->df16, F, m->cscales(m->slot_df(l)),
+                                  m->camax(m->slot_df(l)), m->cvt_hi, 2 * F, T, F, m->gu_amax + l,
+                                  &gu_scales));
+  } else {
+    ctx->amax_out = m->camax(m->slot_df(l));
+    ctx->amax_ready = true;
+    FT_TRY(ft_k_silu_gate_bwd16h(ctx, a.gu16, 2 * F, m->df, F, m->cvt_hi, 2 * F, T, F, m->gu_amax + l,
+                                 &gu_scales));
+  }
   FT_TRY(linear_bwd_fused(m, ly.gu, a.h2_16, nullptr, 2 * F, a.xa16_gu, m->dh, h, nullptr, 0, T,
                           m->cvt_hi, gu_scales));
-  FT_TRY(ft_amax_arm(ctx));
-  FT_TRY(ft_k_rms_norm_bwd(ctx, a.x1, ly.norm2, m->dh, m->dx, nullptr, T, h, c.eps, true));
+  FT_TRY(norm_bwd(a.x1, ly.norm2, k0));
   const bool need_dx = l > 0;
+  const int k1 = k0 + 1;
   if (m->tc_attention) {
     // the o projection's input gradient reports its amax; attention consumes it as f16
-    FT_TRY(linear_bwd_fused(m, ly.o, a.attn16, m->dx, h, a.xa16_o, m->dattn, nq, nullptr, 0, T,
-                            nullptr, nullptr, true));
+    DxOut oa;
+    oa.amax_out = m->camax(m->slot_dattn(l));
+    const __half* do16 = m->cvt_hi;
     const float* scales = nullptr;
-    FT_TRY(ft_to_f16(ctx, m->dattn, nq, m->cvt_hi, nullptr, nq, T, nq, true, &scales, 8));
-    FT_TRY(ft_amax_arm(ctx));
-    FT_TRY(ft_attention_bwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, m->cvt_hi, nq,
-                               m->dqkv, nqkv, m->dqkv + nq, m->dqkv + nq + nkv, nqkv, a.stats,
-                               scales + 1, m->sequences, m->seq_len, c.heads, c.kv_heads,
-                               c.head_dim));
-    // inverse RoPE + f16 rounding in one pass; a rotation grows a component by at most sqrt(2),
-    // hence the target exponent one below the usual one
-    FT_TRY(ft_scales_from_amax_or_pass(ctx, m->dqkv, nqkv, T, nqkv, 7, &scales));
-    FT_TRY(ft_k_rope_to_f16(ctx, m->dqkv, m->cvt_hi, nqkv, T, nq, nkv, m->seq_len, m->rope_table, true,
-                            scales));
+    if (cda) {
+      oa.dX16 = m->dattn16; oa.ld16 = nq;
+      oa.carry_in = m->camax(m->slot_dattn(l + 1)); oa.carry_scales = m->cscales(m->slot_dattn(l));
+    }
+    FT_TRY(linear_bwd_fused(m, ly.o, a.attn16, dx16_of(k1) ? nullptr : m->dx, h, a.xa16_o, m->dattn, nq,
+                            nullptr, 0, T, dx16_of(k1), dxs_of(k1), false, &oa));
+    if (cda) {
+      do16 = m->dattn16;
+      scales = m->cscales(m->slot_dattn(l));
+    } else {
+      ctx->amax_out = m->camax(m->slot_dattn(l));
+      ctx->amax_ready = true;
+      FT_TRY(ft_to_f16(ctx, m->dattn, nq, m->cvt_hi, nullptr, nq, T, nq, true, &scales, 8));
+    }
+    arm_at(ctx, m->camax(m->slot_dqkv(l)));
+    // (a rotation grows a component by at most sqrt(2), hence target exponents one below the
+    // usual ones for dq | dk | dv)
+    if (cda && (m->carry_mask & 8)) {
+      // the attention kernels write the rotated-back, scaled f16 rows themselves; m->cvt_hi is
+      // free here because the output gradient arrived in m->dattn16
+      FtAttnBwdOut16 o16;
+      o16.rows = m->cvt_hi; o16.ld = nqkv; o16.table = m->rope_table;
+      o16.carry_amax = m->camax(m->slot_dqkv(l + 1)); o16.carry_exp = kCarryExp - 1;
+      o16.carry_scales = m->cscales(m->slot_dqkv(l));
+      FT_TRY(ft_attention_bwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, do16, nq,
+                                 nullptr, 0, nullptr, nullptr, 0, a.stats, scales + 1, m->sequences,
+                                 m->seq_len, c.heads, c.kv_heads, c.head_dim, &o16));
+      ctx->amax_out = nullptr;
+      ctx->amax_ready = false;
+      scales = o16.carry_scales;
+    } else {
+      FT_TRY(ft_attention_bwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, do16, nq,
+                                 m->dqkv, nqkv, m->dqkv + nq, m->dqkv + nq + nkv, nqkv, a.stats,
+                                 scales + 1, m->sequences, m->seq_len, c.heads, c.kv_heads,
+                                 c.head_dim));
+      // inverse RoPE + f16 rounding in one pass
+      FT_TRY(ft_scales_from_amax_or_pass(ctx, m->dqkv, nqkv, T, nqkv, 7, &scales));
+      FT_TRY(ft_k_rope_to_f16(ctx, m->dqkv, m->cvt_hi, nqkv, T, nq, nkv, m->seq_len, m->rope_table, true,
+                              scales));
+    }
     FT_TRY(linear_bwd_fused(m, ly.qkv, a.h1_16, nullptr, nqkv, a.xa16_qkv, need_dx ? m->dh : nullptr,
                             h, nullptr, 0, T, m->cvt_hi, scales));
   } else {
@@ -698,10 +823,7 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
     FT_TRY(linear_bwd_fused(m, ly.qkv, a.h1_16, m->dqkv, nqkv, a.xa16_qkv, need_dx ? m->dh : nullptr,
                             h, nullptr, 0, T));
   }
-  if (need_dx) {
-    FT_TRY(ft_amax_arm(ctx));
-    FT_TRY(ft_k_rms_norm_bwd(ctx, x_in, ly.norm1, m->dh, m->dx, nullptr, T, h, c.eps, true));
-  }
+  if (need_dx) FT_TRY(norm_bwd(x_in, ly.norm1, k1));
   return FT_OK;
 }
 
@@ -1070,7 +1192,11 @@ static int step_impl(FtLoraModel* m, const uint32_t* ids, const uint32_t* target
     }
   }
   if (!backward) return FT_OK;   // evaluation: the loss rows are all the caller wants
-  if (fused) FT_TRY(ft_amax_arm(ctx));   // consumed by the last block's first conversion
+  if (fused) {
+    // the pass's amax slots start from zero; the final norm's result reports into the first
+    FT_CUDA(cudaMemsetAsync(m->carry_amax, 0, sizeof(int) * (size_t)m->carry_slots(), ctx->stream));
+    arm_at(ctx, m->camax(m->slot_dx(0)));
+  }
   FT_TRY(ft_k_rms_norm_bwd(ctx, m->x[L], m->final_norm, m->dh, m->dx, nullptr, T, h, c.eps, false));
 
   // ---- blocks, last to first

@@ -275,3 +275,33 @@ def test_zero_b_adapters_leave_a_without_gradient(headline):
                 assert torch.isfinite(g).all() and float(g.abs().max()) > 0.0, name
     finally:
         h.model.load_adapters({k: v.to("cuda:0") for k, v in h.adapters_cpu.items()})
+
+
+def test_carried_scales_against_the_two_pass_route(headline, monkeypatch):
+    """The backward pass writes most activation gradients straight to f16 with a power-of-two
+    scale carried over from the block above (no f32 round trip, no conversion pass); with
+    FT_CARRY=0 every gradient takes the two-pass route (f32 result, own amax, conversion).  The
+    two must agree within operand rounding: the scale is a power of two either way, only the
+    rounding of the down projection's input gradient (f16 before SwiGLU's backward instead of
+    f32) differs.  The forward pass is the same, so the row losses are identical."""
+    from ferrotensor_b200.config import synthetic_batch
+    from ferrotensor_b200.engine import GemmMode
+    h = headline
+    h.ctx.set_gemm_mode(GemmMode.F16)
+    ids, tg, mk = synthetic_batch(h.w, 2)
+    one = (ids[:1], tg[:1], mk[:1])
+
+    def run():
+        h.gradients([one], h.w.seq_len, 1.0)        # another shape: the workspace is planned anew
+        return h.gradients([(ids, tg, mk)], h.w.seq_len, 0.5)
+
+    monkeypatch.setenv("FT_CARRY", "0")
+    two_pass, l0 = run()
+    monkeypatch.delenv("FT_CARRY")
+    carried, l1 = run()
+    h.gradients([one], h.w.seq_len, 1.0)            # leave the default plan behind
+    assert np.array_equal(l0.view(np.uint32), l1.view(np.uint32))
+    assert not torch.equal(two_pass, carried), "FT_CARRY=0 did not change the route"
+    err, scale, rel = _errors(carried.cpu().numpy(), two_pass.cpu().numpy())
+    print(f"\n  carried scales against two passes: relative L2 {rel:.2e}, worst {err.max():.2e} of {scale:.2e}")
+    assert rel < 2e-3
