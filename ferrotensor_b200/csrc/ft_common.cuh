@@ -195,6 +195,11 @@ struct FtGemmArgs {
   const int* carry_amax = nullptr;
   int carry_exp = 0;
   float* carry_scales = nullptr;
+  // rotary epilogue of a q|k|v projection (CTA-pair launches, f16 result only): the columns
+  // are heads of 64; those below rope_cols are rotated by the angles of the row's position
+  // (row % rope_seq) from rope_table ({cos, sin} [rope_seq, 32] f32), after the bias
+  const float* rope_table = nullptr;
+  int rope_seq = 0, rope_cols = 0;
   // adapter pre-tiles: when pre_b is set, the launch first computes
   //   pre_c16[M, 64] (f16, pitch pre_ldc16) = pre_alpha * A . pre_b^T   (pre_b [64, K], f16)
   // which is normally the very buffer a2 points at (the K-concatenated tail operand)

@@ -73,6 +73,8 @@ struct Epilogue {
   const int* carry_amax;   // see FtGemmArgs::carry_amax
   int carry_exp;
   float* carry_scales;
+  const float2* rope_table;   // see FtGemmArgs::rope_table (pair kernel, f16 result only)
+  int rope_seq, rope_cols;
 };
 
 // Adapter pre-tiles.  When the K-concatenated tail operand A2 (= alpha/r * A . Bpre^T, 64 columns)
@@ -799,6 +801,63 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
       if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 4)) break;
       tc_fence_after();
+      if (ep.rope_table) {
+        // q|k|v projection: the rotary rotation (component i of a 64-wide head pairs with
+        // i + 32) and the f16 rounding happen here, on the accumulator; each warp group takes
+        // every other head of the tile, a thread one row of it.
+        const int my_row = m0 + quad * 32 + lane;
+        const float2* trow = ep.rope_table + (size_t)(my_row % ep.rope_seq) * 32;
+#pragma unroll 1
+        for (int hd = grp; hd < BN / 64; hd += 2) {
+          const int col0 = n0 + hd * 64;
+          if (col0 >= N) break;
+          uint32_t ra[32], rb[32];
+          tc_ld32(t_lane + buf * BN + hd * 64, ra);
+          tc_ld32(t_lane + buf * BN + hd * 64 + 32, rb);
+          tc_wait_ld();
+          const bool rot = col0 < ep.rope_cols;
+          uint8_t* st = stage_base + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w1[4], w2[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const int i = 8 * j + e;
+              float a0 = alpha * __uint_as_float(ra[i]), a1 = alpha * __uint_as_float(ra[i + 1]);
+              float b0 = alpha * __uint_as_float(rb[i]), b1 = alpha * __uint_as_float(rb[i + 1]);
+              if (ep.bias) {
+                a0 += ep.bias[col0 + i]; a1 += ep.bias[col0 + i + 1];
+                b0 += ep.bias[col0 + 32 + i]; b1 += ep.bias[col0 + 32 + i + 1];
+              }
+              float o10 = a0, o11 = a1, o20 = b0, o21 = b1;
+              if (rot) {
+                const float4 cs = *(const float4*)(trow + i);   // {cos_i, sin_i, cos_i+1, sin_i+1}
+                o10 = a0 * cs.x - b0 * cs.y; o20 = a0 * cs.y + b0 * cs.x;
+                o11 = a1 * cs.z - b1 * cs.w; o21 = a1 * cs.w + b1 * cs.z;
+              }
+              __half2 h1 = __floats2half2_rn(o10, o11), h2 = __floats2half2_rn(o20, o21);
+              w1[e >> 1] = *(uint32_t*)&h1;
+              w2[e >> 1] = *(uint32_t*)&h2;
+            }
+            *(uint4*)(st + ((j ^ (lane & 7)) << 4)) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+            *(uint4*)(st + (((4 + j) ^ (lane & 7)) << 4)) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+          }
+          __syncwarp();
+          const int u = lane & 7;
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const int rr = 4 * t + (lane >> 3);
+            const int grow = m0 + quad * 32 + rr;
+            const uint4 v = *(const uint4*)(stage_base + rr * 128 + ((u ^ (rr & 7)) << 4));
+            if (grow < M) *(uint4*)(ep.c16 + (long long)grow * ep.ldc16 + col0 + u * 8) = v;
+          }
+          __syncwarp();   // the staging tile is reused by the next head
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_tempty + buf * 8);
+        continue;
+      }
       float* cbase = ep.c;
       uint32_t r[32];
       tc_ld32(t_lane + buf * BN + grp * 32, r);
@@ -1350,6 +1409,12 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
     FT_REQUIRE(pair && g.c16 && g.carry_scales,
                "gemm: a carried scale needs a CTA-pair launch with an f16 result");
   }
+  if (g.rope_table) {
+    FT_REQUIRE(pair && g.c16 && !g.c && !g.residual && !g.carry_amax && !g.want_amax && !g.amax_slot &&
+                   (g.N % 64) == 0 && (g.rope_cols % 64) == 0 && g.rope_seq > 0 && (g.ldc16 % 8) == 0 &&
+                   ((((uintptr_t)g.c16) | ((uintptr_t)g.rope_table)) & 15) == 0,
+               "gemm: the rotary epilogue needs a CTA-pair launch, an f16-only result and 64-wide heads");
+  }
   if (pair) {
     const int fmt = g.ab_type == FT_F16 ? 0 : 1;
     FT_TRY(make_map(ctx, &ma, g.a, dt, (uint64_t)g.K, (uint64_t)g.M, (uint64_t)g.lda, BK, 128));
@@ -1371,6 +1436,7 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
       ctx->amax_ready = true;
     }
     ep.carry_amax = g.carry_amax; ep.carry_exp = g.carry_exp; ep.carry_scales = g.carry_scales;
+    ep.rope_table = (const float2*)g.rope_table; ep.rope_seq = g.rope_seq; ep.rope_cols = g.rope_cols;
     double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
     CUtensorMap mb3 = mb;
     PreTile pre;
@@ -1414,6 +1480,7 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
     ctx->amax_ready = true;
   }
   ep.carry_amax = nullptr; ep.carry_exp = 0; ep.carry_scales = nullptr;
+  ep.rope_table = nullptr; ep.rope_seq = 0; ep.rope_cols = 0;
   double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
   // adapter pre-tiles: the tail operand A2 = pre_alpha * A . pre_b^T is made by this launch
   CUtensorMap mb3;
@@ -1514,6 +1581,7 @@ int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T) 
   ep.alpha_ptr = nullptr; ep.alpha = 1.f; ep.bias = nullptr; ep.residual = nullptr; ep.ldr = 0;
   ep.amax_slot = nullptr;
   ep.carry_amax = nullptr; ep.carry_exp = 0; ep.carry_scales = nullptr;
+  ep.rope_table = nullptr; ep.rope_seq = 0; ep.rope_cols = 0;
   // both operands M/N-major: bits 15 and 16 of the instruction descriptor
   const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
   return launch_tc<64, 8, true>(ctx, ma[0], mb[0], ma[1], mb[1], ep, prob[0].M, 64, T, 0, splits, idesc,

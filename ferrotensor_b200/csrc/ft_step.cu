@@ -130,6 +130,7 @@ struct FtLoraModel {
   // Slots: amax ints and {S, 1/S, 2^-11/S} floats, zeroed at the start of every backward pass.
   int* carry_amax = nullptr;
   float* carry_scales = nullptr;
+  bool rope_in_gemm = false;       // the q|k|v projection's epilogue applies RoPE (FT_CARRY bit 16)
   int carry_mask = 0;              // FT_CARRY bits: 1 residual stream, 2 df, 4 dattn, 8 dq|dk|dv
   __half *dx16 = nullptr, *df16 = nullptr, *dattn16 = nullptr;
   int carry_slots() const { return 5 * cfg.layers + 1; }
@@ -257,7 +258,10 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
     // FT_CARRY=<bits> (read whenever a workspace is planned) switches kinds off: 0 = every
     // gradient takes the two-pass route
     const char* env = getenv("FT_CARRY");
-    const int env_mask = env ? atoi(env) : 15;
+    const int env_mask = env ? atoi(env) : 31;
+    if ((env_mask & 16) && ft_gemm_tc_pair_eligible(m->ctx, (int)T, nqkv) && (nqkv % 64) == 0 &&
+        ((m->nq + m->nkv) % 64) == 0)
+      carry_mask |= 16;
     if (c.hidden >= 1024 && c.hidden <= 4096 && (c.hidden % 8) == 0) carry_mask |= 1;
     if (ft_gemm_tc_pair_eligible(m->ctx, (int)T, c.ffn)) carry_mask |= 2;
     if (ft_gemm_tc_pair_eligible(m->ctx, (int)T, m->nq)) carry_mask |= 4 | 8;
@@ -270,6 +274,7 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   __half* dattn16 = (carry_mask & 4) ? b.take<__half>(T * m->nq) : nullptr;
   if (!dry) {
     m->carry_amax = carry_amax; m->carry_scales = carry_scales; m->carry_mask = carry_mask;
+    m->rope_in_gemm = (carry_mask & 16) != 0;
     m->dx16 = dx16; m->df16 = df16; m->dattn16 = dattn16;
     m->gu_amax = gu_amax;
     m->plan_fused = fused; m->hN16 = hN16; m->xa16_head = xa16_head; m->g16 = g16;
@@ -554,7 +559,8 @@ int pack_all(FtLoraModel* m) {
 // Y[T, n] = X16 . W + (alpha/r)(X16 . A) . B (+ bias) (+ residual); keeps xa16 = (alpha/r) X16 . A
 int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y, long long ldy,
                      __half* xa16, const float* residual, long long ldr, int T,
-                     __half* Y16 = nullptr) {
+                     __half* Y16 = nullptr, const float* rope_table = nullptr, int rope_seq = 0,
+                     int rope_cols = 0) {
   FtContext* ctx = m->ctx;
   FtGemmArgs a;
   a.a = X16; a.lda = g.in; a.b = g.w_nk; a.ldb = g.in;
@@ -566,6 +572,7 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
   }
   a.c = Y; a.ldc = ldy; a.c16 = Y16; a.ldc16 = ldy;   // Y16: the result as f16 (pitch ldy)
   a.bias = g.bias_cat; a.residual = residual; a.ldr = ldr;
+  a.rope_table = rope_table; a.rope_seq = rope_seq; a.rope_cols = rope_cols;
   return ft_gemm_tc_ex(ctx, a);
 }
 
@@ -692,11 +699,18 @@ int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, 
   Layer& ly = m->layers[l];
   const int T = m->T, h = c.hidden, nq = m->nq, nkv = m->nkv, nqkv = nq + 2 * nkv, F = c.ffn;
   FT_TRY(ft_k_rms_norm16(ctx, x_in, ly.norm1, nullptr, a.h1_16, T, h, c.eps));
-  FT_TRY(linear_fwd_fused(m, ly.qkv, a.h1_16, a.qkv, nqkv, a.xa16_qkv, nullptr, 0, T));
+  if (m->tc_attention && m->rope_in_gemm) {
+    // the projection's epilogue rotates and rounds: no f32 q|k|v rows, no pass over them
+    FT_TRY(linear_fwd_fused(m, ly.qkv, a.h1_16, nullptr, nqkv, a.xa16_qkv, nullptr, 0, T, a.qkv16,
+                            m->rope_table, m->seq_len, nq + nkv));
+  } else {
+    FT_TRY(linear_fwd_fused(m, ly.qkv, a.h1_16, a.qkv, nqkv, a.xa16_qkv, nullptr, 0, T));
+  }
   if (m->tc_attention) {
     // RoPE (from the table) and the f16 rounding in one pass; attention on the tensor cores
-    FT_TRY(ft_k_rope_to_f16(ctx, a.qkv, a.qkv16, nqkv, T, nq, nkv, m->seq_len, m->rope_table, false,
-                            nullptr));
+    if (!m->rope_in_gemm)
+      FT_TRY(ft_k_rope_to_f16(ctx, a.qkv, a.qkv16, nqkv, T, nq, nkv, m->seq_len, m->rope_table, false,
+                              nullptr));
     FT_TRY(ft_attention_fwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, nullptr, 0, a.stats,
                                m->sequences, m->seq_len, c.heads, c.kv_heads, c.head_dim));
   } else {

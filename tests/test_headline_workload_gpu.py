@@ -277,13 +277,19 @@ def test_zero_b_adapters_leave_a_without_gradient(headline):
         h.model.load_adapters({k: v.to("cuda:0") for k, v in h.adapters_cpu.items()})
 
 
-def test_carried_scales_against_the_two_pass_route(headline, monkeypatch):
-    """The backward pass writes most activation gradients straight to f16 with a power-of-two
-    scale carried over from the block above (no f32 round trip, no conversion pass); with
-    FT_CARRY=0 every gradient takes the two-pass route (f32 result, own amax, conversion).  The
-    two must agree within operand rounding: the scale is a power of two either way, only the
-    rounding of the down projection's input gradient (f16 before SwiGLU's backward instead of
-    f32) differs.  The forward pass is the same, so the row losses are identical."""
+def test_fused_epilogues_against_the_separate_passes(headline, monkeypatch):
+    """Two fusions that remove passes over activations, each against the route it replaces
+    (FT_CARRY is read when a workspace is planned; 0 switches everything off):
+    * the q|k|v projection's epilogue applies RoPE and rounds to f16 (bit 16) instead of a pass
+      over f32 rows: same arithmetic on the same accumulator values, so losses and gradients
+      agree to the last bits of f16 operands;
+    * the backward pass writes most activation gradients straight to f16 with a power-of-two
+      scale carried over from the block above (bits 1-8: residual-stream gradient, the down and
+      o projections' input gradients, dq|dk|dv with the inverse rotation in the attention
+      kernels) instead of an f32 result, its own amax and a conversion pass.  The scale is a
+      power of two either way; only the rounding of the down projection's input gradient (f16
+      before SwiGLU's backward instead of f32) differs.  The forward pass is the same, so the
+      row losses are identical."""
     from ferrotensor_b200.config import synthetic_batch
     from ferrotensor_b200.engine import GemmMode
     h = headline
@@ -291,17 +297,24 @@ def test_carried_scales_against_the_two_pass_route(headline, monkeypatch):
     ids, tg, mk = synthetic_batch(h.w, 2)
     one = (ids[:1], tg[:1], mk[:1])
 
-    def run():
+    def run(setting):
+        if setting is None:
+            monkeypatch.delenv("FT_CARRY", raising=False)
+        else:
+            monkeypatch.setenv("FT_CARRY", setting)
         h.gradients([one], h.w.seq_len, 1.0)        # another shape: the workspace is planned anew
         return h.gradients([(ids, tg, mk)], h.w.seq_len, 0.5)
 
-    monkeypatch.setenv("FT_CARRY", "0")
-    two_pass, l0 = run()
-    monkeypatch.delenv("FT_CARRY")
-    carried, l1 = run()
+    plain, l_plain = run("0")
+    rope, l_rope = run("16")
+    fused, l_fused = run(None)
     h.gradients([one], h.w.seq_len, 1.0)            # leave the default plan behind
-    assert np.array_equal(l0.view(np.uint32), l1.view(np.uint32))
-    assert not torch.equal(two_pass, carried), "FT_CARRY=0 did not change the route"
-    err, scale, rel = _errors(carried.cpu().numpy(), two_pass.cpu().numpy())
+    assert np.allclose(l_rope, l_plain, rtol=1e-3, atol=1e-5)
+    err, scale, rel = _errors(rope.cpu().numpy(), plain.cpu().numpy())
+    print(f"\n  rotary epilogue against the rotary pass: relative L2 {rel:.2e}")
+    assert rel < 1e-3
+    assert np.array_equal(l_rope.view(np.uint32), l_fused.view(np.uint32))
+    assert not torch.equal(rope, fused), "FT_CARRY did not change the route"
+    err, scale, rel = _errors(fused.cpu().numpy(), rope.cpu().numpy())
     print(f"\n  carried scales against two passes: relative L2 {rel:.2e}, worst {err.max():.2e} of {scale:.2e}")
     assert rel < 2e-3
