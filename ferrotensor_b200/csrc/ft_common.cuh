@@ -200,6 +200,18 @@ struct FtGemmArgs {
   // (row % rope_seq) from rope_table ({cos, sin} [rope_seq, 32] f32), after the bias
   const float* rope_table = nullptr;
   int rope_seq = 0, rope_cols = 0;
+  // SwiGLU inside the epilogue (CTA-pair launches; gate|up columns interleaved in runs of 32).
+  // Forward (gate|up projection): beside c16 = gate|up, swi_f16[row, 32 per 64-column run] =
+  // silu(gate) * up; amax_slot receives the largest |gate| or |up|.
+  __half* swi_f16 = nullptr; long long swi_ldf = 0;
+  // Backward (down projection's input gradient, N = features): no f32/f16 result of its own;
+  // with the saved gate|up rows swi_gu16 it writes S * (d gate | d up) to swi_dgu16, S from the
+  // bound 1.1 * *carry_amax * *swi_gu_amax (published to swi_scales); amax_slot receives the
+  // largest magnitude of the input gradient itself.
+  const __half* swi_gu16 = nullptr; long long swi_ldgu = 0;
+  __half* swi_dgu16 = nullptr; long long swi_lddgu = 0;
+  const int* swi_gu_amax = nullptr;
+  float* swi_scales = nullptr;
   // adapter pre-tiles: when pre_b is set, the launch first computes
   //   pre_c16[M, 64] (f16, pitch pre_ldc16) = pre_alpha * A . pre_b^T   (pre_b [64, K], f16)
   // which is normally the very buffer a2 points at (the K-concatenated tail operand)
@@ -231,6 +243,9 @@ struct FtKoSeg {
   float* out = nullptr;
   int m0 = 0, mcount = 0, n0 = 0, ncount = 0;
   long long som = 0, son = 0;
+  // >= 0: the segment's rows are interleaved in runs of 32 with another segment's: its row m is
+  // row (m / 32) * 64 + il_off + m % 32 of the product (m0 is not used then)
+  int il_off = -1;
 };
 struct FtKoProblem {
   const void* a = nullptr; long long lda = 0;
@@ -299,17 +314,19 @@ int ft_k_scale(FtContext* ctx, float* x, size_t n, float s);
 // 2-D SwiGLU: out[t, j] = silu(a[t*lda + j]) * b[t*ldb + j], j < n
 int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b, long long ldb,
                    float* out, long long ldo, int rows, int n);
+// gu rows hold gate | up as two halves of n columns each, or (il) interleaved in runs of 32:
+// gate 0..31, up 0..31, gate 32..63, ...; the backward forms write d gate | d up the same way
 int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* out, long long ldo,
-                      int rows, int n, int* in_amax);
+                      int rows, int n, int* in_amax, bool il = false);
 int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const float* g,
                           long long ldg, __half* out, long long ldo, int rows, int n,
-                          const int* in_amax, const float** scales_out);
+                          const int* in_amax, const float** scales_out, bool il = false);
 // the same with the upstream gradient as f16 rows carrying the scale g_scales[0]; g_amax is the
 // largest magnitude of the UNSCALED upstream gradient
 int ft_k_silu_gate_bwd16hh(FtContext* ctx, const __half* gu, long long ld, const __half* g16,
                            long long ldg, const float* g_scales, const int* g_amax, __half* out,
                            long long ldo, int rows, int n, const int* in_amax,
-                           const float** scales_out);
+                           const float** scales_out, bool il = false);
 int ft_k_silu_gate_bwd(FtContext* ctx, const float* a, long long lda, const float* b,
                        long long ldb, const float* g, long long ldg, float* ga, long long ldga,
                        float* gb, long long ldgb, int rows, int n);

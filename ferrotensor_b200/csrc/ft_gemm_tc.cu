@@ -75,7 +75,21 @@ struct Epilogue {
   float* carry_scales;
   const float2* rope_table;   // see FtGemmArgs::rope_table (pair kernel, f16 result only)
   int rope_seq, rope_cols;
+  // SwiGLU in the epilogue (pair kernel; columns are gate|up interleaved in runs of 32):
+  __half* swi_f16;            // forward: silu(gate) * up of every 64-column run -> 32 columns here
+  long long swi_ldf;
+  // backward (the columns are the SwiGLU output's features): the result is the gradient of the
+  // SwiGLU output; with the saved gate|up rows it becomes d gate | d up, written interleaved
+  const __half* swi_gu16;
+  long long swi_ldgu;
+  __half* swi_dgu16;
+  long long swi_lddgu;
+  const int* swi_gu_amax;     // largest |gate| or |up| of the forward pass
+  float* swi_scales;          // {S, 1/S, 2^-11/S} of the d gate | d up rows (published)
 };
+
+// sigmoid with the fast exponential and reciprocal (about 2 ulp), as the SwiGLU kernels use
+__device__ __forceinline__ float tc_fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 // Adapter pre-tiles.  When the K-concatenated tail operand A2 (= alpha/r * A . Bpre^T, 64 columns)
 // does not exist yet, the same launch computes it: `tiles` extra tiles of TM rows x 64 columns,
@@ -747,9 +761,23 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     const float alpha = (ep.alpha_ptr ? *ep.alpha_ptr : 1.0f) * ep.alpha;
     // carried scale of the f16 result (a power of two from an earlier tensor's amax)
     float s16 = 1.0f;
-    if (ep.carry_amax) {
+    if (ep.carry_amax && !ep.swi_dgu16) {
       s16 = ft_scale_from_amax_bits(*ep.carry_amax, ep.carry_exp);
       if (blockIdx.x == 0 && warp == 2 && lane == 0) ft_publish_scales(ep.carry_scales, s16);
+    }
+    // SwiGLU backward in the epilogue: every result is at most 1.1 * max|d f| * max(|gate|, |up|);
+    // max|d f| is not known before this launch has finished, so the bound takes the carried one
+    // (the block above) and aims it at 2^9: 128-fold growth between neighbours before f16
+    // overflows.  One thread publishes {S, 1/S, 2^-11/S}.
+    float swi_S = 1.0f;
+    if (ep.swi_dgu16) {
+      const float bound = 1.1f * __int_as_float(*ep.carry_amax) * __int_as_float(*ep.swi_gu_amax);
+      if (bound > 0.f && isfinite(bound)) {
+        int e;
+        frexpf(bound, &e);
+        swi_S = ldexpf(1.0f, 9 - e);
+      }
+      if (blockIdx.x == 0 && warp == 2 && lane == 0) ft_publish_scales(ep.swi_scales, swi_S);
     }
     const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16);
     float amax_seen = 0.f;
@@ -799,8 +827,159 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       const int m0 = mt * TM + (int)rank * BM;
       const int n0 = nt * BN;
       const uint32_t buf = local & 1, acc_phase = (local >> 1) & 1;
+      if (ep.swi_dgu16) {
+        // the saved gate | up rows this thread will want: ask L2 for them while the tile's
+        // products are still running
+        const int my_row = m0 + quad * 32 + lane;
+        if (my_row < M) {
+          const __half* gp = ep.swi_gu16 + (long long)my_row * ep.swi_ldgu + 2 * (long long)n0;
+#pragma unroll
+          for (int cb = 0; cb < NCH / 2; ++cb)
+            if (n0 + (grp + 2 * cb) * 32 < N)
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(gp + 64 * (grp + 2 * cb)));
+        }
+      }
       if (!mbar_wait(bar_tfull + buf * 8, acc_phase, abort_flag, status, 4)) break;
       tc_fence_after();
+      if (ep.swi_f16) {
+        // gate|up projection, forward: a thread holds gate and up of 32 features of one row.
+        // gate | up go out as f16 (interleaved as they are), and silu(gate) * up, computed from
+        // those rounded values as the backward pass will see them, as the down projection's operand
+        uint8_t* st = stage_base + lane * 128;
+        uint8_t* sf = stage_base + lane * 64;
+#pragma unroll 1
+        for (int hd = grp; hd < BN / 64; hd += 2) {
+          const int col0 = n0 + hd * 64;
+          if (col0 >= N) break;
+          uint32_t ra[32], rb[32];
+          tc_ld32(t_lane + buf * BN + hd * 64, ra);
+          tc_ld32(t_lane + buf * BN + hd * 64 + 32, rb);
+          tc_wait_ld();
+          uint32_t wf[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w1[4], w2[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const int i = 8 * j + e;
+              const __half2 hg = __floats2half2_rn(alpha * __uint_as_float(ra[i]), alpha * __uint_as_float(ra[i + 1]));
+              const __half2 hu = __floats2half2_rn(alpha * __uint_as_float(rb[i]), alpha * __uint_as_float(rb[i + 1]));
+              w1[e >> 1] = *(const uint32_t*)&hg;
+              w2[e >> 1] = *(const uint32_t*)&hu;
+              const float2 g = __half22float2(hg), u = __half22float2(hu);
+              amax_seen = fmaxf(amax_seen, fmaxf(fmaxf(fabsf(g.x), fabsf(g.y)), fmaxf(fabsf(u.x), fabsf(u.y))));
+              const __half2 hf = __floats2half2_rn(g.x * tc_fast_sigmoid(g.x) * u.x, g.y * tc_fast_sigmoid(g.y) * u.y);
+              wf[i >> 1] = *(const uint32_t*)&hf;
+            }
+            *(uint4*)(st + ((j ^ (lane & 7)) << 4)) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+            *(uint4*)(st + (((4 + j) ^ (lane & 7)) << 4)) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+          }
+          __syncwarp();
+          {
+            const int u = lane & 7;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              const int rr = 4 * t + (lane >> 3);
+              const int grow = m0 + quad * 32 + rr;
+              const uint4 v = *(const uint4*)(stage_base + rr * 128 + ((u ^ (rr & 7)) << 4));
+              if (grow < M) *(uint4*)(ep.c16 + (long long)grow * ep.ldc16 + col0 + u * 8) = v;
+            }
+          }
+          __syncwarp();
+          // the 32 products of this row: 64 bytes, staged with a 64-byte pitch
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *(uint4*)(sf + ((j ^ ((lane >> 1) & 3)) << 4)) = make_uint4(wf[4 * j], wf[4 * j + 1], wf[4 * j + 2], wf[4 * j + 3]);
+          __syncwarp();
+          {
+            const int u = lane & 3;
+            const int fcol0 = (col0 >> 6) << 5;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const int rr = 8 * t + (lane >> 2);
+              const int grow = m0 + quad * 32 + rr;
+              const uint4 v = *(const uint4*)(stage_base + rr * 64 + ((u ^ ((rr >> 1) & 3)) << 4));
+              if (grow < M) *(uint4*)(ep.swi_f16 + (long long)grow * ep.swi_ldf + fcol0 + u * 8) = v;
+            }
+          }
+          __syncwarp();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_tempty + buf * 8);
+        continue;
+      }
+      if (ep.swi_dgu16) {
+        // down projection, input gradient: column c is feature c of the SwiGLU output.  A
+        // thread holds 32 adjacent features of one row and needs the row's saved gate | up of
+        // those features (128 contiguous bytes); it produces d gate | d up (128 bytes) times S.
+        // Both sides pass through the warp's staging tile so that global accesses stay
+        // coalesced (eight lanes per 128-byte row) instead of one row per lane.
+        const int row_base = m0 + quad * 32;
+        const int u8 = lane & 7;
+        uint8_t* st = stage_base + lane * 128;
+#pragma unroll 1
+        for (int cb = grp; cb < NCH; cb += 2) {
+          const int col0 = n0 + cb * 32;
+          if (col0 >= N) break;
+          uint4 v[8];
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const int grow = row_base + 4 * t + (lane >> 3);
+            v[t] = grow < M ? *(const uint4*)(ep.swi_gu16 + (long long)grow * ep.swi_ldgu + 2 * (long long)col0 + u8 * 8)
+                            : make_uint4(0u, 0u, 0u, 0u);
+          }
+          uint32_t r[32];
+          tc_ld32(t_lane + buf * BN + cb * 32, r);
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const int rr = 4 * t + (lane >> 3);
+            *(uint4*)(stage_base + rr * 128 + ((u8 ^ (rr & 7)) << 4)) = v[t];
+          }
+          __syncwarp();
+          uint4 gu[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) gu[q] = *(const uint4*)(st + ((q ^ (lane & 7)) << 4));
+          __syncwarp();   // every lane holds its row of gate | up: the tile may be overwritten
+          tc_wait_ld();
+          const __half2* gh = (const __half2*)gu;        // gate: halves 0..31
+          const __half2* uh = gh + 16;                   // up: halves 32..63
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t og[4], ou[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = 8 * q + 2 * e;
+              const float2 g = __half22float2(gh[i >> 1]), u = __half22float2(uh[i >> 1]);
+              const float d0 = alpha * __uint_as_float(r[i]), d1 = alpha * __uint_as_float(r[i + 1]);
+              amax_seen = fmaxf(amax_seen, fmaxf(fabsf(d0), fabsf(d1)));
+              const float s0 = tc_fast_sigmoid(g.x), s1 = tc_fast_sigmoid(g.y);
+              const float k0 = d0 * swi_S, k1 = d1 * swi_S;
+              const __half2 hu = __floats2half2_rn(k0 * (g.x * s0), k1 * (g.y * s1));
+              const __half2 hg = __floats2half2_rn(k0 * u.x * (s0 * (1.0f + g.x * (1.0f - s0))),
+                                                   k1 * u.y * (s1 * (1.0f + g.y * (1.0f - s1))));
+              og[e] = *(const uint32_t*)&hg;
+              ou[e] = *(const uint32_t*)&hu;
+            }
+            *(uint4*)(st + ((q ^ (lane & 7)) << 4)) = make_uint4(og[0], og[1], og[2], og[3]);
+            *(uint4*)(st + (((4 + q) ^ (lane & 7)) << 4)) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const int rr = 4 * t + (lane >> 3);
+            const int grow = row_base + rr;
+            const uint4 w = *(const uint4*)(stage_base + rr * 128 + ((u8 ^ (rr & 7)) << 4));
+            if (grow < M)
+              *(uint4*)(ep.swi_dgu16 + (long long)grow * ep.swi_lddgu + 2 * (long long)col0 + u8 * 8) = w;
+          }
+          __syncwarp();   // the staging tile is reused by the next chunk
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_tempty + buf * 8);
+        continue;
+      }
       if (ep.rope_table) {
         // q|k|v projection: the rotary rotation (component i of a 64-wide head pairs with
         // i + 32) and the f16 rounding happen here, on the accumulator; each warp group takes
@@ -980,6 +1159,7 @@ struct SlabSegs {
   int M[6];
   int m0[6], mcount[6], n0[6], ncount[6];
   long long som[6], son[6];
+  int il_off[6];   // FtKoSeg::il_off
 };
 __global__ void k_slab_reduce_multi(int slabs, int ldp, SlabSegs sg,
                                     const float* __restrict__ alpha_ptr, float alpha,
@@ -996,8 +1176,10 @@ __global__ void k_slab_reduce_multi(int slabs, int ldp, SlabSegs sg,
   for (; i < total; i += st) {
     int m = (int)(i / ncount), n = (int)(i % ncount);
     float acc = 0.f;
+    const int il = sg.il_off[seg];
+    const int prow = il < 0 ? sg.m0[seg] + m : ((m >> 5) << 6) + il + (m & 31);
     for (int s = 0; s < slabs; ++s)
-      acc += part[((size_t)s * M + (sg.m0[seg] + m)) * ldp + (sg.n0[seg] + n)];
+      acc += part[((size_t)s * M + prow) * ldp + (sg.n0[seg] + n)];
     float* o = sg.out[seg] + (long long)m * sg.som[seg] + (long long)n * sg.son[seg];
     *o = accumulate ? *o + a * acc : a * acc;
   }
@@ -1405,9 +1587,22 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   const CUtensorMapDataType dt = g.ab_type == FT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const bool pair = ft_gemm_tc_pair_eligible(ctx, g.M, g.N);
-  if (g.carry_amax) {
+  if (g.carry_amax && !g.swi_dgu16) {
     FT_REQUIRE(pair && g.c16 && g.carry_scales,
                "gemm: a carried scale needs a CTA-pair launch with an f16 result");
+  }
+  if (g.swi_f16) {
+    FT_REQUIRE(pair && g.c16 && !g.c && !g.residual && !g.bias && !g.carry_amax && !g.rope_table &&
+                   g.amax_slot && (g.N % 64) == 0 && (g.ldc16 % 8) == 0 && (g.swi_ldf % 8) == 0 &&
+                   ((((uintptr_t)g.c16) | ((uintptr_t)g.swi_f16)) & 15) == 0,
+               "gemm: the SwiGLU epilogue needs a CTA-pair launch, f16 results and 64-column runs");
+  }
+  if (g.swi_dgu16) {
+    FT_REQUIRE(pair && !g.c && !g.c16 && !g.residual && !g.bias && !g.rope_table && !g.swi_f16 &&
+                   g.carry_amax && g.swi_gu16 && g.swi_gu_amax && g.swi_scales && g.amax_slot &&
+                   (g.N % 32) == 0 && (g.swi_ldgu % 8) == 0 && (g.swi_lddgu % 8) == 0 &&
+                   ((((uintptr_t)g.swi_gu16) | ((uintptr_t)g.swi_dgu16)) & 15) == 0,
+               "gemm: the SwiGLU backward epilogue needs a CTA-pair launch and interleaved f16 rows");
   }
   if (g.rope_table) {
     FT_REQUIRE(pair && g.c16 && !g.c && !g.residual && !g.carry_amax && !g.want_amax && !g.amax_slot &&
@@ -1437,6 +1632,9 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
     }
     ep.carry_amax = g.carry_amax; ep.carry_exp = g.carry_exp; ep.carry_scales = g.carry_scales;
     ep.rope_table = (const float2*)g.rope_table; ep.rope_seq = g.rope_seq; ep.rope_cols = g.rope_cols;
+    ep.swi_f16 = g.swi_f16; ep.swi_ldf = g.swi_ldf;
+    ep.swi_gu16 = g.swi_gu16; ep.swi_ldgu = g.swi_ldgu; ep.swi_dgu16 = g.swi_dgu16;
+    ep.swi_lddgu = g.swi_lddgu; ep.swi_gu_amax = g.swi_gu_amax; ep.swi_scales = g.swi_scales;
     double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
     CUtensorMap mb3 = mb;
     PreTile pre;
@@ -1481,6 +1679,8 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   }
   ep.carry_amax = nullptr; ep.carry_exp = 0; ep.carry_scales = nullptr;
   ep.rope_table = nullptr; ep.rope_seq = 0; ep.rope_cols = 0;
+  ep.swi_f16 = nullptr; ep.swi_ldf = 0; ep.swi_gu16 = nullptr; ep.swi_ldgu = 0; ep.swi_dgu16 = nullptr;
+  ep.swi_lddgu = 0; ep.swi_gu_amax = nullptr; ep.swi_scales = nullptr;
   double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
   // adapter pre-tiles: the tail operand A2 = pre_alpha * A . pre_b^T is made by this launch
   CUtensorMap mb3;
@@ -1582,6 +1782,8 @@ int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T) 
   ep.amax_slot = nullptr;
   ep.carry_amax = nullptr; ep.carry_exp = 0; ep.carry_scales = nullptr;
   ep.rope_table = nullptr; ep.rope_seq = 0; ep.rope_cols = 0;
+  ep.swi_f16 = nullptr; ep.swi_ldf = 0; ep.swi_gu16 = nullptr; ep.swi_ldgu = 0; ep.swi_dgu16 = nullptr;
+  ep.swi_lddgu = 0; ep.swi_gu_amax = nullptr; ep.swi_scales = nullptr;
   // both operands M/N-major: bits 15 and 16 of the instruction descriptor
   const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
   return launch_tc<64, 8, true>(ctx, ma[0], mb[0], ma[1], mb[1], ep, prob[0].M, 64, T, 0, splits, idesc,
@@ -1604,7 +1806,7 @@ int ft_slab_reduce_problems(FtContext* ctx, int nprob, const FtKoProblem* prob,
       const int k = sg.count++;
       sg.out[k] = S.out; sg.part[k] = prob[q].slabs; sg.M[k] = prob[q].M;
       sg.m0[k] = S.m0; sg.mcount[k] = S.mcount; sg.n0[k] = S.n0; sg.ncount[k] = S.ncount;
-      sg.som[k] = S.som; sg.son[k] = S.son;
+      sg.som[k] = S.som; sg.son[k] = S.son; sg.il_off[k] = S.il_off;
       most = std::max(most, (size_t)S.mcount * S.ncount);
     }
   }

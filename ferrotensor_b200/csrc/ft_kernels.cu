@@ -491,9 +491,14 @@ __global__ void k_silu_gate(const float* __restrict__ a, long long lda,
 // SwiGLU forward from f16 gate | up rows (the projection wrote them as f16) to the f16 operand
 // of the down projection: 8 columns per thread.  With in_amax the largest |gate| or |up| seen is
 // folded into that slot: the backward pass bounds its output with it.
+// (il: gate and up interleaved in runs of 32 columns, b = a + 32: feature c sits at
+// (c / 32) * 64 + c % 32 of either)
+__device__ __forceinline__ size_t il_feature(size_t c, int il) {
+  return il ? ((c >> 5) << 6) + (c & 31) : c;
+}
 __global__ void k_silu_gate16h(const __half* __restrict__ a, const __half* __restrict__ b,
                                long long ldab, __half* __restrict__ out, long long ldo, int rows,
-                               int n, int* in_amax) {
+                               int n, int* in_amax, int il) {
   ft_pdl_wait();
   ft_pdl_launch();
   const size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
@@ -502,8 +507,8 @@ __global__ void k_silu_gate16h(const __half* __restrict__ a, const __half* __res
   RowWalk w(i, st, per_row);
   __half2 am2 = __float2half2_rn(0.f);
   for (; i < total; i += st, w.next()) {
-    const size_t c = (size_t)w.c * 8;
-    const uint4 xa = *(const uint4*)(a + w.r * ldab + c), ya = *(const uint4*)(b + w.r * ldab + c);
+    const size_t c = (size_t)w.c * 8, ci = il_feature(c, il);
+    const uint4 xa = *(const uint4*)(a + w.r * ldab + ci), ya = *(const uint4*)(b + w.r * ldab + ci);
     const __half2* xh = (const __half2*)&xa;
     const __half2* yh = (const __half2*)&ya;
     uint32_t o[4];
@@ -530,7 +535,7 @@ __global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* _
                                    long long ldab, const float* __restrict__ g, long long ldg,
                                    __half* __restrict__ out, long long ldo, int rows, int n,
                                    const int* __restrict__ g_amax, const int* __restrict__ in_amax,
-                                   float* __restrict__ scales_out) {
+                                   float* __restrict__ scales_out, int il) {
   ft_pdl_wait();
   ft_pdl_launch();
   float S = 1.0f;
@@ -548,13 +553,14 @@ __global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* _
     }
   }
   const size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
+  const size_t up_off = il ? 32 : (size_t)n;   // d(up) relative to d(gate) in an output row
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t st = (size_t)gridDim.x * blockDim.x;
   RowWalk w(i, st, per_row);
   for (; i < total; i += st, w.next()) {
     const long long r = w.r;
-    const size_t c = (size_t)w.c * 8;
-    const uint4 xa = *(const uint4*)(a + r * ldab + c), ya = *(const uint4*)(b + r * ldab + c);
+    const size_t c = (size_t)w.c * 8, ci = il_feature(c, il);
+    const uint4 xa = *(const uint4*)(a + r * ldab + ci), ya = *(const uint4*)(b + r * ldab + ci);
     const float4 g0 = *(const float4*)(g + r * ldg + c), g1 = *(const float4*)(g + r * ldg + c + 4);
     const __half2* xh = (const __half2*)&xa;
     const __half2* yh = (const __half2*)&ya;
@@ -576,8 +582,8 @@ __global__ void k_silu_gate_bwd16h(const __half* __restrict__ a, const __half* _
       oa[k] = *(uint32_t*)&ha;
       ob[k] = *(uint32_t*)&hb;
     }
-    *(uint4*)(out + r * ldo + c) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
-    *(uint4*)(out + r * ldo + n + c) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+    *(uint4*)(out + r * ldo + ci) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    *(uint4*)(out + r * ldo + up_off + ci) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
   }
 }
 
@@ -588,7 +594,7 @@ __global__ void k_silu_gate_bwd16hh(const __half* __restrict__ a, const __half* 
                                     const float* __restrict__ g_scales,
                                     __half* __restrict__ out, long long ldo, int rows, int n,
                                     const int* __restrict__ g_amax, const int* __restrict__ in_amax,
-                                    float* __restrict__ scales_out) {
+                                    float* __restrict__ scales_out, int il) {
   ft_pdl_wait();
   ft_pdl_launch();
   float S = 1.0f;
@@ -602,14 +608,15 @@ __global__ void k_silu_gate_bwd16hh(const __half* __restrict__ a, const __half* 
     if (blockIdx.x == 0 && threadIdx.x == 0) ft_publish_scales(scales_out, S);
   }
   const float SG = S * g_scales[1];   // powers of two: exact
+  const size_t up_off = il ? 32 : (size_t)n;
   const size_t per_row = (size_t)n / 8, total = (size_t)rows * per_row;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t st = (size_t)gridDim.x * blockDim.x;
   RowWalk w(i, st, per_row);
   for (; i < total; i += st, w.next()) {
     const long long r = w.r;
-    const size_t c = (size_t)w.c * 8;
-    const uint4 xa = *(const uint4*)(a + r * ldab + c), ya = *(const uint4*)(b + r * ldab + c);
+    const size_t c = (size_t)w.c * 8, ci = il_feature(c, il);
+    const uint4 xa = *(const uint4*)(a + r * ldab + ci), ya = *(const uint4*)(b + r * ldab + ci);
     const uint4 ga = *(const uint4*)(g16 + r * ldg + c);
     const __half2* xh = (const __half2*)&xa;
     const __half2* yh = (const __half2*)&ya;
@@ -631,8 +638,8 @@ __global__ void k_silu_gate_bwd16hh(const __half* __restrict__ a, const __half* 
       oa[k] = *(uint32_t*)&ha;
       ob[k] = *(uint32_t*)&hb;
     }
-    *(uint4*)(out + r * ldo + c) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
-    *(uint4*)(out + r * ldo + n + c) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+    *(uint4*)(out + r * ldo + ci) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    *(uint4*)(out + r * ldo + up_off + ci) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
   }
 }
 
@@ -1098,12 +1105,13 @@ int ft_k_silu_gate(FtContext* ctx, const float* a, long long lda, const float* b
 }
 
 int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* out, long long ldo,
-                      int rows, int n, int* in_amax) {
+                      int rows, int n, int* in_amax, bool il) {
+  FT_REQUIRE(!il || (n % 32) == 0, "silu_gate16h: interleaved rows need a width that is a multiple of 32");
   FT_REQUIRE((n % 8) == 0 && (ld % 8) == 0 && (ldo % 8) == 0 && (((uintptr_t)gu) & 15) == 0 &&
                  (((uintptr_t)out) & 15) == 0,
              "silu_gate16h: width and pitches must be multiples of 8");
-  FT_LAUNCH_PDL(ctx, k_silu_gate16h, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu, gu + n, ld,
-                out, ldo, rows, n, in_amax);
+  FT_LAUNCH_PDL(ctx, k_silu_gate16h, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu,
+                gu + (il ? 32 : n), ld, out, ldo, rows, n, in_amax, il ? 1 : 0);
   return FT_OK;
 }
 
@@ -1111,7 +1119,8 @@ int ft_k_silu_gate16h(FtContext* ctx, const __half* gu, long long ld, __half* ou
 // ft_k_silu_gate16h); *scales_out points at {S, 1/S, 2^-11/S} on the device.
 int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const float* g,
                           long long ldg, __half* out, long long ldo, int rows, int n,
-                          const int* in_amax, const float** scales_out) {
+                          const int* in_amax, const float** scales_out, bool il) {
+  FT_REQUIRE(!il || (n % 32) == 0, "silu_gate_bwd16h: interleaved rows need a width that is a multiple of 32");
   FT_REQUIRE((n % 8) == 0 && (ld % 8) == 0 && (ldg % 4) == 0 && (ldo % 8) == 0 &&
                  ((((uintptr_t)gu) | ((uintptr_t)g) | ((uintptr_t)out)) & 15) == 0,
              "silu_gate_bwd16h: width and pitches must be multiples of 8");
@@ -1120,8 +1129,9 @@ int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const 
   const int* g_amax = ctx->amax_out;
   ctx->amax_out = nullptr;
   ctx->amax_ready = false;
-  FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16h, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu, gu + n,
-                ld, g, ldg, out, ldo, rows, n, g_amax, in_amax, ctx->scale_buf + 4);
+  FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16h, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu,
+                gu + (il ? 32 : n), ld, g, ldg, out, ldo, rows, n, g_amax, in_amax,
+                ctx->scale_buf + 4, il ? 1 : 0);
   *scales_out = ctx->scale_buf + 4;
   return FT_OK;
 }
@@ -1129,14 +1139,15 @@ int ft_k_silu_gate_bwd16h(FtContext* ctx, const __half* gu, long long ld, const 
 int ft_k_silu_gate_bwd16hh(FtContext* ctx, const __half* gu, long long ld, const __half* g16,
                            long long ldg, const float* g_scales, const int* g_amax, __half* out,
                            long long ldo, int rows, int n, const int* in_amax,
-                           const float** scales_out) {
+                           const float** scales_out, bool il) {
+  FT_REQUIRE(!il || (n % 32) == 0, "silu_gate_bwd16hh: interleaved rows need a width that is a multiple of 32");
   FT_REQUIRE((n % 8) == 0 && (ld % 8) == 0 && (ldg % 8) == 0 && (ldo % 8) == 0 &&
                  ((((uintptr_t)gu) | ((uintptr_t)g16) | ((uintptr_t)out)) & 15) == 0,
              "silu_gate_bwd16hh: width and pitches must be multiples of 8");
   FT_REQUIRE(g_scales && g_amax && in_amax, "silu_gate_bwd16hh: scales and maxima are required");
   FT_LAUNCH_PDL(ctx, k_silu_gate_bwd16hh, ew_grid(ctx, (size_t)rows * n / 8, 256, 2), 256, 0, gu,
-                gu + n, ld, g16, ldg, g_scales, out, ldo, rows, n, g_amax, in_amax,
-                ctx->scale_buf + 4);
+                gu + (il ? 32 : n), ld, g16, ldg, g_scales, out, ldo, rows, n, g_amax, in_amax,
+                ctx->scale_buf + 4, il ? 1 : 0);
   *scales_out = ctx->scale_buf + 4;
   return FT_OK;
 }

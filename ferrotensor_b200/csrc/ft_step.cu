@@ -46,6 +46,16 @@ struct Group {
   __half* a_cat16 = nullptr;   // [in, 64]  backward tail operand:  N = in, K = 64
   float* bias_cat = nullptr;   // [n] concatenated biases, or NULL
   bool tc_lora = false;        // adapters ride on the tensor-core path
+  // gate|up on the fused path: the group's columns are interleaved in runs of 32 (gate 0..31,
+  // up 0..31, gate 32..63, ...), so that a thread of a GEMM epilogue, which holds 64 adjacent
+  // columns of a row, has the gate and the up value of 32 features: SwiGLU and its backward run
+  // inside the projections' epilogues.  Column c of linear j sits at (c / 32) * 64 + 32 j + c % 32.
+  // The interleaved operand copies exist beside the plain ones (which the unfused modes use).
+  bool il = false;
+  __half* w_nk_il = nullptr;   // [n, in] rows interleaved
+  __half* w_kn_il = nullptr;   // [in, n] columns interleaved
+  const __half* fwd_w() const { return il ? w_nk_il : w_nk; }
+  const __half* bwd_w() const { return il ? w_kn_il : w_kn; }
 };
 
 constexpr int RP = 64;
@@ -131,9 +141,11 @@ struct FtLoraModel {
   int* carry_amax = nullptr;
   float* carry_scales = nullptr;
   bool rope_in_gemm = false;       // the q|k|v projection's epilogue applies RoPE (FT_CARRY bit 16)
-  int carry_mask = 0;              // FT_CARRY bits: 1 residual stream, 2 df, 4 dattn, 8 dq|dk|dv
-  __half *dx16 = nullptr, *df16 = nullptr, *dattn16 = nullptr;
-  int carry_slots() const { return 5 * cfg.layers + 1; }
+  int carry_mask = 0;              // FT_CARRY bits: 1 residual stream, 2 df, 4 dattn, 8 dq|dk|dv,
+                                   // 128 SwiGLU backward / 256 SwiGLU forward in GEMM epilogues
+  __half *dx16 = nullptr, *df16 = nullptr, *dattn16 = nullptr, *dgu16 = nullptr;
+  int carry_slots() const { return 6 * cfg.layers + 1; }
+  int slot_dgu(int l) const { return 5 * cfg.layers + 1 + l; }   // scales only
   int slot_dx(int k) const { return k; }                                  // k = 0 .. 2L
   int slot_df(int l) const { return 2 * cfg.layers + 1 + l; }
   int slot_dattn(int l) const { return 3 * cfg.layers + 1 + l; }
@@ -258,13 +270,15 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
     // FT_CARRY=<bits> (read whenever a workspace is planned) switches kinds off: 0 = every
     // gradient takes the two-pass route
     const char* env = getenv("FT_CARRY");
-    const int env_mask = env ? atoi(env) : 31;
+    const int env_mask = env ? atoi(env) : 511;
     if ((env_mask & 16) && ft_gemm_tc_pair_eligible(m->ctx, (int)T, nqkv) && (nqkv % 64) == 0 &&
         ((m->nq + m->nkv) % 64) == 0)
       carry_mask |= 16;
     if (c.hidden >= 1024 && c.hidden <= 4096 && (c.hidden % 8) == 0) carry_mask |= 1;
     if (ft_gemm_tc_pair_eligible(m->ctx, (int)T, c.ffn)) carry_mask |= 2;
     if (ft_gemm_tc_pair_eligible(m->ctx, (int)T, m->nq)) carry_mask |= 4 | 8;
+    if (m->layers[0].gu.il && ft_gemm_tc_pair_eligible(m->ctx, (int)T, c.ffn)) carry_mask |= 128;
+    if (m->layers[0].gu.il && ft_gemm_tc_pair_eligible(m->ctx, (int)T, 2 * c.ffn)) carry_mask |= 256;
     carry_mask &= env_mask;
   }
   int* carry_amax = fused ? b.take<int>((size_t)m->carry_slots()) : nullptr;
@@ -272,10 +286,11 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   __half* dx16 = (carry_mask & 1) ? b.take<__half>(T * c.hidden) : nullptr;
   __half* df16 = (carry_mask & 2) ? b.take<__half>(T * c.ffn) : nullptr;
   __half* dattn16 = (carry_mask & 4) ? b.take<__half>(T * m->nq) : nullptr;
+  __half* dgu16 = (carry_mask & 128) ? b.take<__half>(T * 2 * c.ffn) : nullptr;
   if (!dry) {
     m->carry_amax = carry_amax; m->carry_scales = carry_scales; m->carry_mask = carry_mask;
     m->rope_in_gemm = (carry_mask & 16) != 0;
-    m->dx16 = dx16; m->df16 = df16; m->dattn16 = dattn16;
+    m->dx16 = dx16; m->df16 = df16; m->dattn16 = dattn16; m->dgu16 = dgu16;
     m->gu_amax = gu_amax;
     m->plan_fused = fused; m->hN16 = hN16; m->xa16_head = xa16_head; m->g16 = g16;
     m->rope_table = rope_table; m->table_seq = 0;
@@ -473,6 +488,7 @@ int block_backward(FtLoraModel* m, int l, const float* x_in, BlockActs& a) {
 
 struct PackMeta {
   int nlin, in, n, r;
+  int il;   // columns interleaved in runs of 32 (Group::il)
   int col_off[3], out[3], r_off[3], lora[3];
   unsigned long long a_off[3], b_off[3];
 };
@@ -500,6 +516,11 @@ __global__ void k_pack_adapters(const float* __restrict__ params, const PackJob*
       for (int j = 0; j < g.nlin; ++j)
         if (g.lora[j] && rr >= g.r_off[j] && rr < g.r_off[j] + g.r)
           v = params[g.a_off[j] + (size_t)other * g.r + (rr - g.r_off[j])];
+    } else if (g.il) {
+      // interleaved group column -> (linear, its column)
+      const int j = (other >> 5) & 1, col = ((other >> 6) << 5) + (other & 31);
+      if (g.lora[j] && col < g.out[j] && rr >= g.r_off[j] && rr < g.r_off[j] + g.r)
+        v = params[g.b_off[j] + (size_t)(rr - g.r_off[j]) * g.out[j] + col];
     } else {
       for (int j = 0; j < g.nlin; ++j)
         if (g.lora[j] && other >= g.col_off[j] && other < g.col_off[j] + g.out[j] &&
@@ -514,6 +535,7 @@ void pack_job_of(const FtLoraModel* m, const Group& g, PackJob* job) {
   memset(job, 0, sizeof(*job));
   PackMeta& pm = job->g;
   pm.nlin = g.nlin; pm.in = g.in; pm.n = g.n; pm.r = m->cfg.lora_rank;
+  pm.il = g.il ? 1 : 0;
   for (int j = 0; j < g.nlin; ++j) {
     pm.col_off[j] = g.col_off[j]; pm.out[j] = g.lin[j]->out; pm.r_off[j] = g.r_off[j];
     pm.lora[j] = g.lin[j]->lora ? 1 : 0;
@@ -560,10 +582,11 @@ int pack_all(FtLoraModel* m) {
 int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y, long long ldy,
                      __half* xa16, const float* residual, long long ldr, int T,
                      __half* Y16 = nullptr, const float* rope_table = nullptr, int rope_seq = 0,
-                     int rope_cols = 0) {
+                     int rope_cols = 0, __half* swi_f16 = nullptr, long long swi_ldf = 0,
+                     int* amax_slot = nullptr) {
   FtContext* ctx = m->ctx;
   FtGemmArgs a;
-  a.a = X16; a.lda = g.in; a.b = g.w_nk; a.ldb = g.in;
+  a.a = X16; a.lda = g.in; a.b = g.fwd_w(); a.ldb = g.in;
   a.M = T; a.N = g.n; a.K = g.in;
   if (g.R > 0) {
     // xa16 = (alpha/r) X16 . A is made by pre-tiles of the same launch
@@ -573,6 +596,7 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
   a.c = Y; a.ldc = ldy; a.c16 = Y16; a.ldc16 = ldy;   // Y16: the result as f16 (pitch ldy)
   a.bias = g.bias_cat; a.residual = residual; a.ldr = ldr;
   a.rope_table = rope_table; a.rope_seq = rope_seq; a.rope_cols = rope_cols;
+  a.swi_f16 = swi_f16; a.swi_ldf = swi_ldf; a.amax_slot = amax_slot;
   return ft_gemm_tc_ex(ctx, a);
 }
 
@@ -588,6 +612,12 @@ struct DxOut {
   __half* dX16 = nullptr; long long ld16 = 0;
   const int* carry_in = nullptr;
   float* carry_scales = nullptr;
+  // SwiGLU backward inside the epilogue (FtGemmArgs::swi_dgu16): no input gradient is stored
+  const __half* swi_gu16 = nullptr; long long swi_ldgu = 0;
+  __half* swi_dgu16 = nullptr; long long swi_lddgu = 0;
+  const int* swi_gu_amax = nullptr;
+  float* swi_scales = nullptr;
+  bool stores_f16() const { return dX16 != nullptr || swi_dgu16 != nullptr; }
 };
 // the next producer's largest magnitude goes to `slot` (zero since the pass began)
 void arm_at(FtContext* ctx, int* slot) {
@@ -611,16 +641,16 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     dY16 = m->cvt_hi;
   }
   const float* inv_s = scales + 1;
-  if (g.R > 0 && !dX && !(dxo && dxo->dX16)) {
+  if (g.R > 0 && !dX && !(dxo && dxo->stores_f16())) {
     FtGemmArgs a;   // G16 = (alpha/r) * (S dY) . B^T
     a.a = dY16; a.lda = np; a.b = g.b_bd16; a.ldb = g.n;
     a.M = T; a.N = RP; a.K = g.n;
     a.c16 = m->g16; a.ldc16 = RP; a.alpha = m->scale;
     FT_TRY(ft_gemm_tc_ex(ctx, a));
   }
-  if (dX || (dxo && dxo->dX16)) {
+  if (dX || (dxo && dxo->stores_f16())) {
     FtGemmArgs a;
-    a.a = dY16; a.lda = np; a.b = g.w_kn; a.ldb = g.n;
+    a.a = dY16; a.lda = np; a.b = g.bwd_w(); a.ldb = g.n;
     a.M = T; a.N = g.in; a.K = g.n;
     if (g.R > 0) {
       // G16 = (alpha/r) * (S dY) . B^T is made by pre-tiles of the same launch
@@ -630,7 +660,13 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     a.c = dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
     if (dxo) {
       a.amax_slot = dxo->amax_out;
-      if (dxo->dX16) {
+      if (dxo->swi_dgu16) {
+        a.c = nullptr;
+        a.swi_gu16 = dxo->swi_gu16; a.swi_ldgu = dxo->swi_ldgu;
+        a.swi_dgu16 = dxo->swi_dgu16; a.swi_lddgu = dxo->swi_lddgu;
+        a.swi_gu_amax = dxo->swi_gu_amax; a.swi_scales = dxo->swi_scales;
+        a.carry_amax = dxo->carry_in;
+      } else if (dxo->dX16) {
         a.c = nullptr;
         a.c16 = dxo->dX16; a.ldc16 = dxo->ld16;
         a.carry_amax = dxo->carry_in; a.carry_exp = kCarryExp; a.carry_scales = dxo->carry_scales;
@@ -652,6 +688,7 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
       const Linear& l = *g.lin[j];
       if (!l.lora) continue;
       FtKoSeg& sb = pr[0].seg[pr[0].nseg++];   // lora_b [r, out]
+      sb.il_off = g.il ? 32 * j : -1;
       sb.out = m->grads + l.b_off; sb.m0 = g.col_off[j]; sb.mcount = l.out;
       sb.n0 = g.r_off[j]; sb.ncount = r; sb.som = 1; sb.son = l.out;
       FtKoSeg& sa = pr[1].seg[pr[1].nseg++];   // lora_a [in, r]
@@ -722,8 +759,14 @@ int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, 
   // x1 = x_in + o(attn): the residual rides in the GEMM epilogue
   FT_TRY(linear_fwd_fused(m, ly.o, a.attn16, a.x1, h, a.xa16_o, x_in, h, T));
   FT_TRY(ft_k_rms_norm16(ctx, a.x1, ly.norm2, nullptr, a.h2_16, T, h, c.eps));
-  FT_TRY(linear_fwd_fused(m, ly.gu, a.h2_16, nullptr, 2 * F, a.xa16_gu, nullptr, 0, T, a.gu16));
-  FT_TRY(ft_k_silu_gate16h(ctx, a.gu16, 2 * F, a.f_16, F, T, F, m->gu_amax + l));
+  if (m->carry_mask & 256) {
+    // SwiGLU in the gate|up projection's epilogue: gate|up and silu(gate) * up leave together
+    FT_TRY(linear_fwd_fused(m, ly.gu, a.h2_16, nullptr, 2 * F, a.xa16_gu, nullptr, 0, T, a.gu16, nullptr,
+                            0, 0, a.f_16, F, m->gu_amax + l));
+  } else {
+    FT_TRY(linear_fwd_fused(m, ly.gu, a.h2_16, nullptr, 2 * F, a.xa16_gu, nullptr, 0, T, a.gu16));
+    FT_TRY(ft_k_silu_gate16h(ctx, a.gu16, 2 * F, a.f_16, F, T, F, m->gu_amax + l, ly.gu.il));
+  }
   FT_TRY(linear_fwd_fused(m, ly.down, a.f_16, x_out, h, a.xa16_down, a.x1, h, T));
   return FT_OK;
 }
@@ -757,27 +800,40 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   };
   // The down projection's input gradient reports its amax; SwiGLU's backward bounds its own
   // output with it and writes the gate|up gradient as f16 operands in the same pass.
+  const bool cswi = (m->carry_mask & 128) != 0 && !top;
   DxOut od;
   od.amax_out = m->camax(m->slot_df(l));
-  if (cdf) {
+  if (cswi) {
+    // SwiGLU's backward runs in this product's epilogue: d gate | d up leave as f16 operands,
+    // the gradient of the SwiGLU output itself is never stored
+    od.swi_gu16 = a.gu16; od.swi_ldgu = 2 * F;
+    od.swi_dgu16 = m->dgu16; od.swi_lddgu = 2 * F;
+    od.swi_gu_amax = m->gu_amax + l;
+    od.swi_scales = m->cscales(m->slot_dgu(l));
+    od.carry_in = m->camax(m->slot_df(l + 1));
+  } else if (cdf) {
     od.dX16 = m->df16; od.ld16 = F;
     od.carry_in = m->camax(m->slot_df(l + 1)); od.carry_scales = m->cscales(m->slot_df(l));
   }
   FT_TRY(linear_bwd_fused(m, ly.down, a.f_16, dx16_of(k0) ? nullptr : m->dx, h, a.xa16_down, m->df, F,
                           nullptr, 0, T, dx16_of(k0), dxs_of(k0), false, &od));
   const float* gu_scales = nullptr;
-  if (cdf) {
+  const __half* dgu16 = m->cvt_hi;
+  if (cswi) {
+    gu_scales = od.swi_scales;
+    dgu16 = m->dgu16;
+  } else if (cdf) {
     FT_TRY(ft_k_silu_gate_bwd16hh(ctx, a.gu16, 2 * F, m->df16, F, m->cscales(m->slot_df(l)),
                                   m->camax(m->slot_df(l)), m->cvt_hi, 2 * F, T, F, m->gu_amax + l,
-                                  &gu_scales));
+                                  &gu_scales, ly.gu.il));
   } else {
     ctx->amax_out = m->camax(m->slot_df(l));
     ctx->amax_ready = true;
     FT_TRY(ft_k_silu_gate_bwd16h(ctx, a.gu16, 2 * F, m->df, F, m->cvt_hi, 2 * F, T, F, m->gu_amax + l,
-                                 &gu_scales));
+                                 &gu_scales, ly.gu.il));
   }
   FT_TRY(linear_bwd_fused(m, ly.gu, a.h2_16, nullptr, 2 * F, a.xa16_gu, m->dh, h, nullptr, 0, T,
-                          m->cvt_hi, gu_scales));
+                          dgu16, gu_scales));
   FT_TRY(norm_bwd(a.x1, ly.norm2, k0));
   const bool need_dx = l > 0;
   const int k1 = k0 + 1;
@@ -841,18 +897,23 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
   return FT_OK;
 }
 
+// il_off >= 0: source column c goes to the interleaved column (c / 32) * 64 + il_off + c % 32
+__device__ __forceinline__ long long il_col(long long c, int il_off) {
+  return il_off < 0 ? c : ((c >> 5) << 6) + il_off + (c & 31);
+}
 __global__ void k_copy_f16_2d(const __half* __restrict__ src, long long lds, __half* __restrict__ dst,
-                              long long ldd, int rows, int cols) {
+                              long long ldd, int rows, int cols, int il_off) {
   size_t total = (size_t)rows * cols;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, st = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += st) {
     size_t r = i / cols, c = i % cols;
-    dst[r * ldd + c] = src[r * lds + c];
+    dst[r * ldd + il_col((long long)c, il_off)] = src[r * lds + c];
   }
 }
-// dst[c, r] (pitch ldd) = src[r, c] (pitch lds)
+// dst[c, r] (pitch ldd) = src[r, c] (pitch lds); with il_off >= 0 row c of dst is il_col(c)
 __global__ void k_transpose_f16(const __half* __restrict__ src, long long lds,
-                                __half* __restrict__ dst, long long ldd, int rows, int cols) {
+                                __half* __restrict__ dst, long long ldd, int rows, int cols,
+                                int il_off) {
   __shared__ __half tile[32][34];
   int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
   for (int j = threadIdx.y; j < 32; j += blockDim.y) {
@@ -862,7 +923,7 @@ __global__ void k_transpose_f16(const __half* __restrict__ src, long long lds,
   __syncthreads();
   for (int j = threadIdx.y; j < 32; j += blockDim.y) {
     int c = c0 + j, r = r0 + threadIdx.x;
-    if (r < rows && c < cols) dst[(long long)c * ldd + r] = tile[threadIdx.x][j];
+    if (r < rows && c < cols) dst[il_col(c, il_off) * ldd + r] = tile[threadIdx.x][j];
   }
 }
 
@@ -885,6 +946,15 @@ int prepare_group(FtLoraModel* m, Group& g) {
   }
   bool any_bias = false;
   for (int j = 0; j < g.nlin; ++j) any_bias |= g.lin[j]->bias != nullptr;
+  if (g.il && (any_bias || g.nlin != 2 || g.lin[0]->out != g.lin[1]->out || (g.lin[0]->out % 32)))
+    g.il = false;
+  if (g.il) {
+    for (__half** slot : {&g.w_nk_il, &g.w_kn_il}) {
+      FT_CUDA(cudaMalloc(&p, (size_t)g.n * g.in * sizeof(__half)));
+      m->owned.push_back(p);
+      *slot = (__half*)p;
+    }
+  }
   if (any_bias) {
     FT_CUDA(cudaMalloc(&p, (size_t)g.n * sizeof(float)));
     m->owned.push_back(p);
@@ -912,11 +982,16 @@ int prepare_group(FtLoraModel* m, Group& g) {
     dim3 grid(ft_cdiv(l.out, 32), ft_cdiv(l.in, 32)), block(32, 8);
     FT_REQUIRE(grid.y <= 65535, "prepare: input width too large");
     FT_LAUNCH(ctx, k_transpose_f16, grid, block, 0, w, (long long)l.out,
-              g.w_nk + (size_t)g.col_off[j] * g.in, (long long)g.in, l.in, l.out);
-    if (g.own_kn) {
-      int cg = (int)std::min<size_t>(((size_t)l.in * l.out + 255) / 256, (size_t)ctx->sm_count * 16);
+              g.w_nk + (size_t)g.col_off[j] * g.in, (long long)g.in, l.in, l.out, -1);
+    const int cg = (int)std::min<size_t>(((size_t)l.in * l.out + 255) / 256, (size_t)ctx->sm_count * 16);
+    if (g.own_kn)
       FT_LAUNCH(ctx, k_copy_f16_2d, cg, 256, 0, w, (long long)l.out, g.w_kn + g.col_off[j],
-                (long long)g.n, l.in, l.out);
+                (long long)g.n, l.in, l.out, -1);
+    if (g.il) {
+      FT_LAUNCH(ctx, k_transpose_f16, grid, block, 0, w, (long long)l.out, g.w_nk_il,
+                (long long)g.in, l.in, l.out, 32 * j);
+      FT_LAUNCH(ctx, k_copy_f16_2d, cg, 256, 0, w, (long long)l.out, g.w_kn_il, (long long)g.n, l.in,
+                l.out, 32 * j);
     }
   }
   return FT_OK;
@@ -962,6 +1037,11 @@ extern "C" int ft_model_create(FtContext* ctx, const FtModelConfig* cfg, FtLoraM
     setup_group(ly.qkv, {&ly.lin[FT_Q], &ly.lin[FT_K], &ly.lin[FT_V]}, r);
     setup_group(ly.o, {&ly.lin[FT_O]}, r);
     setup_group(ly.gu, {&ly.lin[FT_GATE], &ly.lin[FT_UP]}, r);
+    {
+      // FT_CARRY bit 64 (read when the model is created): interleaved gate|up operands
+      const char* env = getenv("FT_CARRY");
+      ly.gu.il = cfg->f16_base && ((env ? atoi(env) : 127) & 64) != 0;
+    }
     setup_group(ly.down, {&ly.lin[FT_DOWN]}, r);
   }
   m->head_lin.in = h;

@@ -289,7 +289,13 @@ def test_fused_epilogues_against_the_separate_passes(headline, monkeypatch):
       kernels) instead of an f32 result, its own amax and a conversion pass.  The scale is a
       power of two either way; only the rounding of the down projection's input gradient (f16
       before SwiGLU's backward instead of f32) differs.  The forward pass is the same, so the
-      row losses are identical."""
+      row losses are identical;
+    * SwiGLU inside the gate|up projection's epilogue (bit 256; the group's columns are
+      interleaved in runs of 32 so that a thread of the epilogue holds gate and up of the same
+      features): silu(gate) * up is computed from the f16-rounded gate and up with the kernel's
+      own arithmetic, so losses and gradients are bit-identical to the separate pass; its
+      backward inside the down projection's input-gradient epilogue (bit 128) belongs to the
+      carried-scale route above."""
     from ferrotensor_b200.config import synthetic_batch
     from ferrotensor_b200.engine import GemmMode
     h = headline
@@ -307,12 +313,15 @@ def test_fused_epilogues_against_the_separate_passes(headline, monkeypatch):
 
     plain, l_plain = run("0")
     rope, l_rope = run("16")
+    swi, l_swi = run("272")                         # 16 + 256
     fused, l_fused = run(None)
     h.gradients([one], h.w.seq_len, 1.0)            # leave the default plan behind
     assert np.allclose(l_rope, l_plain, rtol=1e-3, atol=1e-5)
     err, scale, rel = _errors(rope.cpu().numpy(), plain.cpu().numpy())
     print(f"\n  rotary epilogue against the rotary pass: relative L2 {rel:.2e}")
     assert rel < 1e-3
+    assert np.array_equal(l_rope.view(np.uint32), l_swi.view(np.uint32))
+    assert torch.equal(rope.view(torch.int32), swi.view(torch.int32))
     assert np.array_equal(l_rope.view(np.uint32), l_fused.view(np.uint32))
     assert not torch.equal(rope, fused), "FT_CARRY did not change the route"
     err, scale, rel = _errors(fused.cpu().numpy(), rope.cpu().numpy())
