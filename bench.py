@@ -386,6 +386,7 @@ def run_cuda(args):
     resident_step()
     ctx.synchronize()
     gemm_bytes = ctx.profile_bytes()
+    fused_ms, fused_flops, fused_launches = ctx.profile_read_fused()
     gemm_ms, gemm_flops_done, gemm_launches = ctx.profile_read()
     ctx.profile(False)
     # DRAM traffic per launch: the launches' algorithmic bytes (operands once, results once) times
@@ -451,9 +452,24 @@ def run_cuda(args):
                               "padded to 64 columns, pre-tiles, checkpoint replays)",
                      "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"] if peaks["tflops"] else None,
-                     "traffic": traffic, "traffic_unit": "bytes per launch (algorithmic x 1.027, the ncu-measured dram/algorithmic ratio of one launch)",
+                     "traffic": traffic, "traffic_unit": "bytes per launch: the launches' algorithmic bytes x 1.027, an estimate "
+                                     "(ncu gave dram/algorithmic ratios of 1.04, 1.34 and 0.69 on "
+                                     "the three captured shapes, profiles/k_gemm_tc_ncu_full.md)",
                      "peak_source": peaks["source"] + " (sustained)",
-                     "launches_per_step": gemm_launches, "kernel_ms_per_step": gemm_ms},
+                     "launches_per_step": gemm_launches, "kernel_ms_per_step": gemm_ms,
+                     # some launches also do elementwise work of the step in their epilogues
+                     # (RoPE of q|k|v, SwiGLU forward, SwiGLU backward): their time contains what
+                     # used to be separate HBM-bound kernels, so the two groups are also given apart
+                     "fused_epilogue_launches": {
+                         "launches_per_step": fused_launches, "kernel_ms_per_step": fused_ms,
+                         "executed_tflops": fused_flops / (fused_ms * 1e-3) / 1e12 if fused_ms > 0 else None,
+                         "what": "q|k|v projection + RoPE + f16 rounding; gate|up projection + "
+                                 "SwiGLU; down projection's input gradient + SwiGLU backward"},
+                     "plain_launches": {
+                         "launches_per_step": gemm_launches - fused_launches,
+                         "kernel_ms_per_step": gemm_ms - fused_ms,
+                         "executed_tflops": (gemm_flops_done - fused_flops) / ((gemm_ms - fused_ms) * 1e-3) / 1e12
+                         if gemm_ms > fused_ms else None}},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": int(launches),

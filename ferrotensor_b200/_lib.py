@@ -73,6 +73,7 @@ PROTOTYPES = {
     "ft_ctx_profile": [_P, _I],
     "ft_ctx_profile_report": [_P, C.c_char_p, _Z],
     "ft_ctx_profile_read": [_P, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_uint64)],
+    "ft_ctx_profile_read_fused": [_P, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_uint64)],
     "ft_ctx_profile_bytes": [_P, C.POINTER(C.c_double)],
     "ft_ctx_set_gemm_mode": [_P, _I],
     "ft_ctx_set_gemm_tile_m": [_P, _I],

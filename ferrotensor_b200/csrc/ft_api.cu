@@ -214,7 +214,27 @@ extern "C" int ft_ctx_profile_read(FtContext* ctx, double* gemm_ms, double* gemm
   *gemm_launches = ctx->prof_launches;
   ctx->prof_used = 0;
   ctx->prof_flops = 0.0;
+  ctx->prof_fused_flops = 0.0;
   ctx->prof_launches = 0;
+  return FT_OK;
+}
+
+extern "C" int ft_ctx_profile_read_fused(FtContext* ctx, double* ms_out, double* flops_out,
+                                         uint64_t* launches_out) {
+  FT_REQUIRE(ctx && ms_out && flops_out && launches_out, "ft_ctx_profile_read_fused: NULL argument");
+  FT_CUDA(cudaStreamSynchronize(ctx->stream));
+  double ms = 0.0;
+  uint64_t n = 0;
+  for (size_t i = 0; i + 1 < ctx->prof_used; i += 2) {
+    if (i / 2 >= ctx->prof_fused.size() || !ctx->prof_fused[i / 2]) continue;
+    float t = 0.f;
+    FT_CUDA(cudaEventElapsedTime(&t, ctx->prof_events[i], ctx->prof_events[i + 1]));
+    ms += t;
+    ++n;
+  }
+  *ms_out = ms;
+  *flops_out = ctx->prof_fused_flops;
+  *launches_out = n;
   return FT_OK;
 }
 

@@ -51,6 +51,11 @@ struct FtContext {
   double next_launch_bytes = 0.0;
   double prof_bytes = 0.0;   // algorithmic bytes (operands once, results once) of the timed GEMM launches
   uint64_t prof_launches = 0;
+  // the same for the subset of those launches whose epilogue also does elementwise work of the
+  // step (RoPE, SwiGLU forward or backward): marks parallel to the event pairs
+  std::vector<uint8_t> prof_fused;
+  double prof_fused_flops = 0.0;
+  bool next_launch_fused = false;
   // optional timing of EVERY launch by kernel name (ft_ctx_profile(ctx, 2))
   bool profile_all = false;
   struct ProfRec { const char* name; cudaEvent_t e0, e1; };

@@ -1365,6 +1365,9 @@ int launch_tc(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, cons
       FT_CUDA(cudaEventCreate(&e));
       ctx->prof_events.push_back(e);
     }
+    if (ctx->prof_fused.size() < ctx->prof_events.size() / 2) ctx->prof_fused.resize(ctx->prof_events.size() / 2);
+    ctx->prof_fused[ctx->prof_used / 2] = ctx->next_launch_fused ? 1 : 0;
+    if (ctx->next_launch_fused) ctx->prof_fused_flops += flops;
     e0 = ctx->prof_events[ctx->prof_used++];
     e1 = ctx->prof_events[ctx->prof_used++];
     FT_CUDA(cudaEventRecord(e0, ctx->stream));
@@ -1434,6 +1437,9 @@ int launch_tc2(FtContext* ctx, const CUtensorMap& ma, const CUtensorMap& mb, con
       FT_CUDA(cudaEventCreate(&e));
       ctx->prof_events.push_back(e);
     }
+    if (ctx->prof_fused.size() < ctx->prof_events.size() / 2) ctx->prof_fused.resize(ctx->prof_events.size() / 2);
+    ctx->prof_fused[ctx->prof_used / 2] = ctx->next_launch_fused ? 1 : 0;
+    if (ctx->next_launch_fused) ctx->prof_fused_flops += flops;
     e0 = ctx->prof_events[ctx->prof_used++];
     e1 = ctx->prof_events[ctx->prof_used++];
     FT_CUDA(cudaEventRecord(e0, ctx->stream));
@@ -1560,6 +1566,7 @@ bool ft_gemm_tc_pair_eligible(const FtContext* ctx, int M, int N) {
 
 int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   ctx->next_launch_bytes = gemm_algorithmic_bytes(g);
+  ctx->next_launch_fused = g.rope_table || g.swi_f16 || g.swi_dgu16;
   if (g.ab_type != FT_F16 && g.ab_type != FT_BF16) return FT_ERR_UNSUPPORTED;
   if (!tma_ok(g.a, g.lda, g.K) || !tma_ok(g.b, g.ldb, g.K) || g.K < 8) return FT_ERR_UNSUPPORTED;
   const bool tail = g.K2 > 0;

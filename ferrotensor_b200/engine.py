@@ -94,6 +94,13 @@ class CudaContext:
         call("ft_ctx_profile_read", self.handle, C.byref(ms), C.byref(fl), C.byref(n))
         return ms.value, fl.value, n.value
 
+    def profile_read_fused(self):
+        """The same for the GEMM launches whose epilogue also does RoPE or SwiGLU (read before
+        `profile_read`, which closes the interval)."""
+        ms, fl, n = C.c_double(), C.c_double(), C.c_uint64()
+        call("ft_ctx_profile_read_fused", self.handle, C.byref(ms), C.byref(fl), C.byref(n))
+        return ms.value, fl.value, n.value
+
     def profile_bytes(self) -> float:
         """Algorithmic bytes of the GEMM launches timed so far (read before `profile_read`)."""
         b = C.c_double()

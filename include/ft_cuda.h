@@ -76,6 +76,10 @@ int ft_ctx_profile(FtContext* ctx, int enable);   /* 0 off, 1 GEMM launches, 2 e
 int ft_ctx_profile_report(FtContext* ctx, char* buf, size_t cap);
 int ft_ctx_profile_read(FtContext* ctx, double* gemm_ms, double* gemm_flops,
                         uint64_t* gemm_launches);
+/* The part of that interval spent in GEMM launches whose epilogue also does elementwise work of
+ * the step (RoPE of q|k|v, SwiGLU forward or backward): time, FLOPs and count; call it before
+ * ft_ctx_profile_read, which closes the interval. */
+int ft_ctx_profile_read_fused(FtContext* ctx, double* ms, double* flops, uint64_t* launches);
 /* Algorithmic bytes (operands read once, results written once) of the GEMM launches timed since
  * the last call; call it before ft_ctx_profile_read, which closes the same interval. */
 int ft_ctx_profile_bytes(FtContext* ctx, double* gemm_bytes);
