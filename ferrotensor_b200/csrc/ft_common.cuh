@@ -183,6 +183,7 @@ struct FtGemmArgs {
   const void* a2 = nullptr; long long lda2 = 0;
   const void* b2 = nullptr; long long ldb2 = 0;
   int K2 = 0;
+  int k2_used = 0;   // > 0: only the first k2_used columns of the second pair are non-zero
   FtDType ab_type = FT_F16;
   int M = 0, N = 0, K = 0;
   float* c = nullptr; long long ldc = 0;

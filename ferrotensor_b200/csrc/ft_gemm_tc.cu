@@ -86,6 +86,7 @@ struct Epilogue {
   long long swi_lddgu;
   const int* swi_gu_amax;     // largest |gate| or |up| of the forward pass
   float* swi_scales;          // {S, 1/S, 2^-11/S} of the d gate | d up rows (published)
+  int tail_steps;             // 16-column MMA steps of a tail k-block that hold adapter columns (1..4)
 };
 
 // sigmoid with the fast exponential and reciprocal (about 2 ulp), as the SwiGLU kernels use
@@ -732,7 +733,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         if (!mbar_wait(bar_tempty + buf * 8, acc_phase ^ 1, abort_flag, status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < kb_total; ++kb) {
+        for (int kb = 0; kb < kb_main; ++kb) {
           if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, status, 3)) break;
           tc_fence_after();
           const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
@@ -742,6 +743,20 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             tc_mma_f16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
                             (kb > 0 || k > 0) ? 1u : 0u);
           tc_commit_pair(bar_empty + stage * 8, 3);  // frees the stage in both CTAs
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        // adapter tail: the rank-r columns fill only the first tail_steps 16-column steps of
+        // the 64-column k-block (the rest is zero padding and is not multiplied)
+        for (int kb = kb_main; kb < kb_total; ++kb) {
+          if (!mbar_wait(bar_full + stage * 8, phase, abort_flag, status, 3)) break;
+          tc_fence_after();
+          const uint32_t sa = base + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+          const uint64_t da = make_desc_sw128(sa), db = make_desc_sw128(sb);
+          const int steps = (kb == kb_total - 1) ? ep.tail_steps : BK / UMMA_K;
+          for (int k = 0; k < steps; ++k)
+            tc_mma_f16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                            (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit_pair(bar_empty + stage * 8, 3);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (*abort_flag) break;
@@ -1642,6 +1657,13 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
     ep.swi_f16 = g.swi_f16; ep.swi_ldf = g.swi_ldf;
     ep.swi_gu16 = g.swi_gu16; ep.swi_ldgu = g.swi_ldgu; ep.swi_dgu16 = g.swi_dgu16;
     ep.swi_lddgu = g.swi_lddgu; ep.swi_gu_amax = g.swi_gu_amax; ep.swi_scales = g.swi_scales;
+    {
+      const int used = g.k2_used > 0 ? std::min(g.k2_used, g.K2) : g.K2;
+      const int last = used - (ft_cdiv(std::max(used, 1), BK) - 1) * BK;   // columns in the last tail k-block
+      ep.tail_steps = std::max(1, std::min(BK / UMMA_K, ft_cdiv(last, UMMA_K)));
+      static const bool full_tail = getenv("FT_TAIL_FULL") != nullptr;   // A/B switch
+      if (full_tail || g.k2_used <= 0 || ft_cdiv(used, BK) != ft_cdiv(g.K2, BK)) ep.tail_steps = BK / UMMA_K;
+    }
     double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
     CUtensorMap mb3 = mb;
     PreTile pre;
@@ -1688,6 +1710,7 @@ int ft_gemm_tc_ex(FtContext* ctx, const FtGemmArgs& g) {
   ep.rope_table = nullptr; ep.rope_seq = 0; ep.rope_cols = 0;
   ep.swi_f16 = nullptr; ep.swi_ldf = 0; ep.swi_gu16 = nullptr; ep.swi_ldgu = 0; ep.swi_dgu16 = nullptr;
   ep.swi_lddgu = 0; ep.swi_gu_amax = nullptr; ep.swi_scales = nullptr;
+  ep.tail_steps = BK / UMMA_K;
   double flops = 2.0 * g.M * (double)g.N * (double)(g.K + g.K2);
   // adapter pre-tiles: the tail operand A2 = pre_alpha * A . pre_b^T is made by this launch
   CUtensorMap mb3;
@@ -1791,6 +1814,7 @@ int ft_gemm_tc_kouter_pair(FtContext* ctx, int nprob, FtKoProblem* prob, int T) 
   ep.rope_table = nullptr; ep.rope_seq = 0; ep.rope_cols = 0;
   ep.swi_f16 = nullptr; ep.swi_ldf = 0; ep.swi_gu16 = nullptr; ep.swi_ldgu = 0; ep.swi_dgu16 = nullptr;
   ep.swi_lddgu = 0; ep.swi_gu_amax = nullptr; ep.swi_scales = nullptr;
+  ep.tail_steps = BK / UMMA_K;
   // both operands M/N-major: bits 15 and 16 of the instruction descriptor
   const uint32_t idesc = make_idesc(BM, 64, 0, 0) | (1u << 15) | (1u << 16);
   return launch_tc<64, 8, true>(ctx, ma[0], mb[0], ma[1], mb[1], ep, prob[0].M, 64, T, 0, splits, idesc,

@@ -590,7 +590,7 @@ int linear_fwd_fused(FtLoraModel* m, const Group& g, const __half* X16, float* Y
   a.M = T; a.N = g.n; a.K = g.in;
   if (g.R > 0) {
     // xa16 = (alpha/r) X16 . A is made by pre-tiles of the same launch
-    a.a2 = xa16; a.lda2 = RP; a.b2 = g.b_bdT16; a.ldb2 = RP; a.K2 = RP;
+    a.a2 = xa16; a.lda2 = RP; a.b2 = g.b_bdT16; a.ldb2 = RP; a.K2 = RP; a.k2_used = g.R;
     a.pre_b = g.a_catT16; a.pre_ldb = g.in; a.pre_c16 = xa16; a.pre_ldc16 = RP; a.pre_alpha = m->scale;
   }
   a.c = Y; a.ldc = ldy; a.c16 = Y16; a.ldc16 = ldy;   // Y16: the result as f16 (pitch ldy)
@@ -654,7 +654,7 @@ int linear_bwd_fused(FtLoraModel* m, const Group& g, const __half* X16, const fl
     a.M = T; a.N = g.in; a.K = g.n;
     if (g.R > 0) {
       // G16 = (alpha/r) * (S dY) . B^T is made by pre-tiles of the same launch
-      a.a2 = m->g16; a.lda2 = RP; a.b2 = g.a_cat16; a.ldb2 = RP; a.K2 = RP;
+      a.a2 = m->g16; a.lda2 = RP; a.b2 = g.a_cat16; a.ldb2 = RP; a.K2 = RP; a.k2_used = g.R;
       a.pre_b = g.b_bd16; a.pre_ldb = g.n; a.pre_c16 = m->g16; a.pre_ldc16 = RP; a.pre_alpha = m->scale;
     }
     a.c = dX; a.ldc = lddx; a.alpha_ptr = inv_s; a.residual = residual; a.ldr = ldr;
