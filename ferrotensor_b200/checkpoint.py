@@ -455,3 +455,53 @@ def host_tensor_name(ref_name: str) -> str:
     if ref_name.endswith(".lora_B.weight"):
         return ref_name[:-len(".lora_B.weight")] + ".lora_b"
     return ref_name
+
+
+def upgrade_optimizer_names(adam, param_names) -> int:
+    """Moments stored under old Llama-block names move to the names in `param_names` (reference
+    names), so a run started before the rename resumes with its moments
+    (ferrotensor-trainer/src/checkpoint.rs:283-307).  Returns how many were renamed."""
+    renamed = 0
+    for states in (adam.m_states, adam.v_states):
+        for name in param_names:
+            if name in states:
+                continue
+            old = legacy_llama_name(name)
+            if old is not None and old in states:
+                states[name] = states.pop(old)
+                renamed += 1
+    return renamed
+
+
+@dataclass
+class OptimizerLoad:
+    """What `match_moments` found (ferrotensor-autograd/src/lib.rs OptimizerLoad)."""
+    matched: int = 0
+    missing: int = 0      # parameters without both saved moments
+    unused: int = 0       # saved names that took no part
+
+
+def match_moments(shapes: Dict[str, Tuple[int, ...]], adam) -> Tuple[List[str], OptimizerLoad]:
+    """Which saved moments belong to which parameters, without touching a device
+    (ferrotensor-autograd/src/lib.rs:1668-1703).  `shapes` maps reference parameter names to
+    shapes.  A parameter takes its saved state when BOTH moments are stored under its name; a
+    moment whose shape or value count differs from the parameter's is an error."""
+    saved = sorted(set(adam.m_states) | set(adam.v_states))
+    matched: List[str] = []
+    for name in saved:
+        shape = shapes.get(name)
+        m, v = adam.m_states.get(name), adam.v_states.get(name)
+        if shape is None or m is None or v is None:
+            continue
+        want = 1
+        for d in shape:
+            want *= int(d)
+        for kind, moment in (("first", m), ("second", v)):
+            count = int(np.asarray(moment.data).size)
+            if tuple(moment.shape) != tuple(shape) or count != want:
+                raise CheckpointError(
+                    f"saved {kind} moment of {name} has shape {list(moment.shape)} ({count} values), "
+                    f"the parameter has shape {list(shape)}")
+        matched.append(name)
+    return matched, OptimizerLoad(matched=len(matched), missing=len(shapes) - len(matched),
+                                  unused=len(saved) - len(matched))

@@ -385,25 +385,38 @@ class Trainer:
         ck.TrainingCheckpoint(training_state, self.optimizer_checkpoint(), None).save(state_path)
 
     def load_training_checkpoint(self, state_path):
-        """Restores t, the hyper-parameters and the moments; a moment whose shape does not fit is
-        an error and nothing is changed (autograd/lib.rs:1627-1700).  Returns the TrainingState."""
+        """Restores the optimizer from a training checkpoint as `AdamW::load_state` does
+        (ferrotensor-autograd/src/lib.rs:1623-1703, CLI resume: main.rs:1724): moments stored
+        under old Llama-block names are renamed first; a parameter takes its saved state when
+        BOTH moments are stored under its name; a moment that does not fit its parameter is an
+        error and nothing is changed; when no parameter matches the optimizer is left as it was;
+        otherwise the hyper-parameters and step count are restored too and parameters without
+        saved state start from zero moments.  Returns the TrainingState; the match counts are
+        left in `self.last_optimizer_load`."""
         from . import checkpoint as ck
         cp = ck.TrainingCheckpoint.load(state_path)
         a = cp.optimizer_state
+        self.last_optimizer_load = None
         if a is not None:
             m, v = self.model.named_moments()
-            for dst, src, what in ((m, a.m_states, "first"), (v, a.v_states, "second")):
-                for n, t in dst.items():
-                    s = src.get(ck.reference_tensor_name(n))
-                    if s is not None and list(s.shape) != list(t.shape):
-                        raise ck.CheckpointError(f"{what} moment of {n} has shape {list(s.shape)}, expected {list(t.shape)}")
-            for dst, src in ((m, a.m_states), (v, a.v_states)):
-                for n, t in dst.items():
-                    s = src.get(ck.reference_tensor_name(n))
-                    if s is not None:
-                        t.copy_(torch.from_numpy(np.asarray(s.data, np.float32).reshape(s.shape)))
-            o = self.optimizer
-            o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, o.t = a.lr, a.beta1, a.beta2, a.eps, a.weight_decay, a.t
+            ref_of = {n: ck.reference_tensor_name(n) for n in m}
+            ck.upgrade_optimizer_names(a, list(ref_of.values()))
+            shapes = {ref_of[n]: tuple(t.shape) for n, t in m.items()}
+            matched, report = ck.match_moments(shapes, a)      # raises before anything changes
+            self.last_optimizer_load = report
+            if matched:
+                taken = set(matched)
+                for dst, src in ((m, a.m_states), (v, a.v_states)):
+                    for n, t in dst.items():
+                        r = ref_of[n]
+                        if r in taken:
+                            s_ = src[r]
+                            t.copy_(torch.from_numpy(np.asarray(s_.data, np.float32).reshape(s_.shape)))
+                        else:
+                            t.zero_()
+                o = self.optimizer
+                o.lr, o.beta1, o.beta2, o.eps, o.weight_decay, o.t = (a.lr, a.beta1, a.beta2, a.eps,
+                                                                      a.weight_decay, a.t)
         return cp.training_state
 
     def train_arrays(self, ids: np.ndarray, tgt: np.ndarray, msk: np.ndarray) -> List[StepStats]:

@@ -209,3 +209,153 @@ def test_resume_continues_bit_for_bit(cuda_ctx, tmp_path):
     assert cp.metadata.rank == w.lora.rank and cp.metadata.target_modules == list(w.lora.target_modules)
     assert all(k.endswith((".lora_A.weight", ".lora_B.weight")) for k in cp.tensors)
     model.close()
+
+
+# ---- optimizer-state matching (ferrotensor-autograd/src/lib.rs:1668-1703 and its tests :1940-2062),
+# ---- old Llama-block names (ferrotensor-graph/src/lfm.rs:234-255, :775-813)
+
+def _moment(shape):
+    return ck.OptimizerTensorState(shape=list(shape), data=np.full(int(np.prod(shape)), 0.5, np.float32))
+
+
+def _saved_state(params):
+    return ck.AdamWCheckpoint(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, t=3.0,
+                              m_states={n: _moment(s) for n, s in params},
+                              v_states={n: _moment(s) for n, s in params})
+
+
+def test_saved_moments_match_the_same_parameters():
+    shapes = {"a.weight": (2, 3), "b.weight": (4,)}
+    matched, report = ck.match_moments(shapes, _saved_state([("a.weight", (2, 3)), ("b.weight", (4,))]))
+    assert matched == ["a.weight", "b.weight"]
+    assert (report.matched, report.missing, report.unused) == (2, 0, 0)
+
+
+def test_saved_moments_of_other_parameters_match_none():
+    shapes = {"x.weight": (2, 3), "y.weight": (4,)}
+    matched, report = ck.match_moments(shapes, _saved_state([("a.weight", (2, 3)), ("b.weight", (4,))]))
+    assert matched == []
+    assert (report.matched, report.missing, report.unused) == (0, 2, 2)
+
+
+def test_partial_overlap_reports_both_sides():
+    shapes = {"a.weight": (2,), "b.weight": (2,), "c.weight": (2,)}
+    matched, report = ck.match_moments(shapes, _saved_state([("a.weight", (2,)), ("old.weight", (2,))]))
+    assert matched == ["a.weight"]
+    assert (report.matched, report.missing, report.unused) == (1, 2, 1)
+
+
+def test_a_moment_with_only_one_half_is_not_applied():
+    state = _saved_state([("a.weight", (2,))])
+    state.v_states.clear()
+    matched, report = ck.match_moments({"a.weight": (2,)}, state)
+    assert matched == [] and (report.missing, report.unused) == (1, 1)
+
+
+def test_a_moment_of_the_wrong_shape_is_an_error():
+    with pytest.raises(ck.CheckpointError) as e:
+        ck.match_moments({"a.weight": (2, 3)}, _saved_state([("a.weight", (3, 2))]))
+    assert "a.weight" in str(e.value) and "shape" in str(e.value)
+    state = _saved_state([("a.weight", (2, 3))])       # the shape agrees, the value count does not
+    state.v_states["a.weight"].data = state.v_states["a.weight"].data[:-1]
+    with pytest.raises(ck.CheckpointError):
+        ck.match_moments({"a.weight": (2, 3)}, state)
+
+
+def test_llama_block_names_map_to_the_old_names():
+    pairs = [("model.layers.3.input_layernorm.weight", "model.layers.3.operator_norm.weight"),
+             ("model.layers.3.post_attention_layernorm.weight", "model.layers.3.ffn_norm.weight"),
+             ("model.layers.0.mlp.gate_proj.lora_A.weight", "model.layers.0.feed_forward.gate_proj.lora_A.weight"),
+             ("model.layers.11.mlp.down_proj.weight", "model.layers.11.feed_forward.down_proj.weight")]
+    for new, old in pairs:
+        assert ck.legacy_llama_name(new) == old
+    for name in ["model.layers.0.self_attn.q_proj.weight", "model.layers.0.self_attn.q_proj.lora_A.weight",
+                 "model.embed_tokens.weight", "model.norm.weight", "lm_head.weight"]:
+        assert ck.legacy_llama_name(name) is None, name
+
+
+def test_moments_under_old_names_are_renamed_before_matching():
+    new = "model.layers.0.mlp.gate_proj.lora_A.weight"
+    old = "model.layers.0.feed_forward.gate_proj.lora_A.weight"
+    keep = "model.layers.0.self_attn.q_proj.lora_A.weight"
+    state = _saved_state([(old, (4, 2)), (keep, (4, 2))])
+    assert ck.upgrade_optimizer_names(state, [new, keep]) == 2          # one name, both moments
+    assert set(state.m_states) == {new, keep} and set(state.v_states) == {new, keep}
+    assert ck.upgrade_optimizer_names(state, [new, keep]) == 0
+    matched, report = ck.match_moments({new: (4, 2), keep: (4, 2)}, state)
+    assert matched == sorted([new, keep]) and report.unused == 0
+
+
+@pytest.mark.gpu
+def test_optimizer_state_loads_as_the_reference_loads_it(cuda_ctx, tmp_path):
+    """`AdamW::load_state` semantics on the device buffers: a file whose moments belong to other
+    parameters leaves the optimizer untouched; a partial match restores the hyper-parameters and
+    step count, copies the matched moments and zeroes the others; old Llama-block names are
+    renamed first; a moment of the wrong shape is an error and nothing changes."""
+    import copy
+    import json
+    import torch
+    from ferrotensor_b200.config import WORKLOADS, init_adapters, init_weights, synthetic_batch
+    from ferrotensor_b200.model import LoraModel
+    from ferrotensor_b200.trainer import AdamW, Trainer
+    w = copy.deepcopy(WORKLOADS["tiny"])
+    weights = init_weights(w.model, 5, f16_base=w.f16_base)
+    adapters = init_adapters(w.model, w.lora, 5, b_std=0.02)
+    model = LoraModel(cuda_ctx, w.model, w.lora, weights, adapters, f16_base=w.f16_base)
+    tr = Trainer(model, AdamW(1e-2, weight_decay=0.0)).with_grad_accum_steps(2)
+    tr.train_arrays(*synthetic_batch(w, 2, seed=3))
+    path = tmp_path / "run.state.json"
+    tr.save_training_checkpoint(path, ck.TrainingState.new(3))
+    cp = ck.TrainingCheckpoint.load(path)
+    a = cp.optimizer_state
+    names = sorted(a.m_states)
+    assert names and all(float(np.abs(a.m_states[n].data).max()) > 0 for n in names)
+    m_dev, v_dev = model.named_moments()
+    host_of = {ck.reference_tensor_name(n): n for n in m_dev}
+
+    def write(state):
+        ck.TrainingCheckpoint(optimizer_state=state, training_state=cp.training_state).save(tmp_path / "edit.state.json")
+        return tmp_path / "edit.state.json"
+
+    def reset():
+        tr.optimizer.lr, tr.optimizer.t = 7e-3, 9.0
+        for t in list(m_dev.values()) + list(v_dev.values()):
+            t.fill_(0.25)
+
+    # (a) nothing matches: untouched
+    other = copy.deepcopy(a)
+    other.m_states = {"x." + n: s for n, s in a.m_states.items()}
+    other.v_states = {"x." + n: s for n, s in a.v_states.items()}
+    reset()
+    tr.load_training_checkpoint(write(other))
+    assert tr.last_optimizer_load.matched == 0 and tr.last_optimizer_load.unused == len(names)
+    assert tr.optimizer.lr == 7e-3 and tr.optimizer.t == 9.0
+    assert all(float(t.min()) == 0.25 and float(t.max()) == 0.25 for t in m_dev.values())
+
+    # (b) one parameter lost its second moment, one is stored under its old name
+    part = copy.deepcopy(a)
+    dropped = names[0]
+    del part.v_states[dropped]
+    renamed = next(n for n in names if ".mlp." in n)
+    old = ck.legacy_llama_name(renamed)
+    part.m_states[old] = part.m_states.pop(renamed)
+    part.v_states[old] = part.v_states.pop(renamed)
+    reset()
+    tr.load_training_checkpoint(write(part))
+    rep = tr.last_optimizer_load
+    assert (rep.matched, rep.missing, rep.unused) == (len(names) - 1, 1, 1)
+    assert tr.optimizer.lr == a.lr and tr.optimizer.t == a.t
+    assert not m_dev[host_of[dropped]].any() and not v_dev[host_of[dropped]].any()
+    got = m_dev[host_of[renamed]].cpu().numpy().reshape(-1)
+    assert np.array_equal(got, np.asarray(a.m_states[renamed].data, np.float32).reshape(-1))
+
+    # (c) a moment of the wrong shape: an error, nothing changed
+    bad = copy.deepcopy(a)
+    s = bad.v_states[names[1]]
+    s.shape = list(reversed(s.shape)) if len(s.shape) == 2 and s.shape[0] != s.shape[1] else [int(np.prod(s.shape))]
+    reset()
+    with pytest.raises(ck.CheckpointError):
+        tr.load_training_checkpoint(write(bad))
+    assert tr.optimizer.lr == 7e-3 and tr.optimizer.t == 9.0
+    assert all(float(t.min()) == 0.25 and float(t.max()) == 0.25 for t in v_dev.values())
+    model.close()
