@@ -209,7 +209,7 @@ __device__ __forceinline__ void fold_amax(float am, int* amax_slot, int lane) {
 }
 
 // Optional f16 form of the results: rows [tokens, ld] of S * (dq | dk | dv) with the inverse
-// rotary rotation applied to dq and dk (angles from `table`, {cos, sin} [seq, 32]); S is the
+// rotary rotation applied to dq and dk (angles from `table`, {cos, sin} transposed: [32, seq]); S is the
 // power of two carried from *carry_amax (the largest magnitude of the same gradient in the block
 // processed before this one).  When `rows` is set the f32 results are not written.
 struct Out16 {
@@ -221,33 +221,30 @@ struct Out16 {
   float* carry_scales;
 };
 
-__device__ __forceinline__ void prefetch_l1_256(const void* p) {
-  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
-  asm volatile("prefetch.global.L1 [%0];" ::"l"((const char*)p + 128));
-}
-
 // Sixteen of a thread's 32 components of a gradient row (half `hc` of the 64), rotated back by
 // the angles of one position and scaled: ra = raw accumulator words of components c..c+15,
-// rb = of components 32+c..32+c+15, f their factor, trow = the position's {cos, sin} pairs from
-// component c on; writes 16 halves to dst.
+// rb = of components 32+c..32+c+15, f their factor, tcol = the position's {cos, sin} of component
+// c in the transposed table ([32][seq]: the next component is `seq` entries further; lanes own
+// consecutive positions, so the warp's loads are contiguous); writes 16 halves to dst.
 __device__ __forceinline__ void store_rot16(__half* dst, const uint32_t (&ra)[16], const uint32_t (&rb)[16],
-                                            float f, int hc, const float2* __restrict__ trow, float S,
-                                            float& am) {
+                                            float f, int hc, const float2* __restrict__ tcol, size_t seq,
+                                            float S, float& am) {
   uint32_t w[8];
   const float fs = f * S;   // S is a power of two: exact
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
-    const float4 cs = *(const float4*)(trow + i);   // {cos_i, sin_i, cos_i+1, sin_i+1}
+    const float2 c0 = tcol[0], c1 = tcol[seq];
+    tcol += 2 * seq;
     const float a0 = __uint_as_float(ra[i]), a1 = __uint_as_float(ra[i + 1]);
     const float b0 = __uint_as_float(rb[i]), b1 = __uint_as_float(rb[i + 1]);
     float o0, o1;
     if (hc == 0) {   // first half: a cos + b sin
-      o0 = a0 * cs.x + b0 * cs.y;
-      o1 = a1 * cs.z + b1 * cs.w;
+      o0 = a0 * c0.x + b0 * c0.y;
+      o1 = a1 * c1.x + b1 * c1.y;
       am = fmaxf(am, fmaxf(fabsf(a0), fabsf(a1)));
     } else {         // second half: b cos - a sin
-      o0 = b0 * cs.x - a0 * cs.y;
-      o1 = b1 * cs.z - a1 * cs.w;
+      o0 = b0 * c0.x - a0 * c0.y;
+      o1 = b1 * c1.x - a1 * c1.y;
       am = fmaxf(am, fmaxf(fabsf(b0), fabsf(b1)));
     }
     w[i >> 1] = pack_h2(o0 * fs, o1 * fs);
@@ -274,18 +271,18 @@ __device__ __forceinline__ void store_plain16(__half* dst, const uint32_t (&r)[1
 // i pairs with i + 32), then dV, sixteen components at a time; arrives on `bar_read` once the
 // accumulators have been read; returns the largest magnitude written, before the carried scale.
 __device__ __noinline__ float dkv_store16(uint32_t t_dk_lane, uint32_t t_dv_half, int hc, __half* k16,
-                                          __half* v16, const float2* __restrict__ trow, float ak,
+                                          __half* v16, const float2* __restrict__ tcol, size_t seq, float ak,
                                           float av, float s16, uint32_t bar_read, int lane) {
   float amk = 0.f, amv = 0.f;
   uint32_t ra[16], rb[16];
   tc_ld16(t_dk_lane, ra);
   tc_ld16(t_dk_lane + 32, rb);
   tc_wait_ld();
-  if (k16) store_rot16(k16, ra, rb, ak, hc, trow, s16, amk);
+  if (k16) store_rot16(k16, ra, rb, ak, hc, tcol, seq, s16, amk);
   tc_ld16(t_dk_lane + 16, ra);
   tc_ld16(t_dk_lane + 48, rb);
   tc_wait_ld();
-  if (k16) store_rot16(k16 + 16, ra, rb, ak, hc, trow + 16, s16, amk);
+  if (k16) store_rot16(k16 + 16, ra, rb, ak, hc, tcol + 16 * seq, seq, s16, amk);
   tc_ld16(t_dv_half, ra);
   tc_ld16(t_dv_half + 16, rb);
   tc_wait_ld();
@@ -517,19 +514,19 @@ k_attn_bwd_dq_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_cons
         // the rotation pairs component i with i + 32: sixteen components of either half at a
         // time (magnitudes are folded raw and scaled by alpha once)
         float amr = 0.f;
-        const float2* trow = o16.table + (size_t)pend_pos * 32;
+        const float2* tcol = o16.table + pend_pos;   // transposed table: [32][seq]
         uint32_t ra[16], rb[16];
         tc_ld16(t_dq + lane_addr, ra);
         tc_ld16(t_dq + lane_addr + 32, rb);
         tc_wait_ld();
-        if (pend16) store_rot16(pend16, ra, rb, alpha, hc, trow, s16, amr);
+        if (pend16) store_rot16(pend16, ra, rb, alpha, hc, tcol, (size_t)seq, s16, amr);
         tc_ld16(t_dq + lane_addr + 16, ra);
         tc_ld16(t_dq + lane_addr + 48, rb);
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(c.bar(B_ACC_READ));
-        if (pend16) store_rot16(pend16 + 16, ra, rb, alpha, hc, trow + 16, s16, amr);
+        if (pend16) store_rot16(pend16 + 16, ra, rb, alpha, hc, tcol + 16 * (size_t)seq, (size_t)seq, s16, amr);
         am = fmaxf(am, alpha * amr);
         return true;
       }
@@ -634,8 +631,6 @@ k_attn_bwd_dq_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_cons
         pend16 = row_ok ? o16.rows + ((long long)w.tok0 + qi) * o16.ld + q_col0 + (long long)w.h * BD + hc * 32
                         : nullptr;
         pend_pos = qi;
-        // the row's angles are wanted one key block from now: bring them close meanwhile
-        if (row_ok) prefetch_l1_256(o16.table + (size_t)qi * 32);
       } else {
         pend_out = row_ok ? dq + ((long long)w.tok0 + qi) * lddq + (long long)w.h * BD + hc * 32 : nullptr;
       }
@@ -806,7 +801,7 @@ k_attn_bwd_dkv_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
       tc_fence_after();
       if (o16.rows) {
         am = fmaxf(am, dkv_store16(t_dk + lane_addr, t_dv + lane_addr + hc * 32, hc, pend_k16, pend_v16,
-                                   o16.table + (size_t)pend_pos * 32, ak, av, s16, c.bar(B_ACC_READ),
+                                   o16.table + pend_pos, (size_t)seq, ak, av, s16, c.bar(B_ACC_READ),
                                    lane));
         return true;
       }
@@ -928,7 +923,6 @@ k_attn_bwd_dkv_tc2(const __grid_constant__ CUtensorMap map_qkv, const __grid_con
         pend_k16 = row_ok ? o16.rows + tok * o16.ld + k_col0 + (long long)w.kvh * BD + hc * 32 : nullptr;
         pend_v16 = row_ok ? o16.rows + tok * o16.ld + v_col0 + (long long)w.kvh * BD + hc * 32 : nullptr;
         pend_pos = kj;
-        if (row_ok) prefetch_l1_256(o16.table + (size_t)kj * 32);
       } else {
         pend_k = row_ok ? dk + tok * ldd + (long long)w.kvh * BD + hc * 32 : nullptr;
         pend_v = row_ok ? dv + tok * ldd + (long long)w.kvh * BD + hc * 32 : nullptr;

@@ -203,7 +203,7 @@ struct FtGemmArgs {
   float* carry_scales = nullptr;
   // rotary epilogue of a q|k|v projection (CTA-pair launches, f16 result only): the columns
   // are heads of 64; those below rope_cols are rotated by the angles of the row's position
-  // (row % rope_seq) from rope_table ({cos, sin} [rope_seq, 32] f32), after the bias
+  // (row % rope_seq) from rope_table ({cos, sin} transposed: [32, rope_seq] f32), after the bias
   const float* rope_table = nullptr;
   int rope_seq = 0, rope_cols = 0;
   // SwiGLU inside the epilogue (CTA-pair launches; gate|up columns interleaved in runs of 32).
@@ -308,7 +308,9 @@ int ft_k_rms_norm_bwd_carry(FtContext* ctx, const float* x, const float* w, cons
 int ft_k_rope(FtContext* ctx, float* x, long long ld, int tokens, int heads, int head_dim,
               int seq_len, int pos, float theta, bool inverse);
 // RoPE for the tensor-core path.  table: float2 {cos, sin} [seq_len, head_dim/2] built with the
-// same f32 recipe as ft_k_rope.  forward: f32 q|k|v rows -> f16 rows (q, k rotated, v copied).
+// same f32 recipe as ft_k_rope, followed by the same values transposed ([head_dim/2, seq_len]):
+// 2 * seq_len * head_dim floats in all.  ft_k_rope_to_f16 reads the first form; the epilogues
+// that rotate (FtGemmArgs::rope_table, FtAttnBwdOut16::table) take a pointer to the second.  forward: f32 q|k|v rows -> f16 rows (q, k rotated, v copied).
 // backward: f32 gradient rows -> f16 rows times the scale in `scales[0]`, q, k parts rotated
 // by the negated angle.  Rows are [tokens, nq + 2 nkv], head_dim 64.
 int ft_k_rope_table(FtContext* ctx, float* table, int seq_len, int head_dim, float theta);
@@ -414,7 +416,7 @@ int ft_attention_fwd_tc(FtContext* ctx, const __half* qkv16, long long ld, int q
 // scale whose inverse is the device scalar *inv_scale, NULL = 1); stats must hold the forward
 // log-sum-exp at [2*row+1] and receives Delta at [2*row].  dq [tokens, lddq]; dk, dv [tokens, ldd].
 // With out16 the results are written instead as f16 rows in the operands' q|k|v column layout,
-// dq and dk rotated back by the rotary angles of `table` ({cos, sin} [seq, 32] f32) and all
+// dq and dk rotated back by the rotary angles of `table` ({cos, sin} transposed: [32, seq] f32) and all
 // times the power of two carried from *carry_amax (see FtGemmArgs::carry_amax); the armed amax
 // slot still receives the largest unrotated, unscaled magnitude.
 struct FtAttnBwdOut16 {

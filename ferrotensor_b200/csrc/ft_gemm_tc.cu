@@ -999,8 +999,11 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         // q|k|v projection: the rotary rotation (component i of a 64-wide head pairs with
         // i + 32) and the f16 rounding happen here, on the accumulator; each warp group takes
         // every other head of the tile, a thread one row of it.
+        // (the table is transposed, [32][rope_seq]: lanes own consecutive rows, i.e. positions,
+        // so each load of the warp covers consecutive addresses)
         const int my_row = m0 + quad * 32 + lane;
-        const float2* trow = ep.rope_table + (size_t)(my_row % ep.rope_seq) * 32;
+        const float2* tcol = ep.rope_table + (my_row % ep.rope_seq);
+        const size_t tstep = (size_t)ep.rope_seq;
 #pragma unroll 1
         for (int hd = grp; hd < BN / 64; hd += 2) {
           const int col0 = n0 + hd * 64;
@@ -1011,6 +1014,7 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           tc_wait_ld();
           const bool rot = col0 < ep.rope_cols;
           uint8_t* st = stage_base + lane * 128;
+          const float2* tp = tcol;   // walks down the table's rows: one pointer, no index arithmetic
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint32_t w1[4], w2[4];
@@ -1025,9 +1029,10 @@ k_gemm_tc2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               }
               float o10 = a0, o11 = a1, o20 = b0, o21 = b1;
               if (rot) {
-                const float4 cs = *(const float4*)(trow + i);   // {cos_i, sin_i, cos_i+1, sin_i+1}
-                o10 = a0 * cs.x - b0 * cs.y; o20 = a0 * cs.y + b0 * cs.x;
-                o11 = a1 * cs.z - b1 * cs.w; o21 = a1 * cs.w + b1 * cs.z;
+                const float2 c0 = tp[0], c1 = tp[tstep];   // {cos, sin} of components i, i + 1
+                tp += 2 * tstep;
+                o10 = a0 * c0.x - b0 * c0.y; o20 = a0 * c0.y + b0 * c0.x;
+                o11 = a1 * c1.x - b1 * c1.y; o21 = a1 * c1.y + b1 * c1.x;
               }
               __half2 h1 = __floats2half2_rn(o10, o11), h2 = __floats2half2_rn(o20, o21);
               w1[e >> 1] = *(uint32_t*)&h1;

@@ -382,6 +382,9 @@ __global__ void k_rope_table(float2* __restrict__ table, int seq_len, int half, 
   float s, c;
   sincosf((float)pos * freq, &s, &c);
   table[idx] = make_float2(c, s);
+  // second copy, transposed ([i][pos]): threads that own consecutive rows (positions) of a tile
+  // read consecutive addresses
+  table[(size_t)seq_len * half + (size_t)i * seq_len + pos] = make_float2(c, s);
 }
 
 // sigmoid with the fast exponential and reciprocal (about 2 ulp): the results are rounded to

@@ -127,7 +127,8 @@ struct FtLoraModel {
   bool tc_attention = false;       // head_dim 64: attention and RoPE take the tensor-core route
   uint64_t dropout_step_seed = 0;  // seed of the coming forward pass (ft_model_set_dropout_seed)
   bool dropout_on = false;         // training pass of a model with attention dropout
-  float* rope_table = nullptr;     // {cos, sin} [seq_len, 32] in the workspace
+  float* rope_table = nullptr;     // {cos, sin} [seq_len, 32], then transposed [32, seq_len], in the workspace
+  const float* rope_tableT() const { return rope_table + (size_t)seq_len * cfg.head_dim; }
   int table_seq = 0;
   int* gu_amax = nullptr;          // per layer: largest |gate| or |up| of the forward pass
   // Carried scales of the backward pass.  A gradient that a kernel writes as f16 needs its
@@ -260,7 +261,7 @@ size_t plan(FtLoraModel* m, int sequences, int seq_len, bool dry, void* base) {
   size_t cvt = std::max(T * ft_align_up(widest, 8), chunk * ft_align_up((size_t)c.vocab, 8));
   __half* hi = b.take<__half>(cvt);
   __half* lo = fused ? nullptr : b.take<__half>(cvt);
-  float* rope_table = fused ? b.take<float>((size_t)seq_len * c.head_dim) : nullptr;
+  float* rope_table = fused ? b.take<float>(2 * (size_t)seq_len * c.head_dim) : nullptr;
   __half* hN16 = fused ? b.take<__half>(T * c.hidden) : nullptr;
   __half* xa16_head = fused ? b.take<__half>(T * RP) : nullptr;
   __half* g16 = fused ? b.take<__half>(T * RP) : nullptr;
@@ -739,7 +740,7 @@ int block_forward_fused(FtLoraModel* m, int l, const float* x_in, float* x_out, 
   if (m->tc_attention && m->rope_in_gemm) {
     // the projection's epilogue rotates and rounds: no f32 q|k|v rows, no pass over them
     FT_TRY(linear_fwd_fused(m, ly.qkv, a.h1_16, nullptr, nqkv, a.xa16_qkv, nullptr, 0, T, a.qkv16,
-                            m->rope_table, m->seq_len, nq + nkv));
+                            m->rope_tableT(), m->seq_len, nq + nkv));
   } else {
     FT_TRY(linear_fwd_fused(m, ly.qkv, a.h1_16, a.qkv, nqkv, a.xa16_qkv, nullptr, 0, T));
   }
@@ -864,7 +865,7 @@ int block_backward_fused(FtLoraModel* m, int l, const float* x_in, BlockActs& a)
       // the attention kernels write the rotated-back, scaled f16 rows themselves; m->cvt_hi is
       // free here because the output gradient arrived in m->dattn16
       FtAttnBwdOut16 o16;
-      o16.rows = m->cvt_hi; o16.ld = nqkv; o16.table = m->rope_table;
+      o16.rows = m->cvt_hi; o16.ld = nqkv; o16.table = m->rope_tableT();
       o16.carry_amax = m->camax(m->slot_dqkv(l + 1)); o16.carry_exp = kCarryExp - 1;
       o16.carry_scales = m->cscales(m->slot_dqkv(l));
       FT_TRY(ft_attention_bwd_tc(ctx, a.qkv16, nqkv, 0, nq, nq + nkv, a.attn16, nq, do16, nq,
