@@ -33,8 +33,12 @@ class Sampler:
     top_p >= 1 switch those filters off."""
 
     def __init__(self, temperature: float = 0.7, top_k: int = 0, top_p: float = 0.9, seed: Optional[int] = None):
+        import os
+        from .std_rng import StdRng
         self.temperature, self.top_k, self.top_p = float(temperature), int(top_k), float(top_p)
-        self.rng = np.random.default_rng(seed)
+        # the reference's generator: StdRng::seed_from_u64(seed), or seeded from the OS
+        # (tokenizer.rs:519-526); one `gen::<f32>()` per sampled token
+        self.rng = StdRng.seed_from_u64(int(seed)) if seed is not None else StdRng(os.urandom(32))
 
     def is_greedy(self) -> bool:
         return self.temperature <= 0.0 or self.top_k == 1
@@ -51,16 +55,17 @@ class Sampler:
             order = order[:self.top_k]
         f = np.float32
         probs = np.exp((logits[order] - logits[order[0]]) / f(self.temperature)).astype(f)
-        probs = probs / probs.sum(dtype=f)
+        # f32 sums in index order, as `iter().sum()` adds them (np.cumsum accumulates sequentially)
+        probs = probs / np.cumsum(probs, dtype=f)[-1]
         if self.top_p < 1.0:
             reach = np.nonzero(np.cumsum(probs, dtype=f) >= f(self.top_p))[0]
             keep = int(reach[0]) + 1 if reach.size else len(probs)
             order, probs = order[:keep], probs[:keep]
-        r = f(self.rng.random(dtype=f)) * probs.sum(dtype=f)
+        r = f(self.rng.gen_f32()) * np.cumsum(probs, dtype=f)[-1]
         for idx, p in zip(order, probs):
             if r < p:
                 return int(idx)
-            r -= p
+            r = f(r - p)
         return int(order[-1])
 
 
